@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the quantization hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config 2): INT4 g=32 weight-only decode, W[11008,4096] stored [N,K],
+X[1,4096] fp32, y = x * deq(W)^T.  One *step* = `--launches-per-step` forwards cycling through
+`--copies` distinct weight sets (10 x 28.2 MB = 282 MB > 126 MB L2, so every launch streams its
+weights from HBM).  Metric: achieved HBM GB/s = algorithmic bytes / time, whole job.
+
+N > 1 (torchrun): weak scaling of a column-sharded layer — every rank holds its own
+[11008,4096] column slice (N_total = 11008 * ranks), each forward is followed by the NCCL
+all-gather of the [M, 11008] output slices; value = bytes streamed by all ranks / max-over-ranks
+device time.
+
+`--impl reference` times the reference's own CPU QuantizedLinear forward (oracle/_ref, the
+unmodified sources compiled for the host) on the same workload: one forward per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM, N_DIM, GROUP = 4096, 11008, 32
+METRIC, UNIT = "int4_g32_decode_gemv_hbm_gbs", "GB/s"
+
+
+def gemv_bytes(M: int, K: int = K_DIM, N: int = N_DIM, bits: int = 4) -> int:
+    """Algorithmic bytes of one forward: packed weights + scales + x + y (fp32)."""
+    w = N * K // 2 + (N * K // GROUP) * 4 if bits == 4 else N * K + 4
+    return w + M * K * 4 + M * N * 4
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int, period_ms: int = 50):
+        self.lines, self.proc, self.thread = [], None, None
+        self.cmd = ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                    "-lms", str(period_ms)]
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            p = [s.strip() for s in l.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0]))
+                smax.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU implementation on the host cores
+# ------------------------------------------------------------------------------------------
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def reference_linear(M: int):
+    import numpy as np
+    import oracle
+    ref = oracle.load_ref()
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((N_DIM, K_DIM)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((M, K_DIM)).astype(np.float32)
+    if ref is not None:
+        lin = ref.linear(w, oracle.LAYOUT_NK, 4, 0, GROUP, None)
+        return "reference", ref.num_threads(), (lambda iters: lin.time_forward(x, iters, with_bias=False))
+    port = oracle.Port()                                   # the reference was never compiled here
+    packed, scales = port.quantize_int4(w, GROUP)
+
+    def run(iters):
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            port.qlinear_int4(x, packed, scales, K_DIM, N_DIM, oracle.LAYOUT_NK, GROUP, None)
+        return (time.perf_counter() - t0) / iters
+    return "port", host_cores(), run
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    kind, cores, timer = reference_linear(1)
+    for _ in range(min(args.warmup, 3)):
+        timer(1)
+    t0 = time.perf_counter()
+    per = timer(args.steps)
+    wall = time.perf_counter() - t0
+    value = gemv_bytes(1) / per / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config2: INT4 g=32 decode, W[11008,4096] ([N,K]), X[1,4096]; one CPU forward "
+                               "(dequantize + fp32 matmul, as the reference does per call) per step",
+                   "M": 1, "K": K_DIM, "N": N_DIM, "group": GROUP},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{args.steps} forwards of the full workload, {wall:.1f} s"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def time_launches(torch, fn, iters: int, warm: int = 3) -> float:
+    """Average device milliseconds of fn() over `iters` calls, CUDA events on the current stream."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def extras(torch, sgq, peaks, copies_w):
+    """Secondary measurements (reported, not the headline): other batch sizes, the pack kernels and
+    the prefill GEMM of BASELINE config 3."""
+    out = {}
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def guard(name, f):
+        try:
+            out[name] = f()
+        except Exception as e:  # noqa: BLE001
+            out[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+
+    def gemv(M, path):
+        x = torch.randn(M, K_DIM, device=dev, generator=g)
+        y = torch.empty(M, N_DIM, device=dev)
+        ws = sgq.Workspace(dev)
+        state = {"i": 0}
+
+        def f():
+            q = copies_w[state["i"] % len(copies_w)]
+            state["i"] += 1
+            sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)
+        ms = time_launches(torch, f, 200)
+        gbs = gemv_bytes(M) / ms / 1e6
+        return {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "path": sgq.PATH_NAMES[path]}
+
+    for M in (1, 4, 8):
+        guard(f"gemv_M{M}", lambda M=M: gemv(M, sgq.PATH_GEMV))
+    guard("gemv_M16_auto", lambda: gemv(16, sgq.PATH_AUTO))
+    guard("gemv_M1_simt", lambda: gemv(1, sgq.PATH_SIMT))
+
+    def pack(shape, bits):
+        # two inputs > L2 in total for the big shape; alternate so the small one also misses L2
+        ws_ = [torch.randn(shape, device=dev, generator=g) * 0.02 for _ in range(3)]
+        n = ws_[0].numel()
+        state = {"i": 0}
+
+        def f():
+            w = ws_[state["i"] % 3]
+            state["i"] += 1
+            return sgq.quantize_int4(w, GROUP) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
+        ms = time_launches(torch, f, 30)
+        algo = 4.625 * n if bits == 4 else 5.0 * n
+        return {"ms": ms, "gbs_algorithmic": algo / ms / 1e6, "bytes_per_element": 4.625 if bits == 4 else 5.0,
+                "frac_of_measured_hbm": algo / ms / 1e6 / peaks["hbm_gbs"]}
+
+    for shape in ((4096, 4096), (11008, 4096)):
+        guard(f"pack_int4_g32_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 4))
+        guard(f"pack_int8_tensor_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 8))
+
+    def gemm(N, path):
+        M, K = 2048, 4096
+        x = torch.randn(M, K, device=dev, generator=g)
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        q = sgq.quantize_int4(w, GROUP) if path != sgq.PATH_TC_I8 else sgq.quantize_int8(w, sgq.PER_TENSOR)
+        y = torch.empty(M, N, device=dev)
+        ws = sgq.Workspace(dev)
+        if path == sgq.PATH_TC_I8:
+            f = lambda: sgq.linear_w8a8(x, q, None)  # noqa: E731
+        else:
+            f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
+        ms = time_launches(torch, f, 20)
+        tf = 2.0 * M * N * K / ms / 1e9
+        return {"ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                "frac_of_nominal_bf16_2250": tf / 2250.0, "path": sgq.PATH_NAMES[path],
+                "includes": "activation conversion/quantization kernel + GEMM"}
+
+    for N in (4096, 11008):
+        guard(f"prefill_bf16_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16))
+        guard(f"prefill_i8_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_I8))
+    status = sgq.device_status()
+    out["device_status_word"] = status
+    return out
+
+
+def run_ours(args):
+    import torch
+    from __graft_entry__ import load_package
+    sgq = load_package()
+    rank, local_rank, world = dist_env()
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    M, copies, lps = args.M, args.copies, args.launches_per_step
+
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    weights = []
+    for _ in range(copies):
+        w = torch.randn(N_DIM, K_DIM, device=dev, generator=g) * 0.02
+        weights.append(sgq.quantize_int4(w, GROUP))
+        del w
+    x = torch.randn(M, K_DIM, device=dev, generator=g)
+    y_local = torch.empty(M, N_DIM, device=dev)
+    gathered = torch.empty(world, M, N_DIM, device=dev) if world > 1 else None
+    y_full = torch.empty(M, world * N_DIM, device=dev) if world > 1 else None
+    ws = sgq.Workspace(dev)
+    path = sgq.PATH_GEMV if M <= 8 else sgq.PATH_AUTO
+
+    def forward(i):
+        sgq.quantized_matmul(x, weights[i % copies], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, y_local)
+            sgq.interleave_slices(gathered, world, M, N_DIM, y_full)
+
+    def step(s):
+        for i in range(lps):
+            forward(s * lps + i)
+
+    for s in range(args.warmup):
+        step(s)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.steps):
+        step(s)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist:
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_total = float(ms_total.item())
+    launches = args.steps * lps
+    bytes_per_launch = gemv_bytes(M)
+    value = world * launches * bytes_per_launch / (ms_total * 1e-3) / 1e9
+    launch_ms = ms_total / launches
+    achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9 if world == 1 else None
+
+    # ---- end to end through the public call with HOST buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        xh = torch.randn(M, K_DIM).pin_memory()
+        yh = torch.empty(M, (world if world > 1 else 1) * N_DIM).pin_memory()
+        e2e_steps = max(1, min(args.steps, 20))
+
+        def e2e_forward(i):
+            x.copy_(xh, non_blocking=True)
+            forward(i)
+            yh.copy_(y_full if world > 1 else y_local, non_blocking=True)
+        for i in range(3 * min(lps, 50)):
+            e2e_forward(i)
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for s in range(e2e_steps):
+            for i in range(lps):
+                e2e_forward(s * lps + i)
+        f1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([f0.elapsed_time(f1)], device=dev)
+        if dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+        e2e = {"value": world * e2e_steps * lps * bytes_per_launch / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": lps * M * K_DIM * 4, "d2h_bytes_per_step": lps * M * world * N_DIM * 4,
+               "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+               "note": "weights are resident layer parameters; per forward x comes from pinned host memory and y returns to it"}
+
+    status = sgq.device_status()
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            kind, cores, timer = reference_linear(M)
+            t1 = timer(1)
+            iters = max(2, min(400, int(10.0 / max(t1, 1e-4))))
+            t0 = time.perf_counter()
+            per = timer(iters)
+            cpu = {"value": gemv_bytes(M) / per / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+                   "sample": f"{iters} CPU forwards of the same W[11008,4096], M={M} workload "
+                             f"({time.perf_counter() - t0:.1f} s); each dequantizes the whole weight, as the reference does",
+                   "ms_per_forward": per * 1e3}
+        except Exception as e:  # noqa: BLE001
+            cpu = {"error": f"{type(e).__name__}: {e}"[:200]}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 (INT4 nibbles) x bf16-split fp32 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"config2: INT4 g=32 decode GEMV, W[{N_DIM},{K_DIM}] stored [N,K], X[{M},{K_DIM}] fp32"
+                               + (f"; column-sharded, N_total={world * N_DIM}, NCCL all-gather of output slices per forward"
+                                  if world > 1 else ""),
+                   "M": M, "K": K_DIM, "N_per_gpu": N_DIM, "group": GROUP, "launches_per_step": lps, "weight_copies": copies,
+                   "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
+                   "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": args.traffic,
+                     "peak_source": peaks["source"], "kernel": "gemv_int4_nk_kernel",
+                     "launch_us": launch_ms * 1e3},
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * (1 if world == 1 else 2), "clocks": clocks,
+        "device_status_word": status,
+    }
+    if world == 1 and not args.no_extras:
+        line["extra"] = extras(torch, sgq, peaks, weights)
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--copies", type=int, default=10)
+    ap.add_argument("--launches-per-step", type=int, default=1000)
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report (from profiles/)")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,155 @@
+/* sgq.h — C ABI of the B200 (sm_100a) SovereignGrad quantization hot path.
+ *
+ * Drop-in boundary: each entry point replaces one function of the reference's
+ * `sovereigngrad::quantization` namespace (file:line of what it replaces is given per
+ * function; paths are relative to the reference checkout).  Plain pointers and sizes only.
+ *
+ * Conventions
+ *  - Every data pointer is a DEVICE pointer owned by the caller; the library allocates no
+ *    device memory.  Scratch, where a function needs it, is the caller's `workspace`.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream, which is what
+ *    the reference uses throughout).  Calls are asynchronous: they enqueue work and return.
+ *  - Return value: sgq_status (0 = ok).  Nothing throws, aborts or synchronises the device.
+ *    `sgq_last_error()` gives a thread-local detail string for the last non-zero status.
+ *  - Entry points are re-entrant; concurrent calls must not share output or workspace buffers.
+ *
+ * Data layout (the reference keeps integer codes in an fp32 tensor,
+ * src/quantization.cpp:32-38,127-153, and defines no bytes; this is the packed form):
+ *  - INT8 codes: one two's-complement int8 per element, flat row-major order.
+ *  - INT4 codes: two two's-complement nibbles per byte, element 2i in the LOW nibble and
+ *    element 2i+1 in the HIGH nibble, flat row-major order, ceil(numel/2) bytes; the high
+ *    nibble of an odd tail byte is 0.
+ *  - scales: fp32, in the reference's order — [1] per tensor, [rows] per row of the stored
+ *    tensor, [ceil(numel/group)] for INT4 where group g covers flat elements
+ *    [g*group, min(numel,(g+1)*group)).
+ *  - weight `layout`: SGQ_LAYOUT_KN = stored as [K=in, N=out], y = x*W (the reference module's
+ *    native form, include/sovereigngrad/nn.hpp:935-958); SGQ_LAYOUT_NK = stored as [N, K],
+ *    y = x*W^T.  Because INT4 groups run over the flat index they lie along N for KN and
+ *    along K for NK.
+ */
+#ifndef SGQ_H
+#define SGQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGQ_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SGQ_API __attribute__((visibility("default")))
+#else
+#define SGQ_API
+#endif
+
+typedef enum sgq_status {
+    SGQ_OK = 0,
+    SGQ_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+    SGQ_ERR_BAD_SHAPE = 2,      /* negative size, inner dimensions that do not match, ldy < N */
+    SGQ_ERR_BAD_ARGUMENT = 3,   /* unknown layout / scheme / path value */
+    SGQ_ERR_UNSUPPORTED = 4,    /* the requested `path` cannot run this shape (never silently rerouted) */
+    SGQ_ERR_WORKSPACE = 5,      /* workspace missing, too small or not 256-byte aligned */
+    SGQ_ERR_ALIGNMENT = 6,      /* a pointer breaks the alignment the requested path needs */
+    SGQ_ERR_CUDA = 7,           /* a CUDA call or launch failed; see sgq_last_error() */
+    SGQ_ERR_DEVICE = 8,         /* current device is not compute capability 10.x */
+    SGQ_ERR_TIMEOUT = 9         /* a bounded device-side wait gave up (read back from the status word) */
+} sgq_status;
+
+enum { SGQ_LAYOUT_KN = 0, SGQ_LAYOUT_NK = 1 };
+enum { SGQ_PER_TENSOR = 0, SGQ_PER_ROW = 1 };
+
+/* Which kernel family runs a forward.  AUTO picks by shape; the others force one family and
+ * return SGQ_ERR_UNSUPPORTED when it cannot take the shape. */
+enum {
+    SGQ_PATH_AUTO = 0,
+    SGQ_PATH_SIMT = 1,    /* tiled fp32 SIMT kernel, any shape; one fused-multiply-add chain per
+                             output in ascending k, i.e. the reference CPU rounding */
+    SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernel, fp32 accumulation */
+    SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16, weights dequantized to bf16 in shared memory */
+    SGQ_PATH_TC_I8 = 4    /* prefill, INT8 weights only: activations quantized per row, tcgen05 kind::i8 */
+};
+
+SGQ_API const char* sgq_status_string(int status);
+SGQ_API const char* sgq_last_error(void);
+SGQ_API int sgq_abi_version(void);
+
+/* Kernels that wait on hardware barriers (TMA / tensor-core pipelines) bound every wait; one that
+ * runs out writes a code into a device status word instead of hanging.  This call SYNCHRONISES
+ * with the device (a blocking copy), returns SGQ_ERR_TIMEOUT if the word is non-zero, stores it
+ * in *word (may be NULL) and clears it when `clear` is non-zero.  Meant for tests and for error
+ * paths, not for the hot loop.  No counterpart in the reference, whose launches are unchecked. */
+SGQ_API int sgq_device_status(unsigned int* word, int clear);
+
+/* ---- quantize / pack ---------------------------------------------------------------- */
+
+/* Replaces quantization::quantize_int8 (src/quantization.cpp:11-78).
+ * x: rows*cols fp32.  scheme SGQ_PER_TENSOR: absmax over everything, 1 scale (:22-41);
+ * SGQ_PER_ROW: one scale per row (:42-75).  max_abs starts at 1e-8f, scale = max_abs/127,
+ * code = clamp(round_half_away(x * (127/max_abs)), -127, 127).  Bit-exact with the reference.
+ * Per tensor, scales[0] transiently holds the running absmax while the call executes. */
+SGQ_API int sgq_quantize_int8(const float* x, int64_t rows, int64_t cols, int scheme, int8_t* codes, float* scales,
+                      void* stream);
+
+/* Replaces quantization::quantize_int4 (src/quantization.cpp:113-159).  group <= 0 means 32
+ * (:118).  scale = max_abs/7, code = clamp(round_half_away(x * (7/max_abs)), -8, 7), packed two
+ * per byte.  packed: ceil(numel/2) bytes; scales: ceil(numel/group) floats.  Bit-exact. */
+SGQ_API int sgq_quantize_int4(const float* x, int64_t numel, int64_t group, uint8_t* packed, float* scales, void* stream);
+
+/* Replaces quantization::dequantize_int8 (src/quantization.cpp:80-111): out = code * scale. */
+SGQ_API int sgq_dequantize_int8(const int8_t* codes, const float* scales, int64_t rows, int64_t cols, int scheme, float* out,
+                        void* stream);
+/* Replaces quantization::dequantize_int4 (src/quantization.cpp:161-187). */
+SGQ_API int sgq_dequantize_int4(const uint8_t* packed, const float* scales, int64_t numel, int64_t group, float* out,
+                        void* stream);
+
+/* The reference's `QuantizedTensor::qdata` view (include/sovereigngrad/quantization.hpp:18):
+ * integer codes held as fp32, and back.  Used to exchange tensors with reference checkpoints,
+ * which store qdata as fp32 (src/module.cpp:94-112). */
+SGQ_API int sgq_codes_to_f32_int8(const int8_t* codes, int64_t numel, float* out, void* stream);
+SGQ_API int sgq_codes_to_f32_int4(const uint8_t* packed, int64_t numel, float* out, void* stream);
+SGQ_API int sgq_codes_from_f32_int8(const float* codes_f32, int64_t numel, int8_t* codes, void* stream);
+SGQ_API int sgq_codes_from_f32_int4(const float* codes_f32, int64_t numel, uint8_t* packed, void* stream);
+
+/* ---- forward -------------------------------------------------------------------------- */
+
+/* Bytes of scratch the forward needs for this shape and path (0 = none).  bits is 4 or 8. */
+SGQ_API size_t sgq_linear_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int path);
+
+/* Replaces quantization::quantized_matmul_int4 (src/quantization.cpp:199-206), i.e.
+ * dequantize_int4 + matmul (src/ops.cpp:378-455) + broadcast add (src/ops.cpp:132-171) in one
+ * launch: y[m, n] = sum_k x[m,k] * code(k,n) * scale(k,n) + bias[n].
+ * x: [M,K] fp32 row-major.  y: [M,N] fp32 with row stride ldy >= N (ldy lets a rank write its
+ * column slice into a wider buffer).  bias: N floats or NULL (= the reference's undefined
+ * bias, :202).  workspace: NULL or >= sgq_linear_workspace_bytes(...) bytes, 256-byte aligned. */
+SGQ_API int sgq_linear_int4(const float* x, int64_t M, int64_t K, int64_t N, const uint8_t* packed, const float* scales,
+                    int layout, int64_t group, const float* bias, float* y, int64_t ldy, int path, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* Replaces quantization::quantized_matmul_int8 (src/quantization.cpp:189-197).  scheme
+ * SGQ_PER_ROW scales follow the rows of the STORED tensor: index k for KN, n for NK. */
+SGQ_API int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, const int8_t* codes, const float* scales,
+                    int layout, int scheme, const float* bias, float* y, int64_t ldy, int path, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* Integer sub-path behind SGQ_PATH_TC_I8, exposed so its exact parts can be checked: x is
+ * quantized per row with the rule of sgq_quantize_int8(SGQ_PER_ROW) into xq/sx, acc is the exact
+ * int32 product of the codes, y = ((float)acc * sx[m]) * sw + bias.  xq_out [M,K], sx_out [M]
+ * and acc_out [M,N] may each be NULL (then they live in the workspace, or are not materialised).
+ * The reference has no counterpart: it never quantizes activations.  Layout must be NK. */
+SGQ_API int sgq_linear_w8a8(const float* x, int64_t M, int64_t K, int64_t N, const int8_t* codes, const float* scales,
+                    int scheme, const float* bias, float* y, int64_t ldy, int8_t* xq_out, float* sx_out,
+                    int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream);
+SGQ_API size_t sgq_linear_w8a8_workspace_bytes(int64_t M, int64_t K, int64_t N);
+
+/* Copies column slices gathered rank-major, src[r][m][n_local] (the order an all-gather leaves
+ * them in), into row-major dst[m][r*n_local + n_local...] with row stride ldd. */
+SGQ_API int sgq_interleave_slices(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGQ_H */

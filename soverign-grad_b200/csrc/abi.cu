@@ -1,0 +1,313 @@
+// extern "C" entry points of include/sgq.h: argument validation, path selection, launches.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "sgq_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace sgq {
+
+cudaError_t read_status_gemv(uint32_t* v, bool clear);
+cudaError_t read_status_gemm(uint32_t* v, bool clear);
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return SGQ_ERR_CUDA;
+}
+
+namespace {
+struct DeviceInfo {
+    int sms = 0;
+    int major = 0;
+    bool known = false;
+};
+DeviceInfo g_devices[64];
+std::mutex g_devices_mutex;
+
+const DeviceInfo& device_info() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    DeviceInfo& d = g_devices[dev];
+    if (!d.known) {
+        cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (d.sms <= 0) d.sms = 148;
+        d.known = true;
+    }
+    return d;
+}
+}  // namespace
+
+int sm_count() { return device_info().sms; }
+
+bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
+                        uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<EncodeFn>(fn);
+    });
+    if (!encode) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return false;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu pitch=%llu box=%ux%u)",
+                  static_cast<int>(r), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+                  static_cast<unsigned long long>(row_pitch_bytes), box_inner, box_outer);
+        return false;
+    }
+    return true;
+}
+
+namespace {
+
+int check_device() {
+    if (device_info().major != 10) {
+        set_error("this library contains sm_100a code only; current device is compute capability %d.x",
+                  device_info().major);
+        return SGQ_ERR_DEVICE;
+    }
+    return SGQ_OK;
+}
+
+int bad(int code, const char* msg) {
+    set_error("%s", msg);
+    return code;
+}
+
+int validate_linear(const LinearArgs& a, int path) {
+    if (a.M < 0 || a.K < 0 || a.N < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (a.ldy < a.N) return bad(SGQ_ERR_BAD_SHAPE, "ldy < N");
+    if (a.layout != SGQ_LAYOUT_KN && a.layout != SGQ_LAYOUT_NK) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown layout");
+    if (a.bits == 8 && a.scheme != SGQ_PER_TENSOR && a.scheme != SGQ_PER_ROW)
+        return bad(SGQ_ERR_BAD_ARGUMENT, "unknown scheme");
+    if (path < SGQ_PATH_AUTO || path > SGQ_PATH_TC_I8) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown path");
+    if (a.M == 0 || a.N == 0) return SGQ_OK;
+    if (!a.y) return bad(SGQ_ERR_NULL_POINTER, "y is NULL");
+    if (a.K > 0 && (!a.x || !a.wq || !a.scales)) return bad(SGQ_ERR_NULL_POINTER, "x, weights or scales is NULL");
+    if (a.workspace && !aligned(a.workspace, 256)) return bad(SGQ_ERR_WORKSPACE, "workspace is not 256-byte aligned");
+    return SGQ_OK;
+}
+
+int run_linear(LinearArgs a, int path) {
+    int rc = validate_linear(a, path);
+    if (rc != SGQ_OK) return rc;
+    if (a.M == 0 || a.N == 0) return SGQ_OK;
+    if ((rc = check_device()) != SGQ_OK) return rc;
+    if (a.K == 0) return launch_linear_simt(a);  // y = bias
+    if (path == SGQ_PATH_AUTO) {
+        if (gemv_supported(a))
+            path = SGQ_PATH_GEMV;
+        else if (a.M >= 64 && tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
+                 a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
+                 aligned(a.wq, 16) && aligned(a.scales, 16) && aligned(a.x, 16))
+            path = SGQ_PATH_TC_BF16;
+        else
+            path = SGQ_PATH_SIMT;
+    }
+    switch (path) {
+        case SGQ_PATH_SIMT:
+            return launch_linear_simt(a);
+        case SGQ_PATH_GEMV:
+            return launch_linear_gemv(a);
+        case SGQ_PATH_TC_BF16:
+            return launch_linear_tc_bf16(a);
+        case SGQ_PATH_TC_I8:
+            if (a.bits != 8 || a.layout != SGQ_LAYOUT_NK)
+                return bad(SGQ_ERR_UNSUPPORTED, "kind::i8 path needs INT8 weights stored [N,K]");
+            return launch_linear_w8a8(a, nullptr, nullptr, nullptr);
+    }
+    return bad(SGQ_ERR_BAD_ARGUMENT, "unknown path");
+}
+
+}  // namespace
+}  // namespace sgq
+
+using namespace sgq;
+
+extern "C" {
+
+const char* sgq_status_string(int status) {
+    switch (status) {
+        case SGQ_OK: return "ok";
+        case SGQ_ERR_NULL_POINTER: return "null pointer";
+        case SGQ_ERR_BAD_SHAPE: return "bad shape";
+        case SGQ_ERR_BAD_ARGUMENT: return "bad argument";
+        case SGQ_ERR_UNSUPPORTED: return "unsupported by the requested path";
+        case SGQ_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+        case SGQ_ERR_ALIGNMENT: return "misaligned pointer";
+        case SGQ_ERR_CUDA: return "CUDA error";
+        case SGQ_ERR_DEVICE: return "device is not sm_100";
+        case SGQ_ERR_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+const char* sgq_last_error(void) { return g_error; }
+
+int sgq_abi_version(void) { return SGQ_ABI_VERSION; }
+
+int sgq_device_status(unsigned int* word, int clear) {
+    uint32_t a = 0, b = 0;
+    SGQ_CUDA_TRY(read_status_gemv(&a, clear != 0));
+    SGQ_CUDA_TRY(read_status_gemm(&b, clear != 0));
+    const uint32_t v = a ? a : b;
+    if (word) *word = v;
+    if (v != 0) {
+        set_error("device status word 0x%08x (code %u, detail %u)", v, v >> 24, v & 0xFFFFFFu);
+        return SGQ_ERR_TIMEOUT;
+    }
+    return SGQ_OK;
+}
+
+int sgq_quantize_int8(const float* x, int64_t rows, int64_t cols, int scheme, int8_t* codes, float* scales,
+                      void* stream) {
+    if (rows < 0 || cols < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (scheme != SGQ_PER_TENSOR && scheme != SGQ_PER_ROW) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown scheme");
+    if (!scales && (scheme == SGQ_PER_TENSOR || rows > 0)) return bad(SGQ_ERR_NULL_POINTER, "scales is NULL");
+    if (rows * cols > 0 && (!x || !codes)) return bad(SGQ_ERR_NULL_POINTER, "x or codes is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_quantize_int8(x, rows, cols, scheme, codes, scales, static_cast<cudaStream_t>(stream));
+}
+
+int sgq_quantize_int4(const float* x, int64_t numel, int64_t group, uint8_t* packed, float* scales, void* stream) {
+    if (numel < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative element count");
+    if (group <= 0) group = 32;  // src/quantization.cpp:118
+    if (numel > 0 && (!x || !packed || !scales)) return bad(SGQ_ERR_NULL_POINTER, "x, packed or scales is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_quantize_int4(x, numel, group, packed, scales, static_cast<cudaStream_t>(stream));
+}
+
+int sgq_dequantize_int8(const int8_t* codes, const float* scales, int64_t rows, int64_t cols, int scheme, float* out,
+                        void* stream) {
+    if (rows < 0 || cols < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (scheme != SGQ_PER_TENSOR && scheme != SGQ_PER_ROW) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown scheme");
+    if (rows * cols > 0 && (!codes || !scales || !out)) return bad(SGQ_ERR_NULL_POINTER, "codes, scales or out is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_dequantize_int8(codes, scales, rows, cols, scheme, out, static_cast<cudaStream_t>(stream));
+}
+
+int sgq_dequantize_int4(const uint8_t* packed, const float* scales, int64_t numel, int64_t group, float* out,
+                        void* stream) {
+    if (numel < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative element count");
+    if (group <= 0) group = 32;
+    if (numel > 0 && (!packed || !scales || !out)) return bad(SGQ_ERR_NULL_POINTER, "packed, scales or out is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_dequantize_int4(packed, scales, numel, group, out, static_cast<cudaStream_t>(stream));
+}
+
+static int codes_view(int bits, bool to_f32, const void* src, int64_t numel, void* dst, void* stream) {
+    if (numel < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative element count");
+    if (numel > 0 && (!src || !dst)) return bad(SGQ_ERR_NULL_POINTER, "source or destination is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return to_f32 ? launch_codes_to_f32(bits, src, numel, static_cast<float*>(dst), s)
+                  : launch_codes_from_f32(bits, static_cast<const float*>(src), numel, dst, s);
+}
+
+int sgq_codes_to_f32_int8(const int8_t* codes, int64_t numel, float* out, void* stream) {
+    return codes_view(8, true, codes, numel, out, stream);
+}
+int sgq_codes_to_f32_int4(const uint8_t* packed, int64_t numel, float* out, void* stream) {
+    return codes_view(4, true, packed, numel, out, stream);
+}
+int sgq_codes_from_f32_int8(const float* codes_f32, int64_t numel, int8_t* codes, void* stream) {
+    return codes_view(8, false, codes_f32, numel, codes, stream);
+}
+int sgq_codes_from_f32_int4(const float* codes_f32, int64_t numel, uint8_t* packed, void* stream) {
+    return codes_view(4, false, codes_f32, numel, packed, stream);
+}
+
+size_t sgq_linear_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int path) {
+    if (M <= 0 || K <= 0 || N <= 0) return 0;
+    switch (path) {
+        case SGQ_PATH_SIMT: return 0;
+        case SGQ_PATH_GEMV: return gemv_workspace_bytes(bits, M, K, N, layout);
+        case SGQ_PATH_TC_BF16: return tc_bf16_workspace_bytes(bits, M, K, N, layout);
+        case SGQ_PATH_TC_I8: return tc_i8_workspace_bytes(M, K, N);
+        default: {  // AUTO: enough for whichever path AUTO may take
+            size_t a = gemv_workspace_bytes(bits, M, K, N, layout);
+            size_t b = M >= 64 ? tc_bf16_workspace_bytes(bits, M, K, N, layout) : 0;
+            return a > b ? a : b;
+        }
+    }
+}
+
+int sgq_linear_int4(const float* x, int64_t M, int64_t K, int64_t N, const uint8_t* packed, const float* scales,
+                    int layout, int64_t group, const float* bias, float* y, int64_t ldy, int path, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    if (group <= 0) group = 32;
+    LinearArgs a{x, M, K, N, packed, scales, 4, layout, group, SGQ_PER_TENSOR, bias, y, ldy, workspace, workspace_bytes,
+                 static_cast<cudaStream_t>(stream)};
+    return run_linear(a, path);
+}
+
+int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, const int8_t* codes, const float* scales,
+                    int layout, int scheme, const float* bias, float* y, int64_t ldy, int path, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    LinearArgs a{x, M, K, N, codes, scales, 8, layout, 0, scheme, bias, y, ldy, workspace, workspace_bytes,
+                 static_cast<cudaStream_t>(stream)};
+    return run_linear(a, path);
+}
+
+size_t sgq_linear_w8a8_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+    if (M <= 0 || K <= 0 || N <= 0) return 0;
+    return tc_i8_workspace_bytes(M, K, N);
+}
+
+int sgq_linear_w8a8(const float* x, int64_t M, int64_t K, int64_t N, const int8_t* codes, const float* scales,
+                    int scheme, const float* bias, float* y, int64_t ldy, int8_t* xq_out, float* sx_out,
+                    int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream) {
+    LinearArgs a{x, M, K, N, codes, scales, 8, SGQ_LAYOUT_NK, 0, scheme, bias, y, ldy, workspace, workspace_bytes,
+                 static_cast<cudaStream_t>(stream)};
+    int rc = validate_linear(a, SGQ_PATH_TC_I8);
+    if (rc != SGQ_OK) return rc;
+    if (M == 0 || N == 0) return SGQ_OK;
+    if ((rc = check_device()) != SGQ_OK) return rc;
+    return launch_linear_w8a8(a, xq_out, sx_out, acc_out);
+}
+
+int sgq_interleave_slices(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,
+                          void* stream) {
+    if (world < 0 || M < 0 || n_local < 0 || ldd < world * n_local) return bad(SGQ_ERR_BAD_SHAPE, "bad slice shape");
+    if (world * M * n_local > 0 && (!src || !dst)) return bad(SGQ_ERR_NULL_POINTER, "src or dst is NULL");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_interleave(src, world, M, n_local, dst, ldd, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,112 @@
+// Shared helpers of the sm_100a kernels behind include/sgq.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sgq.h"
+
+namespace sgq {
+
+// ---- host side ---------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);  // records the message, returns SGQ_ERR_CUDA
+int sm_count();                                   // SMs of the current device (cached per device)
+
+#define SGQ_CUDA_TRY(expr)                                              \
+    do {                                                                \
+        cudaError_t _e = (expr);                                        \
+        if (_e != cudaSuccess) return ::sgq::cuda_fail(_e, #expr);      \
+    } while (0)
+
+#define SGQ_LAUNCH_CHECK(name)                                          \
+    do {                                                                \
+        cudaError_t _e = cudaGetLastError();                            \
+        if (_e != cudaSuccess) return ::sgq::cuda_fail(_e, name);       \
+    } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// launchers implemented in the individual .cu files
+int launch_quantize_int8(const float* x, int64_t rows, int64_t cols, int scheme, int8_t* codes, float* scales,
+                         cudaStream_t s);
+int launch_quantize_int4(const float* x, int64_t n, int64_t group, uint8_t* packed, float* scales, cudaStream_t s);
+int launch_dequantize_int8(const int8_t* codes, const float* scales, int64_t rows, int64_t cols, int scheme,
+                           float* out, cudaStream_t s);
+int launch_dequantize_int4(const uint8_t* packed, const float* scales, int64_t n, int64_t group, float* out,
+                           cudaStream_t s);
+int launch_codes_to_f32(int bits, const void* codes, int64_t n, float* out, cudaStream_t s);
+int launch_codes_from_f32(int bits, const float* codes_f32, int64_t n, void* codes, cudaStream_t s);
+int launch_interleave(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,
+                      cudaStream_t s);
+
+struct LinearArgs {
+    const float* x;
+    int64_t M, K, N;
+    const void* wq;       // packed nibbles (bits 4) or int8 codes (bits 8)
+    const float* scales;
+    int bits;             // 4 | 8
+    int layout;           // SGQ_LAYOUT_*
+    int64_t group;        // bits 4: group size (> 0)
+    int scheme;           // bits 8: SGQ_PER_*
+    const float* bias;    // nullable
+    float* y;
+    int64_t ldy;
+    void* workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+};
+
+int launch_linear_simt(const LinearArgs& a);
+bool gemv_supported(const LinearArgs& a);
+size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
+int launch_linear_gemv(const LinearArgs& a);
+bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
+size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
+int launch_linear_tc_bf16(const LinearArgs& a);
+bool tc_i8_supported(int64_t M, int64_t K, int64_t N);
+size_t tc_i8_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int launch_linear_w8a8(const LinearArgs& a, int8_t* xq_out, float* sx_out, int32_t* acc_out);
+
+// ---- device side -------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// std::round: half away from zero.  trunc and the subtraction are exact for every float, so
+// this is exact, unlike x + copysign(0.5, x).  NaN and +-Inf pass through.
+__device__ __forceinline__ float round_half_away(float v) {
+    float t = truncf(v);
+    float d = fabsf(v - t);
+    return (d >= 0.5f) ? t + copysignf(1.0f, v) : t;
+}
+
+// std::max(lo, std::min(hi, v)) with the operand order the reference uses: a NaN becomes +hi.
+__device__ __forceinline__ float clamp_like_reference(float v, float lo, float hi) {
+    float m = (v < hi) ? v : hi;
+    return (lo < m) ? m : lo;
+}
+
+// reference: `if (a > max_abs) max_abs = a;` — a NaN never wins; fmaxf has the same property.
+__device__ __forceinline__ float absmax_step(float m, float v) { return fmaxf(m, fabsf(v)); }
+
+template <int QMAX, int QMIN>
+__device__ __forceinline__ int quantize_code(float v, float inv_scale) {
+    float r = round_half_away(__fmul_rn(v, inv_scale));
+    return static_cast<int>(clamp_like_reference(r, static_cast<float>(QMIN), static_cast<float>(QMAX)));
+}
+
+__device__ __forceinline__ int nibble_signed(uint32_t v4) { return static_cast<int>((v4 & 0xFu) ^ 8u) - 8; }
+
+__device__ __forceinline__ int load_code_int4(const uint8_t* packed, int64_t i) {
+    return nibble_signed(static_cast<uint32_t>(packed[i >> 1]) >> ((i & 1) * 4));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace sgq
