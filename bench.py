@@ -161,18 +161,36 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
-def time_launches(torch, fn, iters: int, warm: int = 3) -> float:
-    """Average device milliseconds of fn() over `iters` calls, CUDA events on the current stream."""
+def make_graph(torch, body):
+    """Captures body() (which enqueues launches on the current stream) into a CUDA graph, so that a
+    replay issues them back to back without per-launch host work (a decode forward lasts ~5 us,
+    less than one Python call)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        body()                                  # eager once: lazy module loading, attribute set-up
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    return graph
+
+
+def time_launches(torch, fn, iters: int, inner: int = 20, warm: int = 2) -> float:
+    """Average device milliseconds of one fn() call: `inner` calls per graph, `iters` replays,
+    CUDA events on the launching stream."""
+    graph = make_graph(torch, lambda: [fn() for _ in range(inner)])
     for _ in range(warm):
-        fn()
+        graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
-        fn()
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    return e0.elapsed_time(e1) / (iters * inner)
 
 
 def extras(torch, sgq, peaks, copies_w):
@@ -198,7 +216,7 @@ def extras(torch, sgq, peaks, copies_w):
             q = copies_w[state["i"] % len(copies_w)]
             state["i"] += 1
             sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)
-        ms = time_launches(torch, f, 200)
+        ms = time_launches(torch, f, 20, inner=100)
         gbs = gemv_bytes(M) / ms / 1e6
         return {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "path": sgq.PATH_NAMES[path]}
 
@@ -217,7 +235,7 @@ def extras(torch, sgq, peaks, copies_w):
             w = ws_[state["i"] % 3]
             state["i"] += 1
             return sgq.quantize_int4(w, GROUP) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
-        ms = time_launches(torch, f, 30)
+        ms = time_launches(torch, f, 10, inner=6)
         algo = 4.625 * n if bits == 4 else 5.0 * n
         return {"ms": ms, "gbs_algorithmic": algo / ms / 1e6, "bytes_per_element": 4.625 if bits == 4 else 5.0,
                 "frac_of_measured_hbm": algo / ms / 1e6 / peaks["hbm_gbs"]}
@@ -234,10 +252,10 @@ def extras(torch, sgq, peaks, copies_w):
         y = torch.empty(M, N, device=dev)
         ws = sgq.Workspace(dev)
         if path == sgq.PATH_TC_I8:
-            f = lambda: sgq.linear_w8a8(x, q, None)  # noqa: E731
+            f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
         else:
             f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
-        ms = time_launches(torch, f, 20)
+        ms = time_launches(torch, f, 5, inner=4)
         tf = 2.0 * M * N * K / ms / 1e9
         return {"ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                 "frac_of_nominal_bf16_2250": tf / 2250.0, "path": sgq.PATH_NAMES[path],
@@ -287,9 +305,21 @@ def run_ours(args):
             dist.all_gather_into_tensor(gathered, y_local)
             sgq.interleave_slices(gathered, world, M, N_DIM, y_full)
 
+    use_graph = not args.no_graph
+    if use_graph:
+        try:
+            graph = make_graph(torch, lambda: [forward(i) for i in range(lps)])
+        except Exception as e:  # noqa: BLE001  (e.g. a collective that cannot be captured)
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); launching eagerly\n")
+            use_graph = False
+            torch.cuda.synchronize()
+
     def step(s):
-        for i in range(lps):
-            forward(s * lps + i)
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(lps):
+                forward(s * lps + i)
 
     for s in range(args.warmup):
         step(s)
@@ -331,16 +361,29 @@ def run_ours(args):
             x.copy_(xh, non_blocking=True)
             forward(i)
             yh.copy_(y_full if world > 1 else y_local, non_blocking=True)
-        for i in range(3 * min(lps, 50)):
-            e2e_forward(i)
+        e2e_graph = None
+        if use_graph:
+            try:
+                e2e_graph = make_graph(torch, lambda: [e2e_forward(i) for i in range(lps)])
+            except Exception as e:  # noqa: BLE001
+                sys.stderr.write(f"[bench] e2e graph capture failed ({type(e).__name__}: {e}); launching eagerly\n")
+                torch.cuda.synchronize()
+
+        def e2e_step(s):
+            if e2e_graph is not None:
+                e2e_graph.replay()
+            else:
+                for i in range(lps):
+                    e2e_forward(s * lps + i)
+        for s in range(3):
+            e2e_step(s)
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for s in range(e2e_steps):
-            for i in range(lps):
-                e2e_forward(s * lps + i)
+            e2e_step(s)
         f1.record()
         torch.cuda.synchronize()
         t = torch.tensor([f0.elapsed_time(f1)], device=dev)
@@ -382,7 +425,8 @@ def run_ours(args):
                                   if world > 1 else ""),
                    "M": M, "K": K_DIM, "N_per_gpu": N_DIM, "group": GROUP, "launches_per_step": lps, "weight_copies": copies,
                    "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
-                   "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch},
+                   "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch,
+                   "launch": "one CUDA graph replay per step" if use_graph else "eager launches"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": args.traffic,
                      "peak_source": peaks["source"], "kernel": "gemv_int4_nk_kernel",
@@ -408,6 +452,7 @@ def main():
     ap.add_argument("--launches-per-step", type=int, default=1000)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report (from profiles/)")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

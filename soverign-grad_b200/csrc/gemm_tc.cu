@@ -313,7 +313,8 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cud
     using C = Cfg<MODE>;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    SGQ_CUDA_TRY(cudaFuncSetAttribute(linear_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    static SmemOptIn optin;   // one per MODE instantiation
+    SGQ_CUDA_TRY(optin.ensure(linear_tc_kernel<MODE>, C::kSmemBytes));
     linear_tc_kernel<MODE><<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
     SGQ_LAUNCH_CHECK("linear_tc_kernel");
     return SGQ_OK;

@@ -352,14 +352,13 @@ int launch_linear_gemv(const LinearArgs& a) {
         return SGQ_ERR_CUDA;
     const int64_t ntiles = ceil_div(a.N, kRows);
     const int grid = static_cast<int>(ntiles < sm_count() ? ntiles : sm_count());
+    static SmemOptIn optin1, optin2;
     if (p.nsets == 1) {
-        SGQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int4_nk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(p.smem)));
+        SGQ_CUDA_TRY(optin1.ensure(gemv_int4_nk_kernel<1>, kSmemLimit));
         gemv_int4_nk_kernel<1><<<grid, kThreads, p.smem, a.stream>>>(map_w, map_s, a.x, a.bias, a.y,
                                                                       static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages);
     } else {
-        SGQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int4_nk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(p.smem)));
+        SGQ_CUDA_TRY(optin2.ensure(gemv_int4_nk_kernel<2>, kSmemLimit));
         gemv_int4_nk_kernel<2><<<grid, kThreads, p.smem, a.stream>>>(map_w, map_s, a.x, a.bias, a.y,
                                                                       static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages);
     }

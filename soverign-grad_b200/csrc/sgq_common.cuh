@@ -25,6 +25,23 @@ int sm_count();                                   // SMs of the current device (
         if (_e != cudaSuccess) return ::sgq::cuda_fail(_e, name);       \
     } while (0)
 
+// Runs cudaFuncSetAttribute(max dynamic shared memory) once per (kernel, device); later calls,
+// including those made while a stream is being captured into a graph, touch no CUDA API.
+struct SmemOptIn {
+    unsigned long long done_mask = 0;   // bit d = attribute set on device d (guarded by the caller's call_once-like use)
+    template <typename Kernel>
+    cudaError_t ensure(Kernel kernel, int bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const unsigned long long bit = 1ull << (dev & 63);
+        if (__atomic_load_n(&done_mask, __ATOMIC_ACQUIRE) & bit) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess) __atomic_fetch_or(&done_mask, bit, __ATOMIC_RELEASE);
+        return e;
+    }
+};
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
