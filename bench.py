@@ -193,14 +193,31 @@ def time_launches(torch, fn, iters: int, inner: int = 20, warm: int = 2) -> floa
     return e0.elapsed_time(e1) / (iters * inner)
 
 
-def extras(torch, sgq, peaks, copies_w):
+def eager_time(torch, fn, iters: int) -> float:
+    """A few eager launches (profiling runs: a handful of kernels, no graph)."""
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
     """Secondary measurements (reported, not the headline): other batch sizes, the pack kernels and
     the prefill GEMM of BASELINE config 3."""
     out = {}
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(1)
 
+    timer = (lambda fn, iters, inner=20: eager_time(torch, fn, 3)) if eager else (lambda fn, iters, inner=20: time_launches(torch, fn, iters, inner))
+
     def guard(name, f):
+        if only and name != only:
+            return
         try:
             out[name] = f()
         except Exception as e:  # noqa: BLE001
@@ -216,7 +233,7 @@ def extras(torch, sgq, peaks, copies_w):
             q = copies_w[state["i"] % len(copies_w)]
             state["i"] += 1
             sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)
-        ms = time_launches(torch, f, 20, inner=100)
+        ms = timer(f, 20, inner=100)
         gbs = gemv_bytes(M) / ms / 1e6
         return {"ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "path": sgq.PATH_NAMES[path]}
 
@@ -235,7 +252,7 @@ def extras(torch, sgq, peaks, copies_w):
             w = ws_[state["i"] % 3]
             state["i"] += 1
             return sgq.quantize_int4(w, GROUP) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
-        ms = time_launches(torch, f, 10, inner=6)
+        ms = timer(f, 10, inner=6)
         algo = 4.625 * n if bits == 4 else 5.0 * n
         return {"ms": ms, "gbs_algorithmic": algo / ms / 1e6, "bytes_per_element": 4.625 if bits == 4 else 5.0,
                 "frac_of_measured_hbm": algo / ms / 1e6 / peaks["hbm_gbs"]}
@@ -255,7 +272,7 @@ def extras(torch, sgq, peaks, copies_w):
             f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
         else:
             f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
-        ms = time_launches(torch, f, 5, inner=4)
+        ms = timer(f, 5, inner=4)
         tf = 2.0 * M * N * K / ms / 1e9
         return {"ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                 "frac_of_nominal_bf16_2250": tf / 2250.0, "path": sgq.PATH_NAMES[path],
@@ -285,6 +302,12 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
     M, copies, lps = args.M, args.copies, args.launches_per_step
+    if args.only:
+        # profiling aid: run one secondary case a few times, eagerly, and print it
+        g0 = torch.Generator(device=dev).manual_seed(1234)
+        ws0 = [sgq.quantize_int4(torch.randn(N_DIM, K_DIM, device=dev, generator=g0) * 0.02, GROUP) for _ in range(copies)]
+        print(json.dumps({"only": args.only, **extras(torch, sgq, peaks, ws0, only=args.only, eager=True)}), flush=True)
+        return
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     weights = []
@@ -451,6 +474,7 @@ def main():
     ap.add_argument("--copies", type=int, default=10)
     ap.add_argument("--launches-per-step", type=int, default=1000)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report (from profiles/)")
+    ap.add_argument("--only", default=None, help="run just this secondary case (a key of `extra`), eagerly")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")

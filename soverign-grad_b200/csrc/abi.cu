@@ -55,8 +55,8 @@ const DeviceInfo& device_info() {
 
 int sm_count() { return device_info().sms; }
 
-bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
-                        uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+bool make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint32_t rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -73,19 +73,31 @@ bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void*
         set_error("cuTensorMapEncodeTiled is not available from this driver");
         return false;
     }
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_pitch_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], estr[5];
+    for (uint32_t i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        estr[i] = 1;
+        if (i + 1 < rank) st[i] = strides_bytes[i];
+    }
+    CUresult r = encode(map, dtype, rank, const_cast<void*>(base), d, st, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu pitch=%llu box=%ux%u)",
-                  static_cast<int>(r), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
-                  static_cast<unsigned long long>(row_pitch_bytes), box_inner, box_outer);
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (rank=%u dims=%llu,%llu box=%u,%u pitch=%llu)",
+                  static_cast<int>(r), rank, static_cast<unsigned long long>(dims[0]),
+                  static_cast<unsigned long long>(dims[1]), box[0], box[1], static_cast<unsigned long long>(strides_bytes[0]));
         return false;
     }
     return true;
+}
+
+bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner, uint64_t outer,
+                        uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    const uint64_t dims[2] = {inner, outer};
+    const uint64_t strides[1] = {row_pitch_bytes};
+    const uint32_t box[2] = {box_inner, box_outer};
+    return make_tensor_map(map, dtype, base, 2, dims, strides, box, swizzle);
 }
 
 namespace {

@@ -1,26 +1,30 @@
-// Decode-shape forward (M <= 8) for INT4 g=32 weights stored [N,K]:  y = x * deq(W)^T + bias.
+// Decode-shape forward (M <= 16) for INT4 g=32 weights stored [N,K]:  y = x * deq(W)^T + bias.
 //
 // HBM-bound: every packed byte and every scale is read exactly once.
-//   bytes per weight row-block = 16 rows * (K/2 + K/32*4);  x (M*K*4) and y are negligible.
+//   algorithmic bytes = N*K/2 (nibbles) + N*K/32*4 (scales) + M*K*4 (x) + M*N*4 (y).
 //
-// Structure (one persistent CTA per SM, 8 consumer warps + 1 producer warp):
-//   * the producer thread streams [16 rows x 128 B] boxes of packed weights (128-byte swizzle,
-//     so the per-row word reads below are bank-conflict free) and [16 rows x 32] boxes of fp32
-//     scales through TMA into a ring of stages guarded by full/empty mbarriers;
-//   * x is converted once per CTA to split bf16 (hi + lo, 16 significant bits) and kept in
-//     shared memory in the order the B fragments want it;
-//   * a consumer warp owns one 256-k box of a stage: nibbles become exact bf16 integers in
-//     registers with one LOP3 per pair (0x4300 | (nibble ^ 8) = 136 + code, minus 136), the
-//     16x8 products of 16 rows with the hi/lo columns of up to 4 (8) batch rows come from
-//     mma.sync m16n8k16 with fp32 accumulators, and the group scale is applied in fp32 to each
-//     32-k group sum: y = sum_g scale[n,g] * (sum_{k in g} code[n,k] * x[k]);
-//   * the 8 warps' partial sums of a 16-row tile are added in warp order through shared memory
-//     (fixed order -> run-to-run deterministic), hi+lo are joined, bias is added, y is stored.
+// One persistent CTA per SM: 8 or 16 consumer warps + 1 TMA producer warp + 1 reducer warp.
+//   * The producer thread issues two TMA copies per stage: a 3-D box [8 steps][16 rows][128 B]
+//     of packed weights (128-byte swizzle: the per-row word reads below are bank-conflict free)
+//     and a box [8 steps][16 rows][8] of fp32 scales, into a ring of stages guarded by
+//     full/empty mbarriers.  A step is 256 k of a 16-row tile.
+//   * Integer inner product.  Each activation row is turned once per CTA into fixed point
+//     relative to the power of two above its absmax (22 bits for M <= 5, 14 bits above), split
+//     into balanced base-256 digits (int8).  The 4-bit codes become bytes with two LOP3s per
+//     eight codes ((w & 0x0F0F0F0F) ^ 0x08080808 = code + 8, exact), and a 32-k group of 16
+//     weight rows times up to 8 digit columns is ONE mma.sync m16n8k32 (u8 x s8 -> s32, exact).
+//     The +8 offset is cancelled exactly by starting the accumulator at -8 * sum(digits).
+//   * The exact group sums are converted to fp32, multiplied by the group's fp32 scale and
+//     accumulated in fp32:  y[m,n] = 2^-p_m * sum_j 256^j * sum_g scale[n,g] * S[n,g,m,j].
+//   * A consumer warp that finishes its share of a tile drops its partial sums into a small
+//     ring in shared memory and moves on; a dedicated reducer warp adds the partials in warp
+//     order (fixed order -> run-to-run deterministic), recombines digits, adds bias, stores y.
+//     Consumer warps never wait for one another, only for data and for ring slots.
 //
-// The accumulation differs from the reference's single fp32 chain only in rounding (products
-// with 16-bit x are exact, group sums are fp32): max error ~1e-5 relative, inside the 1e-3 bound.
-#include <cuda_bf16.h>
-
+// Error against the reference's single fp32 chain: the fixed-point step is 2^-22 (2^-14) of the
+// row's power-of-two bound per activation, everything up to the group sums is exact, the rest
+// is fp32 rounding: ~1e-6 (M <= 5) / ~4e-5 (M > 5) relative for Gaussian rows, inside 1e-3.
+// Activations must be finite.
 #include "sgq_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -37,34 +41,59 @@ cudaError_t read_status_gemv(uint32_t* v, bool clear) {
     return e;
 }
 
+#ifdef SGQ_TIMELINE
+// Debug build only: per-warp timestamps (globaltimer, ns) of the kernel's phases.
+__device__ unsigned long long* g_timeline = nullptr;
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define SGQ_MARK(slot)                                                                                     \
+    do {                                                                                                   \
+        if (g_timeline && (threadIdx.x & 31) == 0)                                                         \
+            g_timeline[(blockIdx.x * 32 + (threadIdx.x >> 5)) * 16 + (slot)] = now_ns();                   \
+    } while (0)
+extern "C" __attribute__((visibility("default"))) int sgq_debug_set_timeline(unsigned long long* buf) {
+    return static_cast<int>(cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf)));
+}
+#else
+#define SGQ_MARK(slot) do { } while (0)
+#endif
+
+#ifndef SGQ_EXP
+#define SGQ_EXP 0
+#endif
+
 namespace {
 
 constexpr int kRows = 16;                  // rows of W per tile (mma M)
-constexpr int kStepK = 256;                // k per box
-constexpr int kConsumerWarps = 8;          // one box each per stage
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kWBoxBytes = kRows * 128;    // 2048
-constexpr int kSBoxBytes = kRows * 128;    // 16 rows x 32 fp32 = 4 steps worth of scales
-constexpr int kStageW = kConsumerWarps * kWBoxBytes;          // 16384
-constexpr int kStageS = 2 * kSBoxBytes;                       // 4096
-constexpr int kStageBytes = kStageW + kStageS;                // 20480
+constexpr int kStepK = 256;                // k per step (one 128-byte swizzle row per weight row)
+constexpr int kStepsPerStage = 8;
+constexpr int kWStepBytes = kRows * 128;   // 2048
+constexpr int kSStepBytes = kRows * 32;    // 16 rows x 8 fp32
+constexpr int kStageW = kStepsPerStage * kWStepBytes;   // 16384
+constexpr int kStageS = kStepsPerStage * kSStepBytes;   // 4096
+constexpr int kStageBytes = kStageW + kStageS;          // 20480
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 227 * 1024;
+constexpr int kMaxM = 16;
+constexpr int kPSlots = 2;                 // ring of per-tile partial-sum buffers
 
 struct Smem {
-    // offsets from a 1024-byte aligned base
-    uint32_t stages_off, x_off, partial_off, bars_off, total;
+    uint32_t stages_off, x_off, corr_off, partial_off, misc_off, total;   // from a 1024-byte aligned base
 };
 
-__host__ __device__ inline Smem smem_layout(int nstages, int64_t K, int nsets) {
+// groups = K/32; x digits: 256 B per (group, set); corrections: 32 B per (group, set)
+__host__ __device__ inline Smem smem_layout(int nstages, int64_t K, int nsets, int nwarps) {
     Smem s;
+    const uint32_t groups = static_cast<uint32_t>(K / 32);
     s.stages_off = 0;
     s.x_off = nstages * kStageBytes;
-    const uint32_t ksteps32 = static_cast<uint32_t>((K + kStepK - 1) / kStepK) * (kStepK / 32);  // groups, padded
-    s.partial_off = s.x_off + ksteps32 * 512u * nsets;
-    s.bars_off = s.partial_off + 2u * kConsumerWarps * 512u * nsets;  // double-buffered partials
-    s.total = s.bars_off + 2u * kMaxStages * 8u + 16u;
+    s.corr_off = s.x_off + groups * 256u * nsets;
+    s.partial_off = s.corr_off + groups * 32u * nsets;
+    s.misc_off = s.partial_off + kPSlots * nwarps * (512u * nsets + 16u);   // padded per-warp partial sums
+    s.total = s.misc_off + (2u * kMaxStages + 2u * kPSlots + 1u) * 8u + kMaxM * 8u + 16u;
     return s;
 }
 
@@ -72,69 +101,193 @@ __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
     atomicCAS(&g_status_gemv, 0u, (code << 24) | (detail & 0xFFFFFFu));
 }
 
-// split x into bf16 hi + bf16 lo (x ~= hi + lo, 16 significant bits)
-__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
-    hi = __float2bfloat16_rn(v);
-    const float r = v - __bfloat162float(hi);
-    lo = (fabsf(v) <= 3.0e38f) ? __float2bfloat16_rn(r) : __float2bfloat16_rn(0.0f);
+// D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col) + C
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                               int c0, int c1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c0), "r"(c1));
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 a, __nv_bfloat16 b) {
-    return static_cast<uint32_t>(__bfloat16_as_ushort(a)) | (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
+// Balanced base-256 digits of q (|q| <= 2^22): q = d0 + 256 d1 + 65536 d2 with every d in [-128, 127].
+// Adding 128 to each digit makes them unsigned bytes without carries between byte positions, so
+// the bytes of (q + 0x808080) are d_j + 128 and one more XOR turns them back into signed bytes.
+__device__ __forceinline__ uint32_t digit_bytes(int q) {
+    return (static_cast<uint32_t>(q) + 0x00808080u) ^ 0x00808080u;
+}
+// byte j of four words -> one word (a.j, b.j, c.j, d.j)
+__device__ __forceinline__ uint32_t gather_byte(uint32_t a, uint32_t b, uint32_t c, uint32_t d, int j) {
+    const uint32_t ab = __byte_perm(a, b, 0x0040 + 0x11 * j);   // (a.j, b.j, -, -)
+    const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x11 * j);
+    return __byte_perm(ab, cd, 0x5410);
 }
 
-// 8 nibbles of one row-word -> four bf16x2 registers holding the exact codes
-//   p[j] = (code of nibble j, code of nibble j+4)
-__device__ __forceinline__ void nibbles_to_bf16(uint32_t w, uint32_t (&p)[4]) {
-    const uint32_t kMagic = 0x43084308u;   // bf16 136.0 in both halves; ^8 folds the sign bias in
-    const uint32_t k136 = 0x43084308u;
+// One item = 8 consecutive activations (m, chunk c) already scaled knowledge: row bound bits `mb`.
+// Writes the item's digit bytes into the B-fragment plane and, for the lane with t == 0, the
+// group's correction.  The four lanes holding the four chunks of a 32-k group must call together.
+//   xs  : [group][set][col 8][t 4] x 8 bytes; the 8 bytes of (col, t) are the digits of
+//         k = 32*group + 8t + {0,2,4,6} (b0) and + {1,3,5,7} (b1); column col = m*ndigits + j.
+//   corr: [group][set][col 8] int32 = -8 * sum over the group's 32 k of that column's digits.
+__device__ __forceinline__ void row_scale(uint32_t mb, int frac_bits, float* P, float* invP) {
+    // P = 2^(frac_bits - e) with 2^e > absmax (e = exponent of absmax + 1); absmax 0 -> P = 1
+    const int e = static_cast<int>(mb >> 23) - 127 + 1;
+    int sh = frac_bits - e;                 // kept inside the normal range
+    sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+    *P = (mb == 0) ? 1.0f : __uint_as_float(static_cast<uint32_t>(127 + sh) << 23);
+    *invP = (mb == 0) ? 1.0f : __uint_as_float(static_cast<uint32_t>(127 - sh) << 23);
+}
+
+__device__ __forceinline__ void digits_item(const float (&v)[8], float P, int m, int c, int ndigits, int nsets,
+                                            uint8_t* xs, uint8_t* corr) {
+    uint32_t db[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        uint32_t v = ((w >> (4 * j)) & 0x000F000Fu) ^ kMagic;   // 136 + code, exact in bf16
-        uint32_t r;
-        asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(k136));
-        p[j] = r;
+    for (int j = 0; j < 8; ++j) db[j] = digit_bytes(__float2int_rn(v[j] * P));
+    const int group = c >> 2, t = c & 3;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        if (j < ndigits) {
+            const uint32_t b0 = gather_byte(db[0], db[2], db[4], db[6], j);   // k = 8t + {0,2,4,6}
+            const uint32_t b1 = gather_byte(db[1], db[3], db[5], db[7], j);   // k = 8t + {1,3,5,7}
+            int sum = __dp4a(static_cast<int>(b0), 0x01010101, __dp4a(static_cast<int>(b1), 0x01010101, 0));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
+            *reinterpret_cast<uint2*>(xs + (static_cast<size_t>(group) * nsets + set) * 256 + (cc * 4 + t) * 8) =
+                make_uint2(b0, b1);
+            if (t == 0)
+                *reinterpret_cast<int*>(corr + (static_cast<size_t>(group) * nsets + set) * 32 + cc * 4) = -8 * sum;
+        }
     }
 }
 
-template <int NSETS>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ float absmax8(const float (&v)[8]) {
+    return fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                 fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+}
+
+// Activation planes for batches too large to convert inside every CTA: one CTA per batch row,
+// written once to global scratch in exactly the shared-memory layout the main kernel uses:
+//   [digit planes: groups*nsets*256 B][corrections: groups*nsets*32 B][inv_p: 16 fp32]
+constexpr int kPrepThreads = 512;
+constexpr int kPrepMaxChunks = 8;   // per thread: K <= 8 * 512 * 8 = 32768
+__global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int M, int64_t K,
+                                                                     int ndigits, int nsets, uint8_t* __restrict__ planes) {
+    __shared__ float red[kPrepThreads / 32];
+    const int m = blockIdx.x, lane = threadIdx.x & 31;
+    const int chunks = static_cast<int>(K / 8);
+    const size_t groups = static_cast<size_t>(K / 32);
+    uint8_t* xs = planes;
+    uint8_t* corr = planes + groups * nsets * 256;
+    float* inv_p = reinterpret_cast<float*>(corr + groups * nsets * 32);
+    float v[kPrepMaxChunks][8];
+    float mx = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kPrepMaxChunks; ++r) {
+        const int c = threadIdx.x + r * kPrepThreads;
+        if (c < chunks) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K) + 2 * c);
+            const float4 b = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K) + 2 * c + 1);
+            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
+            mx = fmaxf(mx, absmax8(v[r]));
+        }
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    float all = red[lane < kPrepThreads / 32 ? lane : 0];
+    all = warp_max(all);
+    float P, invP;
+    row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
+    if (threadIdx.x == 0) inv_p[m] = invP;
+#pragma unroll
+    for (int r = 0; r < kPrepMaxChunks; ++r) {
+        const int c = threadIdx.x + r * kPrepThreads;
+        if (c < chunks) digits_item(v[r], P, m, c, ndigits, nsets, xs, corr);   // chunks % 32 == 0: whole warps
+    }
+}
+
+// NSETS: sets of 8 digit columns; WPB: consumer warps per 256-k step (1 or 2);
+// PRE: the activation planes were prepared by gemv_prepare_x_kernel and are copied in by TMA.
+template <int NSETS, int WPB, bool PRE>
+__global__ void __launch_bounds__((kStepsPerStage * WPB + 2) * 32, 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
-                    const float* __restrict__ x, const float* __restrict__ bias, float* __restrict__ y, int M,
-                    int64_t K, int64_t N, int64_t ldy, int nstages) {
+                    const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
+                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages) {
+    constexpr int kWarps = kStepsPerStage * WPB;
+    constexpr int kConsumerThreads = kWarps * 32;
+    constexpr int kGroupsPerWarp = 8 / WPB;
+
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const Smem L = smem_layout(nstages, K, NSETS);
+    const Smem L = smem_layout(nstages, K, NSETS, kWarps);
     uint8_t* stages = smem + L.stages_off;
     uint8_t* xs = smem + L.x_off;
+    uint8_t* corr = smem + L.corr_off;
     float* partial = reinterpret_cast<float*>(smem + L.partial_off);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars_off);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.misc_off);
     uint64_t* empty = full + kMaxStages;
+    uint64_t* pfull = empty + kMaxStages;      // [kPSlots] every consumer warp has left its partial sums
+    uint64_t* pempty = pfull + kPSlots;        // [kPSlots] the reducer is done with the slot
+    uint64_t* xfull = pempty + kPSlots;        // [1] prepared activation planes have landed (PRE)
+    uint32_t* rowmax_bits = reinterpret_cast<uint32_t*>(xfull + 1);            // [16]
+    float* inv_p = reinterpret_cast<float*>(rowmax_bits + kMaxM);              // [16]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
-    const int spt = static_cast<int>((K + kStepK - 1) / kStepK);   // steps (boxes) per tile
-    const int sgroups = static_cast<int>(K / 32);                  // scale columns
+    const int spt = static_cast<int>(K / kStepK);   // steps per tile (K % 256 == 0)
 
+    SGQ_MARK(0);
+    if (threadIdx.x == kWarps * 32) {   // the producer thread: start fetching both descriptors now
+        tma_prefetch_descriptor(&map_w);
+        tma_prefetch_descriptor(&map_s);
+    }
+    // The first kPre items of every consumer thread are requested before anything else, so that
+    // their global-memory latency overlaps barrier set-up and the producer's first TMA issues.
+    constexpr int kPre = PRE ? 1 : 4;
+    const int chunks = static_cast<int>(K / 8);   // 8-float chunks per activation row
+    const int items = chunks * M;
+    float4 pre_a[kPre], pre_b[kPre];
+#pragma unroll
+    for (int r = 0; r < kPre; ++r) {
+        const int it = threadIdx.x + r * kConsumerThreads;
+        if (!PRE && warp < kWarps && it < items) {
+            pre_a[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
+            pre_b[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
+        } else {
+            pre_a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            pre_b[r] = pre_a[r];
+        }
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], kConsumerWarps);
+            mbar_init(&empty[i], kWarps);
         }
+        for (int i = 0; i < kPSlots; ++i) {
+            mbar_init(&pfull[i], kWarps);
+            mbar_init(&pempty[i], 1);
+        }
+        mbar_init(xfull, 1);
         mbar_fence_init();
         fence_proxy_async_smem();
     }
+    if (threadIdx.x < kMaxM) rowmax_bits[threadIdx.x] = 0;
     __syncthreads();
 
-    if (warp == kConsumerWarps) {
+    if (warp == kWarps) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            tma_prefetch_descriptor(&map_w);
-            tma_prefetch_descriptor(&map_s);
+            if (PRE) {
+                // digit planes + corrections, contiguous in both places, in pieces of <= 32 KiB
+                const uint32_t bytes = L.partial_off - L.x_off;
+                mbar_arrive_expect_tx(xfull, bytes);
+                for (uint32_t off = 0; off < bytes; off += 32768u)
+                    bulk_copy_g2s(xs + off, planes + off, (bytes - off < 32768u) ? bytes - off : 32768u, xfull);
+            }
             uint32_t seq = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                for (int c0 = 0; c0 < spt; c0 += kConsumerWarps, ++seq) {
+                for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
                     const int st = seq % nstages;
                     const uint32_t ph = (seq / nstages) & 1u;
                     if (!mbar_wait(&empty[st], ph ^ 1u)) {
@@ -142,228 +295,351 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         ok = false;
                         break;
                     }
-                    const int cnt = (spt - c0 < kConsumerWarps) ? spt - c0 : kConsumerWarps;
-                    const int sboxes = (c0 * 8 + 32 < sgroups) ? 2 : 1;
-                    mbar_arrive_expect_tx(&full[st], cnt * kWBoxBytes + sboxes * kSBoxBytes);
+                    // steps past K/256 are out of range in the third dimension: zero-filled, still counted
+                    mbar_arrive_expect_tx(&full[st], kStageBytes);
                     uint8_t* sw = stages + st * kStageBytes;
-                    for (int b = 0; b < cnt; ++b)
-                        tma_load_2d(sw + b * kWBoxBytes, &map_w, &full[st], (c0 + b) * 128, static_cast<int32_t>(tile * kRows));
-                    for (int b = 0; b < sboxes; ++b)
-                        tma_load_2d(sw + kStageW + b * kSBoxBytes, &map_s, &full[st], c0 * 8 + b * 32,
-                                    static_cast<int32_t>(tile * kRows));
+                    tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
+                    tma_load_3d(sw + kStageW, &map_s, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
+                    if (seq == 0) SGQ_MARK(1);
+                    if (seq == 6) SGQ_MARK(2);
                 }
             }
+            SGQ_MARK(3);
+        }
+        return;
+    }
+
+    constexpr int kPStride = 128 * NSETS + 4;   // floats per warp in a partial-sum slot (padded against bank conflicts)
+    if (warp == kWarps + 1) {
+        // ---------------- reducer ----------------
+        // lane -> output pairs (tile row r, batch row m); per digit column the kWarps partial sums
+        // are added in warp order, then digits are recombined: y = 2^-p * sum_j 256^j v_j + bias.
+        uint32_t tcount = 0;
+        const int pairs = kRows * M;
+        for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
+            const int slot = tcount % kPSlots;
+            const uint32_t pph = (tcount / kPSlots) & 1u;
+            if (!mbar_wait(&pfull[slot], pph)) {
+                report(kDevErrFullWait, 0x800000u | tcount);
+                break;
+            }
+            const float* pbuf = partial + slot * (kWarps * kPStride);
+            for (int p = lane; p < pairs; p += 32) {
+                const int r = p & 15, m = p >> 4;
+                const int gg = r & 7, hi = r >> 3;
+                float acc = 0.0f, weight = 1.0f;
+                for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
+                    const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
+                    const float* src = pbuf + (set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1);
+                    float v = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w) v += src[w * kPStride];
+                    acc = __fmaf_rn(weight, v, acc);
+                }
+                const int64_t n = tile * kRows + r;
+                if (n < N) {
+                    float v = acc * (PRE ? __ldg(reinterpret_cast<const float*>(planes + (L.partial_off - L.x_off)) + m)
+                                         : inv_p[m]);
+                    if (bias) v += bias[n];
+                    y[static_cast<int64_t>(m) * ldy + n] = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pempty[slot]);
         }
         return;
     }
 
     // ---------------- consumers ----------------
-    // x -> split bf16, fragment order: [group s][set][col n (8)][t (4)] x 16 bytes, the 8 values
-    // of (s, t) being k = 32s + 8t + {0,4,1,5,2,6,3,7}.
-    {
-        const int64_t chunks = static_cast<int64_t>(spt) * (kStepK / 8);   // 8-float chunks per row (padded)
-        const int mrows = NSETS * 4;                                       // batch rows covered
-        for (int64_t it = threadIdx.x; it < chunks * mrows; it += kConsumerThreads) {
-            const int m = static_cast<int>(it / chunks);
-            const int64_t c = it % chunks;                                 // chunk = (s, t)
-            float v[8];
-            if (m < M && (c + 1) * 8 <= K) {
-                const float4 a = *reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K + c * 8);
-                const float4 b = *reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K + c * 8 + 4);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            } else {
+    bool alive = true;   // false after a wait ran out: skip the math but keep every barrier balanced
+    if (PRE) {
+        if (!mbar_wait(xfull, 0)) {
+            report(kDevErrFullWait, 0x400000u);
+            alive = false;
+        }
+    } else {
+        // Activations -> int8 digits, inside the CTA (small batches: every item was requested at the top).
+        auto unpack = [](const float4& a, const float4& b, float (&v)[8]) {
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        };
+        auto load_item = [&](int it, float (&v)[8]) {
+            unpack(__ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it)),
+                   __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1), v);
+        };
+        // pass 1: absmax per row (the bit pattern of |x| orders like the value).  items % 32 == 0 and
+        // chunks % 4 == 0, so whole warps are in or out and 4 neighbouring lanes share a row.
+        auto absmax_item = [&](int it, const float (&v)[8]) {
+            float mx = absmax8(v);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            if ((lane & 3) == 0) atomicMax(&rowmax_bits[it / chunks], __float_as_uint(mx));
+        };
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-            }
-            __nv_bfloat16 hi[8], lo[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) split_bf16(v[j], hi[j], lo[j]);
-            const uint4 H = make_uint4(pack_bf16(hi[0], hi[4]), pack_bf16(hi[1], hi[5]), pack_bf16(hi[2], hi[6]),
-                                       pack_bf16(hi[3], hi[7]));
-            const uint4 Lo = make_uint4(pack_bf16(lo[0], lo[4]), pack_bf16(lo[1], lo[5]), pack_bf16(lo[2], lo[6]),
-                                        pack_bf16(lo[3], lo[7]));
-            const int64_t s = c >> 2;
-            const int t = static_cast<int>(c & 3);
-            uint8_t* base = xs + s * (512 * NSETS);
-            if (NSETS == 1) {
-                // columns 0..3 = hi of batch rows 0..3, columns 4..7 = lo
-                *reinterpret_cast<uint4*>(base + (m * 4 + t) * 16) = H;
-                *reinterpret_cast<uint4*>(base + ((m + 4) * 4 + t) * 16) = Lo;
-            } else {
-                // set 0 = hi of batch rows 0..7, set 1 = lo
-                *reinterpret_cast<uint4*>(base + (m * 4 + t) * 16) = H;
-                *reinterpret_cast<uint4*>(base + 512 + (m * 4 + t) * 16) = Lo;
+        for (int r = 0; r < kPre; ++r) {
+            const int it = threadIdx.x + r * kConsumerThreads;
+            if (it < items) {
+                float v[8];
+                unpack(pre_a[r], pre_b[r], v);
+                absmax_item(it, v);
             }
         }
+        for (int it = threadIdx.x + kPre * kConsumerThreads; it < items; it += kConsumerThreads) {
+            float v[8];
+            load_item(it, v);
+            absmax_item(it, v);
+        }
+        // Columns >= M*ndigits of the digit planes stay uninitialised: they only feed accumulator
+        // columns that nobody reads (integer MMA: no NaN can spread).
+        named_barrier_sync(1, kConsumerThreads);
+        const int frac_bits = (ndigits == 3) ? 22 : 14;
+        // pass 2: fixed point + digits.  Four neighbouring lanes own the four t-chunks of one group.
+        auto convert_item = [&](int it, const float (&v)[8]) {
+            const int m = it / chunks, c = it - m * chunks;
+            float P, invP;
+            row_scale(rowmax_bits[m], frac_bits, &P, &invP);
+            if (c == 0) inv_p[m] = invP;
+            digits_item(v, P, m, c, ndigits, NSETS, xs, corr);
+        };
+#pragma unroll
+        for (int r = 0; r < kPre; ++r) {
+            const int it = threadIdx.x + r * kConsumerThreads;
+            if (it < items) {
+                float v[8];
+                unpack(pre_a[r], pre_b[r], v);
+                convert_item(it, v);
+            }
+        }
+        for (int it = threadIdx.x + kPre * kConsumerThreads; it < items; it += kConsumerThreads) {
+            float v[8];
+            load_item(it, v);
+            convert_item(it, v);
+        }
     }
+    SGQ_MARK(1);
     named_barrier_sync(1, kConsumerThreads);
+    SGQ_MARK(2);
 
     const int g = lane >> 2, t = lane & 3;
-    uint32_t seq = 0;
-    int tile_parity = 0;
-    bool alive = true;   // false after a wait ran out: skip the math but keep every barrier balanced
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, tile_parity ^= 1) {
+    const int step_in_stage = warp / WPB;            // which 256-k step of a stage this warp works on
+    const int g0 = (warp % WPB) * kGroupsPerWarp;    // first of its groups inside the step
+    // byte offset of this lane's word inside a step box, for each of its groups (swizzle: chunk ^ row)
+    uint32_t woff[kGroupsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kGroupsPerWarp; ++i) woff[i] = g * 128 + (((g0 + i) ^ g) << 4) + t * 4;
+
+    uint32_t seq = 0, tcount = 0;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
         float total[NSETS][4];
 #pragma unroll
         for (int s = 0; s < NSETS; ++s)
 #pragma unroll
             for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
-        for (int c0 = 0; c0 < spt; c0 += kConsumerWarps, ++seq) {
+        for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
             const int st = seq % nstages;
             const uint32_t ph = (seq / nstages) & 1u;
             if (alive && !mbar_wait(&full[st], ph)) {
                 report(kDevErrFullWait, seq);
                 alive = false;
             }
-            const int step = c0 + warp;
-            if (alive && step < spt) {
-                const uint8_t* wbox = stages + st * kStageBytes + warp * kWBoxBytes;
-                const uint8_t* sbox = stages + st * kStageBytes + kStageW + (warp >> 2) * kSBoxBytes;
-                // the 8 scales of this step for rows g and g+8: 16-byte chunks (warp&3)*2 and +1,
-                // swizzled by the row (chunk ^ (row & 7)); rows g+8 live in the second 1 KiB atom.
-                float sc_lo[8], sc_hi[8];
+            if (seq < 5) SGQ_MARK(3 + 2 * seq);
+            const int step = c0 + step_in_stage;
+            if (alive && step < spt && !(SGQ_EXP & 16)) {
+                const uint8_t* wbox = stages + st * kStageBytes + step_in_stage * kWStepBytes;
+                const uint8_t* sbox = stages + st * kStageBytes + kStageW + step_in_stage * kSStepBytes;
+                float sc_lo[kGroupsPerWarp], sc_hi[kGroupsPerWarp];   // scales of rows g and g+8
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int chunk = ((warp & 3) * 2 + h) ^ g;
-                    const float4 a = *reinterpret_cast<const float4*>(sbox + g * 128 + chunk * 16);
-                    const float4 b = *reinterpret_cast<const float4*>(sbox + 1024 + g * 128 + chunk * 16);
+                for (int h = 0; h < kGroupsPerWarp / 4; ++h) {
+#if (SGQ_EXP & 128)
+                    const float4 a = make_float4(1.f, 2.f, 3.f, 4.f), b = a;
+#else
+                    const float4 a = *reinterpret_cast<const float4*>(sbox + g * 32 + (g0 / 4 + h) * 16);
+                    const float4 b = *reinterpret_cast<const float4*>(sbox + (g + 8) * 32 + (g0 / 4 + h) * 16);
+#endif
                     sc_lo[4 * h + 0] = a.x; sc_lo[4 * h + 1] = a.y; sc_lo[4 * h + 2] = a.z; sc_lo[4 * h + 3] = a.w;
                     sc_hi[4 * h + 0] = b.x; sc_hi[4 * h + 1] = b.y; sc_hi[4 * h + 2] = b.z; sc_hi[4 * h + 3] = b.w;
                 }
-                const uint8_t* xstep = xs + static_cast<int64_t>(step) * 8 * (512 * NSETS) + lane * 16;
+                const size_t group0 = static_cast<size_t>(step) * 8 + g0;
+                const uint8_t* xg = xs + group0 * (256 * NSETS) + lane * 8;
+                const uint8_t* cg = corr + group0 * (32 * NSETS) + t * 8;
+                uint32_t wl[kGroupsPerWarp], wh[kGroupsPerWarp];
 #pragma unroll
-                for (int s8 = 0; s8 < 8; ++s8) {
-                    const int chunk = (s8 ^ g) * 16 + t * 4;
-                    const uint32_t w_lo = *reinterpret_cast<const uint32_t*>(wbox + g * 128 + chunk);
-                    const uint32_t w_hi = *reinterpret_cast<const uint32_t*>(wbox + 1024 + g * 128 + chunk);
-                    uint32_t pl[4], phh[4];
-                    nibbles_to_bf16(w_lo, pl);
-                    nibbles_to_bf16(w_hi, phh);
-                    const uint32_t a1[4] = {pl[0], phh[0], pl[1], phh[1]};
-                    const uint32_t a2[4] = {pl[2], phh[2], pl[3], phh[3]};
+                for (int i = 0; i < kGroupsPerWarp; ++i) {
+                    wl[i] = *reinterpret_cast<const uint32_t*>(wbox + woff[i]);
+                    wh[i] = *reinterpret_cast<const uint32_t*>(wbox + 1024 + woff[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < kGroupsPerWarp; ++i) {
+                    const uint32_t w_lo = wl[i], w_hi = wh[i];
+                    uint32_t a[4];
+                    a[0] = (w_lo & 0x0F0F0F0Fu) ^ 0x08080808u;          // row g,   k = 8t + {0,2,4,6}: code + 8
+                    a[1] = (w_hi & 0x0F0F0F0Fu) ^ 0x08080808u;          // row g+8
+                    a[2] = ((w_lo >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // row g,   k = 8t + {1,3,5,7}
+                    a[3] = ((w_hi >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // row g+8
 #pragma unroll
                     for (int s = 0; s < NSETS; ++s) {
-                        const uint4 xb = *reinterpret_cast<const uint4*>(xstep + s8 * (512 * NSETS) + s * 512);
-                        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        float d[4];
-                        mma_bf16_16816(d, a1, xb.x, xb.y, zero);
-                        mma_bf16_16816(d, a2, xb.z, xb.w, d);
-                        total[s][0] = __fmaf_rn(sc_lo[s8], d[0], total[s][0]);
-                        total[s][1] = __fmaf_rn(sc_lo[s8], d[1], total[s][1]);
-                        total[s][2] = __fmaf_rn(sc_hi[s8], d[2], total[s][2]);
-                        total[s][3] = __fmaf_rn(sc_hi[s8], d[3], total[s][3]);
+#if (SGQ_EXP & 64)
+                        const uint2 xb = make_uint2(seq + i, seq * 3 + s);
+                        const int2 cc = make_int2(i, s);
+#else
+                        const uint2 xb = *reinterpret_cast<const uint2*>(xg + i * (256 * NSETS) + s * 256);
+                        const int2 cc = *reinterpret_cast<const int2*>(cg + i * (32 * NSETS) + s * 32);
+#endif
+                        int d[4];
+#if (SGQ_EXP & 4)
+                        d[0] = a[0] + xb.x + cc.x; d[1] = a[1] + xb.y + cc.y; d[2] = a[2] + xb.x; d[3] = a[3] + xb.y;
+#else
+                        mma_u8s8_16832(d, a, xb.x, xb.y, cc.x, cc.y);
+#endif
+#if (SGQ_EXP & 2)
+                        total[s][0] += __int_as_float(d[0]); total[s][1] += __int_as_float(d[1]);
+                        total[s][2] += __int_as_float(d[2]) * sc_lo[i]; total[s][3] += __int_as_float(d[3]) * sc_hi[i];
+#else
+                        total[s][0] = __fmaf_rn(sc_lo[i], static_cast<float>(d[0]), total[s][0]);
+                        total[s][1] = __fmaf_rn(sc_lo[i], static_cast<float>(d[1]), total[s][1]);
+                        total[s][2] = __fmaf_rn(sc_hi[i], static_cast<float>(d[2]), total[s][2]);
+                        total[s][3] = __fmaf_rn(sc_hi[i], static_cast<float>(d[3]), total[s][3]);
+#endif
                     }
                 }
             }
             __syncwarp();
+            if (seq < 5) SGQ_MARK(4 + 2 * seq);
             if (lane == 0) mbar_arrive(&empty[st]);
         }
+        if (tile == blockIdx.x) SGQ_MARK(13);
 
-        // ---- tile epilogue: fixed-order sum over the 8 warps, join hi+lo, bias, store ----
-        float* pbuf = partial + tile_parity * (kConsumerWarps * 128 * NSETS);
-#pragma unroll
-        for (int s = 0; s < NSETS; ++s)
-            *reinterpret_cast<float4*>(pbuf + ((warp * NSETS + s) * 32 + lane) * 4) =
-                make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
-        named_barrier_sync(1, kConsumerThreads);
+        // ---- hand the tile's partial sums to the reducer warp ----
         {
-            // thread -> (row r of the tile, batch row m)
-            const int r = threadIdx.x >> 3, m = threadIdx.x & 7;
-            if (r < kRows && m < M) {
-                const int gg = r & 7, half = r >> 3;
-                float v;
-                if (NSETS == 1) {
-                    // hi in column m, lo in column m+4
-                    const int l_hi = gg * 4 + (m >> 1), l_lo = gg * 4 + ((m + 4) >> 1);
-                    const int idx = half * 2 + (m & 1);
-                    float vh = 0.0f, vl = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < kConsumerWarps; ++w) {
-                        vh += pbuf[(w * 32 + l_hi) * 4 + idx];
-                        vl += pbuf[(w * 32 + l_lo) * 4 + idx];
-                    }
-                    v = vh + vl;
-                } else {
-                    const int l = gg * 4 + (m >> 1);
-                    const int idx = half * 2 + (m & 1);
-                    float vh = 0.0f, vl = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < kConsumerWarps; ++w) {
-                        vh += pbuf[((w * 2 + 0) * 32 + l) * 4 + idx];
-                        vl += pbuf[((w * 2 + 1) * 32 + l) * 4 + idx];
-                    }
-                    v = vh + vl;
-                }
-                const int64_t n = tile * kRows + r;
-                if (n < N) {
-                    if (bias) v += bias[n];
-                    y[static_cast<int64_t>(m) * ldy + n] = v;
-                }
+            const int slot = tcount % kPSlots;
+            const uint32_t pph = (tcount / kPSlots) & 1u;
+            if (alive && !mbar_wait(&pempty[slot], pph ^ 1u)) {
+                report(kDevErrEmptyWait, 0x800000u | tcount);
+                alive = false;
             }
+            float* pbuf = partial + slot * (kWarps * kPStride) + warp * kPStride;
+#pragma unroll
+            for (int s = 0; s < NSETS; ++s)
+                *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) =
+                    make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pfull[slot]);
         }
+        if (tile == blockIdx.x) SGQ_MARK(14);
     }
+    SGQ_MARK(15);
 }
 
 struct Plan {
-    int nsets;
-    int nstages;
+    int ndigits, nsets, wpb, nstages;
+    bool pre;          // activation planes prepared by a separate launch into the workspace
     uint32_t smem;
+    size_t planes_bytes;
 };
 
-bool make_plan(int64_t M, int64_t K, Plan* p) {
-    p->nsets = (M <= 4) ? 1 : 2;
-    for (int st = kMaxStages; st >= 2; --st) {
-        const Smem L = smem_layout(st, K, p->nsets);
-        if (L.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {
-            p->nstages = st;
-            p->smem = L.total + 1024;
-            return true;
+// In-CTA conversion is used while every consumer thread can hold all its items in registers
+// (4 items of 8 activations per thread); larger batches are converted once by a pre-kernel.
+bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p) {
+    p->ndigits = (M <= 5) ? 3 : 2;
+    p->nsets = static_cast<int>((M * p->ndigits + 7) / 8);
+    p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 288 + kMaxM * 4;
+    // two warps per step while at least 3 stages still fit, else one (smaller partial-sum buffers)
+    for (int wpb = 2; wpb >= 1; --wpb) {
+        for (int st = kMaxStages; st >= (wpb == 2 ? 3 : 2); --st) {
+            const Smem L = smem_layout(st, K, p->nsets, kStepsPerStage * wpb);
+            if (L.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {
+                p->wpb = wpb;
+                p->nstages = st;
+                p->smem = L.total + 1024;
+                p->pre = have_workspace && (M * (K / 8) > 4 * kStepsPerStage * wpb * 32) && K <= 8LL * kPrepMaxChunks * kPrepThreads;
+                return true;
+            }
         }
     }
     return false;
+}
+
+template <int NSETS, int WPB, bool PRE>
+int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid) {
+    static SmemOptIn optin;
+    auto kernel = gemv_int4_nk_kernel<NSETS, WPB, PRE>;
+    SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
+    const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
+    if (PRE) {
+        gemv_prepare_x_kernel<<<static_cast<int>(a.M), kPrepThreads, 0, a.stream>>>(a.x, static_cast<int>(a.M), a.K, p.ndigits,
+                                                                                   p.nsets, static_cast<uint8_t*>(a.workspace));
+        SGQ_LAUNCH_CHECK("gemv_prepare_x_kernel");
+    }
+    kernel<<<grid, (kStepsPerStage * WPB + 2) * 32, p.smem, a.stream>>>(map_w, map_s, a.x, planes, a.bias, a.y,
+                                                                         static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
+                                                                         p.nstages);
+    SGQ_LAUNCH_CHECK("gemv_int4_nk_kernel");
+    return SGQ_OK;
+}
+
+template <int NSETS>
+int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid) {
+    if (p.pre)
+        return p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid)
+                          : launch_variant<NSETS, 1, true>(a, p, map_w, map_s, grid);
+    return p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid)
+                      : launch_variant<NSETS, 1, false>(a, p, map_w, map_s, grid);
 }
 
 }  // namespace
 
 bool gemv_supported(const LinearArgs& a) {
     Plan p;
-    return a.bits == 4 && a.layout == SGQ_LAYOUT_NK && a.group == 32 && a.M >= 1 && a.M <= 8 && a.K >= 128 &&
-           (a.K % 128) == 0 && a.N >= 1 && a.N < (1LL << 31) && a.K < (1LL << 31) && aligned(a.wq, 16) &&
-           aligned(a.scales, 16) && aligned(a.x, 16) && make_plan(a.M, a.K, &p);
+    return a.bits == 4 && a.layout == SGQ_LAYOUT_NK && a.group == 32 && a.M >= 1 && a.M <= kMaxM && a.K >= 256 &&
+           (a.K % 256) == 0 && a.N >= 1 && a.N < (1LL << 31) && a.K < (1LL << 24) && aligned(a.wq, 16) &&
+           aligned(a.scales, 16) && aligned(a.x, 16) && make_plan(a.M, a.K, false, &p);
 }
 
-size_t gemv_workspace_bytes(int, int64_t, int64_t, int64_t, int) { return 0; }
+// Scratch for the prepared activation planes (batches converted by the pre-kernel); 0 when the
+// conversion happens inside the CTAs.
+size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
+    (void)N;
+    Plan p;
+    if (bits != 4 || layout != SGQ_LAYOUT_NK || M < 1 || M > kMaxM || K < 256 || (K % 256) != 0) return 0;
+    if (!make_plan(M, K, true, &p) || !p.pre) return 0;
+    return (p.planes_bytes + 255) / 256 * 256;
+}
 
 int launch_linear_gemv(const LinearArgs& a) {
     Plan p;
-    if (!gemv_supported(a) || !make_plan(a.M, a.K, &p)) {
-        set_error("decode path needs INT4 g=32, layout NK, M<=8, K%%128==0, 16-byte aligned x/packed/scales");
+    const size_t want = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
+    if (!gemv_supported(a) || !make_plan(a.M, a.K, have_ws, &p)) {
+        set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "
+                  "16-byte aligned x/packed/scales");
         return SGQ_ERR_UNSUPPORTED;
     }
+    // packed weights as (128 B, N rows, K/256 steps); scales as (8 fp32, N rows, K/256 steps)
     CUtensorMap map_w, map_s;
-    if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, static_cast<uint64_t>(a.K / 2),
-                            static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), 128, kRows,
-                            CU_TENSOR_MAP_SWIZZLE_128B))
-        return SGQ_ERR_CUDA;
-    if (!make_tensor_map_2d(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.scales, static_cast<uint64_t>(a.K / 32),
-                            static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 32) * 4, 32, kRows,
-                            CU_TENSOR_MAP_SWIZZLE_128B))
-        return SGQ_ERR_CUDA;
+    const uint64_t steps = static_cast<uint64_t>(a.K / kStepK);
+    {
+        const uint64_t dims[3] = {128, static_cast<uint64_t>(a.N), steps};
+        const uint64_t strides[2] = {static_cast<uint64_t>(a.K / 2), 128};
+        const uint32_t box[3] = {128, kRows, kStepsPerStage};
+        if (!make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return SGQ_ERR_CUDA;
+    }
+    {
+        const uint64_t dims[3] = {8, static_cast<uint64_t>(a.N), steps};
+        const uint64_t strides[2] = {static_cast<uint64_t>(a.K / 32) * 4, 32};
+        const uint32_t box[3] = {8, kRows, kStepsPerStage};
+        if (!make_tensor_map(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.scales, 3, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_NONE))
+            return SGQ_ERR_CUDA;
+    }
     const int64_t ntiles = ceil_div(a.N, kRows);
     const int grid = static_cast<int>(ntiles < sm_count() ? ntiles : sm_count());
-    static SmemOptIn optin1, optin2;
-    if (p.nsets == 1) {
-        SGQ_CUDA_TRY(optin1.ensure(gemv_int4_nk_kernel<1>, kSmemLimit));
-        gemv_int4_nk_kernel<1><<<grid, kThreads, p.smem, a.stream>>>(map_w, map_s, a.x, a.bias, a.y,
-                                                                      static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages);
-    } else {
-        SGQ_CUDA_TRY(optin2.ensure(gemv_int4_nk_kernel<2>, kSmemLimit));
-        gemv_int4_nk_kernel<2><<<grid, kThreads, p.smem, a.stream>>>(map_w, map_s, a.x, a.bias, a.y,
-                                                                      static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages);
+    switch (p.nsets) {
+        case 1: return launch_nsets<1>(a, p, map_w, map_s, grid);
+        case 2: return launch_nsets<2>(a, p, map_w, map_s, grid);
+        case 3: return launch_nsets<3>(a, p, map_w, map_s, grid);
+        default: return launch_nsets<4>(a, p, map_w, map_s, grid);
     }
-    SGQ_LAUNCH_CHECK("gemv_int4_nk_kernel");
-    return SGQ_OK;
 }
 
 }  // namespace sgq

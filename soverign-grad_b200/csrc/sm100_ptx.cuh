@@ -12,6 +12,9 @@ namespace sgq {
 // Host: builds a 2-D tiled tensor map (row-major tensor, dim0 = contiguous).  Returns false
 // and records the reason on failure.  The driver entry point is resolved through the runtime,
 // so the library does not link libcuda.
+// General form: rank 2..5, dims[0] contiguous, strides_bytes[i] = pitch of dims[i+1].
+bool make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint32_t rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);
 bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
                         CUtensorMapSwizzle swizzle);
@@ -53,11 +56,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: ~2^22 polls with back-off (well under a second).  false = gave up.
+// Bounded wait: 2^22 polls with back-off (about half a second at most).  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 1024) __nanosleep(64);
+        __nanosleep(i < 64 ? 20 : 100);   // a polling warp must not eat the issue slots of working warps
     }
     return false;
 }
@@ -69,6 +72,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x,
+                                            int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// Untiled bulk copy global -> this CTA's shared memory (both 16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -13,6 +13,14 @@ def rel_err(y, want):
     return float(np.max(np.abs(y - want) / np.maximum(np.abs(want), floor))) if want.size else 0.0
 
 
+def norm_err(y, want):
+    """Normwise relative error: max |y - want| / max |want|."""
+    y = np.asarray(y, np.float64)
+    want = np.asarray(want, np.float64)
+    d = float(np.max(np.abs(want))) if want.size else 1.0
+    return float(np.max(np.abs(y - want))) / (d if d else 1.0) if want.size else 0.0
+
+
 def bf16_round(a):
     """round-to-nearest-even to bfloat16, returned as float32 (numpy has no bf16)."""
     a = np.ascontiguousarray(a, np.float32)
