@@ -60,9 +60,36 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_DIR = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(LIB_DIR, "libsgq_host.so")
+HOST_TEST = os.path.join(LIB_DIR, "sgq_host_test")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+CXX = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+
+
+def build_host(force: bool = False) -> str:
+    """The C++17 host layer (pool, tensor, quantization API, layers) and its test driver."""
+    build()
+    srcs = [os.path.join(HOST_DIR, "src", f) for f in sorted(os.listdir(os.path.join(HOST_DIR, "src"))) if f.endswith(".cpp")]
+    hdrs = [os.path.join(HOST_DIR, "include", "sovereigngrad", f)
+            for f in os.listdir(os.path.join(HOST_DIR, "include", "sovereigngrad"))]
+    inc = ["-I", os.path.join(HOST_DIR, "include"), "-I", os.path.join(os.path.dirname(HERE), "include"),
+           "-I", os.path.join(CUDA_HOME, "include")]
+    link = ["-L", LIB_DIR, "-lsgq", "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN",
+            "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64")]
+    if force or _stale(HOST_LIB, srcs + hdrs + [LIB]):
+        subprocess.check_call([CXX, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", *inc, *srcs, "-o", HOST_LIB, *link])
+    test_src = os.path.join(os.path.dirname(HERE), "tests", "host_test.cpp")
+    if force or _stale(HOST_TEST, [test_src, HOST_LIB] + hdrs):
+        subprocess.check_call([CXX, "-std=c++17", "-O2", "-Wall", *inc, test_src, "-o", HOST_TEST, "-L", LIB_DIR, "-lsgq_host",
+                               *link])
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    print(build_host(a.force))

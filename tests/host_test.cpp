@@ -1,0 +1,221 @@
+// Test driver of the C++ host layer (built by build.py into lib/sgq_host_test).
+//
+//   sgq_host_test cpu
+//       allocator pool on a host-memory stand-in for the device, Tensor metadata, error behaviour.
+//       Needs no GPU.  Prints "ok" lines; exit code 0 on success.
+//   sgq_host_test gpu <dir> <M> <K> <N> <group>
+//       reads <dir>/w.bin ([K,N] fp32), b.bin ([N]), x.bin ([M,K]); runs the flow of the reference's
+//       own quantization test (src/test_suite.cpp:672-726): nn::Linear -> QuantizedLinear(4Bit)::
+//       from_float -> forward; writes codes, scales and outputs for the caller to compare.
+#include <cassert>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "sovereigngrad/nn.hpp"
+
+using namespace sovereigngrad;
+namespace q = sovereigngrad::quantization;
+
+#define CHECK(cond)                                                                   \
+    do {                                                                              \
+        if (!(cond)) {                                                                \
+            std::fprintf(stderr, "CHECK failed at %s:%d: %s\n", __FILE__, __LINE__, #cond); \
+            std::exit(1);                                                             \
+        }                                                                             \
+    } while (0)
+
+template <typename F>
+static bool throws(F f) {
+    try {
+        f();
+    } catch (const std::exception&) {
+        return true;
+    }
+    return false;
+}
+
+// ---- a host-memory stand-in for cudaMalloc/cudaFree ------------------------------------------
+static size_t g_fake_live = 0, g_fake_calls = 0, g_fake_limit = size_t(1) << 40;
+static void* fake_alloc(size_t bytes, int* ordinal) {
+    if (g_fake_live + bytes > g_fake_limit) return nullptr;
+    *ordinal = 0;
+    g_fake_live += bytes;
+    ++g_fake_calls;
+    void* p = std::aligned_alloc(512, bytes);
+    std::memcpy(p, &bytes, sizeof(bytes));   // remember the size for release
+    return p;
+}
+static void fake_release(void* p, int) {
+    size_t bytes;
+    std::memcpy(&bytes, p, sizeof(bytes));
+    g_fake_live -= bytes;
+    std::free(p);
+}
+static const char* fake_error() { return "out of fake device memory"; }
+
+static int run_cpu() {
+    auto& A = MemoryAllocator::instance();
+    RawBackend fake;
+    fake.alloc = fake_alloc;
+    fake.release = fake_release;
+    fake.last_error = fake_error;
+    A.set_cuda_backend(fake);
+
+    // the reference's allocator test (src/test_suite.cpp:52-68), on the CPU pool
+    A.reset_peak_memory_stats();
+    {
+        Tensor a({100, 100}, Device::CPU);
+        Tensor b({200, 200}, Device::CPU);
+        CHECK(A.active_allocations(Device::CPU) >= 2);
+    }
+    CHECK(A.cached_allocations(Device::CPU) >= 1);
+    CHECK(A.peak_memory_allocated(Device::CPU) > 0);
+    CHECK(!A.get_memory_summary(Device::CPU).empty());
+    std::puts("ok cpu pool statistics");
+
+    // device pool on the stand-in: segments of 2 MiB, 512-byte alignment, best fit, split, coalesce
+    void* p1 = A.allocate(1000, Device::CUDA);
+    CHECK(p1 && (reinterpret_cast<uintptr_t>(p1) % 512) == 0);
+    CHECK(g_fake_calls == 1 && A.total_memory_allocated(Device::CUDA) == (2u << 20));
+    void* p2 = A.allocate(300000, Device::CUDA);
+    void* p3 = A.allocate(5000, Device::CUDA);
+    CHECK(g_fake_calls == 1);                       // all carved from the first segment
+    CHECK(static_cast<char*>(p2) == static_cast<char*>(p1) + 1024);   // 1000 rounds up to 1024
+    CHECK(A.active_allocations(Device::CUDA) == 3 && A.cached_allocations(Device::CUDA) == 1);
+    A.free(p2, Device::CUDA);
+    CHECK(A.cached_allocations(Device::CUDA) == 2);  // hole between p1 and p3 + tail
+    void* p4 = A.allocate(200000, Device::CUDA);     // best fit: the hole, not the large tail
+    CHECK(p4 == p2);
+    A.free(p4, Device::CUDA);
+    A.free(p1, Device::CUDA);
+    A.free(p3, Device::CUDA);
+    CHECK(A.active_allocations(Device::CUDA) == 0);
+    CHECK(A.cached_allocations(Device::CUDA) == 1);  // everything merged back into one block
+    CHECK(A.peak_memory_allocated(Device::CUDA) >= 1024 + 300032 + 5120);
+    void* big = A.allocate(size_t(100) << 20, Device::CUDA);   // own segment
+    CHECK(big && g_fake_calls == 2);
+    A.free(big, Device::CUDA);
+    A.free(big, Device::CUDA);                       // double free and unknown pointers are ignored
+    A.free(reinterpret_cast<void*>(0x1234), Device::CUDA);
+    CHECK(A.allocate(0, Device::CUDA) == nullptr);
+    // out of memory: cached segments go back to the driver, then a runtime_error with the reference's wording
+    g_fake_limit = g_fake_live + (1u << 20);
+    bool oom = false;
+    try {
+        A.allocate(size_t(512) << 20, Device::CUDA);
+    } catch (const std::runtime_error& e) {
+        oom = std::string(e.what()).find("CUDA Allocator Out of Memory") != std::string::npos;
+    }
+    CHECK(oom);
+    CHECK(g_fake_live == 0);                         // the retry released both cached segments
+    g_fake_limit = size_t(1) << 40;
+    A.release_all();
+    CHECK(A.total_memory_allocated(Device::CUDA) == 0 && g_fake_live == 0);
+    A.reset_cuda_backend();
+    std::puts("ok device pool on the stand-in backend");
+
+    // Tensor metadata on the host
+    Tensor t(std::vector<float>{1, 2, 3, 4, 5, 6}, {2, 3});
+    CHECK(t.numel() == 6 && t.is_contiguous() && t.strides()[0] == 3);
+    Tensor tt = t.transpose(0, 1);
+    CHECK(!tt.is_contiguous() && tt.shape()[0] == 3);
+    Tensor tc = tt.contiguous();
+    CHECK(tc.to_vector() == (std::vector<float>{1, 4, 2, 5, 3, 6}));
+    CHECK(t.get_element({1, 2}) == 6.0f);
+    CHECK((t - t.clone()).to_vector() == std::vector<float>(6, 0.0f));
+    CHECK(throws([] { Tensor(std::vector<float>{1, 2}, {3}); }));            // "Data size does not match shape!"
+    CHECK(dtype_size(DType::Int8) == 1 && dtype_size(DType::UInt8) == 1 && dtype_size(DType::Float16) == 2);
+    Tensor r1 = Tensor::randn({4, 4}, 0.f, 1.f, Device::CPU, false, 7), r2 = Tensor::randn({4, 4}, 0.f, 1.f, Device::CPU, false, 7);
+    CHECK(r1.to_vector() == r2.to_vector());                                 // seeded draws repeat
+    std::puts("ok tensor metadata");
+
+    // no CPU path: quantizing a host tensor fails loudly
+    CHECK(throws([&] { q::quantize_int4(t, 32); }));
+    CHECK(throws([&] { q::quantize_int8(t); }));
+    nn::Linear lin(8, 4, Device::CPU, 3);
+    CHECK(lin.named_parameters().size() == 2);
+    Tensor y = lin.forward(Tensor(std::vector<float>(16, 1.0f), {2, 8}));
+    CHECK(y.shape() == (std::vector<int64_t>{2, 4}));
+    std::puts("ok no cpu fallback");
+    return 0;
+}
+
+static std::vector<float> read_f32(const std::string& path, size_t n) {
+    std::vector<float> v(n);
+    std::ifstream f(path, std::ios::binary);
+    if (!f.read(reinterpret_cast<char*>(v.data()), n * sizeof(float))) throw std::runtime_error("cannot read " + path);
+    return v;
+}
+static void write_bytes(const std::string& path, const void* p, size_t n) {
+    std::ofstream f(path, std::ios::binary);
+    f.write(static_cast<const char*>(p), n);
+}
+static void dump(const std::string& path, const Tensor& t) {
+    Tensor h = t.to(Device::CPU);
+    write_bytes(path, h.raw(), static_cast<size_t>(h.numel()) * dtype_size(h.dtype()));
+}
+
+static int run_gpu(const std::string& dir, int64_t M, int64_t K, int64_t N, int64_t group) {
+    nn::Linear lin(K, N, Device::CPU);
+    lin.W = Tensor(read_f32(dir + "/w.bin", K * N), {K, N}, Device::CUDA);
+    lin.b = Tensor(read_f32(dir + "/b.bin", N), {1, N}, Device::CUDA);
+    Tensor x(read_f32(dir + "/x.bin", M * K), {M, K}, Device::CUDA);
+
+    auto ql8 = nn::QuantizedLinear::from_float(lin);
+    auto ql4 = nn::QuantizedLinear4Bit::from_float(lin, group);
+    CHECK(ql8->named_parameters().size() == 3 && ql4->named_parameters().size() == 3);
+    Tensor y8 = ql8->forward(x), y4 = (*ql4)(x);
+    CHECK(y8.shape() == (std::vector<int64_t>{M, N}) && y4.shape() == y8.shape());
+    dump(dir + "/q8_codes.bin", ql8->q_weight.qdata);
+    dump(dir + "/q8_scales.bin", ql8->q_weight.scales);
+    dump(dir + "/q4_packed.bin", ql4->q_weight.qdata);
+    dump(dir + "/q4_scales.bin", ql4->q_weight.scales);
+    dump(dir + "/y8.bin", y8);
+    dump(dir + "/y4.bin", y4);
+    dump(dir + "/q4_codes_f32.bin", ql4->q_weight.codes_as_float());
+    dump(dir + "/deq8.bin", q::dequantize_int8(ql8->q_weight));
+    dump(dir + "/deq4.bin", q::dequantize_int4(ql4->q_weight));
+
+    // per-tensor INT8 and the [N,K] convention through the same API
+    auto qt = q::quantize_int8(lin.W, q::QuantizationScheme::PerTensorSymmetric);
+    dump(dir + "/q8t_scales.bin", qt.scales);
+    dump(dir + "/y8t.bin", q::quantized_matmul_int8(x, qt, lin.b));
+    Tensor w_nk = lin.W.transpose(0, 1).contiguous();
+    auto nk = nn::QuantizedLinear4Bit::from_weight_nk(w_nk, lin.b, 32);
+    dump(dir + "/y4_nk.bin", nk->forward(x));
+    dump(dir + "/q4_nk_packed.bin", nk->q_weight.qdata);
+
+    // the tolerance checks of the reference's test (element 0 only, src/test_suite.cpp:719-722)
+    Tensor fy = lin.forward(x);
+    const float d8 = std::abs((fy - y8).to_vector()[0]), d4 = std::abs((fy - y4).to_vector()[0]);
+    std::printf("reference-style check: |float - int8|[0] = %g, |float - int4|[0] = %g\n", d8, d4);
+    CHECK(d8 < 0.15f && d4 < 0.35f);
+
+    // error behaviour on the device
+    CHECK(throws([&] { q::quantized_matmul_int4(Tensor({M, K + 1}, Device::CUDA), ql4->q_weight, Tensor()); }));
+    CHECK(throws([&] { q::quantized_matmul_int4(x, ql8->q_weight, Tensor()); }));
+    CHECK(throws([&] { q::quantized_matmul_int8(x, ql8->q_weight, Tensor({1, N + 1}, Device::CUDA)); }));
+    std::printf("%s\n", MemoryAllocator::instance().get_memory_summary(Device::CUDA).c_str());
+    CHECK(MemoryAllocator::instance().active_allocations(Device::CUDA) > 0);
+    std::puts("ok gpu");
+    return 0;
+}
+
+int main(int argc, char** argv) {
+    try {
+        if (argc >= 2 && std::string(argv[1]) == "cpu") return run_cpu();
+        if (argc >= 7 && std::string(argv[1]) == "gpu")
+            return run_gpu(argv[2], std::atoll(argv[3]), std::atoll(argv[4]), std::atoll(argv[5]), std::atoll(argv[6]));
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "exception: %s\n", e.what());
+        return 2;
+    }
+    std::fprintf(stderr, "usage: sgq_host_test cpu | gpu <dir> M K N group\n");
+    return 64;
+}
