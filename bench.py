@@ -302,6 +302,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
     M, copies, lps = args.M, args.copies, args.launches_per_step
+    if world > 1 and lps > 200:
+        lps = 200
     if args.only:
         # profiling aid: run one secondary case a few times, eagerly, and print it
         g0 = torch.Generator(device=dev).manual_seed(1234)
@@ -317,18 +319,25 @@ def run_ours(args):
         del w
     x = torch.randn(M, K_DIM, device=dev, generator=g)
     y_local = torch.empty(M, N_DIM, device=dev)
-    gathered = torch.empty(world, M, N_DIM, device=dev) if world > 1 else None
-    y_full = torch.empty(M, world * N_DIM, device=dev) if world > 1 else None
     ws = sgq.Workspace(dev)
-    path = sgq.PATH_GEMV if M <= 8 else sgq.PATH_AUTO
+    path = sgq.PATH_GEMV if M <= 16 else sgq.PATH_AUTO
+    sharded = None
+    if world > 1:
+        import importlib
+        sh = importlib.import_module("sgq_b200.sharding")
+        # one column-sharded layer per weight set: local slice through the C ABI, NCCL all-gather, interleave
+        sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
+    y_full = sharded[0]._buffers(M, dev)[2] if sharded else None
 
     def forward(i):
-        sgq.quantized_matmul(x, weights[i % copies], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, y_local)
-            sgq.interleave_slices(gathered, world, M, N_DIM, y_full)
+        if sharded:
+            sharded[i % copies](x)          # every layer writes the same [M, world*N] output buffer shape
+        else:
+            sgq.quantized_matmul(x, weights[i % copies], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
 
-    use_graph = not args.no_graph
+    # collectives are launched eagerly: capturing a thousand NCCL calls into one graph buys nothing
+    # (the all-gather latency dominates a sharded decode forward) and is fragile across NCCL versions
+    use_graph = not args.no_graph and world == 1
     if use_graph:
         try:
             graph = make_graph(torch, lambda: [forward(i) for i in range(lps)])
@@ -383,7 +392,7 @@ def run_ours(args):
         def e2e_forward(i):
             x.copy_(xh, non_blocking=True)
             forward(i)
-            yh.copy_(y_full if world > 1 else y_local, non_blocking=True)
+            yh.copy_(sharded[i % copies]._buffers(M, dev)[2] if sharded else y_local, non_blocking=True)
         e2e_graph = None
         if use_graph:
             try:

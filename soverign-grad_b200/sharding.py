@@ -1,0 +1,108 @@
+"""Column (N) sharding of a quantized linear across the GPUs of one box.
+
+The reference has no distributed code at all (its nn::DataParallel, include/sovereigngrad/nn.hpp:
+1006-1053, is an OpenMP loop on one device).  Here every rank owns a contiguous slice of output
+features — rows [n0, n1) of a weight stored [N, K] — with its packed codes, scales and bias slice,
+sees the whole activation, computes y[:, n0:n1] with the same kernels as the single-GPU path and
+the slices are exchanged with ONE collective, an all-gather over NVLink.  Because each output
+element is produced by exactly one rank running the same instructions, the gathered result equals
+the single-GPU result.
+
+Slices are multiples of 32 rows so that an INT4 group (32 consecutive k of one row) never crosses
+a rank.  INT8 per-tensor weights carry ONE scale for the whole tensor: quantize before slicing
+(`slice_quantized`) so that every rank uses the identical scale.
+
+torch.distributed is plumbing here (process group, NCCL all-gather); the compute is the C ABI.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, world: int, rank: int, multiple: int = 32) -> tuple[int, int]:
+    """Rows [n0, n1) of rank `rank`: equal slices when n divides evenly, else the first ranks get one
+    more block of `multiple` rows.  Every slice except possibly the last is a multiple of `multiple`."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank/world")
+    blocks = (n + multiple - 1) // multiple
+    base, extra = divmod(blocks, world)
+    b0 = rank * base + min(rank, extra)
+    b1 = b0 + base + (1 if rank < extra else 0)
+    return min(b0 * multiple, n), min(b1 * multiple, n)
+
+
+def slice_quantized(q, n0: int, n1: int):
+    """Rows [n0, n1) of an already quantized [N, K] weight (same scales -> same bytes as one GPU)."""
+    from . import PER_TENSOR, QuantizedTensor  # late import: this module is also used by CPU-only tests
+    N, K = q.original_shape
+    if q.bits == 4:
+        if (n0 * K) % (2 * q.group_size) or (K % q.group_size):
+            raise ValueError("INT4 slices must start on a group boundary")
+        qdata = q.qdata[n0 * K // 2: n1 * K // 2]
+        scales = q.scales[n0 * K // q.group_size: n1 * K // q.group_size]
+    else:
+        qdata = q.qdata[n0:n1]
+        per_tensor = q.scheme == PER_TENSOR or q.scales.numel() == 1
+        scales = q.scales if per_tensor else q.scales[n0:n1]
+    return QuantizedTensor(qdata.contiguous(), scales.contiguous(), q.scheme, (n1 - n0, K), q.group_size, q.bits)
+
+
+class ShardedLinear:
+    """y[M, N] = x[M, K] * W^T + b with W[N, K] split by rows over the ranks of `group`.
+
+    local_forward(x, out) computes this rank's [M, n_local] slice into `out`;
+    interleave(gathered, M, n_local) turns the all-gather order [world][M][n_local] into row-major
+    [M, world * n_local].  Both default to the CUDA kernels; CPU tests inject stand-ins.
+    Slices must have equal width (all-gather of equal pieces): N % (32 * world) == 0.
+    """
+
+    def __init__(self, n_total: int, local_forward: Callable, interleave: Optional[Callable] = None,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_total = n_total
+        self.n0, self.n1 = shard_bounds(n_total, self.world, self.rank)
+        widths = {shard_bounds(n_total, self.world, r)[1] - shard_bounds(n_total, self.world, r)[0] for r in range(self.world)}
+        if len(widths) != 1:
+            raise ValueError(f"N={n_total} does not split into {self.world} equal slices of 32-row blocks")
+        self.n_local = self.n1 - self.n0
+        self.local_forward = local_forward
+        self.interleave = interleave
+        self._bufs = {}
+
+    def _buffers(self, M: int, device):
+        key = (M, str(device))
+        if key not in self._bufs:
+            self._bufs[key] = (torch.empty(M, self.n_local, dtype=torch.float32, device=device),
+                               torch.empty(self.world, M, self.n_local, dtype=torch.float32, device=device),
+                               torch.empty(M, self.n_total, dtype=torch.float32, device=device))
+        return self._bufs[key]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        M = x.shape[0]
+        y_local, gathered, y = self._buffers(M, x.device)
+        self.local_forward(x, y_local)
+        if self.world == 1:
+            return y_local
+        dist.all_gather_into_tensor(gathered.view(self.world * M, self.n_local), y_local, group=self.group)
+        if self.interleave is not None:
+            return self.interleave(gathered, M, self.n_local, y)
+        from . import interleave_slices
+        return interleave_slices(gathered, self.world, M, self.n_local, y)
+
+    __call__ = forward
+
+
+def cuda_sharded_linear(q_local, bias_local, n_total: int, path: int = 0, group=None) -> ShardedLinear:
+    """The product path: the local slice runs through sgq_linear_* on this rank's GPU."""
+    from . import LAYOUT_NK, Workspace, quantized_matmul
+    ws = Workspace(q_local.qdata.device)
+
+    def local_forward(x, out):
+        quantized_matmul(x, q_local, bias_local, layout=LAYOUT_NK, path=path, out=out, workspace=ws)
+
+    return ShardedLinear(n_total, local_forward, None, group)
