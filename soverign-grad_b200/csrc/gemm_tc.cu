@@ -8,12 +8,14 @@
 //         shared memory by TMA untouched (128-byte swizzle), int32 accumulation is exact, the
 //         epilogue applies sx[m] * sw[n].  k-block = 128.
 //   kBF16 kind::f16 (bf16 x bf16 -> fp32) — activations are pre-converted to bf16; packed INT4
-//         weights arrive by TMA as raw nibbles and 8 dequant warps expand them in shared memory
+//         weights arrive by TMA as raw nibbles and dequant warps expand them in shared memory
 //         to bf16 (exact integer from one LOP3 per pair, times the bf16-rounded group scale)
 //         directly in the swizzled K-major layout the MMA reads.  k-block = 64 (two groups).
+//         Two groups of 8 dequant warps take alternate k-blocks, so two k-blocks are being
+//         expanded while a third is being multiplied.
 //
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (one thread), 2..5 = epilogue (TMEM lane
-// quarter = warp % 4), 6..13 = dequant (kBF16 only).  All waits are bounded; a wait that runs
+// quarter = warp % 4), 6..21 = dequant (kBF16 only; two groups of 8).  All waits are bounded; a wait that runs
 // out records a code in the device status word and the role winds down to the common exit.
 #include <cuda_bf16.h>
 
@@ -41,7 +43,8 @@ constexpr int BM = 128, BN = 256;
 constexpr int kABytes = BM * 128;     // 128 rows x 128 B
 constexpr int kBBytes = BN * 128;     // 256 rows x 128 B
 constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 8;      // per group: one thread per row of the 256-row weight tile
+constexpr int kDequantGroups = 2;     // groups take alternate k-blocks
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kDequantWarp0 = 6;
 constexpr int kTmemCols = 512;
@@ -51,7 +54,7 @@ struct Cfg {
     static constexpr int kStages = MODE == kI8 ? 4 : 3;
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kWarps = MODE == kI8 ? 6 : 6 + kDequantWarps;
+    static constexpr int kWarps = MODE == kI8 ? 6 : 6 + kDequantWarps * kDequantGroups;
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kStageBytes = kABytes + kBBytes + (MODE == kBF16 ? kRawBytes : 0);
     static constexpr int kBarOffset = kStages * kStageBytes;
@@ -236,13 +239,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (MODE == kBF16) {
         // ------------------------------- dequant ------------------------------------
         // thread r owns row r of the 256-row weight tile: 32 packed bytes in, 128 bytes of bf16 out
-        const int r = threadIdx.x - kDequantWarp0 * 32;
+        const int r = (threadIdx.x - kDequantWarp0 * 32) % (kDequantWarps * 32);
+        const uint32_t my_group = (threadIdx.x - kDequantWarp0 * 32) / (kDequantWarps * 32);
         const int64_t sgroups = p.K / 32;
         uint32_t it = 0;
         bool alive = true;
         for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
             const int64_t n = (tile / m_tiles) * BN + r;
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                if ((it % kDequantGroups) != my_group) continue;
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1u;
                 float2 sc = make_float2(0.0f, 0.0f);
