@@ -134,6 +134,30 @@ SGQ_API int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, con
                     int layout, int scheme, const float* bias, float* y, int64_t ldy, int path, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Decode forward for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: there every call allocates its temporaries through MemoryAllocator.)
+ *
+ * Who needs it: code that runs inside someone else's memory budget — a plugin whose host owns all
+ * device allocations, a process whose pool was sized and frozen at start-up, a token loop that
+ * must stay clear of the allocator and its locks.  Such callers can pass inputs and outputs they
+ * already own, but have nowhere to get the scratch that sgq_linear_int4 wants for batches of
+ * more than 4 rows (the activation planes of the decode kernel).
+ *
+ * Same computation and results as sgq_linear_int4(..., SGQ_LAYOUT_NK, group 32, SGQ_PATH_GEMV),
+ * but the scratch is a fixed array inside the library's device image: 320 KiB on every GPU that
+ * loads the library, held until the process exits.  Limits and rules:
+ *  - shapes the decode kernel takes (M <= 16, K % 256 == 0, 16-byte aligned x/packed/scales) whose
+ *    scratch need, sgq_linear_workspace_bytes(4, M, K, N, SGQ_LAYOUT_NK, SGQ_PATH_GEMV), is at most
+ *    320 KiB (e.g. K = 8192 at M = 16); anything larger returns SGQ_ERR_WORKSPACE;
+ *  - the first call on each device looks up the array's device address (a runtime query, no
+ *    allocation); make that first call outside any stream capture;
+ *  - all calls on a device share the one array, whose contents are simply overwritten by the next
+ *    call: two calls that may overlap on the GPU (different streams, no ordering) race.  Nothing
+ *    in it has to be cleared between calls;
+ *  - no cudaMalloc, cudaFree or other allocating routine is called. */
+SGQ_API int sgq_linear_int4_decode_noalloc(const float* x, int64_t M, int64_t K, int64_t N, const uint8_t* packed,
+                                           const float* scales, const float* bias, float* y, int64_t ldy, void* stream);
+
 /* Integer sub-path behind SGQ_PATH_TC_I8, exposed so its exact parts can be checked: x is
  * quantized per row with the rule of sgq_quantize_int8(SGQ_PER_ROW) into xq/sx, acc is the exact
  * int32 product of the codes, y = ((float)acc * sx[m]) * sw + bias.  xq_out [M,K], sx_out [M]

@@ -31,7 +31,7 @@ EXPORTS = [
     "sgq_quantize_int8", "sgq_quantize_int4", "sgq_dequantize_int8", "sgq_dequantize_int4",
     "sgq_codes_to_f32_int8", "sgq_codes_to_f32_int4", "sgq_codes_from_f32_int8", "sgq_codes_from_f32_int4",
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
-    "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices",
+    "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
 ]
 
 
@@ -66,6 +66,7 @@ def _load() -> C.CDLL:
     lib.sgq_linear_w8a8_workspace_bytes.argtypes = [i64, i64, i64]
     lib.sgq_linear_w8a8.argtypes = [p, i64, i64, i64, p, p, i32, p, p, i64, p, p, p, p, sz, p]
     lib.sgq_interleave_slices.argtypes = [p, i64, i64, i64, p, i64, p]
+    lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
     return lib
 
 

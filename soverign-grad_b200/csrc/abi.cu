@@ -296,6 +296,17 @@ int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, const int8_
     return run_linear(a, path);
 }
 
+int sgq_linear_int4_decode_noalloc(const float* x, int64_t M, int64_t K, int64_t N, const uint8_t* packed,
+                                   const float* scales, const float* bias, float* y, int64_t ldy, void* stream) {
+    LinearArgs a{x, M, K, N, packed, scales, 4, SGQ_LAYOUT_NK, 32, SGQ_PER_TENSOR, bias, y, ldy, nullptr, 0,
+                 static_cast<cudaStream_t>(stream)};
+    int rc = validate_linear(a, SGQ_PATH_GEMV);
+    if (rc != SGQ_OK) return rc;
+    if (M == 0 || N == 0) return SGQ_OK;
+    if ((rc = check_device()) != SGQ_OK) return rc;
+    return launch_linear_gemv_static(a);
+}
+
 size_t sgq_linear_w8a8_workspace_bytes(int64_t M, int64_t K, int64_t N) {
     if (M <= 0 || K <= 0 || N <= 0) return 0;
     return tc_i8_workspace_bytes(M, K, N);

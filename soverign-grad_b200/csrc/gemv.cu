@@ -642,4 +642,51 @@ int launch_linear_gemv(const LinearArgs& a) {
     }
 }
 
+// ---- entry point without any allocation ---------------------------------------------------
+// Some callers of the decode forward cannot obtain device memory at call time: code running
+// under a fixed memory budget that was handed out at start-up, a plugin loaded into a host that
+// owns every allocation, or a serving loop that must not touch the allocator (and its locks)
+// between tokens.  For them the activation planes live in this file-scope array instead of a
+// caller workspace.  Every GPU that loads the library reserves these bytes until the process
+// exits.  The size bounds the batches this entry point accepts: (K/32) * ceil(M*digits/8) * 288
+// + 64 bytes, e.g. K = 8192 with M = 16.
+constexpr size_t kStaticPlanesBytes = 320 * 1024;
+static __device__ __align__(256) unsigned char g_static_planes[kStaticPlanesBytes];
+
+namespace {
+// Device address of g_static_planes, looked up once per device.  In host code the array's name
+// is only a handle for the runtime, not a device pointer, so kernels must be given this address.
+int static_planes_address(void** out) {
+    static void* cached[64] = {};
+    int dev = 0;
+    SGQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("device ordinal %d out of range", dev);
+        return SGQ_ERR_DEVICE;
+    }
+    void* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        SGQ_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_planes));   // with `dev` current: this device's copy
+        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);
+    }
+    *out = p;
+    return SGQ_OK;
+}
+}  // namespace
+
+int launch_linear_gemv_static(LinearArgs a) {
+    const size_t need = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    if (need > kStaticPlanesBytes) {
+        set_error("this batch needs %zu bytes of activation scratch; the built-in scratch holds %zu "
+                  "(use sgq_linear_int4 with a caller workspace)", need, kStaticPlanesBytes);
+        return SGQ_ERR_WORKSPACE;
+    }
+    void* planes = nullptr;
+    int rc = static_planes_address(&planes);
+    if (rc != SGQ_OK) return rc;
+    a.workspace = need ? planes : nullptr;
+    a.workspace_bytes = need ? kStaticPlanesBytes : 0;
+    return launch_linear_gemv(a);
+}
+
 }  // namespace sgq

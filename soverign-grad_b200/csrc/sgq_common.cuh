@@ -79,6 +79,7 @@ int launch_linear_simt(const LinearArgs& a);
 bool gemv_supported(const LinearArgs& a);
 size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_gemv(const LinearArgs& a);
+int launch_linear_gemv_static(LinearArgs a);   // scratch in a file-scope device array
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_tc_bf16(const LinearArgs& a);
