@@ -308,7 +308,7 @@ def run_ours(args):
         # profiling aid: run one secondary case a few times, eagerly, and print it
         g0 = torch.Generator(device=dev).manual_seed(1234)
         ws0 = [sgq.quantize_int4(torch.randn(N_DIM, K_DIM, device=dev, generator=g0) * 0.02, GROUP) for _ in range(copies)]
-        print(json.dumps({"only": args.only, **extras(torch, sgq, peaks, ws0, only=args.only, eager=True)}), flush=True)
+        print(json.dumps({"only": args.only, **extras(torch, sgq, peaks, ws0, only=args.only, eager=not args.only_graph)}), flush=True)
         return
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -484,6 +484,7 @@ def main():
     ap.add_argument("--launches-per-step", type=int, default=1000)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report (from profiles/)")
     ap.add_argument("--only", default=None, help="run just this secondary case (a key of `extra`), eagerly")
+    ap.add_argument("--only-graph", action="store_true", help="with --only: time graph replays instead of a few eager launches")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")

@@ -11,13 +11,14 @@
 //         weights arrive by TMA as raw nibbles and dequant warps expand them in shared memory
 //         to bf16 (exact integer from one LOP3 per pair, times the bf16-rounded group scale)
 //         directly in the swizzled K-major layout the MMA reads.  k-block = 64 (two groups).
-//         Two groups of 8 dequant warps take alternate k-blocks, so two k-blocks are being
-//         expanded while a third is being multiplied.
 //
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (one thread), 2..5 = epilogue (TMEM lane
-// quarter = warp % 4), 6..21 = dequant (kBF16 only; two groups of 8).  All waits are bounded; a wait that runs
-// out records a code in the device status word and the role winds down to the common exit.
+// Warp roles: 0 = TMA producer of A, 1 = MMA issuer (one thread), 2..5 = epilogue (TMEM lane
+// quarter = warp % 4), 6 = TMA producer of B / raw nibbles, 7..22 = dequant (kBF16 only; 512
+// threads, two per weight row).  All waits are bounded; a wait that runs out records a code in the device status
+// word and the role winds down to the common exit.
 #include <cuda_bf16.h>
+
+#include <cstring>
 
 #include "sgq_common.cuh"
 #include "sm100_ptx.cuh"
@@ -35,6 +36,10 @@ cudaError_t read_status_gemm(uint32_t* v, bool clear) {
     return e;
 }
 
+#ifndef SGQ_TC_EXP
+#define SGQ_TC_EXP 0   // debug builds only: 1 = MMA issuer ignores the operand barriers, loaders idle
+#endif
+
 namespace {
 
 enum Mode { kI8 = 0, kBF16 = 1 };
@@ -43,22 +48,32 @@ constexpr int BM = 128, BN = 256;
 constexpr int kABytes = BM * 128;     // 128 rows x 128 B
 constexpr int kBBytes = BN * 128;     // 256 rows x 128 B
 constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles
-constexpr int kDequantWarps = 8;      // per group: one thread per row of the 256-row weight tile
-constexpr int kDequantGroups = 2;     // groups take alternate k-blocks
+constexpr int kDequantWarps = 16;     // two threads per row of the 256-row weight tile (one 32-k group each)
+constexpr int kDequantGroups = 1;
 constexpr int kEpilogueWarp0 = 2;
-constexpr int kDequantWarp0 = 6;
+constexpr int kBProducerWarp = 6;     // loads B (kI8) or the raw nibbles (kBF16)
+constexpr int kDequantWarp0 = 7;
 constexpr int kTmemCols = 512;
 
+// Three rings with their own depth, so that the latency of a TMA load never sits in the chain
+// "MMA frees a slot -> slot refilled -> MMA": A tiles and raw nibbles are requested several
+// k-blocks ahead; the (large) bf16 B tiles only need to cover the dequant time.
 template <int MODE>
 struct Cfg {
-    static constexpr int kStages = MODE == kI8 ? 4 : 3;
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kWarps = MODE == kI8 ? 6 : 6 + kDequantWarps * kDequantGroups;
+    static constexpr int kAStages = 5;
+    static constexpr int kBStages = MODE == kI8 ? 4 : 3;
+    static constexpr int kRawStages = MODE == kI8 ? 0 : 4;
+    static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps * kDequantGroups;
     static constexpr int kThreads = kWarps * 32;
-    static constexpr int kStageBytes = kABytes + kBBytes + (MODE == kBF16 ? kRawBytes : 0);
-    static constexpr int kBarOffset = kStages * kStageBytes;
-    static constexpr int kSmemBytes = kBarOffset + 256 + 1024;      // barriers + alignment slack
+    static constexpr int kAOff = 0;
+    static constexpr int kBOff = kAStages * kABytes;
+    static constexpr int kRawOff = kBOff + kBStages * kBBytes;
+    static constexpr int kOutOff = kRawOff + kRawStages * kRawBytes;   // 4 epilogue warps x [32 rows x 32 fp32], swizzled
+    static constexpr int kBarOffset = kOutOff + 4 * 4096;
+    static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * (kRawStages ? kRawStages : 1) + 4;
+    static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 + 1024;   // barriers + tmem slot + alignment slack
 };
 
 struct Params {
@@ -73,43 +88,75 @@ struct Params {
     int32_t* acc_out;       // optional [M,N]
     // kBF16
     const float* wscales;   // [N, K/32]
+    int vec_store;          // y is 16-byte aligned with ldy % 4 == 0: 128-bit stores
 };
 
 __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
     atomicCAS(&g_status_gemm, 0u, (code << 24) | (detail & 0xFFFFFFu));
 }
 
+// Position in a ring of N slots and the mbarrier phase that goes with it, advanced by steps of
+// `stride` without any division (these loops run in single threads that feed the tensor core).
+template <int N>
+struct Ring {
+    int slot = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int stride = 1) {
+        slot += stride;
+        while (slot >= N) {
+            slot -= N;
+            phase ^= 1u;
+        }
+    }
+};
+
+// Walks this CTA's (tile, k-block) sequence: tiles blockIdx.x, +gridDim.x, ...; kb = 0..kblocks-1.
+struct Walk {
+    int64_t tile;
+    int kb;
+    uint32_t tcount = 0;   // tiles completed so far
+    __device__ __forceinline__ Walk(int64_t first_tile) : tile(first_tile), kb(0) {}
+    __device__ __forceinline__ void advance(int stride, int kblocks, int64_t tile_stride) {
+        kb += stride;
+        while (kb >= kblocks) {
+            kb -= kblocks;
+            tile += tile_stride;
+            ++tcount;
+        }
+    }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(Cfg<MODE>::kThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Params p) {
     using C = Cfg<MODE>;
+    constexpr int NA = C::kAStages, NB = C::kBStages, NR = C::kRawStages ? C::kRawStages : 1;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
-    uint64_t* full = bars;                         // [kStages] operands of a k-block are in shared memory
-    uint64_t* empty = bars + C::kStages;           // [kStages] the MMAs reading the stage have completed
-    uint64_t* raw_full = bars + 2 * C::kStages;    // [kStages] packed nibbles landed (kBF16)
-    uint64_t* raw_empty = bars + 3 * C::kStages;   // [kStages] packed nibbles consumed (kBF16)
-    uint64_t* tmem_full = bars + 4 * C::kStages;   // [2] accumulator complete
-    uint64_t* tmem_empty = tmem_full + 2;          // [2] accumulator drained
+    uint64_t* a_full = bars;                 // [NA] A tile landed
+    uint64_t* a_empty = a_full + NA;         // [NA] the MMAs reading it completed
+    uint64_t* b_full = a_empty + NA;         // [NB] B tile ready (TMA landed, or dequant warps done)
+    uint64_t* b_empty = b_full + NB;         // [NB] the MMAs reading it completed
+    uint64_t* raw_full = b_empty + NB;       // [NR] packed nibbles landed (kBF16)
+    uint64_t* raw_empty = raw_full + NR;     // [NR] packed nibbles are in registers (kBF16)
+    uint64_t* tmem_full = raw_empty + NR;    // [2] accumulator complete
+    uint64_t* tmem_empty = tmem_full + 2;    // [2] accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
     const int64_t tiles = m_tiles * n_tiles;
     const int kblocks = static_cast<int>((p.K + C::kBlockK - 1) / C::kBlockK);
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; `it` counts its k-blocks across tiles
+    const int64_t my_tiles = (tiles > blockIdx.x) ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t total_its = my_tiles * kblocks;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < C::kStages; ++i) {
-            mbar_init(&full[i], MODE == kI8 ? 1 : 1 + kDequantWarps);
-            mbar_init(&empty[i], 1);
-            mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_empty[i], kDequantWarps);
-        }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&tmem_full[i], 1);
-            mbar_init(&tmem_empty[i], 4);
-        }
+        for (int i = 0; i < NA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], MODE == kI8 ? 1 : kDequantWarps); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 4); }
         mbar_fence_init();
         fence_proxy_async_smem();
     }
@@ -123,31 +170,42 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------- TMA producer -------------------------------
-        if (lane == 0) {
+        // ------------------------------- A producer ---------------------------------
+        if (lane == 0 && !(SGQ_TC_EXP & 1)) {
             tma_prefetch_descriptor(&map_a);
+            Ring<NA> ra;
+            Walk w(blockIdx.x);
+            int32_t m0 = static_cast<int32_t>((w.tile % m_tiles) * BM);
+            uint32_t seen_tile = 0;
+            for (int64_t it = 0; it < total_its; ++it, ra.advance(), w.advance(1, kblocks, gridDim.x)) {
+                if (w.tcount != seen_tile) { seen_tile = w.tcount; m0 = static_cast<int32_t>((w.tile % m_tiles) * BM); }
+                const int s = ra.slot;
+                if (!mbar_wait(&a_empty[s], ra.phase ^ 1u)) { report(kDevErrEmptyWait, static_cast<uint32_t>(it)); break; }
+                mbar_arrive_expect_tx(&a_full[s], kABytes);
+                tma_load_2d(smem + C::kAOff + s * kABytes, &map_a, &a_full[s], w.kb * C::kBlockK, m0);
+            }
+        }
+    } else if (warp == kBProducerWarp) {
+        // ------------------------------- B / raw producer ---------------------------
+        if (lane == 0 && !(SGQ_TC_EXP & 1)) {
             tma_prefetch_descriptor(&map_b);
-            uint32_t it = 0;
-            bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-                const int32_t m0 = static_cast<int32_t>((tile % m_tiles) * BM);
-                const int32_t n0 = static_cast<int32_t>((tile / m_tiles) * BN);
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1u;
-                    uint8_t* st = smem + s * C::kStageBytes;
-                    if (!mbar_wait(&empty[s], ph ^ 1u)) { report(kDevErrEmptyWait, it); alive = false; break; }
-                    if (MODE == kI8) {
-                        mbar_arrive_expect_tx(&full[s], kABytes + kBBytes);
-                        tma_load_2d(st, &map_a, &full[s], kb * C::kBlockK, m0);
-                        tma_load_2d(st + kABytes, &map_b, &full[s], kb * C::kBlockK, n0);
-                    } else {
-                        mbar_arrive_expect_tx(&full[s], kABytes);
-                        tma_load_2d(st, &map_a, &full[s], kb * C::kBlockK, m0);
-                        if (!mbar_wait(&raw_empty[s], ph ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | it); alive = false; break; }
-                        mbar_arrive_expect_tx(&raw_full[s], kRawBytes);
-                        tma_load_2d(st + kABytes + kBBytes, &map_b, &raw_full[s], kb * (C::kBlockK / 2), n0);
-                    }
+            Ring<NB> rb;
+            Ring<NR> rr;
+            Walk w(blockIdx.x);
+            int32_t n0 = static_cast<int32_t>((w.tile / m_tiles) * BN);
+            uint32_t seen_tile = 0;
+            for (int64_t it = 0; it < total_its; ++it, rb.advance(), rr.advance(), w.advance(1, kblocks, gridDim.x)) {
+                if (w.tcount != seen_tile) { seen_tile = w.tcount; n0 = static_cast<int32_t>((w.tile / m_tiles) * BN); }
+                if (MODE == kI8) {
+                    const int s = rb.slot;
+                    if (!mbar_wait(&b_empty[s], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | static_cast<uint32_t>(it)); break; }
+                    mbar_arrive_expect_tx(&b_full[s], kBBytes);
+                    tma_load_2d(smem + C::kBOff + s * kBBytes, &map_b, &b_full[s], w.kb * C::kBlockK, n0);
+                } else {
+                    const int s = rr.slot;
+                    if (!mbar_wait(&raw_empty[s], rr.phase ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | static_cast<uint32_t>(it)); break; }
+                    mbar_arrive_expect_tx(&raw_full[s], kRawBytes);
+                    tma_load_2d(smem + C::kRawOff + s * kRawBytes, &map_b, &raw_full[s], w.kb * (C::kBlockK / 2), n0);
                 }
             }
         }
@@ -155,40 +213,48 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------- MMA issuer ---------------------------------
         if (lane == 0) {
             const uint32_t idesc = (MODE == kI8) ? umma_idesc(2u, 1u, BM, BN) : umma_idesc(1u, 1u, BM, BN);
-            uint32_t it = 0, tcount = 0;
-            bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
+            Ring<NA> ra;
+            Ring<NB> rb;
+            Walk w(blockIdx.x);
+            for (int64_t it = 0; it < total_its; ++it, ra.advance(), rb.advance(), w.advance(1, kblocks, gridDim.x)) {
+                const int kb = w.kb;
+                const uint32_t tcount = w.tcount;
                 const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
-                if (!mbar_wait(&tmem_empty[buf], aph ^ 1u)) { report(kDevErrMmaWait, tcount); alive = false; break; }
+                if (kb == 0) {
+                    if (!mbar_wait(&tmem_empty[buf], aph ^ 1u)) { report(kDevErrMmaWait, tcount); break; }
+                    tcgen05_fence_after();
+                }
+                const int sa = ra.slot, sb = rb.slot;
+#if !(SGQ_TC_EXP & 1)
+                if (!mbar_wait(&a_full[sa], ra.phase)) { report(kDevErrFullWait, static_cast<uint32_t>(it)); break; }
+                if (!mbar_wait(&b_full[sb], rb.phase)) { report(kDevErrFullWait, 0x800000u | static_cast<uint32_t>(it)); break; }
+#endif
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1u;
-                    if (!mbar_wait(&full[s], ph)) { report(kDevErrFullWait, it); alive = false; break; }
-                    tcgen05_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
-                    const uint64_t adesc = umma_desc_sw128(a_addr);
-                    const uint64_t bdesc = umma_desc_sw128(a_addr + kABytes);
+                const uint64_t adesc = umma_desc_sw128(smem_u32(smem + C::kAOff + sa * kABytes));
+                const uint64_t bdesc = umma_desc_sw128(smem_u32(smem + C::kBOff + sb * kBBytes));
 #pragma unroll
-                    for (int k = 0; k < C::kBlockK / C::kUmmaK; ++k) {
-                        // +32 bytes per instruction inside the 128-byte swizzle row: +2 in the address field
-                        if (MODE == kI8)
-                            tcgen05_mma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                        else
-                            tcgen05_mma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    }
-                    tcgen05_commit(&empty[s]);
+                for (int k = 0; k < ((SGQ_TC_EXP & 4) ? 2 : C::kBlockK / C::kUmmaK); ++k) {
+                    // +32 bytes per instruction inside the 128-byte swizzle row: +2 in the address field
+                    if (MODE == kI8)
+                        tcgen05_mma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    else
+                        tcgen05_mma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                 }
-                if (alive) tcgen05_commit(&tmem_full[buf]);
+#if !(SGQ_TC_EXP & 8)
+                tcgen05_commit(&a_empty[sa]);
+#endif
+#if !(SGQ_TC_EXP & 2)
+                tcgen05_commit(&b_empty[sb]);
+#endif
+                if (kb == kblocks - 1) tcgen05_commit(&tmem_full[buf]);
             }
         }
-    } else if (warp < kDequantWarp0) {
+    } else if (warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + 4) {
         // ------------------------------- epilogue -----------------------------------
         const int quarter = warp & 3;
         uint32_t tcount = 0;
         bool alive = true;
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && ((p.ldy & 3) == 0);
         for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
@@ -197,38 +263,72 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int64_t m = m0 + quarter * 32 + lane;
             float sxm = 1.0f;
             if (MODE == kI8 && m < p.M) sxm = p.sx[m];
-            for (int c = 0; c < BN / 32; ++c) {
+            // Transposing epilogue.  TMEM hands lane i row i of a [32 x 32] block; stored like that each
+            // store instruction would touch 32 different 128-byte lines.  The block goes through shared
+            // memory instead (16-byte chunk j of row i at position j ^ (i & 7): conflict free both ways)
+            // and leaves with every instruction writing 4 complete 128-byte row segments.
+            uint8_t* stage_out = smem + C::kOutOff + (warp - kEpilogueWarp0) * 4096;
+            const int cq = lane & 7, rq = lane >> 3;                  // after the transpose: columns 4cq..4cq+3, rows rq + 4i
+            const float sw_all = (MODE == kI8 && !p.sw_per_row) ? p.sw[0] : 1.0f;
+            for (int c = 0; c < ((SGQ_TC_EXP & 16) ? 0 : BN / 32); ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + buf * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), v);
                 tmem_ld_wait();
                 const int64_t nb = n0 + c * 32;
-                if (m < p.M && nb < p.N) {
-                    float o[32];
+                if (nb >= p.N) continue;              // uniform across the warp
+                if (MODE == kI8 && p.acc_out && m < p.M) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int64_t n = nb + j;
-                        if (MODE == kI8) {
-                            const float sw = (n < p.N) ? (p.sw_per_row ? p.sw[n] : p.sw[0]) : 0.0f;
-                            o[j] = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(v[j])), sxm), sw);
-                        } else {
-                            o[j] = __uint_as_float(v[j]);
-                        }
-                        if (p.bias && n < p.N) o[j] = __fadd_rn(o[j], p.bias[n]);
-                    }
-                    float* dst = p.y + m * p.ldy + nb;
-                    if (vec_ok && nb + 32 <= p.N) {
+                    for (int j = 0; j < 32; ++j)
+                        if (nb + j < p.N) p.acc_out[m * p.N + nb + j] = static_cast<int32_t>(v[j]);
+                }
+                __syncwarp();                          // the previous block has been read out of the staging buffer
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            reinterpret_cast<float4*>(dst)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                for (int j = 0; j < 8; ++j) {
+                    float4 o;
+                    if (MODE == kI8) {                 // row scale first: y = ((float)acc * sx[m]) * sw[n] + bias[n]
+                        o.x = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 0])), sxm);
+                        o.y = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 1])), sxm);
+                        o.z = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 2])), sxm);
+                        o.w = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 3])), sxm);
                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nb + j < p.N) dst[j] = o[j];
+                        o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                        __uint_as_float(v[4 * j + 3]));
                     }
-                    if (MODE == kI8 && p.acc_out) {
+                    *reinterpret_cast<float4*>(stage_out + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+                }
+                __syncwarp();
+                // column-dependent factors of this lane's 4 columns
+                const int64_t n4 = nb + 4 * cq;
+                float swv[4] = {sw_all, sw_all, sw_all, sw_all}, bv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nb + j < p.N) p.acc_out[m * p.N + nb + j] = static_cast<int32_t>(v[j]);
+                for (int e = 0; e < 4; ++e) {
+                    if (n4 + e < p.N) {
+                        if (MODE == kI8 && p.sw_per_row) swv[e] = p.sw[n4 + e];
+                        if (p.bias) bv[e] = p.bias[n4 + e];
+                    }
+                }
+                const bool vec = p.vec_store && n4 + 4 <= p.N;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row = rq + 4 * i;
+                    const int64_t mm = m0 + quarter * 32 + row;
+                    float4 o = *reinterpret_cast<const float4*>(stage_out + row * 128 + ((cq ^ (row & 7)) << 4));
+                    if (MODE == kI8) {
+                        o.x = __fmul_rn(o.x, swv[0]); o.y = __fmul_rn(o.y, swv[1]); o.z = __fmul_rn(o.z, swv[2]); o.w = __fmul_rn(o.w, swv[3]);
+                    }
+                    if (p.bias) {
+                        o.x = __fadd_rn(o.x, bv[0]); o.y = __fadd_rn(o.y, bv[1]); o.z = __fadd_rn(o.z, bv[2]); o.w = __fadd_rn(o.w, bv[3]);
+                    }
+                    if (mm < p.M) {
+                        float* dst = p.y + mm * p.ldy + n4;
+                        if (vec) {
+                            *reinterpret_cast<float4*>(dst) = o;
+                        } else {
+                            if (n4 + 0 < p.N) dst[0] = o.x;
+                            if (n4 + 1 < p.N) dst[1] = o.y;
+                            if (n4 + 2 < p.N) dst[2] = o.z;
+                            if (n4 + 3 < p.N) dst[3] = o.w;
+                        }
                     }
                 }
             }
@@ -236,52 +336,76 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
-    } else if (MODE == kBF16) {
+    } else if (MODE == kBF16 && warp >= kDequantWarp0) {
         // ------------------------------- dequant ------------------------------------
-        // thread r owns row r of the 256-row weight tile: 32 packed bytes in, 128 bytes of bf16 out
-        const int r = (threadIdx.x - kDequantWarp0 * 32) % (kDequantWarps * 32);
-        const uint32_t my_group = (threadIdx.x - kDequantWarp0 * 32) / (kDequantWarps * 32);
+        // Thread (r, h) owns half h (one 32-k group: 16 packed bytes in, 64 bytes of bf16 out) of row r of
+        // the 256-row weight tile.  The group's scale is requested one k-block ahead so that its L2
+        // latency is never waited for.
+        const int tid = threadIdx.x - kDequantWarp0 * 32;
+        const int r = tid >> 1, h = tid & 1;
         const int64_t sgroups = p.K / 32;
-        uint32_t it = 0;
-        bool alive = true;
-        for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-            const int64_t n = (tile / m_tiles) * BN + r;
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                if ((it % kDequantGroups) != my_group) continue;
-                const int s = it % C::kStages;
-                const uint32_t ph = (it / C::kStages) & 1u;
-                float2 sc = make_float2(0.0f, 0.0f);
-                if (n < p.N) sc = *reinterpret_cast<const float2*>(p.wscales + n * sgroups + 2 * kb);
-                if (!mbar_wait(&raw_full[s], ph)) { report(kDevErrFullWait, 0x800000u | it); alive = false; break; }
-                if (!mbar_wait(&empty[s], ph ^ 1u)) { report(kDevErrEmptyWait, 0x400000u | it); alive = false; break; }
-                uint8_t* st = smem + s * C::kStageBytes;
-                const uint4* raw = reinterpret_cast<const uint4*>(st + kABytes + kBBytes + r * 32);
-                const uint4 w0 = raw[0], w1 = raw[1];
-                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const __nv_bfloat16 s0 = __float2bfloat16_rn(sc.x), s1 = __float2bfloat16_rn(sc.y);
-                const uint32_t s0x2 = static_cast<uint32_t>(__bfloat16_as_ushort(s0)) * 0x00010001u;
-                const uint32_t s1x2 = static_cast<uint32_t>(__bfloat16_as_ushort(s1)) * 0x00010001u;
-                uint8_t* brow = st + kABytes + r * 128;
+        Walk wn(blockIdx.x);                      // walks one k-block ahead, for the scale prefetch
+        auto load_scale = [&](int64_t it, const Walk& w) {
+            float sc = 0.0f;
+            if (it < total_its) {
+                const int64_t n = (w.tile / m_tiles) * BN + r;
+                if (n < p.N) sc = __ldg(p.wscales + n * sgroups + 2 * w.kb + h);
+            }
+            return sc;
+        };
+        // scales are requested kAhead k-blocks before they are used (an L2 round trip is several
+        // k-blocks long at full speed)
+        constexpr int kAhead = 4;
+        float scq[kAhead];
 #pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const uint32_t sx2 = (w < 4) ? s0x2 : s1x2;
+        for (int u = 0; u < kAhead; ++u) {
+            scq[u] = load_scale(u, wn);
+            wn.advance(1, kblocks, gridDim.x);
+        }
+        Ring<NR> rr;
+        Ring<NB> rb;
+        bool alive = !(SGQ_TC_EXP & 1);
+        for (int64_t it0 = 0; it0 < total_its && alive; it0 += kAhead) {
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int64_t it = it0 + u;
+                if (it >= total_its || !alive) break;
+                const float sc = scq[u];
+                scq[u] = load_scale(it + kAhead, wn);
+                wn.advance(1, kblocks, gridDim.x);
+                const int sr = rr.slot, sb = rb.slot;
+                if (!mbar_wait(&raw_full[sr], rr.phase)) { report(kDevErrFullWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
+                const uint4 w0 = *reinterpret_cast<const uint4*>(smem + C::kRawOff + sr * kRawBytes + r * 32 + h * 16);
+                // make sure the load has returned before the slot is handed back to the TMA producer
+                asm volatile("" ::"r"(w0.x), "r"(w0.y), "r"(w0.z), "r"(w0.w) : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[sr]);        // the nibbles are in registers: slot can be refilled
+                if (!mbar_wait(&b_empty[sb], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
+                const uint32_t words[4] = {w0.x, w0.y, w0.z, w0.w};
+                const uint32_t sx2 = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sc))) * 0x00010001u;
+                uint8_t* brow = smem + C::kBOff + sb * kBBytes + r * 128;
+#pragma unroll
+                for (int w = 0; w < ((SGQ_TC_EXP & 32) ? 0 : 4); ++w) {
                     uint32_t o[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t v = ((words[w] >> (4 * j)) & 0x000F000Fu) ^ 0x43084308u;  // 136 + code
+                        // (v - 136) is exact in bf16, then one rounding for code * scale; both as fused
+                        // multiply-adds, which the half-precision pipe executes natively
                         uint32_t c;
-                        asm("sub.bf16x2 %0, %1, %2;" : "=r"(c) : "r"(v), "r"(0x43084308u));
-                        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[j]) : "r"(c), "r"(sx2));
+                        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(c) : "r"(v), "r"(0x3F803F80u), "r"(0xC308C308u));
+                        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(c), "r"(sx2), "r"(0x80008000u));
                     }
-                    // chunk w of the row goes to chunk (w ^ (r & 7)): the 128-byte swizzle the MMA expects
-                    *reinterpret_cast<uint4*>(brow + ((w ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    // chunk (4h + w) of the row goes to chunk ((4h + w) ^ (r & 7)): the 128-byte swizzle the MMA expects
+                    *reinterpret_cast<uint4*>(brow + (((4 * h + w) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
+#if !(SGQ_TC_EXP & 64)
                 fence_proxy_async_smem();
+#endif
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full[s]);
-                    mbar_arrive(&raw_empty[s]);
-                }
+                if (lane == 0) mbar_arrive(&b_full[sb]);
+                rr.advance();
+                rb.advance();
             }
         }
     }
@@ -314,8 +438,9 @@ __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __rest
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 template <int MODE>
-int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream_t stream) {
     using C = Cfg<MODE>;
+    p.vec_store = (aligned(p.y, 16) && (p.ldy % 4) == 0) ? 1 : 0;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     static SmemOptIn optin;   // one per MODE instantiation
