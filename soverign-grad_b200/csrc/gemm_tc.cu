@@ -1,9 +1,9 @@
 // Prefill-shape forward on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM),
 // weights stored [N,K]:  y[M,N] = x[M,K] * deq(W)^T + bias.
 //
-// Two modes share one persistent, warp-specialised kernel (one CTA per SM, 128 x 256 output
-// tile, two TMEM accumulators of 256 columns so the epilogue of tile i overlaps the main loop
-// of tile i+1):
+// Two modes share one persistent, warp-specialised kernel (one CTA per SM, 256 x 256 output
+// tile = two 128-row halves, each with its own 256-column TMEM accumulator, sharing every B tile:
+// half the B traffic and half the dequant work per flop of a 128 x 256 tile):
 //   kI8   kind::i8 — INT8 weight codes and per-row quantized INT8 activations go from HBM to
 //         shared memory by TMA untouched (128-byte swizzle), int32 accumulation is exact, the
 //         epilogue applies sx[m] * sw[n].  k-block = 128.
@@ -44,8 +44,9 @@ namespace {
 
 enum Mode { kI8 = 0, kBF16 = 1 };
 
-constexpr int BM = 128, BN = 256;
-constexpr int kABytes = BM * 128;     // 128 rows x 128 B
+constexpr int BM = 256, BN = 256;     // two UMMA_M = 128 halves per tile
+constexpr int kHalfM = 128;
+constexpr int kABytes = BM * 128;     // 256 rows x 128 B (rows 128.. are the second half)
 constexpr int kBBytes = BN * 128;     // 256 rows x 128 B
 constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles
 constexpr int kDequantWarps = 16;     // two threads per row of the 256-row weight tile (one 32-k group each)
@@ -62,16 +63,16 @@ template <int MODE>
 struct Cfg {
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kAStages = 5;
-    static constexpr int kBStages = MODE == kI8 ? 4 : 3;
-    static constexpr int kRawStages = MODE == kI8 ? 0 : 4;
+    static constexpr int kAStages = 3;
+    static constexpr int kBStages = 3;
+    static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
     static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps * kDequantGroups;
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kAOff = 0;
     static constexpr int kBOff = kAStages * kABytes;
     static constexpr int kRawOff = kBOff + kBStages * kBBytes;
-    static constexpr int kOutOff = kRawOff + kRawStages * kRawBytes;   // 4 epilogue warps x [32 rows x 32 fp32], swizzled
-    static constexpr int kBarOffset = kOutOff + 4 * 4096;
+    static constexpr int kOutOff = kRawOff + kRawStages * kRawBytes;   // 4 epilogue warps x [16 rows x 32 fp32], swizzled
+    static constexpr int kBarOffset = kOutOff + 4 * 2048;
     static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * (kRawStages ? kRawStages : 1) + 4;
     static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 + 1024;   // barriers + tmem slot + alignment slack
 };
@@ -140,8 +141,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* b_empty = b_full + NB;         // [NB] the MMAs reading it completed
     uint64_t* raw_full = b_empty + NB;       // [NR] packed nibbles landed (kBF16)
     uint64_t* raw_empty = raw_full + NR;     // [NR] packed nibbles are in registers (kBF16)
-    uint64_t* tmem_full = raw_empty + NR;    // [2] accumulator complete
-    uint64_t* tmem_empty = tmem_full + 2;    // [2] accumulator drained
+    uint64_t* tmem_full = raw_empty + NR;    // [2] (one used) both accumulators of the tile complete
+    uint64_t* tmem_empty = tmem_full + 2;    // [2] (one used) both accumulators drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,16 +213,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------
         if (lane == 0) {
-            const uint32_t idesc = (MODE == kI8) ? umma_idesc(2u, 1u, BM, BN) : umma_idesc(1u, 1u, BM, BN);
+            const uint32_t idesc = (MODE == kI8) ? umma_idesc(2u, 1u, kHalfM, BN) : umma_idesc(1u, 1u, kHalfM, BN);
             Ring<NA> ra;
             Ring<NB> rb;
             Walk w(blockIdx.x);
             for (int64_t it = 0; it < total_its; ++it, ra.advance(), rb.advance(), w.advance(1, kblocks, gridDim.x)) {
                 const int kb = w.kb;
                 const uint32_t tcount = w.tcount;
-                const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
                 if (kb == 0) {
-                    if (!mbar_wait(&tmem_empty[buf], aph ^ 1u)) { report(kDevErrMmaWait, tcount); break; }
+                    // both accumulators are reused by every tile: wait until the epilogue has drained them
+                    if (!mbar_wait(&tmem_empty[0], (tcount & 1u) ^ 1u)) { report(kDevErrMmaWait, tcount); break; }
                     tcgen05_fence_after();
                 }
                 const int sa = ra.slot, sb = rb.slot;
@@ -230,24 +231,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!mbar_wait(&b_full[sb], rb.phase)) { report(kDevErrFullWait, 0x800000u | static_cast<uint32_t>(it)); break; }
 #endif
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + buf * BN;
-                const uint64_t adesc = umma_desc_sw128(smem_u32(smem + C::kAOff + sa * kABytes));
                 const uint64_t bdesc = umma_desc_sw128(smem_u32(smem + C::kBOff + sb * kBBytes));
 #pragma unroll
-                for (int k = 0; k < ((SGQ_TC_EXP & 4) ? 2 : C::kBlockK / C::kUmmaK); ++k) {
-                    // +32 bytes per instruction inside the 128-byte swizzle row: +2 in the address field
-                    if (MODE == kI8)
-                        tcgen05_mma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    else
-                        tcgen05_mma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t tmem_d = tmem_base + half * BN;
+                    const uint64_t adesc = umma_desc_sw128(smem_u32(smem + C::kAOff + sa * kABytes + half * (kHalfM * 128)));
+#pragma unroll
+                    for (int k = 0; k < C::kBlockK / C::kUmmaK; ++k) {
+                        // +32 bytes per instruction inside the 128-byte swizzle row: +2 in the address field
+                        if (MODE == kI8)
+                            tcgen05_mma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else
+                            tcgen05_mma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
                 }
-#if !(SGQ_TC_EXP & 8)
                 tcgen05_commit(&a_empty[sa]);
-#endif
-#if !(SGQ_TC_EXP & 2)
                 tcgen05_commit(&b_empty[sb]);
-#endif
-                if (kb == kblocks - 1) tcgen05_commit(&tmem_full[buf]);
+                if (kb == kblocks - 1) tcgen05_commit(&tmem_full[0]);
             }
         }
     } else if (warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + 4) {
@@ -255,86 +255,95 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quarter = warp & 3;
         uint32_t tcount = 0;
         bool alive = true;
+        // Transposing epilogue.  TMEM hands lane i row i of a [32 x 32] block; stored like that each
+        // store instruction would touch 32 different 128-byte lines.  The block goes through shared
+        // memory instead, 16 rows at a time (16-byte chunk j of row i at position j ^ (i & 7):
+        // conflict free both ways), and leaves with every instruction writing 4 complete 128-byte
+        // row segments.
+        uint8_t* stage_out = smem + C::kOutOff + (warp - kEpilogueWarp0) * 2048;
+        const int cq = lane & 7, rq = lane >> 3;                  // after the transpose: columns 4cq..4cq+3, rows rq + 4i
+        const float sw_all = (MODE == kI8 && !p.sw_per_row) ? p.sw[0] : 1.0f;
         for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-            const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
-            if (!mbar_wait(&tmem_full[buf], aph)) { report(kDevErrMmaWait, 0x800000u | tcount); alive = false; break; }
+            if (!mbar_wait(&tmem_full[0], tcount & 1u)) { report(kDevErrMmaWait, 0x800000u | tcount); alive = false; break; }
             tcgen05_fence_after();
-            const int64_t m = m0 + quarter * 32 + lane;
-            float sxm = 1.0f;
-            if (MODE == kI8 && m < p.M) sxm = p.sx[m];
-            // Transposing epilogue.  TMEM hands lane i row i of a [32 x 32] block; stored like that each
-            // store instruction would touch 32 different 128-byte lines.  The block goes through shared
-            // memory instead (16-byte chunk j of row i at position j ^ (i & 7): conflict free both ways)
-            // and leaves with every instruction writing 4 complete 128-byte row segments.
-            uint8_t* stage_out = smem + C::kOutOff + (warp - kEpilogueWarp0) * 4096;
-            const int cq = lane & 7, rq = lane >> 3;                  // after the transpose: columns 4cq..4cq+3, rows rq + 4i
-            const float sw_all = (MODE == kI8 && !p.sw_per_row) ? p.sw[0] : 1.0f;
-            for (int c = 0; c < ((SGQ_TC_EXP & 16) ? 0 : BN / 32); ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + buf * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), v);
-                tmem_ld_wait();
-                const int64_t nb = n0 + c * 32;
-                if (nb >= p.N) continue;              // uniform across the warp
-                if (MODE == kI8 && p.acc_out && m < p.M) {
+            for (int half = 0; half < 2; ++half) {
+                const int64_t mrow0 = m0 + half * kHalfM + quarter * 32;   // first row of this warp's block
+                const int64_t m = mrow0 + lane;
+                float sxm = 1.0f;
+                if (MODE == kI8 && m < p.M) sxm = p.sx[m];
+                for (int c = 0; c < ((SGQ_TC_EXP & 16) ? 0 : BN / 32); ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + half * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), v);
+                    tmem_ld_wait();
+                    const int64_t nb = n0 + c * 32;
+                    if (nb >= p.N || mrow0 >= p.M) continue;          // uniform across the warp
+                    if (MODE == kI8 && p.acc_out && m < p.M) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (nb + j < p.N) p.acc_out[m * p.N + nb + j] = static_cast<int32_t>(v[j]);
-                }
-                __syncwarp();                          // the previous block has been read out of the staging buffer
+                        for (int j = 0; j < 32; ++j)
+                            if (nb + j < p.N) p.acc_out[m * p.N + nb + j] = static_cast<int32_t>(v[j]);
+                    }
+                    // column-dependent factors of this lane's 4 columns after the transpose
+                    const int64_t n4 = nb + 4 * cq;
+                    float swv[4] = {sw_all, sw_all, sw_all, sw_all}, bv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float4 o;
-                    if (MODE == kI8) {                 // row scale first: y = ((float)acc * sx[m]) * sw[n] + bias[n]
-                        o.x = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 0])), sxm);
-                        o.y = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 1])), sxm);
-                        o.z = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 2])), sxm);
-                        o.w = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 3])), sxm);
-                    } else {
-                        o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                        __uint_as_float(v[4 * j + 3]));
+                    for (int e = 0; e < 4; ++e) {
+                        if (n4 + e < p.N) {
+                            if (MODE == kI8 && p.sw_per_row) swv[e] = p.sw[n4 + e];
+                            if (p.bias) bv[e] = p.bias[n4 + e];
+                        }
                     }
-                    *reinterpret_cast<float4*>(stage_out + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
-                }
-                __syncwarp();
-                // column-dependent factors of this lane's 4 columns
-                const int64_t n4 = nb + 4 * cq;
-                float swv[4] = {sw_all, sw_all, sw_all, sw_all}, bv[4] = {0.f, 0.f, 0.f, 0.f};
+                    const bool vec = p.vec_store && n4 + 4 <= p.N;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (n4 + e < p.N) {
-                        if (MODE == kI8 && p.sw_per_row) swv[e] = p.sw[n4 + e];
-                        if (p.bias) bv[e] = p.bias[n4 + e];
-                    }
-                }
-                const bool vec = p.vec_store && n4 + 4 <= p.N;
+                    for (int part = 0; part < 2; ++part) {            // rows 0..15, then 16..31 of the block
+                        __syncwarp();                                  // the previous part has been read out
+                        if ((lane >> 4) == part) {
+                            const int lr = lane & 15;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int row = rq + 4 * i;
-                    const int64_t mm = m0 + quarter * 32 + row;
-                    float4 o = *reinterpret_cast<const float4*>(stage_out + row * 128 + ((cq ^ (row & 7)) << 4));
-                    if (MODE == kI8) {
-                        o.x = __fmul_rn(o.x, swv[0]); o.y = __fmul_rn(o.y, swv[1]); o.z = __fmul_rn(o.z, swv[2]); o.w = __fmul_rn(o.w, swv[3]);
-                    }
-                    if (p.bias) {
-                        o.x = __fadd_rn(o.x, bv[0]); o.y = __fadd_rn(o.y, bv[1]); o.z = __fadd_rn(o.z, bv[2]); o.w = __fadd_rn(o.w, bv[3]);
-                    }
-                    if (mm < p.M) {
-                        float* dst = p.y + mm * p.ldy + n4;
-                        if (vec) {
-                            *reinterpret_cast<float4*>(dst) = o;
-                        } else {
-                            if (n4 + 0 < p.N) dst[0] = o.x;
-                            if (n4 + 1 < p.N) dst[1] = o.y;
-                            if (n4 + 2 < p.N) dst[2] = o.z;
-                            if (n4 + 3 < p.N) dst[3] = o.w;
+                            for (int j = 0; j < 8; ++j) {
+                                float4 o;
+                                if (MODE == kI8) {                 // row scale first: y = ((float)acc * sx[m]) * sw[n] + bias[n]
+                                    o.x = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 0])), sxm);
+                                    o.y = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 1])), sxm);
+                                    o.z = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 2])), sxm);
+                                    o.w = __fmul_rn(static_cast<float>(static_cast<int32_t>(v[4 * j + 3])), sxm);
+                                } else {
+                                    o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                    __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                                }
+                                *reinterpret_cast<float4*>(stage_out + lr * 128 + ((j ^ (lr & 7)) << 4)) = o;
+                            }
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int row = rq + 4 * i;                // 0..15 inside the part
+                            const int64_t mm = mrow0 + part * 16 + row;
+                            float4 o = *reinterpret_cast<const float4*>(stage_out + row * 128 + ((cq ^ (row & 7)) << 4));
+                            if (MODE == kI8) {
+                                o.x = __fmul_rn(o.x, swv[0]); o.y = __fmul_rn(o.y, swv[1]); o.z = __fmul_rn(o.z, swv[2]); o.w = __fmul_rn(o.w, swv[3]);
+                            }
+                            if (p.bias) {
+                                o.x = __fadd_rn(o.x, bv[0]); o.y = __fadd_rn(o.y, bv[1]); o.z = __fadd_rn(o.z, bv[2]); o.w = __fadd_rn(o.w, bv[3]);
+                            }
+                            if (mm < p.M) {
+                                float* dst = p.y + mm * p.ldy + n4;
+                                if (vec) {
+                                    *reinterpret_cast<float4*>(dst) = o;
+                                } else {
+                                    if (n4 + 0 < p.N) dst[0] = o.x;
+                                    if (n4 + 1 < p.N) dst[1] = o.y;
+                                    if (n4 + 2 < p.N) dst[2] = o.z;
+                                    if (n4 + 3 < p.N) dst[3] = o.w;
+                                }
+                            }
                         }
                     }
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            if (lane == 0) mbar_arrive(&tmem_empty[0]);
         }
     } else if (MODE == kBF16 && warp >= kDequantWarp0) {
         // ------------------------------- dequant ------------------------------------
