@@ -451,7 +451,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8 (INT4 nibbles) x bf16-split fp32 activations, fp32 accumulate", "data": "synthetic",
+        "dtype": "u8 x s8 -> s32 (INT4 codes x int8 activation digits), fp32 group scales", "data": "synthetic",
         "config": {"workload": f"config2: INT4 g=32 decode GEMV, W[{N_DIM},{K_DIM}] stored [N,K], X[{M},{K_DIM}] fp32"
                                + (f"; column-sharded, N_total={world * N_DIM}, NCCL all-gather of output slices per forward"
                                   if world > 1 else ""),

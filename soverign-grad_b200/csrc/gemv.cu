@@ -544,7 +544,11 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p) {
     p->nsets = static_cast<int>((M * p->ndigits + 7) / 8);
     p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 288 + kMaxM * 4;
     // two warps per step while at least 3 stages still fit, else one (smaller partial-sum buffers)
+#ifdef SGQ_FORCE_WPB
+    for (int wpb = SGQ_FORCE_WPB; wpb >= 1; --wpb) {
+#else
     for (int wpb = 2; wpb >= 1; --wpb) {
+#endif
         for (int st = kMaxStages; st >= (wpb == 2 ? 3 : 2); --st) {
             const Smem L = smem_layout(st, K, p->nsets, kStepsPerStage * wpb);
             if (L.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {

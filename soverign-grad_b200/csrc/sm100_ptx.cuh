@@ -56,11 +56,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: 2^22 polls with back-off (about half a second at most).  false = gave up.
+// Bounded wait: 2^22 polls, the later ones with a short sleep (about half a second at most).
+// false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 2048) __nanosleep(64);    // spin first: a sleep costs far more than the events waited for here
+        if (i > 2048) __nanosleep(64);
     }
     return false;
 }
