@@ -34,6 +34,11 @@ K_DIM, N_DIM, GROUP = 4096, 11008, 32
 METRIC, UNIT = "int4_g32_decode_gemv_hbm_gbs", "GB/s"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from the ncu capture summarised
+# in profiles/gemv_int4_nk_kernel__config2_M1.md (M = 1; the output is 44 KB and stays in L2)
+NCU_TRAFFIC_PER_LAUNCH = {1: 28258560.0}
+
+
 def gemv_bytes(M: int, K: int = K_DIM, N: int = N_DIM, bits: int = 4) -> int:
     """Algorithmic bytes of one forward: packed weights + scales + x + y (fp32)."""
     w = N * K // 2 + (N * K // GROUP) * 4 if bits == 4 else N * K + 4
@@ -460,7 +465,8 @@ def run_ours(args):
                    "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch,
                    "launch": "one CUDA graph replay per step" if use_graph else "eager launches"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": args.traffic,
+                     "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
+                     "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_LAUNCH.get(M) if world == 1 else None,
                      "peak_source": peaks["source"], "kernel": "gemv_int4_nk_kernel",
                      "launch_us": launch_ms * 1e3},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * (1 if world == 1 else 2), "clocks": clocks,
