@@ -1,0 +1,65 @@
+/*
+ * sgq_decoder.h — the fp32 operators that sit between the quantized linears of a LLaMA-style
+ * decoder block (RMSNorm, rotary embedding + KV-cache store, single-query attention over the
+ * cache, SiLU gate), exported from the same library as sgq.h.
+ *
+ * They exist so that a whole greedy-decode step (sixteen blocks, ~200 launches) can be recorded
+ * into one CUDA graph and replayed without host work: every quantity that changes from step to
+ * step (the position in the cache) is read from DEVICE memory, so the recorded launches stay valid.
+ * Arithmetic is fp32 throughout and follows the reference's operators:
+ *
+ *   sgqd_add_rmsnorm     sovereigngrad::rms_norm            src/ops.cpp:1532-1564
+ *   sgqd_rope_kv_store   sovereigngrad::rotary_embedding    src/ops.cpp:1714-1745
+ *                        nn::RotaryEmbedding tables         include/sovereigngrad/nn.hpp:583-607
+ *   sgqd_attn_decode     nn::CausalSelfAttention            include/sovereigngrad/nn.hpp:503-560
+ *                        (last row of the causal softmax(q k^T / sqrt(d)) v; the reference has no
+ *                        KV cache and recomputes every row, models.hpp:262-300)
+ *   sgqd_silu_mul        nn::SwiGLU gate                    include/sovereigngrad/nn.hpp:151-156
+ *                        simd::vec_silu                     include/sovereigngrad/simd.hpp:103-108
+ *
+ * Conventions are those of sgq.h: device pointers owned by the caller, `stream` is a cudaStream_t
+ * passed as void*, calls enqueue and return an sgq_status, nothing is allocated.
+ */
+#ifndef SGQ_DECODER_H
+#define SGQ_DECODER_H
+
+#include "sgq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* h[rows, dim] += delta (skipped when delta is NULL), then out = h * rsqrt(mean(h^2) + eps) * gamma.
+ * h is updated in place: it is the residual stream.  out may not alias h. */
+SGQ_API int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps, int64_t rows, int64_t dim,
+                             float* out, void* stream);
+
+/* qkv[batch * t_new, 3 * n_heads * head_dim] holds, per token, the query, key and value rows of
+ * n_heads heads (token m = b * t_new + i is the i-th new token of sequence b, at position
+ * *pos0 + i).  Rotates q in place, and stores the rotated k and the v of every new token into
+ * k_cache / v_cache[batch, n_heads, max_seq, head_dim].  cos / sin are [max_seq, head_dim / 2]
+ * tables (pair (d, d + head_dim/2), angle pos * base^(-2d/head_dim)).  pos0 is a DEVICE int32:
+ * the number of tokens already in the cache.  Tokens whose position would be >= max_seq are
+ * skipped (nothing is written out of bounds).  head_dim must be a multiple of 8. */
+SGQ_API int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,
+                               const float* cos_table, const float* sin_table, const int32_t* pos0,
+                               float* k_cache, float* v_cache, int64_t max_seq, void* stream);
+
+/* Bytes of scratch sgqd_attn_decode needs (256-byte aligned). */
+SGQ_API size_t sgqd_attn_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq);
+
+/* One query per (sequence, head) against the first *pos0 + 1 cache positions (call after
+ * sgqd_rope_kv_store of the same token): out[b, h*head_dim + d] = sum_t softmax_t(q.k_t /
+ * sqrt(head_dim)) v_t.  q is read from qkv rows of stride q_stride floats (the rotated query part).
+ * head_dim must be 64 or 128. */
+SGQ_API int sgqd_attn_decode(const float* q, int64_t q_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
+                             const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0,
+                             float* out, int64_t out_stride, void* workspace, size_t workspace_bytes, void* stream);
+
+/* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up. */
+SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGQ_DECODER_H */

@@ -207,7 +207,53 @@ class Ref:
         L.sgref_linear_time.argtypes = [C.c_void_p, _f32p, _i64, C.c_int, C.c_int]
         L.sgref_quantize_time.restype = C.c_double
         L.sgref_quantize_time.argtypes = [_f32p, i64p, C.c_int, C.c_int, C.c_int, _i64, C.c_int]
+        if hasattr(L, "sgref_rms_norm"):
+            L.sgref_rms_norm.argtypes = [_f32p, _i64, _i64, _f32p, C.c_float, _f32p]
+            L.sgref_silu.argtypes = [_f32p, _i64, _f32p]
+            L.sgref_softmax_rows.argtypes = [_f32p, _i64, _i64, _f32p]
+            L.sgref_rope_tables.argtypes = [_i64, _i64, C.c_float, _f32p, _f32p]
+            L.sgref_rope.argtypes = [_f32p, _i64, _i64, _i64, C.c_float, _f32p]
+            L.sgref_swiglu.argtypes = [_f32p, _i64, _i64, _i64, _f32p, _f32p, _f32p, _f32p]
         self.L = L
+
+    # -- decode-glue ops (pin oracle/nanollama_oracle.py) -------------------------------------
+    def rms_norm(self, x, gamma, eps=1e-5):
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._check(self.L.sgref_rms_norm(x, x.shape[0], x.shape[1], _f32(gamma), eps, out))
+        return out
+
+    def silu(self, x):
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._check(self.L.sgref_silu(x.reshape(-1), x.size, out.reshape(-1)))
+        return out
+
+    def softmax_rows(self, x):
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._check(self.L.sgref_softmax_rows(x, x.shape[0], x.shape[1], out))
+        return out
+
+    def rope_tables(self, head_dim, max_seq, base=10000.0):
+        cos = np.empty((max_seq, head_dim // 2), np.float32)
+        sin = np.empty_like(cos)
+        self._check(self.L.sgref_rope_tables(head_dim, max_seq, base, cos, sin))
+        return cos, sin
+
+    def rope(self, x, max_seq, base=10000.0):
+        x = _f32(x)
+        out = np.empty_like(x)
+        self._check(self.L.sgref_rope(x, x.shape[0], x.shape[1], max_seq, base, out))
+        return out
+
+    def swiglu(self, x, w_gate, w_up, w_down):
+        """nn::SwiGLU with float weights stored [in, out] (w_down [hidden, in])."""
+        x = _f32(x)
+        D, H = w_gate.shape
+        out = np.empty_like(x)
+        self._check(self.L.sgref_swiglu(x, x.shape[0], D, H, _f32(w_gate), _f32(w_up), _f32(w_down), out))
+        return out
 
     def _check(self, rc):
         if rc != 0:

@@ -251,4 +251,54 @@ double sgref_quantize_time(const float* x, const int64_t* shape, int ndim, int b
     }
 }
 
+
+// ---- decode-glue ops of the reference (used to pin the numpy restatement in oracle/nanollama_oracle.py)
+// sovereigngrad::rms_norm (src/ops.cpp:1532), silu (:561), softmax (:2101),
+// nn::RotaryEmbedding tables + rotary_embedding (include/sovereigngrad/nn.hpp:583, src/ops.cpp:1714).
+int sgref_rms_norm(const float* x, int64_t rows, int64_t D, const float* gamma, float eps, float* out) {
+    SGREF_TRY
+    to_raw(rms_norm(from_raw(x, {rows, D}), from_raw(gamma, {D}), eps), out);
+    SGREF_CATCH
+}
+
+int sgref_silu(const float* x, int64_t n, float* out) {
+    SGREF_TRY
+    to_raw(silu(from_raw(x, {n})), out);
+    SGREF_CATCH
+}
+
+int sgref_softmax_rows(const float* x, int64_t rows, int64_t cols, float* out) {
+    SGREF_TRY
+    to_raw(softmax(from_raw(x, {rows, cols}), -1), out);
+    SGREF_CATCH
+}
+
+int sgref_rope_tables(int64_t head_dim, int64_t max_seq, float base, float* cos_out, float* sin_out) {
+    SGREF_TRY
+    nn::RotaryEmbedding r(head_dim, max_seq, base, Device::CPU);
+    to_raw(r.cos_cached, cos_out);
+    to_raw(r.sin_cached, sin_out);
+    SGREF_CATCH
+}
+
+// x is [T, head_dim] with T <= max_seq, so that the reference's flat table index is the position.
+int sgref_rope(const float* x, int64_t T, int64_t head_dim, int64_t max_seq, float base, float* out) {
+    SGREF_TRY
+    nn::RotaryEmbedding r(head_dim, max_seq, base, Device::CPU);
+    to_raw(r.forward(from_raw(x, {T, head_dim})), out);
+    SGREF_CATCH
+}
+
+// nn::SwiGLU (include/sovereigngrad/nn.hpp:138-160) with caller-provided float weights stored [in, out].
+int sgref_swiglu(const float* x, int64_t M, int64_t D, int64_t H, const float* w_gate, const float* w_up,
+                 const float* w_down, float* out) {
+    SGREF_TRY
+    nn::SwiGLU m(D, H, Device::CPU);
+    std::memcpy(m.w_gate->W.impl->data(), w_gate, sizeof(float) * D * H);
+    std::memcpy(m.w_up->W.impl->data(), w_up, sizeof(float) * D * H);
+    std::memcpy(m.w_down->W.impl->data(), w_down, sizeof(float) * D * H);
+    to_raw(m.forward(from_raw(x, {M, D})), out);
+    SGREF_CATCH
+}
+
 }  // extern "C"

@@ -34,6 +34,10 @@ EXPORTS = [
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
 ]
 
+# every symbol include/sgq_decoder.h declares
+DECODER_EXPORTS = ["sgqd_add_rmsnorm", "sgqd_rope_kv_store", "sgqd_attn_decode_workspace_bytes", "sgqd_attn_decode",
+                   "sgqd_silu_mul"]
+
 
 class SgqError(RuntimeError):
     def __init__(self, status: int, what: str, detail: str):
@@ -67,6 +71,12 @@ def _load() -> C.CDLL:
     lib.sgq_linear_w8a8.argtypes = [p, i64, i64, i64, p, p, i32, p, p, i64, p, p, p, p, sz, p]
     lib.sgq_interleave_slices.argtypes = [p, i64, i64, i64, p, i64, p]
     lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
+    lib.sgqd_add_rmsnorm.argtypes = [p, p, p, C.c_float, i64, i64, p, p]
+    lib.sgqd_rope_kv_store.argtypes = [p, i64, i64, i64, i64, p, p, p, p, p, i64, p]
+    lib.sgqd_attn_decode_workspace_bytes.restype = sz
+    lib.sgqd_attn_decode_workspace_bytes.argtypes = [i64, i64, i64, i64]
+    lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, i64, p, p, i64, p, sz, p]
+    lib.sgqd_silu_mul.argtypes = [p, i64, i64, p, p]
     return lib
 
 

@@ -100,8 +100,6 @@ bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void*
     return make_tensor_map(map, dtype, base, 2, dims, strides, box, swizzle);
 }
 
-namespace {
-
 int check_device() {
     if (device_info().major != 10) {
         set_error("this library contains sm_100a code only; current device is compute capability %d.x",
@@ -115,6 +113,8 @@ int bad(int code, const char* msg) {
     set_error("%s", msg);
     return code;
 }
+
+namespace {
 
 int validate_linear(const LinearArgs& a, int path) {
     if (a.M < 0 || a.K < 0 || a.N < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");

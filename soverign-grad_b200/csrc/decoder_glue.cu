@@ -1,0 +1,352 @@
+// fp32 operators between the quantized linears of a decoder block (include/sgq_decoder.h):
+// residual add + RMSNorm, rotary embedding + KV-cache store, single-query attention over the
+// cache, SiLU gate.  All are HBM/latency bound; none waits on another block, so there is no
+// spin anywhere in this file.  The position in the cache is read from device memory so that a
+// recorded CUDA graph of a decode step stays valid from step to step.
+#include "sgq_common.cuh"
+
+#include "../../include/sgq_decoder.h"
+
+#include <math_constants.h>
+
+namespace sgq {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One block per row.  Pass 1 adds the delta into the residual stream and accumulates the sum of
+// squares; pass 2 re-reads the row (L1/L2) and scales it.  The reference sums the squares of a row
+// sequentially in fp32 (src/ops.cpp:1546-1550); a tree sum differs from it by a few ulps.
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                                  const float* __restrict__ gamma, float eps, int64_t dim,
+                                                                  float* __restrict__ out) {
+    __shared__ float red[kNormThreads / 32];
+    __shared__ float inv_rms_s;
+    float* hr = h + blockIdx.x * dim;
+    const float* dr = delta ? delta + blockIdx.x * dim : nullptr;
+    float* orow = out + blockIdx.x * dim;
+    float ss = 0.f;
+    if ((dim & 3) == 0) {
+        for (int64_t i = threadIdx.x * 4; i < dim; i += kNormThreads * 4) {
+            float4 v = *reinterpret_cast<const float4*>(hr + i);
+            if (dr) {
+                const float4 d = *reinterpret_cast<const float4*>(dr + i);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                *reinterpret_cast<float4*>(hr + i) = v;
+            }
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int64_t i = threadIdx.x; i < dim; i += kNormThreads) {
+            float v = hr[i];
+            if (dr) { v += dr[i]; hr[i] = v; }
+            ss = fmaf(v, v, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < kNormThreads / 32 ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) inv_rms_s = 1.0f / sqrtf(t / static_cast<float>(dim) + eps);
+    }
+    __syncthreads();      // also orders this thread block's writes of h before the re-read below
+    const float inv = inv_rms_s;
+    if ((dim & 3) == 0) {
+        for (int64_t i = threadIdx.x * 4; i < dim; i += kNormThreads * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(hr + i);
+            const float4 g = *reinterpret_cast<const float4*>(gamma + i);
+            float4 o;
+            o.x = v.x * inv * g.x; o.y = v.y * inv * g.y; o.z = v.z * inv * g.z; o.w = v.w * inv * g.w;
+            *reinterpret_cast<float4*>(orow + i) = o;
+        }
+    } else {
+        for (int64_t i = threadIdx.x; i < dim; i += kNormThreads) orow[i] = hr[i] * inv * gamma[i];
+    }
+}
+
+// One block per token; thread items are (head, d) pairs with d < head_dim / 2.
+__global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ qkv, int t_new, int n_heads, int head_dim,
+                                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                            const int32_t* __restrict__ pos0, float* __restrict__ kc,
+                                                            float* __restrict__ vc, int64_t max_seq) {
+    const int64_t m = blockIdx.x;
+    const int b = static_cast<int>(m / t_new), i = static_cast<int>(m % t_new);
+    const int64_t pos = static_cast<int64_t>(*pos0) + i;
+    if (pos < 0 || pos >= max_seq) return;                 // never write outside the cache
+    const int half = head_dim >> 1;
+    const int64_t dim = static_cast<int64_t>(n_heads) * head_dim;
+    float* q = qkv + m * 3 * dim;
+    const float* k = q + dim;
+    const float* v = k + dim;
+    const float* cr = cos_t + pos * half;
+    const float* sr = sin_t + pos * half;
+    for (int it = threadIdx.x; it < n_heads * half; it += blockDim.x) {
+        const int hh = it / half, d = it - hh * half;
+        const float c = cr[d], s = sr[d];
+        const int o = hh * head_dim + d;
+        const float q1 = q[o], q2 = q[o + half];
+        q[o] = q1 * c - q2 * s;                             // src/ops.cpp:1737-1738
+        q[o + half] = q2 * c + q1 * s;
+        const float k1 = k[o], k2 = k[o + half];
+        const int64_t co = ((static_cast<int64_t>(b) * n_heads + hh) * max_seq + pos) * head_dim + d;
+        kc[co] = k1 * c - k2 * s;
+        kc[co + half] = k2 * c + k1 * s;
+        vc[co] = v[o];
+        vc[co + half] = v[o + half];
+    }
+}
+
+constexpr int kAttnWarps = 8;
+constexpr int kKeysPerIter = 8;
+
+// grid (batch * n_heads, splits).  Each warp walks its keys eight at a time (eight independent
+// 512-byte row loads in flight per warp), keeps a running max / sum / weighted value (online
+// softmax) and the warps, then the splits, are merged with the usual exp(m_i - M) weights.  The
+// last split to finish a (sequence, head) — found with a ticket, no waiting — writes the output.
+template <int HD>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* __restrict__ q, int64_t q_stride, int n_heads,
+                                                                      const float* __restrict__ kc, const float* __restrict__ vc,
+                                                                      int64_t max_seq, const int32_t* __restrict__ pos0,
+                                                                      float* __restrict__ out, int64_t out_stride,
+                                                                      float* __restrict__ part, unsigned int* __restrict__ tickets) {
+    constexpr int VEC = HD / 32;
+    __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
+    __shared__ float sm_acc[kAttnWarps][HD];
+    __shared__ unsigned int sm_ticket;
+    const int bh = blockIdx.x, split = blockIdx.y, S = gridDim.y;
+    const int b = bh / n_heads, h = bh - b * n_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int64_t len = static_cast<int64_t>(*pos0) + 1;
+    len = len < 1 ? 1 : (len > max_seq ? max_seq : len);
+    const int64_t chunk = (len + S - 1) / S;
+    const int64_t t0 = split * chunk;
+    const int64_t t1 = (t0 + chunk < len) ? t0 + chunk : len;
+
+    const float scale = rsqrtf(static_cast<float>(HD));
+    float qv[VEC];
+    {
+        const float* qp = q + static_cast<int64_t>(b) * q_stride + h * HD + lane * VEC;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) qv[j] = qp[j] * scale;
+    }
+    const float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
+    const float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
+
+    float m = -CUDART_INF_F, l = 0.f, acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+
+    for (int64_t t = t0 + warp * kKeysPerIter; t < t1; t += kAttnWarps * kKeysPerIter) {
+        float s[kKeysPerIter];
+#pragma unroll
+        for (int i = 0; i < kKeysPerIter; ++i) {
+            float d = 0.f;
+            if (t + i < t1) {
+                const float* kp = kb + (t + i) * HD;
+                if constexpr (VEC == 4) {
+                    const float4 kk = *reinterpret_cast<const float4*>(kp);
+                    d = qv[0] * kk.x + qv[1] * kk.y + qv[2] * kk.z + qv[3] * kk.w;
+                } else {
+                    const float2 kk = *reinterpret_cast<const float2*>(kp);
+                    d = qv[0] * kk.x + qv[1] * kk.y;
+                }
+            }
+            s[i] = d;
+        }
+        float mx = m;
+#pragma unroll
+        for (int i = 0; i < kKeysPerIter; ++i) {
+            s[i] = warp_sum(s[i]);
+            if (t + i >= t1) s[i] = -CUDART_INF_F;
+            mx = fmaxf(mx, s[i]);
+        }
+        const float corr = expf(m - mx);                    // m = -inf on the first pass: exp(-inf) = 0
+        l *= corr;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] *= corr;
+#pragma unroll
+        for (int i = 0; i < kKeysPerIter; ++i) {
+            if (t + i < t1) {
+                const float p = expf(s[i] - mx);
+                l += p;
+                const float* vp = vb + (t + i) * HD;
+                if constexpr (VEC == 4) {
+                    const float4 vv = *reinterpret_cast<const float4*>(vp);
+                    acc[0] = fmaf(p, vv.x, acc[0]); acc[1] = fmaf(p, vv.y, acc[1]);
+                    acc[2] = fmaf(p, vv.z, acc[2]); acc[3] = fmaf(p, vv.w, acc[3]);
+                } else {
+                    const float2 vv = *reinterpret_cast<const float2*>(vp);
+                    acc[0] = fmaf(p, vv.x, acc[0]); acc[1] = fmaf(p, vv.y, acc[1]);
+                }
+            }
+        }
+        m = mx;
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sm_acc[warp][lane * VEC + j] = acc[j];
+    __syncthreads();
+
+    // merge the warps: thread d < HD owns output element d
+    float M = -CUDART_INF_F, L = 0.f, A = 0.f;
+    if (threadIdx.x < HD) {
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float wgt = (sm_m[w] == -CUDART_INF_F) ? 0.f : expf(sm_m[w] - M);
+            L = fmaf(sm_l[w], wgt, L);
+            A = fmaf(sm_acc[w][threadIdx.x], wgt, A);
+        }
+    }
+    float* orow = out + static_cast<int64_t>(b) * out_stride + h * HD;
+    if (S == 1) {
+        if (threadIdx.x < HD) orow[threadIdx.x] = A / L;
+        return;
+    }
+    float* mine = part + (static_cast<int64_t>(bh) * S + split) * (HD + 2);
+    if (threadIdx.x < HD) {
+        mine[2 + threadIdx.x] = A;
+        if (threadIdx.x == 0) { mine[0] = M; mine[1] = L; }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) sm_ticket = atomicAdd(&tickets[bh], 1u);
+    __syncthreads();
+    if (sm_ticket != static_cast<unsigned int>(S - 1)) return;
+    __threadfence();
+    if (threadIdx.x < HD) {
+        const float* base = part + static_cast<int64_t>(bh) * S * (HD + 2);
+        float MM = -CUDART_INF_F;
+        for (int s2 = 0; s2 < S; ++s2) MM = fmaxf(MM, __ldcg(base + s2 * (HD + 2)));
+        float LL = 0.f, AA = 0.f;
+        for (int s2 = 0; s2 < S; ++s2) {
+            const float ms = __ldcg(base + s2 * (HD + 2));
+            const float wgt = (ms == -CUDART_INF_F) ? 0.f : expf(ms - MM);
+            LL = fmaf(__ldcg(base + s2 * (HD + 2) + 1), wgt, LL);
+            AA = fmaf(__ldcg(base + s2 * (HD + 2) + 2 + threadIdx.x), wgt, AA);
+        }
+        orow[threadIdx.x] = AA / LL;
+    }
+}
+
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gu, int64_t rows, int64_t hidden,
+                                                       float* __restrict__ out) {
+    const int64_t n = rows * hidden;
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += gridDim.x * 256ll) {
+        const int64_t r = i / hidden, c = i - r * hidden;
+        const float g = gu[r * 2 * hidden + c], u = gu[r * 2 * hidden + hidden + c];
+        out[i] = g / (1.0f + expf(-g)) * u;              // include/sovereigngrad/simd.hpp:103-108, then gate * up
+    }
+}
+
+int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
+    const int64_t bh = batch * n_heads > 0 ? batch * n_heads : 1;
+    int64_t s = ceil_div(4 * 148, bh);
+    const int64_t cap = ceil_div(max_seq, 64);
+    if (s > cap) s = cap;
+    if (s > 8) s = 8;
+    if (s < 1) s = 1;
+    return static_cast<int>(s);
+}
+
+size_t attn_part_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq) {
+    const size_t part = static_cast<size_t>(batch * n_heads) * attn_splits(batch, n_heads, max_seq) * (head_dim + 2) * sizeof(float);
+    return (part + 255) & ~static_cast<size_t>(255);
+}
+
+}  // namespace
+}  // namespace sgq
+
+using namespace sgq;
+
+extern "C" {
+
+int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps, int64_t rows, int64_t dim, float* out,
+                     void* stream) {
+    if (rows < 0 || dim < 0 || rows > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad rows/dim");
+    if (rows == 0 || dim == 0) return SGQ_OK;
+    if (!h || !gamma || !out) return bad(SGQ_ERR_NULL_POINTER, "h, gamma or out is NULL");
+    if (out == h) return bad(SGQ_ERR_BAD_ARGUMENT, "out may not alias h");
+    if ((dim & 3) == 0 && !(aligned(h, 16) && aligned(out, 16) && aligned(gamma, 16) && (!delta || aligned(delta, 16))))
+        return bad(SGQ_ERR_ALIGNMENT, "rows must be 16-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    add_rmsnorm_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, gamma, eps, dim, out);
+    SGQ_LAUNCH_CHECK("add_rmsnorm_kernel");
+    return SGQ_OK;
+}
+
+int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim, const float* cos_table,
+                       const float* sin_table, const int32_t* pos0, float* k_cache, float* v_cache, int64_t max_seq,
+                       void* stream) {
+    if (batch < 0 || t_new < 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0 || batch * t_new > 0x7fffffff)
+        return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
+    if (head_dim % 8) return bad(SGQ_ERR_BAD_SHAPE, "head_dim must be a multiple of 8");
+    if (batch * t_new == 0) return SGQ_OK;
+    if (!qkv || !cos_table || !sin_table || !pos0 || !k_cache || !v_cache) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    rope_kv_store_kernel<<<static_cast<unsigned>(batch * t_new), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        qkv, static_cast<int>(t_new), static_cast<int>(n_heads), static_cast<int>(head_dim), cos_table, sin_table, pos0, k_cache,
+        v_cache, max_seq);
+    SGQ_LAUNCH_CHECK("rope_kv_store_kernel");
+    return SGQ_OK;
+}
+
+size_t sgqd_attn_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq) {
+    if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
+    return attn_part_bytes(batch, n_heads, head_dim, max_seq) + ((static_cast<size_t>(batch * n_heads) * 4 + 255) & ~static_cast<size_t>(255));
+}
+
+int sgqd_attn_decode(const float* q, int64_t q_stride, int64_t batch, int64_t n_heads, int64_t head_dim, const float* k_cache,
+                     const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+    if (batch < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
+    if (head_dim != 64 && head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+    if (q_stride < n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride < n_heads * head_dim");
+    if (batch == 0) return SGQ_OK;
+    if (!q || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (!aligned(q, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || (q_stride & 3)) return bad(SGQ_ERR_ALIGNMENT, "q / caches must be 16-byte aligned");
+    const size_t need = sgqd_attn_decode_workspace_bytes(batch, n_heads, head_dim, max_seq);
+    if (!workspace || workspace_bytes < need || !aligned(workspace, 256)) return bad(SGQ_ERR_WORKSPACE, "attention workspace missing, too small or not 256-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t part_bytes = attn_part_bytes(batch, n_heads, head_dim, max_seq);
+    float* part = static_cast<float*>(workspace);
+    unsigned int* tickets = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + part_bytes);
+    const int S = attn_splits(batch, n_heads, max_seq);
+    if (S > 1) SGQ_CUDA_TRY(cudaMemsetAsync(tickets, 0, static_cast<size_t>(batch * n_heads) * 4, s));
+    const dim3 grid(static_cast<unsigned>(batch * n_heads), static_cast<unsigned>(S));
+    if (head_dim == 128)
+        attn_decode_kernel<128><<<grid, kAttnWarps * 32, 0, s>>>(q, q_stride, static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride, part, tickets);
+    else
+        attn_decode_kernel<64><<<grid, kAttnWarps * 32, 0, s>>>(q, q_stride, static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride, part, tickets);
+    SGQ_LAUNCH_CHECK("attn_decode_kernel");
+    return SGQ_OK;
+}
+
+int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream) {
+    if (rows < 0 || hidden < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (rows * hidden == 0) return SGQ_OK;
+    if (!gate_up || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    int64_t blocks = ceil_div(rows * hidden, 256);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, rows, hidden, out);
+    SGQ_LAUNCH_CHECK("silu_mul_kernel");
+    return SGQ_OK;
+}
+
+}  // extern "C"

@@ -12,6 +12,8 @@ namespace sgq {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);  // records the message, returns SGQ_ERR_CUDA
 int sm_count();                                   // SMs of the current device (cached per device)
+int check_device();                               // SGQ_ERR_DEVICE unless the current device is compute capability 10.x
+int bad(int code, const char* msg);               // records msg, returns code
 
 #define SGQ_CUDA_TRY(expr)                                              \
     do {                                                                \

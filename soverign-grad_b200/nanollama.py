@@ -1,0 +1,324 @@
+"""NanoLLaMA-INT4: greedy decoding of a LLaMA-style decoder whose every Linear is an INT4 (group 32)
+QuantizedLinear4Bit served by the C ABI.
+
+The reference's NanoLLaMA (include/sovereigngrad/models.hpp:193-305) is a toy: no batch, no heads,
+no rotary call, no KV cache, and generate() re-runs the whole context for each new token
+(models.hpp:262-300).  The model here is the benchmarked configuration — dim 2048, 16 blocks,
+16 heads of 128, SwiGLU hidden 5632, RMSNorm (eps 1e-5), RoPE base 1e4, vocab 32000 — assembled from
+the reference's operators: nn::RMSNorm (nn.hpp:67-85), nn::RotaryEmbedding (nn.hpp:583-612),
+nn::CausalSelfAttention (nn.hpp:503-560), nn::SwiGLU (nn.hpp:138-160), nn::Embedding (nn.hpp:390-410)
+and greedy selection (models.hpp:286-298: first index of the strict maximum).
+
+What runs where: every Linear goes through sgq_linear_int4 (decode kernel for the M = batch steps,
+tcgen05 kernel for the prefill); RMSNorm, RoPE + KV-cache store, cache attention and the SiLU gate
+are the sgqd_* kernels of include/sgq_decoder.h; torch supplies device memory, the embedding gather,
+the prefill attention (fp32 math kernels) and argmax.  A decode step touches no host state — the
+cache position lives in device memory — so one step is recorded into a CUDA graph and replayed.
+
+Sharding (world > 1): heads, SwiGLU columns, output features of wo / w_down and the vocabulary are
+split by column over the ranks; each split output is all-gathered over NCCL and re-interleaved
+(`sharding.ShardedLinear` has the single-layer version of the same scheme).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
+               quantize_int4, quantized_matmul)
+
+
+@dataclass
+class NanoLlamaConfig:
+    dim: int = 2048
+    n_layers: int = 16
+    n_heads: int = 16
+    hidden: int = 5632
+    vocab: int = 32000
+    max_seq: int = 640
+    rope_base: float = 10000.0
+    eps: float = 1e-5
+    group: int = 32
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+
+LAYER_WEIGHTS = ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
+
+
+def weight_shape(cfg: NanoLlamaConfig, name: str) -> tuple[int, int]:
+    """[out, in] of a float weight; `embed` and `lm_head` are [vocab, dim]."""
+    if name in ("wq", "wk", "wv", "wo"):
+        return cfg.dim, cfg.dim
+    if name in ("w_gate", "w_up"):
+        return cfg.hidden, cfg.dim
+    if name == "w_down":
+        return cfg.dim, cfg.hidden
+    if name in ("embed", "lm_head"):
+        return cfg.vocab, cfg.dim
+    raise KeyError(name)
+
+
+def default_init(cfg: NanoLlamaConfig, device, seed: int) -> Callable[[str, int], torch.Tensor]:
+    """Random weights with the reference's initialisers: nn::Linear N(0, sqrt(2 / (in + out)))
+    (nn.hpp:23-26), nn::Embedding N(0, sqrt(1 / dim)) (nn.hpp:396-400)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def make(name: str, layer: int) -> torch.Tensor:
+        out_f, in_f = weight_shape(cfg, name)
+        std = (1.0 / cfg.dim) ** 0.5 if name == "embed" else (2.0 / (in_f + out_f)) ** 0.5
+        return torch.randn(out_f, in_f, device=device, generator=gen) * std
+    return make
+
+
+def rope_tables(cfg: NanoLlamaConfig, device):
+    """nn::RotaryEmbedding (nn.hpp:583-607): float32 inv_freq and theta, tables [max_seq, head_dim/2]."""
+    half = cfg.head_dim // 2
+    i = torch.arange(half, dtype=torch.float32)
+    inv_freq = 1.0 / torch.pow(torch.tensor(cfg.rope_base, dtype=torch.float32), (2.0 * i) / float(cfg.head_dim))
+    theta = torch.arange(cfg.max_seq, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    return torch.cos(theta.double()).float().to(device).contiguous(), torch.sin(theta.double()).float().to(device).contiguous()
+
+
+def _rows(w: torch.Tensor, r0: int, r1: int) -> torch.Tensor:
+    return w[r0:r1]
+
+
+class _Linear:
+    """One column slice of an INT4 linear: rows [n0, n1) of the [N, K] weight on this rank."""
+
+    def __init__(self, w_local: torch.Tensor, group: int, ws: Workspace):
+        self.q: QuantizedTensor = quantize_int4(w_local.contiguous(), group)
+        self.n_local, self.k = w_local.shape
+        self.ws = ws
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, path: int) -> torch.Tensor:
+        return quantized_matmul(x, self.q, None, layout=LAYOUT_NK, path=path, out=out, workspace=self.ws)
+
+
+class NanoLlamaInt4:
+    def __init__(self, cfg: NanoLlamaConfig, device, batch: int, *, seed: int = 0,
+                 init: Optional[Callable[[str, int], torch.Tensor]] = None, rank: int = 0, world: int = 1, group=None,
+                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO):
+        if cfg.n_heads % world or cfg.hidden % (32 * world) or cfg.dim % (32 * world) or cfg.vocab % (32 * world):
+            raise ValueError("heads, hidden, dim and vocab must split into equal 32-row slices per rank")
+        self.cfg, self.device, self.batch = cfg, torch.device(device), batch
+        self.rank, self.world, self.group = rank, world, group
+        self.decode_path, self.prefill_path = decode_path, prefill_path
+        init = init or default_init(cfg, self.device, seed)
+        dev = self.device
+        self.ws = Workspace(dev)
+        hd, H = cfg.head_dim, cfg.n_heads
+        self.h_local = H // world
+        self.dim_local = self.h_local * hd
+        self.hid_local = cfg.hidden // world
+        self.voc_local = cfg.vocab // world
+        d0, d1 = rank * self.dim_local, (rank + 1) * self.dim_local
+        f0, f1 = rank * self.hid_local, (rank + 1) * self.hid_local
+        v0, v1 = rank * self.voc_local, (rank + 1) * self.voc_local
+
+        self.embed = init("embed", -1).to(dev).float().contiguous()
+        self.layers = []
+        for li in range(cfg.n_layers):
+            w = {n: init(n, li).to(dev).float() for n in LAYER_WEIGHTS}
+            qkv = torch.cat([_rows(w["wq"], d0, d1), _rows(w["wk"], d0, d1), _rows(w["wv"], d0, d1)], 0)
+            gu = torch.cat([_rows(w["w_gate"], f0, f1), _rows(w["w_up"], f0, f1)], 0)
+            self.layers.append({
+                "qkv": _Linear(qkv, cfg.group, self.ws), "wo": _Linear(_rows(w["wo"], d0, d1), cfg.group, self.ws),
+                "gu": _Linear(gu, cfg.group, self.ws), "down": _Linear(_rows(w["w_down"], d0, d1), cfg.group, self.ws),
+                "attn_norm": torch.ones(cfg.dim, device=dev), "ffn_norm": torch.ones(cfg.dim, device=dev)})
+            del w, qkv, gu
+        self.final_norm = torch.ones(cfg.dim, device=dev)
+        self.lm_head = _Linear(_rows(init("lm_head", -1).to(dev).float(), v0, v1), cfg.group, self.ws)
+
+        self.cos, self.sin = rope_tables(cfg, dev)
+        shape = (cfg.n_layers, batch, self.h_local, cfg.max_seq, hd)
+        self.k_cache = torch.zeros(shape, device=dev)
+        self.v_cache = torch.zeros(shape, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        nb = int(lib.sgqd_attn_decode_workspace_bytes(batch, self.h_local, hd, cfg.max_seq))
+        self.attn_ws = torch.empty(max(nb, 256), dtype=torch.uint8, device=dev)
+        self._bufs = {}
+        self._graph = None
+        self.tok = torch.zeros(batch, dtype=torch.int64, device=dev)
+        self.launches_per_decode_step = 0
+
+    # ---- buffers -------------------------------------------------------------------------
+    def _buffers(self, M: int):
+        if M not in self._bufs:
+            c, dev, W = self.cfg, self.device, self.world
+            f = lambda *s: torch.empty(*s, device=dev)  # noqa: E731
+            b = {"h": f(M, c.dim), "n": f(M, c.dim), "qkv": f(M, 3 * self.dim_local), "attn": f(M, self.dim_local),
+                 "o": f(M, c.dim // W), "gu": f(M, 2 * self.hid_local), "act": f(M, self.hid_local), "d": f(M, c.dim // W)}
+            if W > 1:
+                b.update({"g_attn": f(W, M, self.dim_local), "g_o": f(W, M, c.dim // W), "g_act": f(W, M, self.hid_local),
+                          "attn_full": f(M, c.dim), "o_full": f(M, c.dim), "act_full": f(M, c.hidden), "d_full": f(M, c.dim)})
+            self._bufs[M] = b
+        return self._bufs[M]
+
+    def _gather(self, local: torch.Tensor, gathered: torch.Tensor, full: torch.Tensor) -> torch.Tensor:
+        """[M, n_local] slices of every rank -> row-major [M, world * n_local]; identity on one GPU."""
+        if self.world == 1:
+            return local
+        import torch.distributed as dist
+        M, n_local = local.shape
+        dist.all_gather_into_tensor(gathered.view(self.world * M, n_local), local, group=self.group)
+        self._count(1)
+        return interleave_slices(gathered, self.world, M, n_local, full)
+
+    def _count(self, n: int = 1):
+        self._launches += n
+
+    # ---- the C-ABI operators ---------------------------------------------------------------
+    def _add_rmsnorm(self, h, delta, gamma, out):
+        check(lib.sgqd_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(gamma), self.cfg.eps, h.shape[0], h.shape[1], _ptr(out), _stream()),
+              "sgqd_add_rmsnorm")
+        self._count()
+
+    def _linear(self, lin: _Linear, x, out, path):
+        lin(x, out, path)
+        M, K = x.shape
+        # the decode kernel converts activations inside its CTAs up to 2048 eight-value chunks; larger
+        # batches and the tensor-core path run a conversion kernel first
+        self._count(2 if (M > 16 or M * (K // 8) > 2048) else 1)
+
+    # ---- one pass over t_new new tokens per sequence ---------------------------------------
+    def _forward(self, tokens: torch.Tensor, t_new: int, path: int) -> torch.Tensor:
+        """tokens [batch * t_new] (sequence-major).  Returns the final-normed hidden state [M, dim]."""
+        c, B = self.cfg, self.batch
+        M = B * t_new
+        b = self._buffers(M)
+        h, n = b["h"], b["n"]
+        torch.index_select(self.embed, 0, tokens, out=h)                       # nn::Embedding lookup
+        self._count()
+        delta = None
+        for li, L in enumerate(self.layers):
+            self._add_rmsnorm(h, delta, L["attn_norm"], n)
+            self._linear(L["qkv"], n, b["qkv"], path)
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            check(lib.sgqd_rope_kv_store(_ptr(b["qkv"]), B, t_new, self.h_local, c.head_dim, _ptr(self.cos), _ptr(self.sin),
+                                         _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
+            self._count()
+            if t_new == 1:
+                check(lib.sgqd_attn_decode(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(kc), _ptr(vc),
+                                           c.max_seq, _ptr(self.pos), _ptr(b["attn"]), self.dim_local, _ptr(self.attn_ws),
+                                           self.attn_ws.numel(), _stream()), "sgqd_attn_decode")
+                self._count()
+            else:
+                self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"])
+            attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"))
+            self._linear(L["wo"], attn, b["o"], path)
+            o = self._gather(b["o"], b.get("g_o"), b.get("o_full"))
+            self._add_rmsnorm(h, o, L["ffn_norm"], n)
+            self._linear(L["gu"], n, b["gu"], path)
+            check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _stream()), "sgqd_silu_mul")
+            self._count()
+            act = self._gather(b["act"], b.get("g_act"), b.get("act_full"))
+            self._linear(L["down"], act, b["d"], path)
+            delta = self._gather(b["d"], b.get("g_o"), b.get("d_full"))
+        self._add_rmsnorm(h, delta, self.final_norm, n)
+        return n
+
+    def _prefill_attention(self, qkv, kc, vc, T: int, out):
+        """Causal attention of a prompt that starts at position 0: q from the rotated qkv rows, k and v
+        from the cache rows just written.  torch fp32 math kernels (exact fp32 matmuls, no TF32)."""
+        B, Hl, hd = self.batch, self.h_local, self.cfg.head_dim
+        q = qkv.view(B, T, 3, Hl, hd)[:, :, 0].permute(0, 2, 1, 3)                       # [B, Hl, T, hd]
+        k, v = kc[:, :, :T], vc[:, :, :T]
+        scores = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / hd ** 0.5)
+        mask = torch.ones(T, T, dtype=torch.bool, device=self.device).triu_(1)
+        scores.masked_fill_(mask, float("-inf"))
+        ctx = torch.matmul(torch.softmax(scores, dim=-1), v)                              # [B, Hl, T, hd]
+        out.view(B, T, Hl, hd).copy_(ctx.permute(0, 2, 1, 3))
+        self._count(6)
+
+    def _logits(self, n_rows: torch.Tensor, path: int) -> torch.Tensor:
+        M = n_rows.shape[0]
+        key = ("logits", M)
+        if key not in self._bufs:
+            f = lambda *s: torch.empty(*s, device=self.device)  # noqa: E731
+            self._bufs[key] = (f(M, self.voc_local), f(self.world, M, self.voc_local) if self.world > 1 else None,
+                               f(M, self.cfg.vocab) if self.world > 1 else None)
+        loc, g, full = self._bufs[key]
+        self._linear(self.lm_head, n_rows, loc, path)
+        return self._gather(loc, g, full)
+
+    # ---- public ---------------------------------------------------------------------------
+    def reset(self):
+        self.pos.zero_()
+
+    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
+        """prompt [batch, P] int64 at positions 0..P-1.  Returns the logits of the last position [batch, vocab]."""
+        B, P = prompt.shape
+        if B != self.batch or P > self.cfg.max_seq:
+            raise ValueError("prompt shape does not fit the model's batch / max_seq")
+        self._launches = 0
+        self.reset()
+        n = self._forward(prompt.reshape(-1).to(self.device), P, self.prefill_path)
+        last = n.view(B, P, self.cfg.dim)[:, -1].contiguous()
+        logits = self._logits(last, self.decode_path)
+        self.pos.fill_(P)
+        return logits
+
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [batch] int64: the token at position *pos of every sequence.  Appends it to the cache,
+        advances the position and returns the logits of the next token [batch, vocab]."""
+        self._launches = 0
+        n = self._forward(tokens, 1, self.decode_path)
+        logits = self._logits(n, self.decode_path)
+        self.pos.add_(1)
+        self._count()
+        return logits
+
+    def _greedy_step(self):
+        logits = self.decode_step(self.tok)
+        torch.argmax(logits, dim=-1, out=self.tok)       # first index of the maximum (models.hpp:289-296)
+        self._count(2)
+        self.launches_per_decode_step = self._launches
+        return logits
+
+    def capture_decode_graph(self):
+        """Records one greedy decode step (token buffer -> next token buffer) into a CUDA graph."""
+        if self.world > 1:
+            raise RuntimeError("the sharded model launches its collectives eagerly")
+        saved_pos, saved_tok = self.pos.clone(), self.tok.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._greedy_step()                          # eager once: lazy kernel loading
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._greedy_step()
+        self._graph = graph
+        self.pos.copy_(saved_pos)
+        self.tok.copy_(saved_tok)
+        torch.cuda.synchronize()
+
+    def generate(self, prompt: torch.Tensor, n_new: int, *, use_graph: bool = True, keep_logits: bool = False):
+        """Greedy generation.  Returns tokens [batch, n_new] (and the list of per-step logits)."""
+        B, P = prompt.shape
+        if P + n_new > self.cfg.max_seq + 1:
+            raise ValueError("prompt + new tokens exceed max_seq")
+        logits = self.prefill(prompt)
+        out = torch.empty(B, n_new, dtype=torch.int64, device=self.device)
+        kept = [logits.clone()] if keep_logits else None
+        torch.argmax(logits, dim=-1, out=self.tok)
+        out[:, 0].copy_(self.tok)
+        use_graph = use_graph and self.world == 1 and not keep_logits
+        if use_graph and self._graph is None:
+            self.capture_decode_graph()
+        for s in range(1, n_new):
+            if use_graph:
+                self._graph.replay()
+            else:
+                lg = self._greedy_step()
+                if keep_logits:
+                    kept.append(lg.clone())
+            out[:, s].copy_(self.tok)
+        return (out, kept) if keep_logits else out

@@ -35,9 +35,43 @@ def sha(a: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
+def glue_inputs():
+    """Seeded inputs of the decode-glue fixtures (tests/golden/glue.npz)."""
+    r = np.random.default_rng(20240611)
+    return {
+        "rms/x": (r.standard_normal((5, 256)) * 1.7).astype(np.float32),
+        "rms/gamma": (1.0 + 0.1 * r.standard_normal(256)).astype(np.float32),
+        "silu/x": np.concatenate([r.standard_normal(500) * 4.0, [-30.0, -0.0, 0.0, 30.0, 88.0]]).astype(np.float32),
+        "softmax/x": (r.standard_normal((6, 97)) * 3.0).astype(np.float32),
+        "rope/x": r.standard_normal((40, 128)).astype(np.float32),
+        "swiglu/x": r.standard_normal((3, 64)).astype(np.float32),
+        "swiglu/w_gate": (r.standard_normal((64, 160)) * 0.1).astype(np.float32),
+        "swiglu/w_up": (r.standard_normal((64, 160)) * 0.1).astype(np.float32),
+        "swiglu/w_down": (r.standard_normal((160, 64)) * 0.1).astype(np.float32),
+    }
+
+
+def make_glue(ref):
+    """Outputs of the reference's own rms_norm / silu / softmax / RotaryEmbedding / SwiGLU."""
+    g = glue_inputs()
+    g["rms/y"] = ref.rms_norm(g["rms/x"], g["rms/gamma"], 1e-5)
+    g["silu/y"] = ref.silu(g["silu/x"])
+    g["softmax/y"] = ref.softmax_rows(g["softmax/x"])
+    g["rope/cos"], g["rope/sin"] = ref.rope_tables(128, 640, 10000.0)
+    g["rope/y"] = ref.rope(g["rope/x"], 640, 10000.0)
+    g["swiglu/y"] = ref.swiglu(g["swiglu/x"], g["swiglu/w_gate"], g["swiglu/w_up"], g["swiglu/w_down"])
+    g["rope/cos"] = g["rope/cos"][::7].copy()          # keep the file small: every 7th position
+    g["rope/sin"] = g["rope/sin"][::7].copy()
+    np.savez_compressed(os.path.join(HERE, "glue.npz"), **g)
+    print("glue.npz", os.path.getsize(os.path.join(HERE, "glue.npz")), "bytes")
+
+
 def main():
     ref = oracle.load_ref()
     assert ref is not None, "build oracle/_ref first (make -C oracle ref)"
+    make_glue(ref)
+    if sys.argv[1:] == ["glue"]:
+        return
     q = {}
     for name, shape, gen in cases.QUANT_CASES:
         x = gen()

@@ -14,10 +14,10 @@ def sgq():
     return load_package()
 
 
-def header_symbols():
-    text = open(os.path.join(ROOT, "include", "sgq.h")).read()
+def header_symbols(name="sgq.h", prefix="sgq_"):
+    text = open(os.path.join(ROOT, "include", name)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(sgq_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(" + prefix + r"[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol(sgq):
@@ -26,6 +26,28 @@ def test_library_exports_every_declared_symbol(sgq):
     assert sorted(sgq.EXPORTS) == declared, "python binding list and header disagree"
     for name in declared:
         assert hasattr(sgq.lib, name), f"{name} is declared in sgq.h but not exported by libsgq.so"
+
+
+def test_library_exports_every_decoder_symbol(sgq):
+    declared = header_symbols("sgq_decoder.h", "sgqd_")
+    assert sorted(sgq.DECODER_EXPORTS) == declared
+    for name in declared:
+        assert hasattr(sgq.lib, name), f"{name} is declared in sgq_decoder.h but not exported by libsgq.so"
+
+
+def test_decoder_argument_validation_needs_no_device(sgq):
+    L = sgq.lib
+    one = C.c_void_p(256)
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, -1, 8, one, None) == 2
+    assert L.sgqd_add_rmsnorm(None, None, one, 1e-5, 2, 8, one, None) == 1
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 8, one, None) == 3              # out aliases h
+    assert L.sgqd_add_rmsnorm(None, None, None, 1e-5, 0, 8, None, None) == 0           # empty
+    assert L.sgqd_rope_kv_store(one, 1, 1, 2, 12, one, one, one, one, one, 8, None) == 2   # head_dim % 8
+    assert L.sgqd_attn_decode(one, 256, 1, 2, 96, one, one, 8, one, one, 256, one, 4096, None) == 4   # head_dim 96
+    assert L.sgqd_attn_decode(one, 100, 1, 2, 128, one, one, 8, one, one, 256, one, 4096, None) == 2  # stride too small
+    assert L.sgqd_silu_mul(None, 2, 8, None, None) == 1
+    assert int(L.sgqd_attn_decode_workspace_bytes(8, 16, 128, 640)) % 256 == 0
+    assert int(L.sgqd_attn_decode_workspace_bytes(8, 16, 128, 640)) >= 8 * 16 * 5 * 130 * 4
 
 
 def test_abi_version_and_status_strings(sgq):

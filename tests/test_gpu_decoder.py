@@ -1,0 +1,184 @@
+"""Decoder glue (include/sgq_decoder.h) and the NanoLLaMA-INT4 greedy decoder against the numpy
+restatement in oracle/nanollama_oracle.py, which evaluates the model the way the reference's
+generate() does: one full causal pass over the whole sequence, no KV cache.  Float tolerances:
+1e-3 (fp32 paths) and 2e-2 (bf16 tensor-core prefill), relative to the largest reference value."""
+import ctypes as C
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nanollama_oracle as no
+from util import TOL_BF16, TOL_FP32, norm_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def sgq():
+    from __graft_entry__ import load_package
+    return load_package()
+
+
+@pytest.fixture(scope="module")
+def nl(sgq):
+    return importlib.import_module("sgq_b200.nanollama")
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype).cuda()
+
+
+def ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("rows,dim,with_delta", [(1, 256, False), (8, 2048, True), (5, 100, True), (300, 513, False)])
+def test_add_rmsnorm(sgq, rows, dim, with_delta):
+    r = np.random.default_rng(rows * 7 + dim)
+    h = r.standard_normal((rows, dim)).astype(np.float32) * 2
+    d = r.standard_normal((rows, dim)).astype(np.float32) if with_delta else None
+    g = (1 + 0.2 * r.standard_normal(dim)).astype(np.float32)
+    ht, dt, gt = dev(h), (dev(d) if with_delta else None), dev(g)
+    out = torch.empty_like(ht)
+    sgq.check(sgq.lib.sgqd_add_rmsnorm(ptr(ht), ptr(dt), ptr(gt), 1e-5, rows, dim, ptr(out), stream()))
+    hsum = h.astype(np.float64) + (d if with_delta else 0)
+    assert np.max(np.abs(ht.cpu().numpy() - hsum)) <= 1e-6 * np.max(np.abs(hsum))     # residual stream updated in place
+    assert norm_err(out.cpu().numpy(), no.rms_norm(hsum.astype(np.float32), g, 1e-5)) <= 5e-6
+
+
+def test_add_rmsnorm_rejects_alias(sgq):
+    h = torch.zeros(2, 64, device="cuda")
+    g = torch.ones(64, device="cuda")
+    assert sgq.lib.sgqd_add_rmsnorm(ptr(h), None, ptr(g), 1e-5, 2, 64, ptr(h), stream()) == 3
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 5632), (8, 704), (3, 37)])
+def test_silu_mul(sgq, rows, hidden):
+    r = np.random.default_rng(hidden)
+    gu = (r.standard_normal((rows, 2 * hidden)) * 3).astype(np.float32)
+    out = torch.empty(rows, hidden, device="cuda")
+    gt = dev(gu)
+    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gt), rows, hidden, ptr(out), stream()))
+    want = no.silu(gu[:, :hidden]) * gu[:, hidden:].astype(np.float64)
+    assert norm_err(out.cpu().numpy(), want) <= 2e-6
+
+
+@pytest.mark.parametrize("B,T,H,hd,pos0,max_seq", [(2, 1, 2, 128, 0, 16), (2, 1, 3, 64, 9, 16), (2, 5, 2, 128, 3, 16),
+                                                   (1, 4, 1, 128, 14, 16)])
+def test_rope_kv_store(sgq, B, T, H, hd, pos0, max_seq):
+    r = np.random.default_rng(B * 100 + T * 10 + pos0)
+    dim = H * hd
+    qkv = r.standard_normal((B * T, 3 * dim)).astype(np.float32)
+    cos, sin = no.rope_tables(hd, max_seq)
+    kc = torch.full((B, H, max_seq, hd), 7.0, device="cuda")
+    vc = torch.full((B, H, max_seq, hd), 7.0, device="cuda")
+    qt = dev(qkv)
+    pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    ct, st = dev(cos), dev(sin)
+    sgq.check(sgq.lib.sgqd_rope_kv_store(ptr(qt), B, T, H, hd, ptr(ct), ptr(st), ptr(pos), ptr(kc), ptr(vc), max_seq, stream()))
+    got, kcn, vcn = qt.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy()
+    for b in range(B):
+        for i in range(T):
+            m, p = b * T + i, pos0 + i
+            q = qkv[m, :dim].reshape(H, hd)
+            k = qkv[m, dim:2 * dim].reshape(H, hd)
+            v = qkv[m, 2 * dim:].reshape(H, hd)
+            if p >= max_seq:                                   # skipped token: nothing rotated, nothing stored
+                np.testing.assert_array_equal(got[m, :dim].reshape(H, hd), q)
+                continue
+            assert norm_err(got[m, :dim].reshape(H, hd), no.rope(q, cos, sin, [p])) <= 2e-6
+            assert norm_err(kcn[b, :, p], no.rope(k, cos, sin, [p])) <= 2e-6
+            np.testing.assert_array_equal(vcn[b, :, p], v)
+            np.testing.assert_array_equal(got[m, dim:], qkv[m, dim:])          # k and v rows of qkv are left alone
+    untouched = np.ones(max_seq, bool)
+    untouched[pos0:min(pos0 + T, max_seq)] = False
+    assert (kcn[:, :, untouched] == 7.0).all() and (vcn[:, :, untouched] == 7.0).all()
+
+
+@pytest.mark.parametrize("B,H,hd,length,max_seq", [(1, 1, 128, 1, 8), (2, 2, 128, 7, 64), (8, 16, 128, 130, 640),
+                                                   (8, 16, 128, 640, 640), (3, 5, 64, 333, 512), (40, 32, 64, 100, 128)])
+def test_attn_decode(sgq, B, H, hd, length, max_seq):
+    r = np.random.default_rng(length * 3 + hd)
+    dim = H * hd
+    qkv = r.standard_normal((B, 3 * dim)).astype(np.float32)
+    kc = (r.standard_normal((B, H, max_seq, hd)) * 1.5).astype(np.float32)
+    vc = r.standard_normal((B, H, max_seq, hd)).astype(np.float32)
+    pos = torch.tensor([length - 1], dtype=torch.int32, device="cuda")
+    nb = int(sgq.lib.sgqd_attn_decode_workspace_bytes(B, H, hd, max_seq))
+    ws = torch.empty(max(nb, 256), dtype=torch.uint8, device="cuda")
+    out = torch.empty(B, dim, device="cuda")
+    qt, kt, vt = dev(qkv), dev(kc), dev(vc)
+    for _ in range(2):                                         # twice: the ticket counters are re-armed per call
+        sgq.check(sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, ptr(ws),
+                                           ws.numel(), stream()))
+    q = qkv[:, :dim].reshape(B, H, 1, hd).astype(np.float64)
+    k, v = kc[:, :, :length].astype(np.float64), vc[:, :, :length].astype(np.float64)
+    p = no.softmax(np.einsum("bhqd,bhtd->bhqt", q, k) / np.sqrt(hd))
+    want = np.einsum("bhqt,bhtd->bhqd", p, v).reshape(B, dim)
+    assert norm_err(out.cpu().numpy(), want) <= 5e-6
+    assert sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, None, 0,
+                                    stream()) == 5             # workspace missing
+
+
+# ---- the whole model ------------------------------------------------------------------------------
+def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3):
+    cfg = nl.NanoLlamaConfig(dim=256, n_layers=2, n_heads=2, hidden=512, vocab=512, max_seq=64)
+    B = 2
+    r = np.random.default_rng(seed)
+    floats = {}
+
+    def init(name, layer):
+        out_f, in_f = nl.weight_shape(cfg, name)
+        std = 1.0 if name == "embed" else 2.5 * (2.0 / (in_f + out_f)) ** 0.5     # livelier logits than the default init
+        w = (r.standard_normal((out_f, in_f)) * std).astype(np.float32)
+        floats[(name, layer)] = w
+        return torch.from_numpy(w)
+
+    model = nl.NanoLlamaInt4(cfg, "cuda", B, init=init, prefill_path=prefill_path)
+    prompt = torch.from_numpy(r.integers(0, cfg.vocab, (B, prompt_len)))
+    tokens, logits = model.generate(prompt, n_new, use_graph=False, keep_logits=True)
+
+    def deq(name, layer):
+        w = floats[(name, layer)]
+        packed, scales = port.quantize_int4(w, 32)
+        return port.dequantize_int4(packed, scales, w.shape, 32)
+
+    params = {"embed": floats[("embed", -1)], "n_heads": cfg.n_heads, "rope_base": cfg.rope_base, "eps": cfg.eps,
+              "final_norm": np.ones(cfg.dim), "lm_head": deq("lm_head", -1),
+              "layers": [dict({n: deq(n, li) for n in nl.LAYER_WEIGHTS}, attn_norm=np.ones(cfg.dim), ffn_norm=np.ones(cfg.dim))
+                         for li in range(cfg.n_layers)]}
+    seq = np.concatenate([prompt.numpy(), tokens.cpu().numpy()], axis=1)
+    want = no.forward_full(params, seq[:, :-1])                  # logits at every position of the final sequence
+    return model, prompt, tokens.cpu().numpy(), [l.cpu().numpy() for l in logits], want
+
+
+# The bf16 prefill rounds activations and dequantized weights to 8 mantissa bits in each of the eight
+# chained linears; at this model's K = 256..512 a single such linear already needs the small-K bound
+# of the linear tests (4 x TOL_BF16), and that is what the chain is held to.
+@pytest.mark.parametrize("prompt_len,n_new,prefill,tol", [(9, 6, "simt", TOL_FP32), (32, 5, "tc_bf16", 4 * TOL_BF16)])
+def test_greedy_decode_matches_full_recompute(sgq, nl, port, prompt_len, n_new, prefill, tol):
+    path = {"simt": sgq.PATH_SIMT, "tc_bf16": sgq.PATH_TC_BF16}[prefill]
+    model, prompt, tokens, logits, want = tiny_model(nl, port, prompt_len=prompt_len, n_new=n_new, prefill_path=path)
+    assert len(logits) == n_new
+    for s in range(n_new):
+        ref = want[:, prompt_len - 1 + s]
+        assert norm_err(logits[s], ref) <= tol, f"step {s}"
+        top2 = np.sort(ref, axis=-1)[:, -2:]
+        decided = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.max(np.abs(ref))
+        assert (tokens[decided, s] == no.greedy(ref)[decided]).all(), f"token of step {s}"
+    assert sgq.device_status() == 0
+
+
+def test_graph_replay_equals_eager(sgq, nl, port):
+    model, prompt, tokens, _, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT)
+    again = model.generate(prompt, 6, use_graph=True).cpu().numpy()
+    np.testing.assert_array_equal(again, tokens)
+    third = model.generate(prompt, 6, use_graph=True).cpu().numpy()          # the recorded graph is reused
+    np.testing.assert_array_equal(third, tokens)
+    assert model.launches_per_decode_step > 0
