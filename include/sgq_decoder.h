@@ -13,7 +13,7 @@
  *                        nn::RotaryEmbedding tables         include/sovereigngrad/nn.hpp:583-607
  *   sgqd_attn_decode     nn::CausalSelfAttention            include/sovereigngrad/nn.hpp:503-560
  *                        (last row of the causal softmax(q k^T / sqrt(d)) v; the reference has no
- *                        KV cache and recomputes every row, models.hpp:262-300)
+ *                        KV cache and recomputes every row, models.hpp:262-300) + rotary_embedding
  *   sgqd_silu_mul        nn::SwiGLU gate                    include/sovereigngrad/nn.hpp:151-156
  *                        simd::vec_silu                     include/sovereigngrad/simd.hpp:103-108
  *
@@ -45,16 +45,16 @@ SGQ_API int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t
                                const float* cos_table, const float* sin_table, const int32_t* pos0,
                                float* k_cache, float* v_cache, int64_t max_seq, void* stream);
 
-/* Bytes of scratch sgqd_attn_decode needs (256-byte aligned). */
-SGQ_API size_t sgqd_attn_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq);
-
-/* One query per (sequence, head) against the first *pos0 + 1 cache positions (call after
- * sgqd_rope_kv_store of the same token): out[b, h*head_dim + d] = sum_t softmax_t(q.k_t /
- * sqrt(head_dim)) v_t.  q is read from qkv rows of stride q_stride floats (the rotated query part).
- * head_dim must be 64 or 128. */
-SGQ_API int sgqd_attn_decode(const float* q, int64_t q_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
-                             const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0,
-                             float* out, int64_t out_stride, void* workspace, size_t workspace_bytes, void* stream);
+/* One decode step of attention for one NEW token per sequence, fused with that token's rotary
+ * embedding and cache append.  qkv[batch, qkv_stride] holds the un-rotated query, key and value of
+ * the token at position *pos0 (same layout as above, t_new = 1; qkv is not modified).  The kernel
+ * rotates q and k, appends k and v to the caches at position *pos0, and writes
+ *   out[b, h*head_dim + d] = sum_{t <= pos0} softmax_t(q . k_t / sqrt(head_dim)) v_t[d].
+ * Do not call sgqd_rope_kv_store for the same token.  If *pos0 is outside [0, max_seq) nothing is
+ * stored and the query attends to the cache contents only.  head_dim must be 64 or 128. */
+SGQ_API int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
+                             const float* cos_table, const float* sin_table, float* k_cache, float* v_cache,
+                             int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* stream);
 
 /* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up. */
 SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream);

@@ -35,8 +35,7 @@ EXPORTS = [
 ]
 
 # every symbol include/sgq_decoder.h declares
-DECODER_EXPORTS = ["sgqd_add_rmsnorm", "sgqd_rope_kv_store", "sgqd_attn_decode_workspace_bytes", "sgqd_attn_decode",
-                   "sgqd_silu_mul"]
+DECODER_EXPORTS = ["sgqd_add_rmsnorm", "sgqd_rope_kv_store", "sgqd_attn_decode", "sgqd_silu_mul"]
 
 
 class SgqError(RuntimeError):
@@ -73,9 +72,7 @@ def _load() -> C.CDLL:
     lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
     lib.sgqd_add_rmsnorm.argtypes = [p, p, p, C.c_float, i64, i64, p, p]
     lib.sgqd_rope_kv_store.argtypes = [p, i64, i64, i64, i64, p, p, p, p, p, i64, p]
-    lib.sgqd_attn_decode_workspace_bytes.restype = sz
-    lib.sgqd_attn_decode_workspace_bytes.argtypes = [i64, i64, i64, i64]
-    lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, i64, p, p, i64, p, sz, p]
+    lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, p, p, i64, p, p, i64, p]
     lib.sgqd_silu_mul.argtypes = [p, i64, i64, p, p]
     return lib
 

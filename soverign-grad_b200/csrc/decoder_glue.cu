@@ -7,6 +7,7 @@
 
 #include "../../include/sgq_decoder.h"
 
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 namespace sgq {
@@ -105,67 +106,93 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ 
 }
 
 constexpr int kAttnWarps = 8;
-constexpr int kKeysPerIter = 8;
+constexpr int kKeysPerIter = 4;
+constexpr int kAttnCtasPerSm = 4;      // 256 threads x <= 64 registers
 
-// grid (batch * n_heads, splits).  Each warp walks its keys eight at a time (eight independent
-// 512-byte row loads in flight per warp), keeps a running max / sum / weighted value (online
-// softmax) and the warps, then the splits, are merged with the usual exp(m_i - M) weights.  The
-// last split to finish a (sequence, head) — found with a ticket, no waiting — writes the output.
+// Rotary pair (d, d + HD/2) when a warp holds one head with VEC consecutive elements per lane:
+// lane l < 16 holds x1 of the pairs whose x2 sits in lane l + 16.  src/ops.cpp:1737-1738.
+template <int VEC>
+__device__ __forceinline__ void rope_lanes(float (&v)[VEC], const float* cos_row, const float* sin_row, int lane) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        const float c = cos_row[(lane & 15) * VEC + j], s = sin_row[(lane & 15) * VEC + j];
+        v[j] = (lane < 16) ? v[j] * c - other * s : v[j] * c + other * s;
+    }
+}
+
+// Decode attention of one new token per sequence, fused with its rotary embedding and KV-cache
+// store.  grid (batch * n_heads, S) launched as clusters of S CTAs: the S CTAs of a cluster split
+// the cache positions [0, pos) of one (sequence, head); the last one also takes the new token,
+// whose rotated key and value come straight from the qkv row (and are appended to the cache for
+// later steps).  Each warp walks its keys four at a time with K and V rows loaded together, keeps
+// a running max / sum / weighted value (online softmax); warps are merged through shared memory
+// and the CTAs of the cluster through distributed shared memory, rank 0 writing the output.
 template <int HD>
-__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* __restrict__ q, int64_t q_stride, int n_heads,
-                                                                      const float* __restrict__ kc, const float* __restrict__ vc,
-                                                                      int64_t max_seq, const int32_t* __restrict__ pos0,
-                                                                      float* __restrict__ out, int64_t out_stride,
-                                                                      float* __restrict__ part, unsigned int* __restrict__ tickets) {
+__global__ void __launch_bounds__(kAttnWarps * 32, kAttnCtasPerSm)
+attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_heads, const float* __restrict__ cos_t,
+                   const float* __restrict__ sin_t, float* __restrict__ kc, float* __restrict__ vc, int64_t max_seq,
+                   const int32_t* __restrict__ pos0, float* __restrict__ out, int64_t out_stride) {
     constexpr int VEC = HD / 32;
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
     __shared__ float sm_acc[kAttnWarps][HD];
-    __shared__ unsigned int sm_ticket;
+    __shared__ float sm_part[HD + 2];                      // this CTA's (max, sum, weighted value), read by rank 0
     const int bh = blockIdx.x, split = blockIdx.y, S = gridDim.y;
     const int b = bh / n_heads, h = bh - b * n_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int64_t len = static_cast<int64_t>(*pos0) + 1;
-    len = len < 1 ? 1 : (len > max_seq ? max_seq : len);
-    const int64_t chunk = (len + S - 1) / S;
+    int64_t pos = static_cast<int64_t>(*pos0);
+    const bool in_range = pos >= 0 && pos < max_seq;       // else: attend to the cache only, store nothing
+    pos = pos < 0 ? 0 : (pos > max_seq ? max_seq : pos);
+    const int64_t chunk = (pos + S - 1) / S;
     const int64_t t0 = split * chunk;
-    const int64_t t1 = (t0 + chunk < len) ? t0 + chunk : len;
+    const int64_t t1 = (t0 + chunk < pos) ? t0 + chunk : pos;
+    const int64_t dim = static_cast<int64_t>(n_heads) * HD;
 
-    const float scale = rsqrtf(static_cast<float>(HD));
+    const float* row = qkv + static_cast<int64_t>(b) * qkv_stride + h * HD + lane * VEC;
+    const float* cos_row = cos_t + (in_range ? pos : 0) * (HD / 2);
+    const float* sin_row = sin_t + (in_range ? pos : 0) * (HD / 2);
     float qv[VEC];
-    {
-        const float* qp = q + static_cast<int64_t>(b) * q_stride + h * HD + lane * VEC;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) qv[j] = qp[j] * scale;
-    }
-    const float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
-    const float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
+    for (int j = 0; j < VEC; ++j) qv[j] = row[j];
+    rope_lanes<VEC>(qv, cos_row, sin_row, lane);
+    const float scale = rsqrtf(static_cast<float>(HD));
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) qv[j] *= scale;
+
+    float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
+    float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
 
     float m = -CUDART_INF_F, l = 0.f, acc[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
 
     for (int64_t t = t0 + warp * kKeysPerIter; t < t1; t += kAttnWarps * kKeysPerIter) {
-        float s[kKeysPerIter];
+        float kk[kKeysPerIter][VEC], vv[kKeysPerIter][VEC], s[kKeysPerIter];
 #pragma unroll
         for (int i = 0; i < kKeysPerIter; ++i) {
-            float d = 0.f;
-            if (t + i < t1) {
-                const float* kp = kb + (t + i) * HD;
-                if constexpr (VEC == 4) {
-                    const float4 kk = *reinterpret_cast<const float4*>(kp);
-                    d = qv[0] * kk.x + qv[1] * kk.y + qv[2] * kk.z + qv[3] * kk.w;
-                } else {
-                    const float2 kk = *reinterpret_cast<const float2*>(kp);
-                    d = qv[0] * kk.x + qv[1] * kk.y;
-                }
+            const int64_t tt = (t + i < t1) ? t + i : t1 - 1;          // clamped: the tail reloads a valid row
+            if constexpr (VEC == 4) {
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(kb + tt * HD));
+                const float4 c = __ldcs(reinterpret_cast<const float4*>(vb + tt * HD));
+                kk[i][0] = a.x; kk[i][1] = a.y; kk[i][2] = a.z; kk[i][3] = a.w;
+                vv[i][0] = c.x; vv[i][1] = c.y; vv[i][2] = c.z; vv[i][3] = c.w;
+            } else {
+                const float2 a = __ldcs(reinterpret_cast<const float2*>(kb + tt * HD));
+                const float2 c = __ldcs(reinterpret_cast<const float2*>(vb + tt * HD));
+                kk[i][0] = a.x; kk[i][1] = a.y;
+                vv[i][0] = c.x; vv[i][1] = c.y;
             }
-            s[i] = d;
         }
         float mx = m;
 #pragma unroll
         for (int i = 0; i < kKeysPerIter; ++i) {
-            s[i] = warp_sum(s[i]);
-            if (t + i >= t1) s[i] = -CUDART_INF_F;
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) d = fmaf(qv[j], kk[i][j], d);
+            d = warp_sum(d);
+            s[i] = (t + i < t1) ? d : -CUDART_INF_F;
             mx = fmaxf(mx, s[i]);
         }
         const float corr = expf(m - mx);                    // m = -inf on the first pass: exp(-inf) = 0
@@ -174,21 +201,34 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const floa
         for (int j = 0; j < VEC; ++j) acc[j] *= corr;
 #pragma unroll
         for (int i = 0; i < kKeysPerIter; ++i) {
-            if (t + i < t1) {
-                const float p = expf(s[i] - mx);
-                l += p;
-                const float* vp = vb + (t + i) * HD;
-                if constexpr (VEC == 4) {
-                    const float4 vv = *reinterpret_cast<const float4*>(vp);
-                    acc[0] = fmaf(p, vv.x, acc[0]); acc[1] = fmaf(p, vv.y, acc[1]);
-                    acc[2] = fmaf(p, vv.z, acc[2]); acc[3] = fmaf(p, vv.w, acc[3]);
-                } else {
-                    const float2 vv = *reinterpret_cast<const float2*>(vp);
-                    acc[0] = fmaf(p, vv.x, acc[0]); acc[1] = fmaf(p, vv.y, acc[1]);
-                }
-            }
+            const float p = expf(s[i] - mx);                // 0 for the clamped tail
+            l += p;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[j] = fmaf(p, vv[i][j], acc[j]);
         }
         m = mx;
+    }
+
+    // the new token: warp 0 of the last split rotates its key, appends key and value to the cache
+    if (split == S - 1 && warp == 0) {
+        float kn[VEC], vn[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { kn[j] = row[dim + j]; vn[j] = row[2 * dim + j]; }
+        rope_lanes<VEC>(kn, cos_row, sin_row, lane);
+        if (in_range) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) { kb[pos * HD + j] = kn[j]; vb[pos * HD + j] = vn[j]; }
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) d = fmaf(qv[j], kn[j], d);
+            d = warp_sum(d);
+            const float mx = fmaxf(m, d);
+            const float corr = expf(m - mx), p = expf(d - mx);
+            l = l * corr + p;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[j] = fmaf(p, vn[j], acc[j] * corr);
+            m = mx;
+        }
     }
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
@@ -196,8 +236,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const floa
     __syncthreads();
 
     // merge the warps: thread d < HD owns output element d
-    float M = -CUDART_INF_F, L = 0.f, A = 0.f;
     if (threadIdx.x < HD) {
+        float M = -CUDART_INF_F, L = 0.f, A = 0.f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
 #pragma unroll
@@ -206,36 +246,25 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const floa
             L = fmaf(sm_l[w], wgt, L);
             A = fmaf(sm_acc[w][threadIdx.x], wgt, A);
         }
+        sm_part[2 + threadIdx.x] = A;
+        if (threadIdx.x == 0) { sm_part[0] = M; sm_part[1] = L; }
     }
-    float* orow = out + static_cast<int64_t>(b) * out_stride + h * HD;
-    if (S == 1) {
-        if (threadIdx.x < HD) orow[threadIdx.x] = A / L;
-        return;
-    }
-    float* mine = part + (static_cast<int64_t>(bh) * S + split) * (HD + 2);
-    if (threadIdx.x < HD) {
-        mine[2 + threadIdx.x] = A;
-        if (threadIdx.x == 0) { mine[0] = M; mine[1] = L; }
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) sm_ticket = atomicAdd(&tickets[bh], 1u);
-    __syncthreads();
-    if (sm_ticket != static_cast<unsigned int>(S - 1)) return;
-    __threadfence();
-    if (threadIdx.x < HD) {
-        const float* base = part + static_cast<int64_t>(bh) * S * (HD + 2);
+    cluster.sync();                                        // every CTA's partial result is in its shared memory
+    if (cluster.block_rank() == 0 && threadIdx.x < HD) {
         float MM = -CUDART_INF_F;
-        for (int s2 = 0; s2 < S; ++s2) MM = fmaxf(MM, __ldcg(base + s2 * (HD + 2)));
+        for (int r = 0; r < S; ++r) MM = fmaxf(MM, cluster.map_shared_rank(sm_part, r)[0]);
         float LL = 0.f, AA = 0.f;
-        for (int s2 = 0; s2 < S; ++s2) {
-            const float ms = __ldcg(base + s2 * (HD + 2));
+        for (int r = 0; r < S; ++r) {
+            const float* rp = cluster.map_shared_rank(sm_part, r);
+            const float ms = rp[0];
             const float wgt = (ms == -CUDART_INF_F) ? 0.f : expf(ms - MM);
-            LL = fmaf(__ldcg(base + s2 * (HD + 2) + 1), wgt, LL);
-            AA = fmaf(__ldcg(base + s2 * (HD + 2) + 2 + threadIdx.x), wgt, AA);
+            LL = fmaf(rp[1], wgt, LL);
+            AA = fmaf(rp[2 + threadIdx.x], wgt, AA);
         }
-        orow[threadIdx.x] = AA / LL;
+        // LL > 0 whenever there is at least one key; an out-of-range position with an empty cache yields 0
+        out[static_cast<int64_t>(b) * out_stride + h * HD + threadIdx.x] = LL > 0.f ? AA / LL : 0.f;
     }
+    cluster.sync();                                        // keep shared memory alive until rank 0 has read it
 }
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gu, int64_t rows, int64_t hidden,
@@ -249,18 +278,36 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 }
 
 int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
+    // as many splits as keep every CTA resident at once (one wave), at least 32 keys each, at most
+    // the portable cluster size
     const int64_t bh = batch * n_heads > 0 ? batch * n_heads : 1;
-    int64_t s = ceil_div(4 * 148, bh);
-    const int64_t cap = ceil_div(max_seq, 64);
+    int64_t s = (static_cast<int64_t>(kAttnCtasPerSm) * sm_count()) / bh;
+    const int64_t cap = ceil_div(max_seq, 32);
     if (s > cap) s = cap;
     if (s > 8) s = 8;
     if (s < 1) s = 1;
     return static_cast<int>(s);
 }
 
-size_t attn_part_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq) {
-    const size_t part = static_cast<size_t>(batch * n_heads) * attn_splits(batch, n_heads, max_seq) * (head_dim + 2) * sizeof(float);
-    return (part + 255) & ~static_cast<size_t>(255);
+template <int HD>
+int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads, const float* cos_t, const float* sin_t, float* kc,
+                float* vc, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, cudaStream_t s) {
+    const int S = attn_splits(batch, n_heads, max_seq);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(batch * n_heads), static_cast<unsigned>(S), 1);
+    cfg.blockDim = dim3(kAttnWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(S);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0, out,
+                                    out_stride));
+    return SGQ_OK;
 }
 
 }  // namespace
@@ -302,37 +349,24 @@ int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t n_heads
     return SGQ_OK;
 }
 
-size_t sgqd_attn_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t head_dim, int64_t max_seq) {
-    if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
-    return attn_part_bytes(batch, n_heads, head_dim, max_seq) + ((static_cast<size_t>(batch * n_heads) * 4 + 255) & ~static_cast<size_t>(255));
-}
-
-int sgqd_attn_decode(const float* q, int64_t q_stride, int64_t batch, int64_t n_heads, int64_t head_dim, const float* k_cache,
-                     const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* workspace,
-                     size_t workspace_bytes, void* stream) {
+int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim, const float* cos_table,
+                     const float* sin_table, float* k_cache, float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
+                     int64_t out_stride, void* stream) {
     if (batch < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
     if (head_dim != 64 && head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
-    if (q_stride < n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride < n_heads * head_dim");
+    if (qkv_stride < 3 * n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride too small");
     if (batch == 0) return SGQ_OK;
-    if (!q || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
-    if (!aligned(q, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || (q_stride & 3)) return bad(SGQ_ERR_ALIGNMENT, "q / caches must be 16-byte aligned");
-    const size_t need = sgqd_attn_decode_workspace_bytes(batch, n_heads, head_dim, max_seq);
-    if (!workspace || workspace_bytes < need || !aligned(workspace, 256)) return bad(SGQ_ERR_WORKSPACE, "attention workspace missing, too small or not 256-byte aligned");
+    if (!qkv || !cos_table || !sin_table || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (!aligned(qkv, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || (qkv_stride & 3))
+        return bad(SGQ_ERR_ALIGNMENT, "qkv rows and caches must be 16-byte aligned");
     int rc = check_device();
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t part_bytes = attn_part_bytes(batch, n_heads, head_dim, max_seq);
-    float* part = static_cast<float*>(workspace);
-    unsigned int* tickets = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + part_bytes);
-    const int S = attn_splits(batch, n_heads, max_seq);
-    if (S > 1) SGQ_CUDA_TRY(cudaMemsetAsync(tickets, 0, static_cast<size_t>(batch * n_heads) * 4, s));
-    const dim3 grid(static_cast<unsigned>(batch * n_heads), static_cast<unsigned>(S));
     if (head_dim == 128)
-        attn_decode_kernel<128><<<grid, kAttnWarps * 32, 0, s>>>(q, q_stride, static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride, part, tickets);
-    else
-        attn_decode_kernel<64><<<grid, kAttnWarps * 32, 0, s>>>(q, q_stride, static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride, part, tickets);
-    SGQ_LAUNCH_CHECK("attn_decode_kernel");
-    return SGQ_OK;
+        return launch_attn<128>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0,
+                                out, out_stride, s);
+    return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0, out,
+                           out_stride, s);
 }
 
 int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream) {

@@ -140,8 +140,6 @@ class NanoLlamaInt4:
         self.k_cache = torch.zeros(shape, device=dev)
         self.v_cache = torch.zeros(shape, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
-        nb = int(lib.sgqd_attn_decode_workspace_bytes(batch, self.h_local, hd, cfg.max_seq))
-        self.attn_ws = torch.empty(max(nb, 256), dtype=torch.uint8, device=dev)
         self._bufs = {}
         self._graph = None
         self.tok = torch.zeros(batch, dtype=torch.int64, device=dev)
@@ -200,15 +198,15 @@ class NanoLlamaInt4:
             self._add_rmsnorm(h, delta, L["attn_norm"], n)
             self._linear(L["qkv"], n, b["qkv"], path)
             kc, vc = self.k_cache[li], self.v_cache[li]
-            check(lib.sgqd_rope_kv_store(_ptr(b["qkv"]), B, t_new, self.h_local, c.head_dim, _ptr(self.cos), _ptr(self.sin),
-                                         _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
-            self._count()
-            if t_new == 1:
-                check(lib.sgqd_attn_decode(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(kc), _ptr(vc),
-                                           c.max_seq, _ptr(self.pos), _ptr(b["attn"]), self.dim_local, _ptr(self.attn_ws),
-                                           self.attn_ws.numel(), _stream()), "sgqd_attn_decode")
+            if t_new == 1:       # rotary embedding, cache append and attention of the new token in one kernel
+                check(lib.sgqd_attn_decode(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(self.cos),
+                                           _ptr(self.sin), _ptr(kc), _ptr(vc), c.max_seq, _ptr(self.pos), _ptr(b["attn"]),
+                                           self.dim_local, _stream()), "sgqd_attn_decode")
                 self._count()
             else:
+                check(lib.sgqd_rope_kv_store(_ptr(b["qkv"]), B, t_new, self.h_local, c.head_dim, _ptr(self.cos), _ptr(self.sin),
+                                             _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
+                self._count()
                 self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"])
             attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"))
             self._linear(L["wo"], attn, b["o"], path)

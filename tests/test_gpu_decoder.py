@@ -102,28 +102,52 @@ def test_rope_kv_store(sgq, B, T, H, hd, pos0, max_seq):
 
 
 @pytest.mark.parametrize("B,H,hd,length,max_seq", [(1, 1, 128, 1, 8), (2, 2, 128, 7, 64), (8, 16, 128, 130, 640),
-                                                   (8, 16, 128, 640, 640), (3, 5, 64, 333, 512), (40, 32, 64, 100, 128)])
+                                                   (8, 16, 128, 640, 640), (3, 5, 64, 333, 512), (40, 32, 64, 100, 128),
+                                                   (8, 2, 128, 513, 640)])
 def test_attn_decode(sgq, B, H, hd, length, max_seq):
+    """`length` counts the new token: the cache holds length - 1 rotated keys, the kernel rotates and
+    appends the new one at position length - 1 and attends to all of them."""
     r = np.random.default_rng(length * 3 + hd)
-    dim = H * hd
+    dim, pos0 = H * hd, length - 1
     qkv = r.standard_normal((B, 3 * dim)).astype(np.float32)
     kc = (r.standard_normal((B, H, max_seq, hd)) * 1.5).astype(np.float32)
     vc = r.standard_normal((B, H, max_seq, hd)).astype(np.float32)
-    pos = torch.tensor([length - 1], dtype=torch.int32, device="cuda")
-    nb = int(sgq.lib.sgqd_attn_decode_workspace_bytes(B, H, hd, max_seq))
-    ws = torch.empty(max(nb, 256), dtype=torch.uint8, device="cuda")
+    cos, sin = no.rope_tables(hd, max_seq)
+    pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
     out = torch.empty(B, dim, device="cuda")
-    qt, kt, vt = dev(qkv), dev(kc), dev(vc)
-    for _ in range(2):                                         # twice: the ticket counters are re-armed per call
-        sgq.check(sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, ptr(ws),
-                                           ws.numel(), stream()))
-    q = qkv[:, :dim].reshape(B, H, 1, hd).astype(np.float64)
-    k, v = kc[:, :, :length].astype(np.float64), vc[:, :, :length].astype(np.float64)
+    qt, kt, vt, ct, st = dev(qkv), dev(kc), dev(vc), dev(cos), dev(sin)
+    for _ in range(2):                                         # a second call over the already appended row changes nothing
+        sgq.check(sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out),
+                                           dim, stream()))
+    q = no.rope(qkv[:, :dim].reshape(B, H, 1, hd), cos, sin, [pos0])
+    k_new = no.rope(qkv[:, dim:2 * dim].reshape(B, H, 1, hd), cos, sin, [pos0])
+    v_new = qkv[:, 2 * dim:].reshape(B, H, 1, hd)
+    k = np.concatenate([kc[:, :, :pos0].astype(np.float64), k_new], axis=2)
+    v = np.concatenate([vc[:, :, :pos0].astype(np.float64), v_new], axis=2)
     p = no.softmax(np.einsum("bhqd,bhtd->bhqt", q, k) / np.sqrt(hd))
     want = np.einsum("bhqt,bhtd->bhqd", p, v).reshape(B, dim)
     assert norm_err(out.cpu().numpy(), want) <= 5e-6
-    assert sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, None, 0,
-                                    stream()) == 5             # workspace missing
+    kcn, vcn = kt.cpu().numpy(), vt.cpu().numpy()
+    assert norm_err(kcn[:, :, pos0], k_new[:, :, 0]) <= 2e-6                      # appended rows
+    np.testing.assert_array_equal(vcn[:, :, pos0], v_new[:, :, 0])
+    keep = np.arange(max_seq) != pos0
+    np.testing.assert_array_equal(kcn[:, :, keep], kc[:, :, keep])                # everything else untouched
+    np.testing.assert_array_equal(vcn[:, :, keep], vc[:, :, keep])
+    np.testing.assert_array_equal(qt.cpu().numpy(), qkv)                          # qkv is read only
+
+
+def test_attn_decode_position_out_of_range_stores_nothing(sgq):
+    B, H, hd, max_seq = 2, 2, 128, 16
+    r = np.random.default_rng(5)
+    qkv, kc, vc = (dev(r.standard_normal(s).astype(np.float32)) for s in ((B, 3 * H * hd), (B, H, max_seq, hd), (B, H, max_seq, hd)))
+    cos, sin = (dev(t) for t in no.rope_tables(hd, max_seq))
+    k0, v0 = kc.clone(), vc.clone()
+    out = torch.empty(B, H * hd, device="cuda")
+    pos = torch.tensor([max_seq], dtype=torch.int32, device="cuda")
+    sgq.check(sgq.lib.sgqd_attn_decode(ptr(qkv), 3 * H * hd, B, H, hd, ptr(cos), ptr(sin), ptr(kc), ptr(vc), max_seq, ptr(pos), ptr(out),
+                                       H * hd, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(kc, k0) and torch.equal(vc, v0) and torch.isfinite(out).all()
 
 
 # ---- the whole model ------------------------------------------------------------------------------
