@@ -134,6 +134,22 @@ SGQ_API int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, con
                     int layout, int scheme, const float* bias, float* y, int64_t ldy, int path, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Prepared activations: the decode kernel's own operand format (int8 digit planes of the
+ * activations with one power-of-two scale per row).  (No counterpart in the reference.)  A decode
+ * forward normally converts x on the fly; a caller that runs several linears on the same x, or
+ * whose previous operator can emit the format directly (sgq_decoder.h), converts once and calls
+ * sgq_linear_int4_prepared, which computes exactly what sgq_linear_int4(..., SGQ_LAYOUT_NK,
+ * group 32, SGQ_PATH_GEMV) computes for that x.  The format is opaque, depends on (M, K) and is
+ * only valid for the library build that wrote it.
+ *   sgq_prepared_x_bytes  bytes of the prepared form of x[M, K]; 0 when there is none (it needs
+ *                         1 <= M <= 16, K % 256 == 0 and planes that fit in shared memory)
+ *   sgq_prepare_x         x[M, K] fp32 (16-byte aligned) -> prepared (256-byte aligned) */
+SGQ_API size_t sgq_prepared_x_bytes(int64_t M, int64_t K);
+SGQ_API int sgq_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, size_t prepared_bytes, void* stream);
+SGQ_API int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes, int64_t M, int64_t K, int64_t N,
+                                     const uint8_t* packed, const float* scales, const float* bias, float* y,
+                                     int64_t ldy, void* stream);
+
 /* Decode forward for callers that cannot allocate device memory.  (No counterpart in the
  * reference: there every call allocates its temporaries through MemoryAllocator.)
  *

@@ -30,9 +30,11 @@ extern "C" {
 #endif
 
 /* h[rows, dim] += delta (skipped when delta is NULL), then out = h * rsqrt(mean(h^2) + eps) * gamma.
- * h is updated in place: it is the residual stream.  out may not alias h. */
+ * h is updated in place: it is the residual stream.  out may not alias h.
+ * prepared_out (optional, NULL to skip): also writes out in the prepared-activation format of
+ * sgq.h (sgq_prepared_x_bytes(rows, dim) bytes, 256-byte aligned) for sgq_linear_int4_prepared. */
 SGQ_API int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps, int64_t rows, int64_t dim,
-                             float* out, void* stream);
+                             float* out, void* prepared_out, size_t prepared_bytes, void* stream);
 
 /* qkv[batch * t_new, 3 * n_heads * head_dim] holds, per token, the query, key and value rows of
  * n_heads heads (token m = b * t_new + i is the i-th new token of sequence b, at position
@@ -56,8 +58,10 @@ SGQ_API int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int6
                              const float* cos_table, const float* sin_table, float* k_cache, float* v_cache,
                              int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* stream);
 
-/* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up. */
-SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream);
+/* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up.
+ * prepared_out: as for sgqd_add_rmsnorm, the prepared form of out[rows, hidden]. */
+SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out,
+                          size_t prepared_bytes, void* stream);
 
 #ifdef __cplusplus
 }

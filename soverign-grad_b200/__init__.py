@@ -32,6 +32,7 @@ EXPORTS = [
     "sgq_codes_to_f32_int8", "sgq_codes_to_f32_int4", "sgq_codes_from_f32_int8", "sgq_codes_from_f32_int4",
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
+    "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared",
 ]
 
 # every symbol include/sgq_decoder.h declares
@@ -70,10 +71,14 @@ def _load() -> C.CDLL:
     lib.sgq_linear_w8a8.argtypes = [p, i64, i64, i64, p, p, i32, p, p, i64, p, p, p, p, sz, p]
     lib.sgq_interleave_slices.argtypes = [p, i64, i64, i64, p, i64, p]
     lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
-    lib.sgqd_add_rmsnorm.argtypes = [p, p, p, C.c_float, i64, i64, p, p]
+    lib.sgq_prepared_x_bytes.restype = sz
+    lib.sgq_prepared_x_bytes.argtypes = [i64, i64]
+    lib.sgq_prepare_x.argtypes = [p, i64, i64, p, sz, p]
+    lib.sgq_linear_int4_prepared.argtypes = [p, sz, i64, i64, i64, p, p, p, p, i64, p]
+    lib.sgqd_add_rmsnorm.argtypes = [p, p, p, C.c_float, i64, i64, p, p, sz, p]
     lib.sgqd_rope_kv_store.argtypes = [p, i64, i64, i64, i64, p, p, p, p, p, i64, p]
     lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, p, p, i64, p, p, i64, p]
-    lib.sgqd_silu_mul.argtypes = [p, i64, i64, p, p]
+    lib.sgqd_silu_mul.argtypes = [p, i64, i64, p, p, sz, p]
     return lib
 
 
@@ -240,6 +245,35 @@ def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: Optional[torch.T
         rc = lib.sgq_linear_int8(_ptr(x), M, K, N, _ptr(q.qdata), _ptr(q.scales), layout,
                                  PER_TENSOR if per_tensor else PER_ROW, _ptr(b), _ptr(out), ldy, path, wsp, wsb, _stream())
     check(rc, "sgq_linear")
+    return out
+
+
+def prepared_x_bytes(M: int, K: int) -> int:
+    """Bytes of the decode kernel's prepared form of x[M, K]; 0 when this shape has none."""
+    return int(lib.sgq_prepared_x_bytes(M, K))
+
+
+def prepare_x(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[M, K] fp32 -> prepared activations (an opaque uint8 buffer) for linear_int4_prepared."""
+    x = _f32_cuda(x)
+    M, K = x.shape
+    nb = prepared_x_bytes(M, K)
+    if nb == 0:
+        raise SgqError(4, "prepare_x", "no prepared form for this shape (M <= 16, K % 256 == 0)")
+    if out is None:
+        out = torch.empty(nb, dtype=torch.uint8, device=x.device)
+    check(lib.sgq_prepare_x(_ptr(x), M, K, _ptr(out), out.numel(), _stream()), "sgq_prepare_x")
+    return out
+
+
+def linear_int4_prepared(prepared: torch.Tensor, M: int, q: QuantizedTensor, bias: Optional[torch.Tensor] = None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode forward of an INT4 g=32 weight stored [N, K] on activations already in prepared form."""
+    N, K = q.original_shape
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=prepared.device)
+    check(lib.sgq_linear_int4_prepared(_ptr(prepared), prepared.numel(), M, K, N, _ptr(q.qdata), _ptr(q.scales), _ptr(bias), _ptr(out),
+                                       out.stride(0), _stream()), "sgq_linear_int4_prepared")
     return out
 
 

@@ -324,6 +324,40 @@ int sgq_linear_w8a8(const float* x, int64_t M, int64_t K, int64_t N, const int8_
     return launch_linear_w8a8(a, xq_out, sx_out, acc_out);
 }
 
+size_t sgq_prepared_x_bytes(int64_t M, int64_t K) { return gemv_prepared_bytes(M, K); }
+
+int sgq_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, size_t prepared_bytes, void* stream) {
+    if (M < 0 || K < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (M == 0) return SGQ_OK;
+    const size_t need = gemv_prepared_bytes(M, K);
+    if (need == 0) return bad(SGQ_ERR_UNSUPPORTED, "no prepared-activation form for this (M, K): M <= 16, K % 256 == 0");
+    if (!x || !prepared) return bad(SGQ_ERR_NULL_POINTER, "x or prepared is NULL");
+    if (prepared_bytes < need || !aligned(prepared, 256)) return bad(SGQ_ERR_WORKSPACE, "prepared buffer too small or not 256-byte aligned");
+    if (!aligned(x, 16)) return bad(SGQ_ERR_ALIGNMENT, "x must be 16-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    return launch_prepare_x(x, M, K, prepared, static_cast<cudaStream_t>(stream));
+}
+
+int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes, int64_t M, int64_t K, int64_t N, const uint8_t* packed,
+                             const float* scales, const float* bias, float* y, int64_t ldy, void* stream) {
+    if (M < 0 || K < 0 || N < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
+    if (ldy < N) return bad(SGQ_ERR_BAD_SHAPE, "ldy < N");
+    if (M == 0 || N == 0) return SGQ_OK;
+    const size_t need = gemv_prepared_bytes(M, K);
+    if (need == 0) return bad(SGQ_ERR_UNSUPPORTED, "no prepared-activation form for this (M, K): M <= 16, K % 256 == 0");
+    if (!prepared || !packed || !scales || !y) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (prepared_bytes < need || !aligned(prepared, 256)) return bad(SGQ_ERR_WORKSPACE, "prepared buffer too small or not 256-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    LinearArgs a = {};
+    a.x = nullptr; a.M = M; a.K = K; a.N = N; a.wq = packed; a.scales = scales; a.bits = 4; a.layout = SGQ_LAYOUT_NK;
+    a.group = 32; a.scheme = 0; a.bias = bias; a.y = y; a.ldy = ldy;
+    a.workspace = const_cast<void*>(prepared); a.workspace_bytes = prepared_bytes;
+    a.stream = static_cast<cudaStream_t>(stream);
+    return launch_linear_gemv_prepared(a);
+}
+
 int sgq_interleave_slices(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,
                           void* stream) {
     if (world < 0 || M < 0 || n_local < 0 || ldd < world * n_local) return bad(SGQ_ERR_BAD_SHAPE, "bad slice shape");

@@ -4,6 +4,7 @@
 // spin anywhere in this file.  The position in the cache is read from device memory so that a
 // recorded CUDA graph of a decode step stays valid from step to step.
 #include "sgq_common.cuh"
+#include "gemv_prepare.cuh"
 
 #include "../../include/sgq_decoder.h"
 
@@ -21,12 +22,25 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Block-wide maximum, known to every thread afterwards.  `red` holds THREADS / 32 floats.
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    __syncthreads();                                   // red may still be read by an earlier reduction
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[(threadIdx.x & 31) < THREADS / 32 ? (threadIdx.x & 31) : 0];
+    return warp_max(t);
+}
+
 // One block per row.  Pass 1 adds the delta into the residual stream and accumulates the sum of
 // squares; pass 2 re-reads the row (L1/L2) and scales it.  The reference sums the squares of a row
 // sequentially in fp32 (src/ops.cpp:1546-1550); a tree sum differs from it by a few ulps.
+// PREP: the normalised row is also converted to the decode kernel's prepared-activation format.
+template <bool PREP>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                   const float* __restrict__ gamma, float eps, int64_t dim,
-                                                                  float* __restrict__ out) {
+                                                                  float* out, int ndigits, int nsets, uint8_t* planes) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float inv_rms_s;
     float* hr = h + blockIdx.x * dim;
@@ -60,6 +74,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
     }
     __syncthreads();      // also orders this thread block's writes of h before the re-read below
     const float inv = inv_rms_s;
+    float amax = 0.f;
     if ((dim & 3) == 0) {
         for (int64_t i = threadIdx.x * 4; i < dim; i += kNormThreads * 4) {
             const float4 v = *reinterpret_cast<const float4*>(hr + i);
@@ -67,9 +82,14 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
             float4 o;
             o.x = v.x * inv * g.x; o.y = v.y * inv * g.y; o.z = v.z * inv * g.z; o.w = v.w * inv * g.w;
             *reinterpret_cast<float4*>(orow + i) = o;
+            if (PREP) amax = fmaxf(fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y))), fmaxf(fabsf(o.z), fabsf(o.w)));
         }
     } else {
         for (int64_t i = threadIdx.x; i < dim; i += kNormThreads) orow[i] = hr[i] * inv * gamma[i];
+    }
+    if (PREP) {
+        const float all = block_max<kNormThreads>(amax, red);      // its barriers also publish this block's stores of orow
+        prepare_row_block<kNormThreads>(orow, all, blockIdx.x, dim, ndigits, nsets, planes);
     }
 }
 
@@ -277,6 +297,27 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
     }
 }
 
+// One block per row; also converts the row to the decode kernel's prepared-activation format.
+__global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const float* __restrict__ gu, int64_t hidden, float* out,
+                                                                       int ndigits, int nsets, uint8_t* planes) {
+    __shared__ float red[kNormThreads / 32];
+    const float* g = gu + blockIdx.x * 2 * hidden;
+    const float* u = g + hidden;
+    float* orow = out + blockIdx.x * hidden;
+    float amax = 0.f;
+    for (int64_t i = threadIdx.x * 4; i < hidden; i += kNormThreads * 4) {
+        const float4 a = *reinterpret_cast<const float4*>(g + i);
+        const float4 b = *reinterpret_cast<const float4*>(u + i);
+        float4 o;
+        o.x = a.x / (1.0f + expf(-a.x)) * b.x; o.y = a.y / (1.0f + expf(-a.y)) * b.y;
+        o.z = a.z / (1.0f + expf(-a.z)) * b.z; o.w = a.w / (1.0f + expf(-a.w)) * b.w;
+        *reinterpret_cast<float4*>(orow + i) = o;
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y))), fmaxf(fabsf(o.z), fabsf(o.w)));
+    }
+    const float all = block_max<kNormThreads>(amax, red);
+    prepare_row_block<kNormThreads>(orow, all, blockIdx.x, hidden, ndigits, nsets, planes);
+}
+
 int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
     // as many splits as keep every CTA resident at once (one wave), at least 32 keys each, at most
     // the portable cluster size
@@ -317,17 +358,37 @@ using namespace sgq;
 
 extern "C" {
 
+namespace {
+// prepared_out is optional; when given, (rows, width) must have a prepared form and the buffer must hold it
+int check_prepared(void* prepared_out, size_t prepared_bytes, int64_t rows, int64_t width, PreparedLayout* L) {
+    if (!prepared_out) return SGQ_OK;
+    const size_t need = gemv_prepared_bytes(rows, width);
+    if (need == 0) return bad(SGQ_ERR_UNSUPPORTED, "no prepared-activation form for this (rows, width): rows <= 16, width % 256 == 0");
+    if (prepared_bytes < need || !aligned(prepared_out, 256)) return bad(SGQ_ERR_WORKSPACE, "prepared buffer too small or not 256-byte aligned");
+    *L = prepared_layout(rows, width);
+    return SGQ_OK;
+}
+}  // namespace
+
 int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps, int64_t rows, int64_t dim, float* out,
-                     void* stream) {
+                     void* prepared_out, size_t prepared_bytes, void* stream) {
     if (rows < 0 || dim < 0 || rows > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad rows/dim");
     if (rows == 0 || dim == 0) return SGQ_OK;
     if (!h || !gamma || !out) return bad(SGQ_ERR_NULL_POINTER, "h, gamma or out is NULL");
     if (out == h) return bad(SGQ_ERR_BAD_ARGUMENT, "out may not alias h");
     if ((dim & 3) == 0 && !(aligned(h, 16) && aligned(out, 16) && aligned(gamma, 16) && (!delta || aligned(delta, 16))))
         return bad(SGQ_ERR_ALIGNMENT, "rows must be 16-byte aligned");
-    int rc = check_device();
+    PreparedLayout L = {};
+    int rc = check_prepared(prepared_out, prepared_bytes, rows, dim, &L);
     if (rc != SGQ_OK) return rc;
-    add_rmsnorm_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, gamma, eps, dim, out);
+    rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (prepared_out)
+        add_rmsnorm_kernel<true><<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(h, delta, gamma, eps, dim, out, L.ndigits, L.nsets,
+                                                                                      static_cast<uint8_t*>(prepared_out));
+    else
+        add_rmsnorm_kernel<false><<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(h, delta, gamma, eps, dim, out, 0, 0, nullptr);
     SGQ_LAUNCH_CHECK("add_rmsnorm_kernel");
     return SGQ_OK;
 }
@@ -369,16 +430,28 @@ int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_he
                            out_stride, s);
 }
 
-int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* stream) {
+int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out, size_t prepared_bytes,
+                  void* stream) {
     if (rows < 0 || hidden < 0) return bad(SGQ_ERR_BAD_SHAPE, "negative dimension");
     if (rows * hidden == 0) return SGQ_OK;
     if (!gate_up || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
-    int rc = check_device();
+    PreparedLayout L = {};
+    int rc = check_prepared(prepared_out, prepared_bytes, rows, hidden, &L);
     if (rc != SGQ_OK) return rc;
+    if (prepared_out && !(aligned(gate_up, 16) && aligned(out, 16))) return bad(SGQ_ERR_ALIGNMENT, "rows must be 16-byte aligned");
+    rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (prepared_out) {
+        silu_mul_prepare_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(gate_up, hidden, out, L.ndigits, L.nsets,
+                                                                                     static_cast<uint8_t*>(prepared_out));
+        SGQ_LAUNCH_CHECK("silu_mul_prepare_kernel");
+        return SGQ_OK;
+    }
     int64_t blocks = ceil_div(rows * hidden, 256);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
-    silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, rows, hidden, out);
+    silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(gate_up, rows, hidden, out);
     SGQ_LAUNCH_CHECK("silu_mul_kernel");
     return SGQ_OK;
 }

@@ -26,6 +26,7 @@
 // is fp32 rounding: ~1e-6 (M <= 5) / ~4e-5 (M > 5) relative for Gaussian rows, inside 1e-3.
 // Activations must be finite.
 #include "sgq_common.cuh"
+#include "gemv_prepare.cuh"
 #include "sm100_ptx.cuh"
 
 namespace sgq {
@@ -107,62 +108,6 @@ __device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], const uint32_t (&a)[
     asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c0), "r"(c1));
-}
-
-// Balanced base-256 digits of q (|q| <= 2^22): q = d0 + 256 d1 + 65536 d2 with every d in [-128, 127].
-// Adding 128 to each digit makes them unsigned bytes without carries between byte positions, so
-// the bytes of (q + 0x808080) are d_j + 128 and one more XOR turns them back into signed bytes.
-__device__ __forceinline__ uint32_t digit_bytes(int q) {
-    return (static_cast<uint32_t>(q) + 0x00808080u) ^ 0x00808080u;
-}
-// byte j of four words -> one word (a.j, b.j, c.j, d.j)
-__device__ __forceinline__ uint32_t gather_byte(uint32_t a, uint32_t b, uint32_t c, uint32_t d, int j) {
-    const uint32_t ab = __byte_perm(a, b, 0x0040 + 0x11 * j);   // (a.j, b.j, -, -)
-    const uint32_t cd = __byte_perm(c, d, 0x0040 + 0x11 * j);
-    return __byte_perm(ab, cd, 0x5410);
-}
-
-// One item = 8 consecutive activations (m, chunk c) already scaled knowledge: row bound bits `mb`.
-// Writes the item's digit bytes into the B-fragment plane and, for the lane with t == 0, the
-// group's correction.  The four lanes holding the four chunks of a 32-k group must call together.
-//   xs  : [group][set][col 8][t 4] x 8 bytes; the 8 bytes of (col, t) are the digits of
-//         k = 32*group + 8t + {0,2,4,6} (b0) and + {1,3,5,7} (b1); column col = m*ndigits + j.
-//   corr: [group][set][col 8] int32 = -8 * sum over the group's 32 k of that column's digits.
-__device__ __forceinline__ void row_scale(uint32_t mb, int frac_bits, float* P, float* invP) {
-    // P = 2^(frac_bits - e) with 2^e > absmax (e = exponent of absmax + 1); absmax 0 -> P = 1
-    const int e = static_cast<int>(mb >> 23) - 127 + 1;
-    int sh = frac_bits - e;                 // kept inside the normal range
-    sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
-    *P = (mb == 0) ? 1.0f : __uint_as_float(static_cast<uint32_t>(127 + sh) << 23);
-    *invP = (mb == 0) ? 1.0f : __uint_as_float(static_cast<uint32_t>(127 - sh) << 23);
-}
-
-__device__ __forceinline__ void digits_item(const float (&v)[8], float P, int m, int c, int ndigits, int nsets,
-                                            uint8_t* xs, uint8_t* corr) {
-    uint32_t db[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) db[j] = digit_bytes(__float2int_rn(v[j] * P));
-    const int group = c >> 2, t = c & 3;
-#pragma unroll
-    for (int j = 0; j < 3; ++j) {
-        if (j < ndigits) {
-            const uint32_t b0 = gather_byte(db[0], db[2], db[4], db[6], j);   // k = 8t + {0,2,4,6}
-            const uint32_t b1 = gather_byte(db[1], db[3], db[5], db[7], j);   // k = 8t + {1,3,5,7}
-            int sum = __dp4a(static_cast<int>(b0), 0x01010101, __dp4a(static_cast<int>(b1), 0x01010101, 0));
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
-            *reinterpret_cast<uint2*>(xs + (static_cast<size_t>(group) * nsets + set) * 256 + (cc * 4 + t) * 8) =
-                make_uint2(b0, b1);
-            if (t == 0)
-                *reinterpret_cast<int*>(corr + (static_cast<size_t>(group) * nsets + set) * 32 + cc * 4) = -8 * sum;
-        }
-    }
-}
-
-__device__ __forceinline__ float absmax8(const float (&v)[8]) {
-    return fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
-                 fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
 }
 
 // Activation planes for batches too large to convert inside every CTA: one CTA per batch row,
@@ -564,12 +509,13 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p) {
 }
 
 template <int NSETS, int WPB, bool PRE>
-int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid) {
+int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
+                   bool planes_ready) {
     static SmemOptIn optin;
     auto kernel = gemv_int4_nk_kernel<NSETS, WPB, PRE>;
     SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
-    if (PRE) {
+    if (PRE && !planes_ready) {
         gemv_prepare_x_kernel<<<static_cast<int>(a.M), kPrepThreads, 0, a.stream>>>(a.x, static_cast<int>(a.M), a.K, p.ndigits,
                                                                                    p.nsets, static_cast<uint8_t*>(a.workspace));
         SGQ_LAUNCH_CHECK("gemv_prepare_x_kernel");
@@ -582,12 +528,13 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
 }
 
 template <int NSETS>
-int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid) {
+int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
+                 bool planes_ready) {
     if (p.pre)
-        return p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid)
-                          : launch_variant<NSETS, 1, true>(a, p, map_w, map_s, grid);
-    return p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid)
-                      : launch_variant<NSETS, 1, false>(a, p, map_w, map_s, grid);
+        return p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid, planes_ready)
+                          : launch_variant<NSETS, 1, true>(a, p, map_w, map_s, grid, planes_ready);
+    return p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid, false)
+                      : launch_variant<NSETS, 1, false>(a, p, map_w, map_s, grid, false);
 }
 
 }  // namespace
@@ -609,15 +556,46 @@ size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layou
     return (p.planes_bytes + 255) / 256 * 256;
 }
 
-int launch_linear_gemv(const LinearArgs& a) {
+namespace {
+int launch_gemv_impl(const LinearArgs& a, bool planes_ready);
+}
+
+int launch_linear_gemv(const LinearArgs& a) { return launch_gemv_impl(a, false); }
+
+// a.workspace holds activations already converted to the prepared format (a.x is not read).
+int launch_linear_gemv_prepared(const LinearArgs& a) { return launch_gemv_impl(a, true); }
+
+size_t gemv_prepared_bytes(int64_t M, int64_t K) {
     Plan p;
-    const size_t want = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    if (M < 1 || M > kMaxM || K < 256 || (K % 256) != 0 || K >= (1LL << 24) || !make_plan(M, K, true, &p)) return 0;
+    return (p.planes_bytes + 255) / 256 * 256;
+}
+
+int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s) {
+    const PreparedLayout L = prepared_layout(M, K);
+    if (K > 8LL * kPrepMaxChunks * kPrepThreads) {
+        set_error("K too large for the conversion kernel");
+        return SGQ_ERR_UNSUPPORTED;
+    }
+    gemv_prepare_x_kernel<<<static_cast<int>(M), kPrepThreads, 0, s>>>(x, static_cast<int>(M), K, L.ndigits, L.nsets,
+                                                                      static_cast<uint8_t*>(prepared));
+    SGQ_LAUNCH_CHECK("gemv_prepare_x_kernel");
+    return SGQ_OK;
+}
+
+namespace {
+int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
+    Plan p;
+    const size_t want = planes_ready ? gemv_prepared_bytes(a.M, a.K) : gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
     const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
-    if (!gemv_supported(a) || !make_plan(a.M, a.K, have_ws, &p)) {
+    LinearArgs probe = a;
+    if (planes_ready) probe.x = static_cast<const float*>(a.workspace);      // x is not read: only its alignment rule is waived
+    if (!gemv_supported(probe) || !make_plan(a.M, a.K, have_ws, &p) || (planes_ready && !have_ws)) {
         set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "
                   "16-byte aligned x/packed/scales");
         return SGQ_ERR_UNSUPPORTED;
     }
+    if (planes_ready) p.pre = true;
     // packed weights as (128 B, N rows, K/256 steps); scales as (8 fp32, N rows, K/256 steps)
     CUtensorMap map_w, map_s;
     const uint64_t steps = static_cast<uint64_t>(a.K / kStepK);
@@ -639,12 +617,13 @@ int launch_linear_gemv(const LinearArgs& a) {
     const int64_t ntiles = ceil_div(a.N, kRows);
     const int grid = static_cast<int>(ntiles < sm_count() ? ntiles : sm_count());
     switch (p.nsets) {
-        case 1: return launch_nsets<1>(a, p, map_w, map_s, grid);
-        case 2: return launch_nsets<2>(a, p, map_w, map_s, grid);
-        case 3: return launch_nsets<3>(a, p, map_w, map_s, grid);
-        default: return launch_nsets<4>(a, p, map_w, map_s, grid);
+        case 1: return launch_nsets<1>(a, p, map_w, map_s, grid, planes_ready);
+        case 2: return launch_nsets<2>(a, p, map_w, map_s, grid, planes_ready);
+        case 3: return launch_nsets<3>(a, p, map_w, map_s, grid, planes_ready);
+        default: return launch_nsets<4>(a, p, map_w, map_s, grid, planes_ready);
     }
 }
+}  // namespace
 
 // ---- entry point without any allocation ---------------------------------------------------
 // Some callers of the decode forward cannot obtain device memory at call time: code running

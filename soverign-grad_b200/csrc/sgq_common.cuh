@@ -82,6 +82,9 @@ bool gemv_supported(const LinearArgs& a);
 size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_gemv(const LinearArgs& a);
 int launch_linear_gemv_static(LinearArgs a);   // scratch in a file-scope device array
+size_t gemv_prepared_bytes(int64_t M, int64_t K);            // 0: no prepared form for this (M, K)
+int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s);
+int launch_linear_gemv_prepared(const LinearArgs& a);        // a.workspace = prepared activations, a.x unused
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_tc_bf16(const LinearArgs& a);

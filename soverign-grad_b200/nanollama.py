@@ -27,7 +27,7 @@ from typing import Callable, Optional
 import torch
 
 from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
-               quantize_int4, quantized_matmul)
+               linear_int4_prepared, prepared_x_bytes, quantize_int4, quantized_matmul)
 
 
 @dataclass
@@ -99,6 +99,9 @@ class _Linear:
     def __call__(self, x: torch.Tensor, out: torch.Tensor, path: int) -> torch.Tensor:
         return quantized_matmul(x, self.q, None, layout=LAYOUT_NK, path=path, out=out, workspace=self.ws)
 
+    def prepared(self, planes: torch.Tensor, M: int, out: torch.Tensor) -> torch.Tensor:
+        return linear_int4_prepared(planes, M, self.q, None, out)
+
 
 class NanoLlamaInt4:
     def __init__(self, cfg: NanoLlamaConfig, device, batch: int, *, seed: int = 0,
@@ -152,7 +155,12 @@ class NanoLlamaInt4:
             f = lambda *s: torch.empty(*s, device=dev)  # noqa: E731
             b = {"h": f(M, c.dim), "n": f(M, c.dim), "qkv": f(M, 3 * self.dim_local), "attn": f(M, self.dim_local),
                  "o": f(M, c.dim // W), "gu": f(M, 2 * self.hid_local), "act": f(M, self.hid_local), "d": f(M, c.dim // W)}
+            use_prep = self.decode_path in (PATH_AUTO, PATH_GEMV)
+            for key, width in (("p_dim", c.dim), ("p_hid", c.hidden)):
+                nb = prepared_x_bytes(M, width) if use_prep else 0
+                b[key] = torch.empty(nb, dtype=torch.uint8, device=dev) if nb else None
             if W > 1:
+                b["p_hid"] = None          # the SiLU gate output is a column slice per rank: converted after the gather
                 b.update({"g_attn": f(W, M, self.dim_local), "g_o": f(W, M, c.dim // W), "g_act": f(W, M, self.hid_local),
                           "attn_full": f(M, c.dim), "o_full": f(M, c.dim), "act_full": f(M, c.hidden), "d_full": f(M, c.dim)})
             self._bufs[M] = b
@@ -172,12 +180,17 @@ class NanoLlamaInt4:
         self._launches += n
 
     # ---- the C-ABI operators ---------------------------------------------------------------
-    def _add_rmsnorm(self, h, delta, gamma, out):
-        check(lib.sgqd_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(gamma), self.cfg.eps, h.shape[0], h.shape[1], _ptr(out), _stream()),
-              "sgqd_add_rmsnorm")
+    def _add_rmsnorm(self, h, delta, gamma, out, planes=None):
+        check(lib.sgqd_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(gamma), self.cfg.eps, h.shape[0], h.shape[1], _ptr(out),
+                                   _ptr(planes), planes.numel() if planes is not None else 0, _stream()), "sgqd_add_rmsnorm")
         self._count()
 
-    def _linear(self, lin: _Linear, x, out, path):
+    def _linear(self, lin: _Linear, x, out, path, planes=None):
+        """planes: x already in the decode kernel's prepared form (written by the operator before)."""
+        if planes is not None:
+            lin.prepared(planes, x.shape[0], out)
+            self._count()
+            return
         lin(x, out, path)
         M, K = x.shape
         # the decode kernel converts activations inside its CTAs up to 2048 eight-value chunks; larger
@@ -194,9 +207,12 @@ class NanoLlamaInt4:
         torch.index_select(self.embed, 0, tokens, out=h)                       # nn::Embedding lookup
         self._count()
         delta = None
+        p_dim, p_hid = b["p_dim"], b["p_hid"]          # None for batches the decode kernel does not take
+        if path not in (PATH_AUTO, PATH_GEMV):
+            p_dim = p_hid = None
         for li, L in enumerate(self.layers):
-            self._add_rmsnorm(h, delta, L["attn_norm"], n)
-            self._linear(L["qkv"], n, b["qkv"], path)
+            self._add_rmsnorm(h, delta, L["attn_norm"], n, p_dim)
+            self._linear(L["qkv"], n, b["qkv"], path, p_dim)
             kc, vc = self.k_cache[li], self.v_cache[li]
             if t_new == 1:       # rotary embedding, cache append and attention of the new token in one kernel
                 check(lib.sgqd_attn_decode(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(self.cos),
@@ -211,14 +227,16 @@ class NanoLlamaInt4:
             attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"))
             self._linear(L["wo"], attn, b["o"], path)
             o = self._gather(b["o"], b.get("g_o"), b.get("o_full"))
-            self._add_rmsnorm(h, o, L["ffn_norm"], n)
-            self._linear(L["gu"], n, b["gu"], path)
-            check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _stream()), "sgqd_silu_mul")
+            self._add_rmsnorm(h, o, L["ffn_norm"], n, p_dim)
+            self._linear(L["gu"], n, b["gu"], path, p_dim)
+            check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _ptr(p_hid),
+                                    p_hid.numel() if p_hid is not None else 0, _stream()), "sgqd_silu_mul")
             self._count()
             act = self._gather(b["act"], b.get("g_act"), b.get("act_full"))
-            self._linear(L["down"], act, b["d"], path)
+            self._linear(L["down"], act, b["d"], path, p_hid)
             delta = self._gather(b["d"], b.get("g_o"), b.get("d_full"))
-        self._add_rmsnorm(h, delta, self.final_norm, n)
+        self._add_rmsnorm(h, delta, self.final_norm, n, p_dim)
+        self._final_planes = p_dim
         return n
 
     def _prefill_attention(self, qkv, kc, vc, T: int, out):
@@ -234,7 +252,7 @@ class NanoLlamaInt4:
         out.view(B, T, Hl, hd).copy_(ctx.permute(0, 2, 1, 3))
         self._count(6)
 
-    def _logits(self, n_rows: torch.Tensor, path: int) -> torch.Tensor:
+    def _logits(self, n_rows: torch.Tensor, path: int, planes=None) -> torch.Tensor:
         M = n_rows.shape[0]
         key = ("logits", M)
         if key not in self._bufs:
@@ -242,7 +260,7 @@ class NanoLlamaInt4:
             self._bufs[key] = (f(M, self.voc_local), f(self.world, M, self.voc_local) if self.world > 1 else None,
                                f(M, self.cfg.vocab) if self.world > 1 else None)
         loc, g, full = self._bufs[key]
-        self._linear(self.lm_head, n_rows, loc, path)
+        self._linear(self.lm_head, n_rows, loc, path, planes)
         return self._gather(loc, g, full)
 
     # ---- public ---------------------------------------------------------------------------
@@ -267,7 +285,7 @@ class NanoLlamaInt4:
         advances the position and returns the logits of the next token [batch, vocab]."""
         self._launches = 0
         n = self._forward(tokens, 1, self.decode_path)
-        logits = self._logits(n, self.decode_path)
+        logits = self._logits(n, self.decode_path, self._final_planes)
         self.pos.add_(1)
         self._count()
         return logits

@@ -38,15 +38,21 @@ def test_library_exports_every_decoder_symbol(sgq):
 def test_decoder_argument_validation_needs_no_device(sgq):
     L = sgq.lib
     one = C.c_void_p(256)
-    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, -1, 8, one, None) == 2
-    assert L.sgqd_add_rmsnorm(None, None, one, 1e-5, 2, 8, one, None) == 1
-    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 8, one, None) == 3              # out aliases h
-    assert L.sgqd_add_rmsnorm(None, None, None, 1e-5, 0, 8, None, None) == 0           # empty
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, -1, 8, one, None, 0, None) == 2
+    assert L.sgqd_add_rmsnorm(None, None, one, 1e-5, 2, 8, one, None, 0, None) == 1
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 8, one, None, 0, None) == 3     # out aliases h
+    assert L.sgqd_add_rmsnorm(None, None, None, 1e-5, 0, 8, None, None, 0, None) == 0  # empty
+    two = C.c_void_p(512)
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 100, two, two, 4096, None) == 4  # no prepared form for dim 100
+    assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 256, two, two, 16, None) == 5    # prepared buffer too small
+    assert int(L.sgq_prepared_x_bytes(8, 2048)) == ((2048 // 32) * 2 * 288 + 64 + 255) // 256 * 256
+    assert L.sgq_linear_int4_prepared(one, 64, 8, 2048, 64, one, one, None, one, 64, None) == 5
+    assert L.sgq_linear_int4_prepared(one, 1 << 20, 8, 2050, 64, one, one, None, one, 64, None) == 4
     assert L.sgqd_rope_kv_store(one, 1, 1, 2, 12, one, one, one, one, one, 8, None) == 2   # head_dim % 8
     assert L.sgqd_attn_decode(one, 768, 1, 2, 96, one, one, one, one, 8, one, one, 256, None) == 4    # head_dim 96
     assert L.sgqd_attn_decode(one, 100, 1, 2, 128, one, one, one, one, 8, one, one, 256, None) == 2   # stride too small
     assert L.sgqd_attn_decode(None, 768, 1, 2, 128, one, one, one, one, 8, one, one, 256, None) == 1
-    assert L.sgqd_silu_mul(None, 2, 8, None, None) == 1
+    assert L.sgqd_silu_mul(None, 2, 8, None, None, 0, None) == 1
 
 
 def test_abi_version_and_status_strings(sgq):

@@ -46,7 +46,7 @@ def test_add_rmsnorm(sgq, rows, dim, with_delta):
     g = (1 + 0.2 * r.standard_normal(dim)).astype(np.float32)
     ht, dt, gt = dev(h), (dev(d) if with_delta else None), dev(g)
     out = torch.empty_like(ht)
-    sgq.check(sgq.lib.sgqd_add_rmsnorm(ptr(ht), ptr(dt), ptr(gt), 1e-5, rows, dim, ptr(out), stream()))
+    sgq.check(sgq.lib.sgqd_add_rmsnorm(ptr(ht), ptr(dt), ptr(gt), 1e-5, rows, dim, ptr(out), None, 0, stream()))
     hsum = h.astype(np.float64) + (d if with_delta else 0)
     assert np.max(np.abs(ht.cpu().numpy() - hsum)) <= 1e-6 * np.max(np.abs(hsum))     # residual stream updated in place
     assert norm_err(out.cpu().numpy(), no.rms_norm(hsum.astype(np.float32), g, 1e-5)) <= 5e-6
@@ -55,7 +55,7 @@ def test_add_rmsnorm(sgq, rows, dim, with_delta):
 def test_add_rmsnorm_rejects_alias(sgq):
     h = torch.zeros(2, 64, device="cuda")
     g = torch.ones(64, device="cuda")
-    assert sgq.lib.sgqd_add_rmsnorm(ptr(h), None, ptr(g), 1e-5, 2, 64, ptr(h), stream()) == 3
+    assert sgq.lib.sgqd_add_rmsnorm(ptr(h), None, ptr(g), 1e-5, 2, 64, ptr(h), None, 0, stream()) == 3
 
 
 @pytest.mark.parametrize("rows,hidden", [(1, 5632), (8, 704), (3, 37)])
@@ -64,9 +64,49 @@ def test_silu_mul(sgq, rows, hidden):
     gu = (r.standard_normal((rows, 2 * hidden)) * 3).astype(np.float32)
     out = torch.empty(rows, hidden, device="cuda")
     gt = dev(gu)
-    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gt), rows, hidden, ptr(out), stream()))
+    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gt), rows, hidden, ptr(out), None, 0, stream()))
     want = no.silu(gu[:, :hidden]) * gu[:, hidden:].astype(np.float64)
     assert norm_err(out.cpu().numpy(), want) <= 2e-6
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 2048, 512), (5, 256, 48), (8, 2048, 6144), (8, 5632, 2048), (16, 4096, 1024)])
+def test_prepared_activations_give_the_decode_kernels_bits(sgq, M, K, N):
+    """sgq_prepare_x + sgq_linear_int4_prepared, and the operators that emit the prepared form
+    themselves, against sgq_linear_int4 on the same fp32 activations: identical bits."""
+    g = torch.Generator(device="cuda").manual_seed(M * K + N)
+    x = torch.randn(M, K, device="cuda", generator=g) * 3
+    q = sgq.quantize_int4(torch.randn(N, K, device="cuda", generator=g) * 0.05, 32)
+    bias = torch.randn(N, device="cuda", generator=g)
+    want = sgq.quantized_matmul(x, q, bias, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=sgq.Workspace(x.device))
+    nb = sgq.prepared_x_bytes(M, K)
+    assert nb > 0 and nb % 256 == 0
+    got = sgq.linear_int4_prepared(sgq.prepare_x(x), M, q, bias)
+    assert torch.equal(got, want)
+    # RMSNorm emitting the prepared form of its output
+    h, gamma = x.clone(), 1 + 0.1 * torch.randn(K, device="cuda", generator=g)
+    n, planes = torch.empty_like(h), torch.empty(nb, dtype=torch.uint8, device="cuda")
+    sgq.check(sgq.lib.sgqd_add_rmsnorm(ptr(h), None, ptr(gamma), 1e-5, M, K, ptr(n), ptr(planes), nb, stream()))
+    want_n = sgq.quantized_matmul(n, q, None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=sgq.Workspace(x.device))
+    assert torch.equal(sgq.linear_int4_prepared(planes, M, q), want_n)
+    # SiLU gate emitting the prepared form of its output
+    gu = torch.randn(M, 2 * K, device="cuda", generator=g) * 2
+    act = torch.empty(M, K, device="cuda")
+    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gu), M, K, ptr(act), ptr(planes), nb, stream()))
+    plain = torch.empty(M, K, device="cuda")
+    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gu), M, K, ptr(plain), None, 0, stream()))
+    assert torch.equal(act, plain)
+    want_a = sgq.quantized_matmul(act, q, None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=sgq.Workspace(x.device))
+    assert torch.equal(sgq.linear_int4_prepared(planes, M, q), want_a)
+
+
+def test_prepared_activations_reject_unsupported_shapes(sgq):
+    assert sgq.prepared_x_bytes(17, 2048) == 0 and sgq.prepared_x_bytes(4, 300) == 0 and sgq.prepared_x_bytes(0, 2048) == 0
+    x = torch.zeros(17, 2048, device="cuda")
+    with pytest.raises(sgq.SgqError):
+        sgq.prepare_x(x)
+    buf = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    assert sgq.lib.sgq_prepare_x(ptr(x[:4]), 4, 2048, ptr(buf), buf.numel(), stream()) == 5      # buffer too small
+    assert sgq.lib.sgqd_silu_mul(ptr(x), 4, 1024, ptr(x), ptr(buf), buf.numel(), stream()) == 5
 
 
 @pytest.mark.parametrize("B,T,H,hd,pos0,max_seq", [(2, 1, 2, 128, 0, 16), (2, 1, 3, 64, 9, 16), (2, 5, 2, 128, 3, 16),
