@@ -416,6 +416,7 @@ def run_ours(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
+    sgq.set_stream_overlap(not args.no_overlap)     # consecutive forwards overlap their prologue and first weight tiles
     M, copies, lps = args.M, args.copies, args.launches_per_step
     if world > 1 and lps > 200:
         lps = 200
@@ -573,7 +574,9 @@ def run_ours(args):
                    "M": M, "K": K_DIM, "N_per_gpu": N_DIM, "group": GROUP, "launches_per_step": lps, "weight_copies": copies,
                    "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
                    "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch,
-                   "launch": "one CUDA graph replay per step" if use_graph else "eager launches"},
+                   "launch": "one CUDA graph replay per step" if use_graph else "eager launches",
+                   "stream_overlap": "on: programmatic dependent launch, a forward's first weight tiles are fetched while the "
+                                     "previous forward finishes" if not args.no_overlap else "off"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
                      "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_LAUNCH.get(M) if world == 1 else None,
@@ -611,6 +614,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

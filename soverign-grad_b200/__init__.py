@@ -32,7 +32,7 @@ EXPORTS = [
     "sgq_codes_to_f32_int8", "sgq_codes_to_f32_int4", "sgq_codes_from_f32_int8", "sgq_codes_from_f32_int4",
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
-    "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared",
+    "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared", "sgq_set_stream_overlap",
 ]
 
 # every symbol include/sgq_decoder.h declares
@@ -71,6 +71,7 @@ def _load() -> C.CDLL:
     lib.sgq_linear_w8a8.argtypes = [p, i64, i64, i64, p, p, i32, p, p, i64, p, p, p, p, sz, p]
     lib.sgq_interleave_slices.argtypes = [p, i64, i64, i64, p, i64, p]
     lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
+    lib.sgq_set_stream_overlap.argtypes = [i32]
     lib.sgq_prepared_x_bytes.restype = sz
     lib.sgq_prepared_x_bytes.argtypes = [i64, i64]
     lib.sgq_prepare_x.argtypes = [p, i64, i64, p, sz, p]
@@ -88,6 +89,12 @@ lib = _load()
 def check(status: int, what: str = "sgq call") -> None:
     if status != 0:
         raise SgqError(status, f"{what} failed: {lib.sgq_status_string(status).decode()}", lib.sgq_last_error().decode())
+
+
+def set_stream_overlap(enabled: bool) -> bool:
+    """Programmatic dependent launch for every kernel of the library (see sgq_set_stream_overlap in
+    include/sgq.h for the one rule it adds).  Returns the previous setting."""
+    return bool(lib.sgq_set_stream_overlap(1 if enabled else 0))
 
 
 def device_status(clear: bool = True) -> int:

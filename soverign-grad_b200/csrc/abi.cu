@@ -100,6 +100,11 @@ bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void*
     return make_tensor_map(map, dtype, base, 2, dims, strides, box, swizzle);
 }
 
+namespace {
+int g_stream_overlap = 0;
+}
+bool stream_overlap_enabled() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) != 0; }
+
 int check_device() {
     if (device_info().major != 10) {
         set_error("this library contains sm_100a code only; current device is compute capability %d.x",
@@ -187,6 +192,10 @@ const char* sgq_status_string(int status) {
 const char* sgq_last_error(void) { return g_error; }
 
 int sgq_abi_version(void) { return SGQ_ABI_VERSION; }
+
+int sgq_set_stream_overlap(int enabled) {
+    return __atomic_exchange_n(&g_stream_overlap, enabled ? 1 : 0, __ATOMIC_RELAXED);
+}
 
 int sgq_device_status(unsigned int* word, int clear) {
     uint32_t a = 0, b = 0;

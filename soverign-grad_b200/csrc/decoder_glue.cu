@@ -5,6 +5,7 @@
 // recorded CUDA graph of a decode step stays valid from step to step.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
+#include "sm100_ptx.cuh"
 
 #include "../../include/sgq_decoder.h"
 
@@ -43,6 +44,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
                                                                   float* out, int ndigits, int nsets, uint8_t* planes) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float inv_rms_s;
+    pdl_launch_dependents();
+    pdl_wait();
     float* hr = h + blockIdx.x * dim;
     const float* dr = delta ? delta + blockIdx.x * dim : nullptr;
     float* orow = out + blockIdx.x * dim;
@@ -98,6 +101,8 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ 
                                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                             const int32_t* __restrict__ pos0, float* __restrict__ kc,
                                                             float* __restrict__ vc, int64_t max_seq) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t m = blockIdx.x;
     const int b = static_cast<int>(m / t_new), i = static_cast<int>(m % t_new);
     const int64_t pos = static_cast<int64_t>(*pos0) + i;
@@ -162,6 +167,8 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
     const int bh = blockIdx.x, split = blockIdx.y, S = gridDim.y;
     const int b = bh / n_heads, h = bh - b * n_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();                                            // qkv, the caches and *pos0 come from earlier kernels
     int64_t pos = static_cast<int64_t>(*pos0);
     const bool in_range = pos >= 0 && pos < max_seq;       // else: attend to the cache only, store nothing
     pos = pos < 0 ? 0 : (pos > max_seq ? max_seq : pos);
@@ -289,6 +296,8 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ gu, int64_t rows, int64_t hidden,
                                                        float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t n = rows * hidden;
     for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += gridDim.x * 256ll) {
         const int64_t r = i / hidden, c = i - r * hidden;
@@ -301,6 +310,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const float* __restrict__ gu, int64_t hidden, float* out,
                                                                        int ndigits, int nsets, uint8_t* planes) {
     __shared__ float red[kNormThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* g = gu + blockIdx.x * 2 * hidden;
     const float* u = g + hidden;
     float* orow = out + blockIdx.x * hidden;
@@ -339,13 +350,15 @@ int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads
     cfg.blockDim = dim3(kAttnWarps * 32, 1, 1);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = static_cast<unsigned>(S);
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = stream_overlap_enabled() ? 2 : 1;
     SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0, out,
                                     out_stride));
     return SGQ_OK;
@@ -384,12 +397,13 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
     rc = check_device();
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool ov = stream_overlap_enabled();
     if (prepared_out)
-        add_rmsnorm_kernel<true><<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(h, delta, gamma, eps, dim, out, L.ndigits, L.nsets,
-                                                                                      static_cast<uint8_t*>(prepared_out));
+        SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
+                                   gamma, eps, dim, out, L.ndigits, L.nsets, static_cast<uint8_t*>(prepared_out)));
     else
-        add_rmsnorm_kernel<false><<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(h, delta, gamma, eps, dim, out, 0, 0, nullptr);
-    SGQ_LAUNCH_CHECK("add_rmsnorm_kernel");
+        SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
+                                   gamma, eps, dim, out, 0, 0, static_cast<uint8_t*>(nullptr)));
     return SGQ_OK;
 }
 
@@ -403,10 +417,10 @@ int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t n_heads
     if (!qkv || !cos_table || !sin_table || !pos0 || !k_cache || !v_cache) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
     int rc = check_device();
     if (rc != SGQ_OK) return rc;
-    rope_kv_store_kernel<<<static_cast<unsigned>(batch * t_new), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        qkv, static_cast<int>(t_new), static_cast<int>(n_heads), static_cast<int>(head_dim), cos_table, sin_table, pos0, k_cache,
-        v_cache, max_seq);
-    SGQ_LAUNCH_CHECK("rope_kv_store_kernel");
+    SGQ_CUDA_TRY(launch_kernel(rope_kv_store_kernel, dim3(static_cast<unsigned>(batch * t_new)), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), stream_overlap_enabled(), qkv, static_cast<int>(t_new),
+                               static_cast<int>(n_heads), static_cast<int>(head_dim), cos_table, sin_table, pos0, k_cache, v_cache,
+                               max_seq));
     return SGQ_OK;
 }
 
@@ -443,16 +457,16 @@ int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (prepared_out) {
-        silu_mul_prepare_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, s>>>(gate_up, hidden, out, L.ndigits, L.nsets,
-                                                                                     static_cast<uint8_t*>(prepared_out));
-        SGQ_LAUNCH_CHECK("silu_mul_prepare_kernel");
+        SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets,
+                                   static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
     }
     int64_t blocks = ceil_div(rows * hidden, 256);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
-    silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(gate_up, rows, hidden, out);
-    SGQ_LAUNCH_CHECK("silu_mul_kernel");
+    SGQ_CUDA_TRY(launch_kernel(silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, s, stream_overlap_enabled(), gate_up,
+                               rows, hidden, out));
     return SGQ_OK;
 }
 

@@ -118,6 +118,8 @@ constexpr int kPrepMaxChunks = 8;   // per thread: K <= 8 * 512 * 8 = 32768
 __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int M, int64_t K,
                                                                      int ndigits, int nsets, uint8_t* __restrict__ planes) {
     __shared__ float red[kPrepThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();                                        // x comes from the kernel before this one
     const int m = blockIdx.x, lane = threadIdx.x & 31;
     const int chunks = static_cast<int>(K / 8);
     const size_t groups = static_cast<size_t>(K / 32);
@@ -154,10 +156,10 @@ __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const floa
 // NSETS: sets of 8 digit columns; WPB: consumer warps per 256-k step (1 or 2);
 // PRE: the activation planes were prepared by gemv_prepare_x_kernel and are copied in by TMA.
 template <int NSETS, int WPB, bool PRE>
-__global__ void __launch_bounds__((kStepsPerStage * WPB + 2) * 32, 1)
+__global__ void __launch_bounds__((kStepsPerStage * WPB + 2) * 32, WPB == 1 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
-                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages) {
+                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages, int early_weights) {
     constexpr int kWarps = kStepsPerStage * WPB;
     constexpr int kConsumerThreads = kWarps * 32;
     constexpr int kGroupsPerWarp = 8 / WPB;
@@ -182,26 +184,10 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int spt = static_cast<int>(K / kStepK);   // steps per tile (K % 256 == 0)
 
     SGQ_MARK(0);
+    pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
     if (threadIdx.x == kWarps * 32) {   // the producer thread: start fetching both descriptors now
         tma_prefetch_descriptor(&map_w);
         tma_prefetch_descriptor(&map_s);
-    }
-    // The first kPre items of every consumer thread are requested before anything else, so that
-    // their global-memory latency overlaps barrier set-up and the producer's first TMA issues.
-    constexpr int kPre = PRE ? 1 : 4;
-    const int chunks = static_cast<int>(K / 8);   // 8-float chunks per activation row
-    const int items = chunks * M;
-    float4 pre_a[kPre], pre_b[kPre];
-#pragma unroll
-    for (int r = 0; r < kPre; ++r) {
-        const int it = threadIdx.x + r * kConsumerThreads;
-        if (!PRE && warp < kWarps && it < items) {
-            pre_a[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
-            pre_b[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
-        } else {
-            pre_a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-            pre_b[r] = pre_a[r];
-        }
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; ++i) {
@@ -218,21 +204,57 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     if (threadIdx.x < kMaxM) rowmax_bits[threadIdx.x] = 0;
     __syncthreads();
+    // Everything above touches no global data.  From here on every thread except the producer
+    // first waits for the kernels this launch depends on (they wrote x / the planes, and may still
+    // be reading y); the producer decides for itself below, because weights are not their output.
+    if (warp != kWarps) pdl_wait();
+    SGQ_MARK(12);
+    // The first kPre items of every consumer thread are requested before anything else, so that
+    // their global-memory latency overlaps the producer's first TMA issues.
+    constexpr int kPre = PRE ? 1 : 4;
+    const int chunks = static_cast<int>(K / 8);   // 8-float chunks per activation row
+    const int items = chunks * M;
+    float4 pre_a[kPre], pre_b[kPre];
+#pragma unroll
+    for (int r = 0; r < kPre; ++r) {
+        const int it = threadIdx.x + r * kConsumerThreads;
+        if (!PRE && warp < kWarps && it < items) {
+            pre_a[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
+            pre_b[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
+        } else {
+            pre_a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            pre_b[r] = pre_a[r];
+        }
+    }
 
     if (warp == kWarps) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            if (PRE) {
-                // digit planes + corrections, contiguous in both places, in pieces of <= 32 KiB
-                const uint32_t bytes = L.partial_off - L.x_off;
-                mbar_arrive_expect_tx(xfull, bytes);
-                for (uint32_t off = 0; off < bytes; off += 32768u)
-                    bulk_copy_g2s(xs + off, planes + off, (bytes - off < 32768u) ? bytes - off : 32768u, xfull);
-            }
+            // Weights and scales are parameters, not the output of the kernel before this one: with
+            // early_weights the first ring of stages is requested before the dependency wait, so the
+            // weight stream overlaps the tail of that kernel.  The activation planes are its output
+            // and are copied only after the wait.
+            bool synced = false;
+            auto dependency_sync = [&]() {
+                if (synced) return;
+                synced = true;
+                pdl_wait();
+                SGQ_MARK(4);
+                if (PRE) {
+                    fence_proxy_async_all();        // the planes were written through the generic proxy
+                    // digit planes + corrections, contiguous in both places, in pieces of <= 32 KiB
+                    const uint32_t bytes = L.partial_off - L.x_off;
+                    mbar_arrive_expect_tx(xfull, bytes);
+                    for (uint32_t off = 0; off < bytes; off += 32768u)
+                        bulk_copy_g2s(xs + off, planes + off, (bytes - off < 32768u) ? bytes - off : 32768u, xfull);
+                }
+            };
+            if (!early_weights) dependency_sync();
             uint32_t seq = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
+                    if (seq == static_cast<uint32_t>(nstages)) dependency_sync();   // the ring is full: nothing more to request early
                     const int st = seq % nstages;
                     const uint32_t ph = (seq / nstages) & 1u;
                     if (!mbar_wait(&empty[st], ph ^ 1u)) {
@@ -249,6 +271,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (seq == 6) SGQ_MARK(2);
                 }
             }
+            dependency_sync();
             SGQ_MARK(3);
         }
         return;
@@ -484,19 +507,26 @@ struct Plan {
 
 // In-CTA conversion is used while every consumer thread can hold all its items in registers
 // (4 items of 8 activations per thread); larger batches are converted once by a pre-kernel.
-bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p) {
+//
+// compact: a CTA that leaves room for a second one on the same SM (half the shared memory, 10
+// warps).  With overlapped launches the CTA of the NEXT kernel then sits beside the one still
+// running and streams its first weight stages in the meantime, so the pipeline fill, the launch
+// latency and the tail of consecutive decode forwards hide behind each other.
+constexpr int kCompactSmem = 112 * 1024;
+bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact = false) {
     p->ndigits = (M <= 5) ? 3 : 2;
     p->nsets = static_cast<int>((M * p->ndigits + 7) / 8);
     p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 288 + kMaxM * 4;
+    const int limit = compact ? kCompactSmem : kSmemLimit;
     // two warps per step while at least 3 stages still fit, else one (smaller partial-sum buffers)
 #ifdef SGQ_FORCE_WPB
     for (int wpb = SGQ_FORCE_WPB; wpb >= 1; --wpb) {
 #else
-    for (int wpb = 2; wpb >= 1; --wpb) {
+    for (int wpb = compact ? 1 : 2; wpb >= 1; --wpb) {
 #endif
         for (int st = kMaxStages; st >= (wpb == 2 ? 3 : 2); --st) {
             const Smem L = smem_layout(st, K, p->nsets, kStepsPerStage * wpb);
-            if (L.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {
+            if (L.total + 1024 <= static_cast<uint32_t>(limit)) {
                 p->wpb = wpb;
                 p->nstages = st;
                 p->smem = L.total + 1024;
@@ -515,15 +545,14 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     auto kernel = gemv_int4_nk_kernel<NSETS, WPB, PRE>;
     SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
+    const bool overlap = stream_overlap_enabled();
     if (PRE && !planes_ready) {
-        gemv_prepare_x_kernel<<<static_cast<int>(a.M), kPrepThreads, 0, a.stream>>>(a.x, static_cast<int>(a.M), a.K, p.ndigits,
-                                                                                   p.nsets, static_cast<uint8_t*>(a.workspace));
-        SGQ_LAUNCH_CHECK("gemv_prepare_x_kernel");
+        SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap,
+                                   a.x, static_cast<int>(a.M), a.K, p.ndigits, p.nsets, static_cast<uint8_t*>(a.workspace)));
     }
-    kernel<<<grid, (kStepsPerStage * WPB + 2) * 32, p.smem, a.stream>>>(map_w, map_s, a.x, planes, a.bias, a.y,
-                                                                         static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
-                                                                         p.nstages);
-    SGQ_LAUNCH_CHECK("gemv_int4_nk_kernel");
+    SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((kStepsPerStage * WPB + 2) * 32), p.smem, a.stream,
+                               overlap, map_w, map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
+                               p.nstages, overlap ? 1 : 0));
     return SGQ_OK;
 }
 
@@ -552,7 +581,10 @@ size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layou
     (void)N;
     Plan p;
     if (bits != 4 || layout != SGQ_LAYOUT_NK || M < 1 || M > kMaxM || K < 256 || (K % 256) != 0) return 0;
-    if (!make_plan(M, K, true, &p) || !p.pre) return 0;
+    if (!make_plan(M, K, true, &p)) return 0;
+    Plan c;
+    const bool compact_pre = make_plan(M, K, true, &c, true) && c.pre;    // what an overlapped launch would want
+    if (!p.pre && !compact_pre) return 0;
     return (p.planes_bytes + 255) / 256 * 256;
 }
 
@@ -577,9 +609,9 @@ int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaS
         set_error("K too large for the conversion kernel");
         return SGQ_ERR_UNSUPPORTED;
     }
-    gemv_prepare_x_kernel<<<static_cast<int>(M), kPrepThreads, 0, s>>>(x, static_cast<int>(M), K, L.ndigits, L.nsets,
-                                                                      static_cast<uint8_t*>(prepared));
-    SGQ_LAUNCH_CHECK("gemv_prepare_x_kernel");
+    SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M)), dim3(kPrepThreads), 0, s,
+                               stream_overlap_enabled(), x, static_cast<int>(M), K, L.ndigits, L.nsets,
+                               static_cast<uint8_t*>(prepared)));
     return SGQ_OK;
 }
 
@@ -590,7 +622,9 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
     LinearArgs probe = a;
     if (planes_ready) probe.x = static_cast<const float*>(a.workspace);      // x is not read: only its alignment rule is waived
-    if (!gemv_supported(probe) || !make_plan(a.M, a.K, have_ws, &p) || (planes_ready && !have_ws)) {
+    const bool compact = stream_overlap_enabled();
+    if (!gemv_supported(probe) || !((compact && make_plan(a.M, a.K, have_ws, &p, true)) || make_plan(a.M, a.K, have_ws, &p)) ||
+        (planes_ready && !have_ws)) {
         set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "
                   "16-byte aligned x/packed/scales");
         return SGQ_ERR_UNSUPPORTED;

@@ -44,6 +44,30 @@ struct SmemOptIn {
     }
 };
 
+// Process-wide switch (sgq_set_stream_overlap): kernels are launched with programmatic stream
+// serialization, so that a kernel's prologue, and for the decode kernel its first weight tiles,
+// overlap the tail of the kernel before it in the stream.
+bool stream_overlap_enabled();
+
+#ifdef __CUDACC__
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute when `overlap`.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool overlap,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -26,8 +26,10 @@ from typing import Callable, Optional
 
 import torch
 
+import contextlib
+
 from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
-               linear_int4_prepared, prepared_x_bytes, quantize_int4, quantized_matmul)
+               linear_int4_prepared, prepared_x_bytes, quantize_int4, quantized_matmul, set_stream_overlap)
 
 
 @dataclass
@@ -106,12 +108,15 @@ class _Linear:
 class NanoLlamaInt4:
     def __init__(self, cfg: NanoLlamaConfig, device, batch: int, *, seed: int = 0,
                  init: Optional[Callable[[str, int], torch.Tensor]] = None, rank: int = 0, world: int = 1, group=None,
-                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO):
+                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO, overlap: bool = True):
         if cfg.n_heads % world or cfg.hidden % (32 * world) or cfg.dim % (32 * world) or cfg.vocab % (32 * world):
             raise ValueError("heads, hidden, dim and vocab must split into equal 32-row slices per rank")
         self.cfg, self.device, self.batch = cfg, torch.device(device), batch
         self.rank, self.world, self.group = rank, world, group
         self.decode_path, self.prefill_path = decode_path, prefill_path
+        # consecutive kernels overlap (sgq_set_stream_overlap): legal here because no weight is ever
+        # written by the kernel in front of the linear that reads it
+        self.overlap = overlap
         init = init or default_init(cfg, self.device, seed)
         dev = self.device
         self.ws = Workspace(dev)
@@ -263,6 +268,14 @@ class NanoLlamaInt4:
         self._linear(self.lm_head, n_rows, loc, path, planes)
         return self._gather(loc, g, full)
 
+    @contextlib.contextmanager
+    def _overlapped(self):
+        prev = set_stream_overlap(self.overlap)
+        try:
+            yield
+        finally:
+            set_stream_overlap(prev)
+
     # ---- public ---------------------------------------------------------------------------
     def reset(self):
         self.pos.zero_()
@@ -274,9 +287,10 @@ class NanoLlamaInt4:
             raise ValueError("prompt shape does not fit the model's batch / max_seq")
         self._launches = 0
         self.reset()
-        n = self._forward(prompt.reshape(-1).to(self.device), P, self.prefill_path)
-        last = n.view(B, P, self.cfg.dim)[:, -1].contiguous()
-        logits = self._logits(last, self.decode_path)
+        with self._overlapped():
+            n = self._forward(prompt.reshape(-1).to(self.device), P, self.prefill_path)
+            last = n.view(B, P, self.cfg.dim)[:, -1].contiguous()
+            logits = self._logits(last, self.decode_path)
         self.pos.fill_(P)
         return logits
 
@@ -284,8 +298,9 @@ class NanoLlamaInt4:
         """tokens [batch] int64: the token at position *pos of every sequence.  Appends it to the cache,
         advances the position and returns the logits of the next token [batch, vocab]."""
         self._launches = 0
-        n = self._forward(tokens, 1, self.decode_path)
-        logits = self._logits(n, self.decode_path, self._final_planes)
+        with self._overlapped():
+            n = self._forward(tokens, 1, self.decode_path)
+            logits = self._logits(n, self.decode_path, self._final_planes)
         self.pos.add_(1)
         self._count()
         return logits

@@ -191,7 +191,7 @@ def test_attn_decode_position_out_of_range_stores_nothing(sgq):
 
 
 # ---- the whole model ------------------------------------------------------------------------------
-def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3):
+def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3, overlap=True):
     cfg = nl.NanoLlamaConfig(dim=256, n_layers=2, n_heads=2, hidden=512, vocab=512, max_seq=64)
     B = 2
     r = np.random.default_rng(seed)
@@ -204,7 +204,7 @@ def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3):
         floats[(name, layer)] = w
         return torch.from_numpy(w)
 
-    model = nl.NanoLlamaInt4(cfg, "cuda", B, init=init, prefill_path=prefill_path)
+    model = nl.NanoLlamaInt4(cfg, "cuda", B, init=init, prefill_path=prefill_path, overlap=overlap)
     prompt = torch.from_numpy(r.integers(0, cfg.vocab, (B, prompt_len)))
     tokens, logits = model.generate(prompt, n_new, use_graph=False, keep_logits=True)
 
@@ -236,6 +236,56 @@ def test_greedy_decode_matches_full_recompute(sgq, nl, port, prompt_len, n_new, 
         top2 = np.sort(ref, axis=-1)[:, -2:]
         decided = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.max(np.abs(ref))
         assert (tokens[decided, s] == no.greedy(ref)[decided]).all(), f"token of step {s}"
+    assert sgq.device_status() == 0
+
+
+def test_overlapped_launches_agree_with_serial_ones(sgq, nl, port):
+    """Programmatic dependent launch on (the default of the model) and off: same tokens, and logits
+    equal up to fp32 summation order (an overlapped decode forward runs as two smaller CTAs per SM,
+    which add their partial sums in a different order)."""
+    _, _, tok_on, log_on, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=True)
+    _, _, tok_off, log_off, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=False)
+    np.testing.assert_array_equal(tok_on, tok_off)
+    for a, b in zip(log_on, log_off):
+        assert norm_err(a, b) <= 2e-5
+    assert sgq.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K", [(1, 4096), (4, 4096), (8, 2048), (16, 2048), (8, 5632), (3, 256)])
+def test_overlap_switch_on_back_to_back_linears(sgq, M, K):
+    """A chain of decode forwards whose inputs are the previous outputs, with and without overlap
+    (overlapped launches use the two-CTAs-per-SM form of the decode kernel)."""
+    g = torch.Generator(device="cuda").manual_seed(11 + M)
+    qs = [sgq.quantize_int4(torch.randn(K, K, device="cuda", generator=g) * (1.5 / K ** 0.5), 32) for _ in range(4)]
+    x0 = torch.randn(M, K, device="cuda", generator=g)
+    torch.cuda.synchronize()
+
+    def chain(keep=None):
+        x, ws = x0, sgq.Workspace(x0.device)
+        for _ in range(3):
+            for q in qs:
+                if keep is not None:
+                    keep.append(x)
+                x = sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws)
+        return x
+
+    prev = sgq.set_stream_overlap(False)
+    try:
+        inputs = []
+        want = chain(inputs)
+        outputs = inputs[1:] + [want]
+        sgq.set_stream_overlap(True)
+        got = chain()
+        again = chain()
+        ws = sgq.Workspace(x0.device)      # every layer on the serial run's input, launched back to back
+        singles = [sgq.quantized_matmul(x, qs[i % 4], None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws)
+                   for i, x in enumerate(inputs)]
+    finally:
+        sgq.set_stream_overlap(prev)
+    assert torch.equal(again, got)                                        # run to run: bit-identical
+    for y, ref in zip(singles, outputs):                                  # same digits, another order of fp32 partial sums
+        assert norm_err(y.cpu().numpy(), ref.cpu().numpy()) <= 2e-5
+    assert norm_err(got.cpu().numpy(), want.cpu().numpy()) <= 2e-3        # twelve chained layers amplify that rounding
     assert sgq.device_status() == 0
 
 
