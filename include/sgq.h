@@ -164,6 +164,29 @@ SGQ_API int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes
                                      const uint8_t* packed, const float* scales, const float* bias, float* y,
                                      int64_t ldy, void* stream);
 
+/* Fused all-gather for a decode forward whose output features are split over the GPUs of one box
+ * (rank q owns rows [n_offset, n_offset + N_local) of the [N_total, K] weight).  (No counterpart in
+ * the reference, which is single-device.)  The decode kernel stores its [M, N_local] slice straight
+ * into the full-width output y_ranks[r][m * ldy + n_offset + n] of EVERY rank r (plain peer stores
+ * over NVLink; y_ranks is a HOST array of `world` device pointers, entry `rank` being this GPU's own
+ * buffer, the others peer-mapped).  Same shapes as SGQ_PATH_GEMV (M <= 16, INT4 g=32, [N,K]).
+ * Follow it with sgq_peer_barrier on every rank before anything reads the outputs, and alternate
+ * between two sets of output buffers from one forward to the next: a rank that runs ahead then
+ * writes the other set while a slower rank still reads this one. */
+SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
+                                      const float* scales, const float* bias, float* const* y_ranks, int world,
+                                      int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
+                                      void* stream);
+
+/* Barrier between the GPUs of one box, in stream order, no host involvement.  signals: HOST array of
+ * `world` device pointers, signals[r] = rank r's array of `world` 64-bit slots (zero-initialised,
+ * writable by every rank: symmetric / peer-mapped memory).  local_epoch: one zero-initialised 64-bit
+ * counter in this GPU's own memory.  Every rank must call it the same number of times.  All peer
+ * stores this GPU issued before the barrier are visible on their targets once the targets' barriers
+ * return.  The wait is bounded (a few tenths of a second): if a rank never arrives the kernel gives
+ * up and sgq_device_status() reports it. */
+SGQ_API int sgq_peer_barrier(void* const* signals, int rank, int world, void* local_epoch, void* stream);
+
 /* Decode forward for callers that cannot allocate device memory.  (No counterpart in the
  * reference: there every call allocates its temporaries through MemoryAllocator.)
  *

@@ -11,6 +11,7 @@ namespace sgq {
 
 cudaError_t read_status_gemv(uint32_t* v, bool clear);
 cudaError_t read_status_gemm(uint32_t* v, bool clear);
+cudaError_t read_status_peer(uint32_t* v, bool clear);
 
 namespace {
 thread_local char g_error[512] = "";
@@ -198,10 +199,11 @@ int sgq_set_stream_overlap(int enabled) {
 }
 
 int sgq_device_status(unsigned int* word, int clear) {
-    uint32_t a = 0, b = 0;
+    uint32_t a = 0, b = 0, c = 0;
     SGQ_CUDA_TRY(read_status_gemv(&a, clear != 0));
     SGQ_CUDA_TRY(read_status_gemm(&b, clear != 0));
-    const uint32_t v = a ? a : b;
+    SGQ_CUDA_TRY(read_status_peer(&c, clear != 0));
+    const uint32_t v = a ? a : (b ? b : c);
     if (word) *word = v;
     if (v != 0) {
         set_error("device status word 0x%08x (code %u, detail %u)", v, v >> 24, v & 0xFFFFFFu);
@@ -365,6 +367,25 @@ int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes, int64_
     a.workspace = const_cast<void*>(prepared); a.workspace_bytes = prepared_bytes;
     a.stream = static_cast<cudaStream_t>(stream);
     return launch_linear_gemv_prepared(a);
+}
+
+int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed, const float* scales,
+                              const float* bias, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+    if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
+    if (n_offset < 0 || ldy < n_offset + N_local) return bad(SGQ_ERR_BAD_SHAPE, "ldy < n_offset + N_local");
+    if (!y_ranks) return bad(SGQ_ERR_NULL_POINTER, "y_ranks is NULL");
+    LinearArgs a{x, M, K, N_local, packed, scales, 4, SGQ_LAYOUT_NK, 32, SGQ_PER_TENSOR, bias, y_ranks[0], ldy, workspace,
+                 workspace_bytes, static_cast<cudaStream_t>(stream)};
+    for (int r = 0; r < world; ++r) {
+        if (!y_ranks[r]) return bad(SGQ_ERR_NULL_POINTER, "an output pointer is NULL");
+        a.peers.p[r] = y_ranks[r] + n_offset;
+    }
+    a.peers.n = world;
+    a.y = a.peers.p[0];
+    a.ldy = ldy;
+    // validate_linear wants ldy >= N for the single-output case; here rows are ldy apart and N_local wide
+    return run_linear(a, SGQ_PATH_GEMV);
 }
 
 int sgq_interleave_slices(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,

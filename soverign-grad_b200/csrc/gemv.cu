@@ -159,7 +159,8 @@ template <int NSETS, int WPB, bool PRE>
 __global__ void __launch_bounds__((kStepsPerStage * WPB + 2) * 32, WPB == 1 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
-                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages, int early_weights) {
+                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages, int early_weights,
+                    const __grid_constant__ PeerOut peers) {
     constexpr int kWarps = kStepsPerStage * WPB;
     constexpr int kConsumerThreads = kWarps * 32;
     constexpr int kGroupsPerWarp = 8 / WPB;
@@ -309,7 +310,12 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     float v = acc * (PRE ? __ldg(reinterpret_cast<const float*>(planes + (L.partial_off - L.x_off)) + m)
                                          : inv_p[m]);
                     if (bias) v += bias[n];
-                    y[static_cast<int64_t>(m) * ldy + n] = v;
+                    if (peers.n == 0) {
+                        y[static_cast<int64_t>(m) * ldy + n] = v;
+                    } else {
+                        // fused all-gather: the slice goes into every GPU's full-width output (plain peer stores)
+                        for (int r = 0; r < peers.n; ++r) peers.p[r][static_cast<int64_t>(m) * ldy + n] = v;
+                    }
                 }
             }
             __syncwarp();
@@ -552,7 +558,7 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     }
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((kStepsPerStage * WPB + 2) * 32), p.smem, a.stream,
                                overlap, map_w, map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
-                               p.nstages, overlap ? 1 : 0));
+                               p.nstages, overlap ? 1 : 0, a.peers));
     return SGQ_OK;
 }
 

@@ -84,6 +84,14 @@ int launch_codes_from_f32(int bits, const float* codes_f32, int64_t n, void* cod
 int launch_interleave(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,
                       cudaStream_t s);
 
+// Output slices written straight into the output buffers of every GPU of the box (this one
+// included): y of rank r is p[r].  n == 0: the ordinary single output LinearArgs::y.
+constexpr int kMaxPeers = 8;
+struct PeerOut {
+    float* p[kMaxPeers];
+    int n;
+};
+
 struct LinearArgs {
     const float* x;
     int64_t M, K, N;
@@ -99,6 +107,7 @@ struct LinearArgs {
     void* workspace;
     size_t workspace_bytes;
     cudaStream_t stream;
+    PeerOut peers;        // decode kernel only
 };
 
 int launch_linear_simt(const LinearArgs& a);

@@ -23,7 +23,7 @@ bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void*
 
 // Device-side status word: 0 = ok; otherwise (code << 24) | detail.  Written by a kernel whose
 // bounded wait ran out; read back by sgq_device_status().
-enum : uint32_t { kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErrMmaWait = 3, kDevErrTmemAlloc = 4 };
+enum : uint32_t { kDevErrFullWait = 1, kDevErrEmptyWait = 2, kDevErrMmaWait = 3, kDevErrTmemAlloc = 4, kDevErrPeerWait = 5 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -97,6 +97,79 @@ class ShardedLinear:
     __call__ = forward
 
 
+class PeerExchange:
+    """Symmetric memory for the fused all-gather: `n_buffers` full-width outputs [M, n_total] per
+    rank that every rank can store into, plus the barrier's signal slots.  torch's symmetric-memory
+    allocator does the mapping (plumbing); the stores and the barrier are this library's kernels."""
+
+    def __init__(self, M: int, n_total: int, device, group=None, n_buffers: int = 2):
+        import ctypes as C
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer stores only: no multicast object is bound
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.M, self.n_total, self.n_buffers = M, n_total, n_buffers
+        per = ((M * n_total + 63) // 64) * 64
+        self._out = symm.empty(n_buffers * per, dtype=torch.float32, device=device)
+        self._sig = symm.empty(64, dtype=torch.int64, device=device)
+        self._out.zero_()
+        self._sig.zero_()
+        h_out = symm.rendezvous(self._out, self.group)
+        h_sig = symm.rendezvous(self._sig, self.group)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)                       # every rank's signals are zero before anyone signals
+        self.local = [self._out[i * per: i * per + M * n_total].view(M, n_total) for i in range(n_buffers)]
+        out_ptrs = [int(p) for p in h_out.buffer_ptrs]
+        self._y_ranks = [(C.c_void_p * self.world)(*[p + i * per * 4 for p in out_ptrs]) for i in range(n_buffers)]
+        self._signals = (C.c_void_p * self.world)(*[int(p) for p in h_sig.buffer_ptrs])
+        self._epoch = torch.zeros(1, dtype=torch.int64, device=device)
+        self._handles = (h_out, h_sig)
+        self.turn = 0
+
+    def next_buffer(self) -> int:
+        i = self.turn
+        self.turn = (self.turn + 1) % self.n_buffers
+        return i
+
+    def y_ranks(self, i: int):
+        return self._y_ranks[i]
+
+    def barrier(self):
+        from . import _ptr, _stream, check, lib
+        check(lib.sgq_peer_barrier(self._signals, self.rank, self.world, _ptr(self._epoch), _stream()), "sgq_peer_barrier")
+
+
+class PeerShardedLinear:
+    """Column-sharded decode forward with the all-gather fused into the kernel's epilogue: every rank's
+    decode kernel stores its [M, n_local] slice into all ranks' [M, n_total] outputs, then one barrier
+    kernel.  Two launches per forward, no collective library on the data path."""
+
+    def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange):
+        from . import Workspace
+        self.q, self.bias, self.n_total, self.ex = q_local, bias_local, n_total, exchange
+        self.n_local = q_local.original_shape[0]
+        self.n0, self.n1 = shard_bounds(n_total, exchange.world, exchange.rank)
+        if self.n1 - self.n0 != self.n_local:
+            raise ValueError("local weight does not match this rank's slice")
+        self.ws = Workspace(q_local.qdata.device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import LAYOUT_NK, PATH_GEMV, _ptr, _stream, check, lib, linear_workspace_bytes
+        M, K = x.shape
+        i = self.ex.next_buffer()
+        need = linear_workspace_bytes(4, M, K, self.n_local, LAYOUT_NK, PATH_GEMV)
+        ws = self.ws.get(need) if need else None
+        check(lib.sgq_linear_int4_allgather(_ptr(x), M, K, self.n_local, _ptr(self.q.qdata), _ptr(self.q.scales), _ptr(self.bias),
+                                            self.ex.y_ranks(i), self.ex.world, self.n_total, self.n0,
+                                            _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0, _stream()),
+              "sgq_linear_int4_allgather")
+        self.ex.barrier()
+        return self.ex.local[i]
+
+    __call__ = forward
+
+
 def cuda_sharded_linear(q_local, bias_local, n_total: int, path: int = 0, group=None) -> ShardedLinear:
     """The product path: the local slice runs through sgq_linear_* on this rank's GPU."""
     from . import LAYOUT_NK, Workspace, quantized_matmul

@@ -44,6 +44,21 @@ def worker(rank, world, port, out_dir):
         want8 = sgq.quantized_matmul(x, q8, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_SIMT)
         lin8 = sh.cuda_sharded_linear(sh.slice_quantized(q8, n0, n1), b[n0:n1].contiguous(), N, path=sgq.PATH_SIMT)
         assert torch.equal(lin8(x), want8)
+    # fused all-gather: peer stores from the decode kernel + the barrier kernel, no NCCL on the data path
+    for (M, K, N) in [(1, 1024, 512), (8, 2048, 1024), (16, 1024, 256)]:
+        x = torch.randn(M, K, device="cuda", generator=g)
+        w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+        b = torch.randn(N, device="cuda", generator=g)
+        q_full = sgq.quantize_int4(w, 32)
+        n0, n1 = sh.shard_bounds(N, world, rank)
+        ex = sh.PeerExchange(M, N, torch.device("cuda", rank))
+        lin = sh.PeerShardedLinear(sh.slice_quantized(q_full, n0, n1), b[n0:n1].contiguous(), N, ex)
+        for rep in range(5):                                     # alternates between the two output sets
+            xr = x * (rep + 1)
+            want = sgq.quantized_matmul(xr, q_full, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV)
+            y = lin(xr)
+            torch.cuda.synchronize()
+            assert torch.equal(y, want), ("peer", M, K, N, rep)
     assert sgq.device_status() == 0
     dist.barrier()
     if rank == 0:
