@@ -9,9 +9,10 @@ X[1,4096] fp32, y = x * deq(W)^T.  One *step* = `--launches-per-step` forwards c
 weights from HBM).  Metric: achieved HBM GB/s = algorithmic bytes / time, whole job.
 
 N > 1 (torchrun): weak scaling of a column-sharded layer — every rank holds its own
-[11008,4096] column slice (N_total = 11008 * ranks), each forward is followed by the NCCL
-all-gather of the [M, 11008] output slices; value = bytes streamed by all ranks / max-over-ranks
-device time.
+[11008,4096] column slice (N_total = 11008 * ranks) and the full-width output is assembled on every
+rank per forward: the decode kernel stores its [M, 11008] slice into all ranks' outputs over NVLink
+peer mappings and a barrier kernel follows (`--nccl`: local forward + NCCL all-gather + interleave
+instead); value = bytes streamed by all ranks / max-over-ranks device time.
 
 `--impl reference` times the reference's own CPU QuantizedLinear forward (oracle/_ref, the
 unmodified sources compiled for the host) on the same workload: one forward per step.
@@ -416,9 +417,11 @@ def run_ours(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
+    if world > 1:
+        args.no_overlap = True      # measured on 2 GPUs: the per-forward barrier leaves nothing to overlap (17.3 us serial, 19.2 us overlapped)
     sgq.set_stream_overlap(not args.no_overlap)     # consecutive forwards overlap their prologue and first weight tiles
     M, copies, lps = args.M, args.copies, args.launches_per_step
-    if world > 1 and lps > 200:
+    if world > 1 and args.nccl and lps > 200:
         lps = 200
     if args.only:
         # profiling aid: run one secondary case a few times, eagerly, and print it
@@ -441,19 +444,26 @@ def run_ours(args):
     if world > 1:
         import importlib
         sh = importlib.import_module("sgq_b200.sharding")
-        # one column-sharded layer per weight set: local slice through the C ABI, NCCL all-gather, interleave
-        sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
-    y_full = sharded[0]._buffers(M, dev)[2] if sharded else None
+        if args.nccl or M > 16:
+            # one column-sharded layer per weight set: local slice through the C ABI, NCCL all-gather, interleave
+            sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
+        else:
+            # fused all-gather: the decode kernel stores its slice into every rank's output (peer stores), then one
+            # barrier kernel; two alternating output sets, shared by all layers of this shape
+            exchange = sh.PeerExchange(M, world * N_DIM, dev)
+            # barrier as its own small kernel: measured faster than the in-kernel form (17.3 vs 19.6 us per forward at N=2)
+            sharded = [sh.PeerShardedLinear(q, None, world * N_DIM, exchange, fused_barrier=False) for q in weights]
+    last = {}
 
     def forward(i):
         if sharded:
-            sharded[i % copies](x)          # every layer writes the same [M, world*N] output buffer shape
+            last["y"] = sharded[i % copies](x)          # every layer writes the same [M, world*N] output buffer shape
         else:
             sgq.quantized_matmul(x, weights[i % copies], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
 
     # collectives are launched eagerly: capturing a thousand NCCL calls into one graph buys nothing
     # (the all-gather latency dominates a sharded decode forward) and is fragile across NCCL versions
-    use_graph = not args.no_graph and world == 1
+    use_graph = not args.no_graph and (world == 1 or not args.nccl)
     if use_graph:
         try:
             graph = make_graph(torch, lambda: [forward(i) for i in range(lps)])
@@ -508,7 +518,7 @@ def run_ours(args):
         def e2e_forward(i):
             x.copy_(xh, non_blocking=True)
             forward(i)
-            yh.copy_(sharded[i % copies]._buffers(M, dev)[2] if sharded else y_local, non_blocking=True)
+            yh.copy_(last["y"] if sharded else y_local, non_blocking=True)
         e2e_graph = None
         if use_graph:
             try:
@@ -569,7 +579,9 @@ def run_ours(args):
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8 x s8 -> s32 (INT4 codes x int8 activation digits), fp32 group scales", "data": "synthetic",
         "config": {"workload": f"config2: INT4 g=32 decode GEMV, W[{N_DIM},{K_DIM}] stored [N,K], X[{M},{K_DIM}] fp32"
-                               + (f"; column-sharded, N_total={world * N_DIM}, NCCL all-gather of output slices per forward"
+                               + (f"; column-sharded, N_total={world * N_DIM}, "
+                                  + ("NCCL all-gather of output slices per forward" if args.nccl else
+                                     "output slices stored into every GPU's output by the decode kernel (NVLink peer stores) + barrier kernel")
                                   if world > 1 else ""),
                    "M": M, "K": K_DIM, "N_per_gpu": N_DIM, "group": GROUP, "launches_per_step": lps, "weight_copies": copies,
                    "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
@@ -582,7 +594,7 @@ def run_ours(args):
                      "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_LAUNCH.get(M) if world == 1 else None,
                      "peak_source": peaks["source"], "kernel": "gemv_int4_nk_kernel",
                      "launch_us": launch_ms * 1e3},
-        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * (1 if world == 1 else 2), "clocks": clocks,
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * (2 if world > 1 else 1), "clocks": clocks,
         "device_status_word": status,
     }
     if world == 1 and not args.no_extras:
@@ -615,6 +627,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--nccl", action="store_true", help="N > 1: exchange output slices with an NCCL all-gather instead of peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -170,13 +170,16 @@ SGQ_API int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes
  * into the full-width output y_ranks[r][m * ldy + n_offset + n] of EVERY rank r (plain peer stores
  * over NVLink; y_ranks is a HOST array of `world` device pointers, entry `rank` being this GPU's own
  * buffer, the others peer-mapped).  Same shapes as SGQ_PATH_GEMV (M <= 16, INT4 g=32, [N,K]).
- * Follow it with sgq_peer_barrier on every rank before anything reads the outputs, and alternate
+ * The outputs are whole once every rank has passed a barrier: either pass `signals`, `rank` and
+ * `local_state` (as for sgq_peer_barrier below; local_state = 16 zero-initialised bytes of this GPU's
+ * memory, 8-byte aligned, shared by all calls that use the same signals) and the barrier runs in the
+ * tail of the kernel itself, or pass signals = NULL and call sgq_peer_barrier afterwards.  Alternate
  * between two sets of output buffers from one forward to the next: a rank that runs ahead then
  * writes the other set while a slower rank still reads this one. */
 SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
                                       const float* scales, const float* bias, float* const* y_ranks, int world,
                                       int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
-                                      void* stream);
+                                      void* const* signals, int rank, void* local_state, void* stream);
 
 /* Barrier between the GPUs of one box, in stream order, no host involvement.  signals: HOST array of
  * `world` device pointers, signals[r] = rank r's array of `world` 64-bit slots (zero-initialised,

@@ -73,7 +73,7 @@ def _load() -> C.CDLL:
     lib.sgq_interleave_slices.argtypes = [p, i64, i64, i64, p, i64, p]
     lib.sgq_linear_int4_decode_noalloc.argtypes = [p, i64, i64, i64, p, p, p, p, i64, p]
     lib.sgq_set_stream_overlap.argtypes = [i32]
-    lib.sgq_linear_int4_allgather.argtypes = [p, i64, i64, i64, p, p, p, C.POINTER(p), i32, i64, i64, p, sz, p]
+    lib.sgq_linear_int4_allgather.argtypes = [p, i64, i64, i64, p, p, p, C.POINTER(p), i32, i64, i64, p, sz, C.POINTER(p), i32, p, p]
     lib.sgq_peer_barrier.argtypes = [C.POINTER(p), i32, i32, p, p]
     lib.sgq_prepared_x_bytes.restype = sz
     lib.sgq_prepared_x_bytes.argtypes = [i64, i64]

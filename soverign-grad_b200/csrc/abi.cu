@@ -371,7 +371,7 @@ int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes, int64_
 
 int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed, const float* scales,
                               const float* bias, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+                              size_t workspace_bytes, void* const* signals, int rank, void* local_state, void* stream) {
     if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
     if (n_offset < 0 || ldy < n_offset + N_local) return bad(SGQ_ERR_BAD_SHAPE, "ldy < n_offset + N_local");
     if (!y_ranks) return bad(SGQ_ERR_NULL_POINTER, "y_ranks is NULL");
@@ -382,6 +382,15 @@ int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_lo
         a.peers.p[r] = y_ranks[r] + n_offset;
     }
     a.peers.n = world;
+    if (signals) {
+        if (rank < 0 || rank >= world || !local_state || !aligned(local_state, 8)) return bad(SGQ_ERR_BAD_ARGUMENT, "bad rank or local_state");
+        for (int r = 0; r < world; ++r) {
+            if (!signals[r] || !aligned(signals[r], 8)) return bad(SGQ_ERR_NULL_POINTER, "a signal array is NULL or misaligned");
+            a.peers.sig[r] = static_cast<unsigned long long*>(signals[r]);
+        }
+        a.peers.rank = rank;
+        a.peers.state = static_cast<unsigned long long*>(local_state);
+    }
     a.y = a.peers.p[0];
     a.ldy = ldy;
     // validate_linear wants ldy >= N for the single-output case; here rows are ldy apart and N_local wide

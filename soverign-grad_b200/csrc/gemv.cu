@@ -321,6 +321,22 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&pempty[slot]);
         }
+        if (peers.n > 0 && peers.sig[0] != nullptr) {
+            // Barrier fused into the tail: this CTA's slices are out; the last CTA of the launch to get
+            // here tells every rank and waits for every rank, so the kernel ends when all outputs are whole.
+            __syncwarp();
+            __threadfence_system();
+            unsigned int* counter = reinterpret_cast<unsigned int*>(peers.state + 1);
+            unsigned int ticket = 0;
+            if (lane == 0) ticket = atomicAdd(counter, 1u);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket == gridDim.x - 1) {
+                if (lane == 0) *counter = 0;          // re-armed for the next launch, which counts only at its own end
+                int late = 0;
+                if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late) && lane == 0)
+                    report(kDevErrPeerWait, 0x10000u);
+            }
+        }
         return;
     }
 

@@ -30,40 +30,14 @@ struct PeerSignals {
     unsigned long long* p[kMaxPeers];   // p[r] = the signal array of rank r
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-
-constexpr uint32_t kPeerPolls = 1u << 21;   // x >= 100 ns back-off: gives up after a few tenths of a second
-
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant__ PeerSignals sig, int rank, int world,
                                                           unsigned long long* local_epoch) {
     const int lane = threadIdx.x;
-    unsigned long long epoch = 0;
-    if (lane == 0) {
-        epoch = *local_epoch + 1;
-        *local_epoch = epoch;
-    }
-    epoch = __shfl_sync(0xffffffffu, epoch, 0);
-    __threadfence_system();                       // everything this GPU stored before the barrier, peer stores included
-    if (lane < world) {
-        st_release_sys(sig.p[lane] + rank, epoch);
-        const unsigned long long* mine = sig.p[rank] + lane;
-        uint32_t polls = 0;
-        while (ld_acquire_sys(mine) < epoch) {
-            if (++polls > kPeerPolls) {
-                atomicCAS(&g_status_peer, 0u, (kDevErrPeerWait << 24) | (static_cast<uint32_t>(lane) << 16) |
-                                                  static_cast<uint32_t>(epoch & 0xFFFFu));
-                break;
-            }
-            if (polls > 64) __nanosleep(polls > 4096 ? 400 : 100);
-        }
-    }
+    pdl_launch_dependents();      // the next kernel may set itself up (and fetch weights); it still waits for this grid
+    pdl_wait();                   // the kernel that stored the slices has finished and its stores are visible here
+    int late = 0;
+    if (!peer_signal_and_wait(sig.p, rank, world, local_epoch, lane, &late) && lane == 0)
+        atomicCAS(&g_status_peer, 0u, (kDevErrPeerWait << 24) | 0x10000u);
 }
 
 }  // namespace
@@ -83,9 +57,8 @@ int sgq_peer_barrier(void* const* signals, int rank, int world, void* local_epoc
     }
     int rc = check_device();
     if (rc != SGQ_OK) return rc;
-    // launched without overlap: it must not start before the kernel that wrote the slices has finished
-    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(sig, rank, world, static_cast<unsigned long long*>(local_epoch));
-    SGQ_LAUNCH_CHECK("peer_barrier_kernel");
+    SGQ_CUDA_TRY(launch_kernel(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), stream_overlap_enabled(),
+                               sig, rank, world, static_cast<unsigned long long*>(local_epoch)));
     return SGQ_OK;
 }
 

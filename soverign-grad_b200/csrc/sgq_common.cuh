@@ -90,7 +90,45 @@ constexpr int kMaxPeers = 8;
 struct PeerOut {
     float* p[kMaxPeers];
     int n;
+    // optional barrier fused into the kernel's tail (sig[0] == nullptr: none): the signal arrays of all
+    // ranks, this rank's index, and 16 bytes of local state {u64 epoch, u32 finished-CTA counter}
+    unsigned long long* sig[kMaxPeers];
+    int rank;
+    unsigned long long* state;
 };
+
+#ifdef __CUDACC__
+// One warp: publish this GPU's next epoch to every rank and wait (bounded) until every rank has
+// published it here.  Returns false if a peer did not arrive in time.
+__device__ __forceinline__ bool peer_signal_and_wait(unsigned long long* const* sig, int rank, int world,
+                                                     unsigned long long* local_epoch, int lane, int* late_rank) {
+    unsigned long long epoch = 0;
+    if (lane == 0) {
+        epoch = *local_epoch + 1;
+        *local_epoch = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    __threadfence_system();                       // everything this GPU stored before, peer stores included
+    bool ok = true;
+    if (lane < world) {
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(sig[lane] + rank), "l"(epoch) : "memory");
+        const unsigned long long* mine = sig[rank] + lane;
+        unsigned int polls = 0;
+        for (;;) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+            if (v >= epoch) break;
+            if (++polls > (1u << 21)) {           // x >= 100 ns back-off: gives up after a few seconds at most
+                ok = false;
+                *late_rank = lane;
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 400 : 100);
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+#endif
 
 struct LinearArgs {
     const float* x;

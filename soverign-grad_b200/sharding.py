@@ -123,7 +123,7 @@ class PeerExchange:
         out_ptrs = [int(p) for p in h_out.buffer_ptrs]
         self._y_ranks = [(C.c_void_p * self.world)(*[p + i * per * 4 for p in out_ptrs]) for i in range(n_buffers)]
         self._signals = (C.c_void_p * self.world)(*[int(p) for p in h_sig.buffer_ptrs])
-        self._epoch = torch.zeros(1, dtype=torch.int64, device=device)
+        self._epoch = torch.zeros(2, dtype=torch.int64, device=device)       # {epoch, finished-CTA counter} of the barrier
         self._handles = (h_out, h_sig)
         self.turn = 0
 
@@ -142,11 +142,13 @@ class PeerExchange:
 
 class PeerShardedLinear:
     """Column-sharded decode forward with the all-gather fused into the kernel's epilogue: every rank's
-    decode kernel stores its [M, n_local] slice into all ranks' [M, n_total] outputs, then one barrier
-    kernel.  Two launches per forward, no collective library on the data path."""
+    decode kernel stores its [M, n_local] slice into all ranks' [M, n_total] outputs and runs the
+    barrier between the ranks in its own tail (fused_barrier) or as a second small kernel.  No
+    collective library on the data path."""
 
-    def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange):
+    def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange, fused_barrier: bool = True):
         from . import Workspace
+        self.fused_barrier = fused_barrier
         self.q, self.bias, self.n_total, self.ex = q_local, bias_local, n_total, exchange
         self.n_local = q_local.original_shape[0]
         self.n0, self.n1 = shard_bounds(n_total, exchange.world, exchange.rank)
@@ -162,9 +164,12 @@ class PeerShardedLinear:
         ws = self.ws.get(need) if need else None
         check(lib.sgq_linear_int4_allgather(_ptr(x), M, K, self.n_local, _ptr(self.q.qdata), _ptr(self.q.scales), _ptr(self.bias),
                                             self.ex.y_ranks(i), self.ex.world, self.n_total, self.n0,
-                                            _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0, _stream()),
+                                            _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0,
+                                            self.ex._signals if self.fused_barrier else None, self.ex.rank, _ptr(self.ex._epoch),
+                                            _stream()),
               "sgq_linear_int4_allgather")
-        self.ex.barrier()
+        if not self.fused_barrier:
+            self.ex.barrier()
         return self.ex.local[i]
 
     __call__ = forward

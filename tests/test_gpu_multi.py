@@ -52,13 +52,14 @@ def worker(rank, world, port, out_dir):
         q_full = sgq.quantize_int4(w, 32)
         n0, n1 = sh.shard_bounds(N, world, rank)
         ex = sh.PeerExchange(M, N, torch.device("cuda", rank))
-        lin = sh.PeerShardedLinear(sh.slice_quantized(q_full, n0, n1), b[n0:n1].contiguous(), N, ex)
-        for rep in range(5):                                     # alternates between the two output sets
-            xr = x * (rep + 1)
-            want = sgq.quantized_matmul(xr, q_full, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV)
-            y = lin(xr)
-            torch.cuda.synchronize()
-            assert torch.equal(y, want), ("peer", M, K, N, rep)
+        for fused in (True, False):                              # barrier in the kernel's tail / as its own kernel
+            lin = sh.PeerShardedLinear(sh.slice_quantized(q_full, n0, n1), b[n0:n1].contiguous(), N, ex, fused_barrier=fused)
+            for rep in range(5):                                 # alternates between the two output sets
+                xr = x * (rep + 1)
+                want = sgq.quantized_matmul(xr, q_full, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV)
+                y = lin(xr)
+                torch.cuda.synchronize()
+                assert torch.equal(y, want), ("peer", M, K, N, rep, fused)
     assert sgq.device_status() == 0
     dist.barrier()
     if rank == 0:
