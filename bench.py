@@ -267,11 +267,12 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
         guard(f"pack_int4_g32_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 4))
         guard(f"pack_int8_tensor_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 8))
 
-    def gemm(N, path):
+    def gemm(N, path, bits=None):
         M, K = 2048, 4096
         x = torch.randn(M, K, device=dev, generator=g)
         w = torch.randn(N, K, device=dev, generator=g) * 0.02
-        q = sgq.quantize_int4(w, GROUP) if path != sgq.PATH_TC_I8 else sgq.quantize_int8(w, sgq.PER_TENSOR)
+        bits = bits or (8 if path == sgq.PATH_TC_I8 else 4)
+        q = sgq.quantize_int4(w, GROUP) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
         y = torch.empty(M, N, device=dev)
         ws = sgq.Workspace(dev)
         if path == sgq.PATH_TC_I8:
@@ -286,6 +287,7 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
 
     for N in (4096, 11008):
         guard(f"prefill_bf16_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16))
+        guard(f"prefill_bf16_int8w_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16, bits=8))
         guard(f"prefill_i8_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_I8))
     status = sgq.device_status()
     out["device_status_word"] = status

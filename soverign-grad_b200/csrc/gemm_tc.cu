@@ -42,13 +42,13 @@ cudaError_t read_status_gemm(uint32_t* v, bool clear) {
 
 namespace {
 
-enum Mode { kI8 = 0, kBF16 = 1 };
+enum Mode { kI8 = 0, kBF16 = 1, kBF16W8 = 2 };   // W8A8 | bf16 x INT4 g=32 | bf16 x INT8 codes (scale in the epilogue)
 
 constexpr int BM = 256, BN = 256;     // two UMMA_M = 128 halves per tile
 constexpr int kHalfM = 128;
 constexpr int kABytes = BM * 128;     // 256 rows x 128 B (rows 128.. are the second half)
 constexpr int kBBytes = BN * 128;     // 256 rows x 128 B
-constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles
+constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles (kBF16); the INT8 form is twice that, Cfg::kRawStageBytes
 constexpr int kDequantWarps = 16;     // two threads per row of the 256-row weight tile (one 32-k group each)
 constexpr int kDequantGroups = 1;
 constexpr int kEpilogueWarp0 = 2;
@@ -63,15 +63,16 @@ template <int MODE>
 struct Cfg {
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kAStages = 3;
+    static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage
     static constexpr int kBStages = 3;
     static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
+    static constexpr int kRawStageBytes = MODE == kBF16W8 ? BN * 64 : kRawBytes;
     static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps * kDequantGroups;
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kAOff = 0;
     static constexpr int kBOff = kAStages * kABytes;
     static constexpr int kRawOff = kBOff + kBStages * kBBytes;
-    static constexpr int kOutOff = kRawOff + kRawStages * kRawBytes;   // 4 epilogue warps x [16 rows x 32 fp32], swizzled
+    static constexpr int kOutOff = kRawOff + kRawStages * kRawStageBytes;   // 4 epilogue warps x [16 rows x 32 fp32], swizzled
     static constexpr int kBarOffset = kOutOff + 4 * 2048;
     static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * (kRawStages ? kRawStages : 1) + 4;
     static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 + 1024;   // barriers + tmem slot + alignment slack
@@ -205,8 +206,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 } else {
                     const int s = rr.slot;
                     if (!mbar_wait(&raw_empty[s], rr.phase ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | static_cast<uint32_t>(it)); break; }
-                    mbar_arrive_expect_tx(&raw_full[s], kRawBytes);
-                    tma_load_2d(smem + C::kRawOff + s * kRawBytes, &map_b, &raw_full[s], w.kb * (C::kBlockK / 2), n0);
+                    mbar_arrive_expect_tx(&raw_full[s], C::kRawStageBytes);
+                    tma_load_2d(smem + C::kRawOff + s * C::kRawStageBytes, &map_b, &raw_full[s],
+                                w.kb * (MODE == kBF16W8 ? C::kBlockK : C::kBlockK / 2), n0);
                 }
             }
         }
@@ -262,7 +264,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // row segments.
         uint8_t* stage_out = smem + C::kOutOff + (warp - kEpilogueWarp0) * 2048;
         const int cq = lane & 7, rq = lane >> 3;                  // after the transpose: columns 4cq..4cq+3, rows rq + 4i
-        const float sw_all = (MODE == kI8 && !p.sw_per_row) ? p.sw[0] : 1.0f;
+        constexpr bool kScaleN = MODE == kI8 || MODE == kBF16W8;       // weight scale applied per output column here
+        const float sw_all = (kScaleN && !p.sw_per_row) ? p.sw[0] : 1.0f;
         for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             if (!mbar_wait(&tmem_full[0], tcount & 1u)) { report(kDevErrMmaWait, 0x800000u | tcount); alive = false; break; }
@@ -289,7 +292,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         if (n4 + e < p.N) {
-                            if (MODE == kI8 && p.sw_per_row) swv[e] = p.sw[n4 + e];
+                            if (kScaleN && p.sw_per_row) swv[e] = p.sw[n4 + e];
                             if (p.bias) bv[e] = p.bias[n4 + e];
                         }
                     }
@@ -320,7 +323,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             const int row = rq + 4 * i;                // 0..15 inside the part
                             const int64_t mm = mrow0 + part * 16 + row;
                             float4 o = *reinterpret_cast<const float4*>(stage_out + row * 128 + ((cq ^ (row & 7)) << 4));
-                            if (MODE == kI8) {
+                            if (kScaleN) {
                                 o.x = __fmul_rn(o.x, swv[0]); o.y = __fmul_rn(o.y, swv[1]); o.z = __fmul_rn(o.z, swv[2]); o.w = __fmul_rn(o.w, swv[3]);
                             }
                             if (p.bias) {
@@ -344,6 +347,51 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[0]);
+        }
+    } else if (MODE == kBF16W8 && warp >= kDequantWarp0) {
+        // ------------------------------- int8 -> bf16 --------------------------------
+        // Thread (r, h) owns 32 consecutive codes of row r (32 bytes in, 64 bytes of bf16 out).  A code
+        // c = 16*hi + lo (hi signed, lo unsigned nibble) is built exactly from two magic numbers:
+        // 0x4300|lo = 128 + lo, 0x4300|(hi^8) = 136 + hi, t = fma(136 + hi, 16, -2304) = 16 hi - 128,
+        // c = fma(128 + lo, 1, t).  The weight scale is applied in fp32 by the epilogue, so the only
+        // rounding of this path is x -> bf16.  Bytes (0,2) and (1,3) of a word leave as pairs: inside
+        // every 4 codes the order is k+{0,2,1,3}, which is the order the activations were stored in.
+        const int tid = threadIdx.x - kDequantWarp0 * 32;
+        const int r = tid >> 1, h = tid & 1;
+        Ring<NR> rr;
+        Ring<NB> rb;
+        bool alive = true;
+        for (int64_t it = 0; it < total_its && alive; ++it) {
+            const int sr = rr.slot, sb = rb.slot;
+            if (!mbar_wait(&raw_full[sr], rr.phase)) { report(kDevErrFullWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
+            const uint8_t* src = smem + C::kRawOff + sr * C::kRawStageBytes + r * 64 + h * 32;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(src);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(src + 16);
+            asm volatile("" ::"r"(w0.x), "r"(w0.y), "r"(w0.z), "r"(w0.w), "r"(w1.x), "r"(w1.y), "r"(w1.z), "r"(w1.w) : "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[sr]);            // the codes are in registers: slot can be refilled
+            if (!mbar_wait(&b_empty[sb], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
+            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            uint8_t* brow = smem + C::kBOff + sb * kBBytes + r * 128;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {                           // output chunk w: words 2w and 2w+1
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t word = words[2 * w + (j >> 1)] >> (8 * (j & 1));     // bytes (0,2), then (1,3)
+                    const uint32_t lo = (word & 0x000F000Fu) | 0x43004300u;            // 128 + lo
+                    const uint32_t hi = ((word >> 4) & 0x000F000Fu) ^ 0x43084308u;     // 136 + hi
+                    uint32_t t;
+                    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(t) : "r"(hi), "r"(0x41804180u), "r"(0xC510C510u));   // 16 hi - 128
+                    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(lo), "r"(0x3F803F80u), "r"(t));
+                }
+                *reinterpret_cast<uint4*>(brow + (((4 * h + w) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&b_full[sb]);
+            rr.advance();
+            rb.advance();
         }
     } else if (MODE == kBF16 && warp >= kDequantWarp0) {
         // ------------------------------- dequant ------------------------------------
@@ -429,6 +477,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 // x fp32 [M,K] -> bf16 [M,K]; inside every aligned group of 8 the order is k+{0,4,1,5,2,6,3,7},
 // the order in which the dequant warps emit the 8 nibbles of a packed word.
+// kCodeBytes (INT8 weights): inside every aligned group of 8 the order is k+{0,2,1,3,4,6,5,7} instead.
+template <bool kCodeBytes>
 __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __restrict__ x, uint4* __restrict__ out,
                                                              int64_t chunks) {
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -440,7 +490,8 @@ __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __rest
             return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
                    (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
         };
-        out[i] = make_uint4(pk(a.x, b.x), pk(a.y, b.y), pk(a.z, b.z), pk(a.w, b.w));
+        out[i] = kCodeBytes ? make_uint4(pk(a.x, a.z), pk(a.y, a.w), pk(b.x, b.z), pk(b.y, b.w))
+                            : make_uint4(pk(a.x, b.x), pk(a.y, b.y), pk(a.z, b.z), pk(a.w, b.w));
     }
 }
 
@@ -462,7 +513,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
 }  // namespace
 
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group) {
-    return bits == 4 && layout == SGQ_LAYOUT_NK && group == 32 && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 &&
+    return ((bits == 4 && group == 32) || bits == 8) && layout == SGQ_LAYOUT_NK && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 &&
            M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31);
 }
 
@@ -473,7 +524,7 @@ size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int la
 
 int launch_linear_tc_bf16(const LinearArgs& a) {
     if (!tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group)) {
-        set_error("bf16 tensor-core path needs INT4 g=32 weights stored [N,K] and K%%64==0");
+        set_error("bf16 tensor-core path needs INT4 g=32 or INT8 weights stored [N,K] and K%%64==0");
         return SGQ_ERR_UNSUPPORTED;
     }
     if (!aligned(a.x, 16) || !aligned(a.wq, 16) || !aligned(a.scales, 8)) {
@@ -488,19 +539,30 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
     const int64_t chunks = a.M * a.K / 8;
     int64_t blocks = ceil_div(chunks, 256);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-    convert_x_bf16_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, a.stream>>>(
-        a.x, static_cast<uint4*>(a.workspace), chunks);
+    const int cgrid = static_cast<int>(blocks < cap ? blocks : cap);
+    if (a.bits == 8)
+        convert_x_bf16_kernel<true><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
+    else
+        convert_x_bf16_kernel<false><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
     SGQ_LAUNCH_CHECK("convert_x_bf16_kernel");
 
     CUtensorMap ma, mb;
     if (!make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.workspace, static_cast<uint64_t>(a.K),
                             static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K) * 2, 64, BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return SGQ_ERR_CUDA;
+    Params p{};
+    p.bias = a.bias; p.y = a.y; p.ldy = a.ldy; p.M = a.M; p.N = a.N; p.K = a.K;
+    if (a.bits == 8) {
+        if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
+                                static_cast<uint64_t>(a.K), 64, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return SGQ_ERR_CUDA;
+        p.sw = a.scales;
+        p.sw_per_row = (a.scheme == SGQ_PER_ROW) ? 1 : 0;
+        return launch_tc<kBF16W8>(ma, mb, p, a.stream);
+    }
     if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, static_cast<uint64_t>(a.K / 2),
                             static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
         return SGQ_ERR_CUDA;
-    Params p{};
-    p.bias = a.bias; p.y = a.y; p.ldy = a.ldy; p.M = a.M; p.N = a.N; p.K = a.K;
     p.wscales = a.scales;
     return launch_tc<kBF16>(ma, mb, p, a.stream);
 }

@@ -175,6 +175,32 @@ def test_tc_bf16_against_port(sgq, port, M, K, N):
     assert rel_err(y, want) <= (TOL_BF16 if K >= 1024 else 8e-2), rel_err(y, want)
 
 
+@pytest.mark.parametrize("M,K,N", TC_SHAPES)
+def test_tc_bf16_int8_weights_against_port(sgq, port, M, K, N):
+    """INT8 weight codes on the bf16 tensor-core path: the codes are exact in bf16 and the weight
+    scale is applied in fp32 by the epilogue, so the only rounding is x -> bf16."""
+    rng = np.random.default_rng(3 * M + 7 * K + 13 * N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = cases.weight_with_outliers(M + K + N + 1, (N, K))
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    for scheme in (cases.PER_TENSOR, cases.PER_ROW):
+        wq, ws = port.quantize_int8(w, scheme)
+        want = port.qlinear_int8(x, wq, ws, K, N, cases.LAYOUT_NK, scheme, b)
+        q = sgq.quantize_int8(dev(w), scheme)
+        y = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_TC_BF16).cpu().numpy()
+        check_status(sgq)
+        sw = np.broadcast_to(np.asarray(ws, np.float32).reshape(-1, 1) if scheme == cases.PER_ROW else np.float32(ws[0]), (N, 1))
+        acc = (bf16_round(x).astype(np.float64) @ wq.astype(np.float64).T).astype(np.float32)
+        model = (acc * sw.reshape(1, N)).astype(np.float32) + b[None, :]
+        assert rel_err(y, model) <= 2e-5, ("layout/pipeline error, not rounding", rel_err(y, model))
+        assert norm_err(y, want) <= TOL_BF16, norm_err(y, want)
+        assert rel_err(y, want) <= (TOL_BF16 if K >= 1024 else 8e-2), rel_err(y, want)
+    if M >= 64:     # AUTO takes this path for INT8 weights stored [N,K] when a workspace is supplied
+        y_auto = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO,
+                                      workspace=sgq.Workspace(torch.device("cuda"))).cpu().numpy()
+        assert np.array_equal(y_auto, y)
+
+
 I8_SHAPES = [(128, 128, 256), (128, 512, 256), (200, 1024, 300), (1, 16, 8), (260, 272, 520), (64, 4096, 128)]
 
 
