@@ -248,6 +248,23 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
     guard("gemv_M16_auto", lambda: gemv(16, sgq.PATH_AUTO))
     guard("gemv_M1_simt", lambda: gemv(1, sgq.PATH_SIMT))
 
+    def gemv_int8(M, N, K):
+        # one 235 MB weight (config 5 shape) is larger than L2 by itself
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        q = sgq.quantize_int8(w, sgq.PER_TENSOR)
+        del w
+        x = torch.randn(M, K, device=dev, generator=g)
+        y = torch.empty(M, N, device=dev)
+        ws = sgq.Workspace(dev)
+        f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, out=y, workspace=ws)  # noqa: E731
+        ms = timer(f, 10, inner=10)
+        nbytes = N * K + 4 + M * K * 4 + M * N * 4
+        return {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                "path": "gemv (int8 codes x int8 activation digits -> s32)", "launches_per_forward": 2}
+
+    for M in (1, 16):
+        guard(f"gemv_int8_tensor_M{M}_28672x8192", lambda M=M: gemv_int8(M, 28672, 8192))
+
     def pack(shape, bits):
         # two inputs > L2 in total for the big shape; alternate so the small one also misses L2
         ws_ = [torch.randn(shape, device=dev, generator=g) * 0.02 for _ in range(3)]

@@ -12,6 +12,7 @@ namespace sgq {
 cudaError_t read_status_gemv(uint32_t* v, bool clear);
 cudaError_t read_status_gemm(uint32_t* v, bool clear);
 cudaError_t read_status_peer(uint32_t* v, bool clear);
+cudaError_t read_status_gemv_i8(uint32_t* v, bool clear);
 
 namespace {
 thread_local char g_error[512] = "";
@@ -143,7 +144,8 @@ int run_linear(LinearArgs a, int path) {
     if ((rc = check_device()) != SGQ_OK) return rc;
     if (a.K == 0) return launch_linear_simt(a);  // y = bias
     if (path == SGQ_PATH_AUTO) {
-        if (gemv_supported(a))
+        if (gemv_supported(a) || (gemv_i8_supported(a) && a.workspace && aligned(a.workspace, 256) &&
+                                  a.workspace_bytes >= gemv_i8_workspace_bytes(a.M, a.K)))
             path = SGQ_PATH_GEMV;
         else if (a.M >= 64 && tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
                  a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
@@ -156,7 +158,7 @@ int run_linear(LinearArgs a, int path) {
         case SGQ_PATH_SIMT:
             return launch_linear_simt(a);
         case SGQ_PATH_GEMV:
-            return launch_linear_gemv(a);
+            return a.bits == 8 ? launch_linear_gemv_i8(a) : launch_linear_gemv(a);
         case SGQ_PATH_TC_BF16:
             return launch_linear_tc_bf16(a);
         case SGQ_PATH_TC_I8:
@@ -199,11 +201,12 @@ int sgq_set_stream_overlap(int enabled) {
 }
 
 int sgq_device_status(unsigned int* word, int clear) {
-    uint32_t a = 0, b = 0, c = 0;
+    uint32_t a = 0, b = 0, c = 0, d = 0;
     SGQ_CUDA_TRY(read_status_gemv(&a, clear != 0));
     SGQ_CUDA_TRY(read_status_gemm(&b, clear != 0));
     SGQ_CUDA_TRY(read_status_peer(&c, clear != 0));
-    const uint32_t v = a ? a : (b ? b : c);
+    SGQ_CUDA_TRY(read_status_gemv_i8(&d, clear != 0));
+    const uint32_t v = a ? a : (b ? b : (c ? c : d));
     if (word) *word = v;
     if (v != 0) {
         set_error("device status word 0x%08x (code %u, detail %u)", v, v >> 24, v & 0xFFFFFFu);
@@ -279,11 +282,12 @@ size_t sgq_linear_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int
     if (M <= 0 || K <= 0 || N <= 0) return 0;
     switch (path) {
         case SGQ_PATH_SIMT: return 0;
-        case SGQ_PATH_GEMV: return gemv_workspace_bytes(bits, M, K, N, layout);
+        case SGQ_PATH_GEMV:
+            return bits == 8 ? (layout == SGQ_LAYOUT_NK ? gemv_i8_workspace_bytes(M, K) : 0) : gemv_workspace_bytes(bits, M, K, N, layout);
         case SGQ_PATH_TC_BF16: return tc_bf16_workspace_bytes(bits, M, K, N, layout);
         case SGQ_PATH_TC_I8: return tc_i8_workspace_bytes(M, K, N);
         default: {  // AUTO: enough for whichever path AUTO may take
-            size_t a = gemv_workspace_bytes(bits, M, K, N, layout);
+            size_t a = bits == 8 ? (layout == SGQ_LAYOUT_NK ? gemv_i8_workspace_bytes(M, K) : 0) : gemv_workspace_bytes(bits, M, K, N, layout);
             size_t b = M >= 64 ? tc_bf16_workspace_bytes(bits, M, K, N, layout) : 0;
             return a > b ? a : b;
         }

@@ -156,6 +156,9 @@ int launch_linear_gemv_static(LinearArgs a);   // scratch in a file-scope device
 size_t gemv_prepared_bytes(int64_t M, int64_t K);            // 0: no prepared form for this (M, K)
 int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s);
 int launch_linear_gemv_prepared(const LinearArgs& a);        // a.workspace = prepared activations, a.x unused
+bool gemv_i8_supported(const LinearArgs& a);                 // INT8 weights stored [N,K], M <= 16
+size_t gemv_i8_workspace_bytes(int64_t M, int64_t K);
+int launch_linear_gemv_i8(const LinearArgs& a);
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_tc_bf16(const LinearArgs& a);

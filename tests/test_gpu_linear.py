@@ -115,6 +115,43 @@ def test_decode_kernel_against_port(sgq, port, M, K, N):
     assert np.array_equal(y2, sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV).cpu().numpy())
 
 
+DECODE_I8_SHAPES = [(1, 128, 16), (1, 1024, 40), (2, 1152, 17), (3, 4096, 100), (4, 4096, 512), (5, 2304, 48), (6, 2048, 129),
+                    (8, 2048, 1000), (9, 8192, 33), (16, 8192, 272), (16, 640, 64), (1, 8192, 2400)]
+
+
+@pytest.mark.parametrize("M,K,N", DECODE_I8_SHAPES)
+def test_decode_int8_kernel_against_port(sgq, port, M, K, N):
+    """INT8 weights (per tensor and per row) on the integer decode kernel against the reference-order
+    fp32 forward of the port, and against an exact model of the kernel's own arithmetic."""
+    rng = np.random.default_rng(M * 1000003 + K * 101 + N + 5)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.1, 30.0, (M, 1))).astype(np.float32)     # rows of different magnitude
+    w = cases.weight_with_outliers(K + N + 1, (N, K))
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    ws = sgq.Workspace(torch.device("cuda"))
+    for scheme in (cases.PER_TENSOR, cases.PER_ROW):
+        wq, sw = port.quantize_int8(w, scheme)
+        want = port.qlinear_int8(x, wq, sw, K, N, cases.LAYOUT_NK, scheme, b)
+        q = sgq.quantize_int8(dev(w), scheme)
+        assert sgq.linear_workspace_bytes(8, M, K, N, cases.LAYOUT_NK, sgq.PATH_GEMV) > 0
+        y = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+        check_status(sgq)
+        assert rel_err(y, want) <= TOL_FP32, (M, K, N, scheme, rel_err(y, want))
+        # the kernel's own arithmetic: x in fixed point (22 / 14 fractional bits below the power of two
+        # above the row's absmax, round to nearest), exact integer dot products, then fp32 scaling
+        frac = 22 if M <= 5 else 14
+        e = np.floor(np.log2(np.abs(x).max(axis=1, keepdims=True).astype(np.float64))) + 1
+        xq = np.rint(x.astype(np.float64) * 2.0 ** (frac - e))
+        model = (xq @ wq.astype(np.float64).T) * 2.0 ** (e - frac) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
+        assert rel_err(y, model) <= 2e-6, ("layout/pipeline error, not rounding", rel_err(y, model))
+        y_auto = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws).cpu().numpy()
+        assert np.array_equal(y_auto, y)                         # AUTO takes this kernel when a workspace is supplied
+    with pytest.raises(sgq.SgqError) as err:                     # no workspace: refused, never silently rerouted
+        sgq.lib  # noqa: B018
+        sgq.check(sgq.lib.sgq_linear_int8(q.qdata.data_ptr(), M, K, N, q.qdata.data_ptr(), q.scales.data_ptr(), cases.LAYOUT_NK,
+                                          cases.PER_ROW, None, q.qdata.data_ptr(), N, sgq.PATH_GEMV, None, 0, None))
+    assert err.value.status == 5
+
+
 def test_decode_kernel_rejects_what_it_cannot_run(sgq):
     w = torch.randn(64, 96, device="cuda")       # K = 96 is not a multiple of 256
     q = sgq.quantize_int4(w, 32)
