@@ -63,7 +63,7 @@ template <int MODE>
 struct Cfg {
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage
+    static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage         // the INT8 raw ring takes the room of one A stage
     static constexpr int kBStages = 3;
     static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
     static constexpr int kRawStageBytes = MODE == kBF16W8 ? BN * 64 : kRawBytes;
@@ -367,9 +367,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint8_t* src = smem + C::kRawOff + sr * C::kRawStageBytes + r * 64 + h * 32;
             const uint4 w0 = *reinterpret_cast<const uint4*>(src);
             const uint4 w1 = *reinterpret_cast<const uint4*>(src + 16);
-            asm volatile("" ::"r"(w0.x), "r"(w0.y), "r"(w0.z), "r"(w0.w), "r"(w1.x), "r"(w1.y), "r"(w1.z), "r"(w1.w) : "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[sr]);            // the codes are in registers: slot can be refilled
+            // the slot is handed back only once the codes really are in registers
+            const uint32_t landed = loads_landed(w0.x ^ w0.y ^ w0.z ^ w0.w ^ w1.x ^ w1.y ^ w1.z ^ w1.w);
+            if (lane == 0) mbar_arrive_after(&raw_empty[sr], landed);
             if (!mbar_wait(&b_empty[sb], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
             const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
             uint8_t* brow = smem + C::kBOff + sb * kBBytes + r * 128;
@@ -434,9 +434,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!mbar_wait(&raw_full[sr], rr.phase)) { report(kDevErrFullWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
                 const uint4 w0 = *reinterpret_cast<const uint4*>(smem + C::kRawOff + sr * kRawBytes + r * 32 + h * 16);
                 // make sure the load has returned before the slot is handed back to the TMA producer
-                asm volatile("" ::"r"(w0.x), "r"(w0.y), "r"(w0.z), "r"(w0.w) : "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&raw_empty[sr]);        // the nibbles are in registers: slot can be refilled
+                // the slot is handed back only once the nibbles really are in registers
+                const uint32_t landed = loads_landed(w0.x ^ w0.y ^ w0.z ^ w0.w);
+                if (lane == 0) mbar_arrive_after(&raw_empty[sr], landed);
                 if (!mbar_wait(&b_empty[sb], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x400000u | static_cast<uint32_t>(it)); alive = false; break; }
                 const uint32_t words[4] = {w0.x, w0.y, w0.z, w0.w};
                 const uint32_t sx2 = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sc))) * 0x00010001u;

@@ -493,9 +493,13 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
             }
-            __syncwarp();
+            // everything loaded from the stage has been consumed once the accumulators are final
+            uint32_t fold = 0;
+#pragma unroll
+            for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
+            const uint32_t landed = loads_landed(fold);
             if (seq < 5) SGQ_MARK(4 + 2 * seq);
-            if (lane == 0) mbar_arrive(&empty[st]);
+            if (lane == 0) mbar_arrive_after(&empty[st], landed);
         }
         if (tile == blockIdx.x) SGQ_MARK(13);
 

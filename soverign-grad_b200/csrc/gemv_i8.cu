@@ -238,8 +238,12 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[st]);
+            // everything loaded from the stage has been consumed once the accumulators are final
+            uint32_t fold = 0;
+#pragma unroll
+            for (int s = 0; s < NSETS; ++s) fold ^= static_cast<uint32_t>(acc[s][0] ^ acc[s][3]);
+            const uint32_t landed = loads_landed(fold);
+            if (lane == 0) mbar_arrive_after(&empty[st], landed);
         }
 
         // ---- tile epilogue: partial sums -> shared memory, one barrier, one output per thread ----

@@ -49,6 +49,21 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Handing a shared-memory slot back to the producer must not overtake the warp's own loads from
+// that slot: an arrive is not ordered behind loads whose results nothing has consumed yet (seen as
+// corrupted weight rows when a refill from L2 landed before a pending 128-bit shared load).
+// loads_landed() makes the warp consume the loaded registers in a vote, mbar_arrive_after() makes
+// the arrive depend on that vote.  (The vote is 0 unless all 32 lanes hold one particular pattern.)
+__device__ __forceinline__ uint32_t loads_landed(uint32_t v) { return __ballot_sync(0xffffffffu, v == 0x9E3779B9u); }
+__device__ __forceinline__ void mbar_arrive_after(uint64_t* bar, uint32_t vote) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.u32 p, %1, 0xFFFFFFFF;\n"
+        "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n"
+        "}" ::"r"(smem_u32(bar)), "r"(vote)
+        : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");

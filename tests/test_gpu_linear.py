@@ -311,3 +311,40 @@ def test_column_slices_reassemble(sgq):
     # all-gather order [world][M][n_local] -> row-major
     gathered = torch.stack([full[:, r * nl:(r + 1) * nl].contiguous() for r in range(world)])
     assert torch.equal(sgq.interleave_slices(gathered, world, M, nl), full)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 1024, 8192])
+def test_config5_large_shapes(sgq, port, M):
+    """BASELINE config 5 at full size on one GPU: W[28672, 8192] as INT4 g=32 and INT8 per tensor,
+    X[M, 8192].  Too large for a CPU forward, so: 24 sampled output features against the port on the
+    GPU's own codes (the quantizer is bit-exact, tested elsewhere), and Y(2x) = 2 Y(x) exactly (a
+    power-of-two factor moves no digit, no bf16 mantissa and no fp32 product)."""
+    N, K = 28672, 8192
+    g = torch.Generator(device="cuda").manual_seed(5 + M)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    x = torch.randn(M, K, device="cuda", generator=g)
+    b = torch.randn(N, device="cuda", generator=g) * 0.1
+    rows = np.unique(np.concatenate([[0, 15, 16, N - 1], np.random.default_rng(M).integers(0, N, 20)]))
+    ws = sgq.Workspace(torch.device("cuda"))
+    xs = x[: min(M, 64)].cpu().numpy()                       # the port forward on 64 batch rows is enough
+    bn = b.cpu().numpy()
+    for bits in (4, 8):
+        q = sgq.quantize_int4(w, 32) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
+        y = sgq.quantized_matmul(x, q, b, layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws)
+        check_status(sgq)
+        if bits == 4:
+            packed = q.qdata.view(N, K // 2)[rows].cpu().numpy().reshape(-1)
+            scales = q.scales.view(N, K // 32)[rows].cpu().numpy().reshape(-1)
+            want = port.qlinear_int4(xs, packed, scales, K, len(rows), cases.LAYOUT_NK, 32, bn[rows])
+        else:
+            codes = q.qdata.view(N, K)[rows].cpu().numpy()
+            want = port.qlinear_int8(xs, codes, q.scales.cpu().numpy(), K, len(rows), cases.LAYOUT_NK, cases.PER_TENSOR, bn[rows])
+        got = y[: xs.shape[0]][:, torch.from_numpy(rows).cuda()].cpu().numpy()
+        tensor_core = M >= 64
+        assert norm_err(got, want) <= (TOL_BF16 if tensor_core else TOL_FP32), (bits, M, norm_err(got, want))
+        assert rel_err(got, want) <= (TOL_BF16 if tensor_core else TOL_FP32), (bits, M, rel_err(got, want))
+        y0 = sgq.quantized_matmul(x, q, None, layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws)
+        y2 = sgq.quantized_matmul(x * 2, q, None, layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws)
+        assert torch.equal(y2, y0 * 2), (bits, M)
+        del q, y, y0, y2
+    check_status(sgq)
