@@ -292,17 +292,30 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 report(kDevErrFullWait, 0x800000u | tcount);
                 break;
             }
-            const float* pbuf = partial + slot * (kWarps * kPStride);
+            if (tcount < 6) SGQ_MARK(2 * tcount);
+            float* pbuf = partial + slot * (kWarps * kPStride);
+            // Step 1: add the warps' partial sums fragment-wise, in warp order (fixed order -> the same
+            // bits every run): lane L owns the float4 every consumer lane L wrote, so these are
+            // conflict-free 128-bit reads.  The sum goes back into warp 0's part of the slot.
+#pragma unroll
+            for (int s = 0; s < NSETS; ++s) {
+                float4 sum = *reinterpret_cast<const float4*>(pbuf + (s * 32 + lane) * 4);
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) {
+                    const float4 v = *reinterpret_cast<const float4*>(pbuf + w * kPStride + (s * 32 + lane) * 4);
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) = sum;
+            }
+            __syncwarp();
+            // Step 2: one value per (output, digit): recombine the digits, scale, add bias, store.
             for (int p = lane; p < pairs; p += 32) {
                 const int r = p & 15, m = p >> 4;
                 const int gg = r & 7, hi = r >> 3;
                 float acc = 0.0f, weight = 1.0f;
                 for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
                     const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
-                    const float* src = pbuf + (set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1);
-                    float v = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < kWarps; ++w) v += src[w * kPStride];
+                    const float v = pbuf[(set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1)];
                     acc = __fmaf_rn(weight, v, acc);
                 }
                 const int64_t n = tile * kRows + r;
@@ -314,11 +327,12 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         y[static_cast<int64_t>(m) * ldy + n] = v;
                     } else {
                         // fused all-gather: the slice goes into every GPU's full-width output (plain peer stores)
-                        for (int r = 0; r < peers.n; ++r) peers.p[r][static_cast<int64_t>(m) * ldy + n] = v;
+                        for (int r2 = 0; r2 < peers.n; ++r2) peers.p[r2][static_cast<int64_t>(m) * ldy + n] = v;
                     }
                 }
             }
             __syncwarp();
+            if (tcount < 6) SGQ_MARK(2 * tcount + 1);
             if (lane == 0) mbar_arrive(&pempty[slot]);
         }
         if (peers.n > 0 && peers.sig[0] != nullptr) {
@@ -485,10 +499,11 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         total[s][0] += __int_as_float(d[0]); total[s][1] += __int_as_float(d[1]);
                         total[s][2] += __int_as_float(d[2]) * sc_lo[i]; total[s][3] += __int_as_float(d[3]) * sc_hi[i];
 #else
-                        total[s][0] = __fmaf_rn(sc_lo[i], static_cast<float>(d[0]), total[s][0]);
-                        total[s][1] = __fmaf_rn(sc_lo[i], static_cast<float>(d[1]), total[s][1]);
-                        total[s][2] = __fmaf_rn(sc_hi[i], static_cast<float>(d[2]), total[s][2]);
-                        total[s][3] = __fmaf_rn(sc_hi[i], static_cast<float>(d[3]), total[s][3]);
+                        // d holds 12582912.0f + (exact group sum) as fp32 bits: one subtraction instead of a conversion
+                        total[s][0] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[0]), kGroupSumBiasF), total[s][0]);
+                        total[s][1] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[1]), kGroupSumBiasF), total[s][1]);
+                        total[s][2] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[2]), kGroupSumBiasF), total[s][2]);
+                        total[s][3] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[3]), kGroupSumBiasF), total[s][3]);
 #endif
                     }
                 }

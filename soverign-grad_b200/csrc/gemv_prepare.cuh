@@ -15,6 +15,13 @@ namespace sgq {
 
 constexpr int kPreparedMaxM = 16;
 
+// The accumulator of a group's integer MMA starts at (-8 * sum of digits) + kGroupSumBias.  The first
+// term cancels the +8 offset of the unpacked nibbles; the second makes the int32 result, read as
+// fp32 bits, equal to 12582912.0f + S for the exact group sum S (|S| <= 32 * 15 * 128 < 2^22), so the
+// kernel gets S as a float with one full-rate subtraction instead of an int-to-float conversion.
+constexpr int kGroupSumBias = 0x4B400000;
+constexpr float kGroupSumBiasF = 12582912.0f;
+
 struct PreparedLayout {
     int ndigits, nsets;
     size_t bytes;          // digit planes + corrections + row scales
@@ -48,7 +55,7 @@ __device__ __forceinline__ uint32_t gather_byte(uint32_t a, uint32_t b, uint32_t
 // group's correction.  The four lanes holding the four chunks of a 32-k group must call together.
 //   xs  : [group][set][col 8][t 4] x 8 bytes; the 8 bytes of (col, t) are the digits of
 //         k = 32*group + 8t + {0,2,4,6} (b0) and + {1,3,5,7} (b1); column col = m*ndigits + j.
-//   corr: [group][set][col 8] int32 = -8 * sum over the group's 32 k of that column's digits.
+//   corr: [group][set][col 8] int32 = kGroupSumBias - 8 * sum over the group's 32 k of that column's digits.
 __device__ __forceinline__ void row_scale(uint32_t mb, int frac_bits, float* P, float* invP) {
     // P = 2^(frac_bits - e) with 2^e > absmax (e = exponent of absmax + 1); absmax 0 -> P = 1
     const int e = static_cast<int>(mb >> 23) - 127 + 1;
@@ -76,7 +83,7 @@ __device__ __forceinline__ void digits_item(const float (&v)[8], float P, int m,
             *reinterpret_cast<uint2*>(xs + (static_cast<size_t>(group) * nsets + set) * 256 + (cc * 4 + t) * 8) =
                 make_uint2(b0, b1);
             if (t == 0)
-                *reinterpret_cast<int*>(corr + (static_cast<size_t>(group) * nsets + set) * 32 + cc * 4) = -8 * sum;
+                *reinterpret_cast<int*>(corr + (static_cast<size_t>(group) * nsets + set) * 32 + cc * 4) = kGroupSumBias - 8 * sum;
         }
     }
 }
