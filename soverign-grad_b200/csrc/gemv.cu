@@ -579,6 +579,17 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
     return false;
 }
 
+// Rows of the batch one launch can take: the largest m <= M whose activation planes fit in shared
+// memory next to the pipeline stages (0: not even one row fits).  Larger batches run as several
+// launches over row blocks; each streams the weights again, which is still far better than the
+// any-shape kernel.
+int64_t rows_per_launch(int64_t M, int64_t K) {
+    Plan p;
+    for (int64_t m = M; m >= 1; --m)
+        if (make_plan(m, K, false, &p)) return m;
+    return 0;
+}
+
 template <int NSETS, int WPB, bool PRE>
 int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                    bool planes_ready) {
@@ -613,7 +624,7 @@ bool gemv_supported(const LinearArgs& a) {
     Plan p;
     return a.bits == 4 && a.layout == SGQ_LAYOUT_NK && a.group == 32 && a.M >= 1 && a.M <= kMaxM && a.K >= 256 &&
            (a.K % 256) == 0 && a.N >= 1 && a.N < (1LL << 31) && a.K < (1LL << 24) && aligned(a.wq, 16) &&
-           aligned(a.scales, 16) && aligned(a.x, 16) && make_plan(a.M, a.K, false, &p);
+           aligned(a.scales, 16) && aligned(a.x, 16) && rows_per_launch(a.M, a.K) >= 1;
 }
 
 // Scratch for the prepared activation planes (batches converted by the pre-kernel); 0 when the
@@ -622,6 +633,9 @@ size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layou
     (void)N;
     Plan p;
     if (bits != 4 || layout != SGQ_LAYOUT_NK || M < 1 || M > kMaxM || K < 256 || (K % 256) != 0) return 0;
+    const int64_t rows = rows_per_launch(M, K);
+    if (rows < 1) return 0;
+    if (rows < M) M = rows;                          // the row blocks of a split batch reuse one scratch
     if (!make_plan(M, K, true, &p)) return 0;
     Plan c;
     const bool compact_pre = make_plan(M, K, true, &c, true) && c.pre;    // what an overlapped launch would want
@@ -659,6 +673,22 @@ int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaS
 namespace {
 int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     Plan p;
+    if (!planes_ready && a.bits == 4 && a.M >= 1 && a.M <= kMaxM && a.K >= 256 && (a.K % 256) == 0) {
+        const int64_t rows = rows_per_launch(a.M, a.K);
+        if (rows >= 1 && rows < a.M) {               // planes of the whole batch do not fit: row blocks
+            for (int64_t m0 = 0; m0 < a.M; m0 += rows) {
+                LinearArgs sub = a;
+                sub.M = (a.M - m0 < rows) ? a.M - m0 : rows;
+                sub.x = a.x + m0 * a.K;
+                sub.y = a.y + m0 * a.ldy;
+                for (int r = 0; r < sub.peers.n; ++r) sub.peers.p[r] = a.peers.p[r] + m0 * a.ldy;
+                if (m0 + sub.M < a.M) sub.peers.sig[0] = nullptr;     // a fused barrier belongs to the last block only
+                const int rc = launch_gemv_impl(sub, false);
+                if (rc != SGQ_OK) return rc;
+            }
+            return SGQ_OK;
+        }
+    }
     const size_t want = planes_ready ? gemv_prepared_bytes(a.M, a.K) : gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
     const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
     LinearArgs probe = a;
@@ -733,7 +763,12 @@ int static_planes_address(void** out) {
 }  // namespace
 
 int launch_linear_gemv_static(LinearArgs a) {
-    const size_t need = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    // the limit is stated for the whole batch, whether or not it then runs as several row blocks
+    size_t need = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    if (a.M >= 1 && a.M <= kMaxM && a.K >= 256 && (a.K % 256) == 0 && rows_per_launch(a.M, a.K) < a.M) {
+        const size_t whole = (prepared_layout(a.M, a.K).bytes + 255) / 256 * 256;
+        if (whole > need) need = whole;
+    }
     if (need > kStaticPlanesBytes) {
         set_error("this batch needs %zu bytes of activation scratch; the built-in scratch holds %zu "
                   "(use sgq_linear_int4 with a caller workspace)", need, kStaticPlanesBytes);

@@ -88,6 +88,12 @@ def test_workspace_queries(sgq):
     assert sgq.linear_workspace_bytes(4, 2048, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_SIMT) == 0
     assert sgq.linear_workspace_bytes(4, 0, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_AUTO) == 0
     assert int(sgq.lib.sgq_linear_w8a8_workspace_bytes(128, 1024, 1024)) == 128 * 1024 + 512
+    # INT8 decode kernel: digit planes of the whole batch (256 B per 32-k group and set of 8 columns) + 16 row scales
+    assert sgq.linear_workspace_bytes(8, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * 4 * 256 + 256
+    assert sgq.linear_workspace_bytes(8, 4, 100, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == 0          # K % 128 != 0: no such path
+    assert sgq.linear_workspace_bytes(8, 2048, 4096, 64, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2
+    # an INT4 batch too large for one launch's shared memory asks for the scratch of one row block
+    assert 0 < sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) < (8192 // 32) * 4 * 288 + 256
 
 
 def test_no_cpu_fallback(sgq):
