@@ -67,7 +67,8 @@ enum {
     SGQ_PATH_AUTO = 0,
     SGQ_PATH_SIMT = 1,    /* tiled fp32 SIMT kernel, any shape; one fused-multiply-add chain per
                              output in ascending k, i.e. the reference CPU rounding */
-    SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernel, fp32 accumulation */
+    SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernels, fp32 accumulation ([N,K]: INT4 g=32 and
+                             INT8 on integer tensor-core tiles; [K,N], the reference module's layout: fp32) */
     SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16, weights dequantized to bf16 in shared memory */
     SGQ_PATH_TC_I8 = 4    /* prefill, INT8 weights only: activations quantized per row, tcgen05 kind::i8 */
 };

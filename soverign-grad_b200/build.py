@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(LIB_DIR, "libsgq.so")
-SOURCES = ["abi.cu", "quantize.cu", "linear_simt.cu", "gemv.cu", "gemm_tc.cu", "decoder_glue.cu", "peer.cu", "gemv_i8.cu"]
+SOURCES = ["abi.cu", "quantize.cu", "linear_simt.cu", "gemv.cu", "gemm_tc.cu", "decoder_glue.cu", "peer.cu", "gemv_i8.cu", "linear_kn.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]

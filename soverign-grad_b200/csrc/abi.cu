@@ -145,7 +145,9 @@ int run_linear(LinearArgs a, int path) {
     if (a.K == 0) return launch_linear_simt(a);  // y = bias
     if (path == SGQ_PATH_AUTO) {
         if (gemv_supported(a) || (gemv_i8_supported(a) && a.workspace && aligned(a.workspace, 256) &&
-                                  a.workspace_bytes >= gemv_i8_workspace_bytes(a.M, a.K)))
+                                  a.workspace_bytes >= gemv_i8_workspace_bytes(a.M, a.K)) ||
+            (kn_decode_supported(a) && a.workspace && aligned(a.workspace, 256) &&
+             a.workspace_bytes >= kn_decode_workspace_bytes(a.bits, a.M, a.K, a.N)))
             path = SGQ_PATH_GEMV;
         else if (a.M >= 64 && tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
                  a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
@@ -158,6 +160,7 @@ int run_linear(LinearArgs a, int path) {
         case SGQ_PATH_SIMT:
             return launch_linear_simt(a);
         case SGQ_PATH_GEMV:
+            if (a.layout == SGQ_LAYOUT_KN) return launch_linear_kn_decode(a);
             return a.bits == 8 ? launch_linear_gemv_i8(a) : launch_linear_gemv(a);
         case SGQ_PATH_TC_BF16:
             return launch_linear_tc_bf16(a);
@@ -283,11 +286,13 @@ size_t sgq_linear_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int
     switch (path) {
         case SGQ_PATH_SIMT: return 0;
         case SGQ_PATH_GEMV:
-            return bits == 8 ? (layout == SGQ_LAYOUT_NK ? gemv_i8_workspace_bytes(M, K) : 0) : gemv_workspace_bytes(bits, M, K, N, layout);
+            if (layout == SGQ_LAYOUT_KN) return kn_decode_workspace_bytes(bits, M, K, N);
+            return bits == 8 ? gemv_i8_workspace_bytes(M, K) : gemv_workspace_bytes(bits, M, K, N, layout);
         case SGQ_PATH_TC_BF16: return tc_bf16_workspace_bytes(bits, M, K, N, layout);
         case SGQ_PATH_TC_I8: return tc_i8_workspace_bytes(M, K, N);
         default: {  // AUTO: enough for whichever path AUTO may take
-            size_t a = bits == 8 ? (layout == SGQ_LAYOUT_NK ? gemv_i8_workspace_bytes(M, K) : 0) : gemv_workspace_bytes(bits, M, K, N, layout);
+            size_t a = layout == SGQ_LAYOUT_KN ? kn_decode_workspace_bytes(bits, M, K, N)
+                                               : (bits == 8 ? gemv_i8_workspace_bytes(M, K) : gemv_workspace_bytes(bits, M, K, N, layout));
             size_t b = M >= 64 ? tc_bf16_workspace_bytes(bits, M, K, N, layout) : 0;
             return a > b ? a : b;
         }

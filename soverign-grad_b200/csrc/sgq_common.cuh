@@ -159,6 +159,9 @@ int launch_linear_gemv_prepared(const LinearArgs& a);        // a.workspace = pr
 bool gemv_i8_supported(const LinearArgs& a);                 // INT8 weights stored [N,K], M <= 16
 size_t gemv_i8_workspace_bytes(int64_t M, int64_t K);
 int launch_linear_gemv_i8(const LinearArgs& a);
+bool kn_decode_supported(const LinearArgs& a);               // weights stored [K,N] (the reference module's layout), M <= 16
+size_t kn_decode_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N);
+int launch_linear_kn_decode(const LinearArgs& a);
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);
 int launch_linear_tc_bf16(const LinearArgs& a);

@@ -338,3 +338,49 @@ def test_config5_large_shapes(sgq, port, M):
         assert torch.equal(y2, y0 * 2), (bits, M)
         del q, y, y0, y2
     check_status(sgq)
+
+
+KN_DECODE_SHAPES = [(1, 512, 64, 16), (3, 1000, 2048, 32), (4, 4096, 4096, 32), (16, 777, 160, 32), (7, 2048, 48, 16),
+                    (2, 300, 4128, 32), (1, 4096, 11008, 32), (5, 17, 32, 32)]
+
+
+@pytest.mark.parametrize("M,K,N,group", KN_DECODE_SHAPES)
+def test_kn_decode_kernel_against_port(sgq, port, M, K, N, group):
+    """Weights kept in the reference module's own [in, out] layout (INT4 groups along the flat index,
+    INT8 per stored row or per tensor) on the streaming decode kernel for that layout."""
+    rng = np.random.default_rng(M * 1000003 + K * 101 + N + group)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = cases.weight_with_outliers(K + N + 2, (K, N))
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    ws = sgq.Workspace(torch.device("cuda"))
+    packed, scales = port.quantize_int4(w, group)
+    want = port.qlinear_int4(x, packed, scales, K, N, cases.LAYOUT_KN, group, b)
+    q = sgq.quantize_int4(dev(w), group)
+    assert sgq.linear_workspace_bytes(4, M, K, N, cases.LAYOUT_KN, sgq.PATH_GEMV) > 0
+    y = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+    assert rel_err(y, want) <= TOL_FP32, (M, K, N, rel_err(y, want))
+    y_auto = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_KN, path=sgq.PATH_AUTO, workspace=ws).cpu().numpy()
+    assert np.array_equal(y_auto, y)                                   # AUTO takes it when a workspace is supplied, and
+    again = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+    assert np.array_equal(again, y)                                    # slices are added in a fixed order
+    y_none = sgq.quantized_matmul(dev(x), q, None, layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+    assert rel_err(y_none, want - b[None, :]) <= TOL_FP32
+    for scheme in (cases.PER_TENSOR, cases.PER_ROW):
+        codes, sw = port.quantize_int8(w, scheme)
+        want8 = port.qlinear_int8(x, codes, sw, K, N, cases.LAYOUT_KN, scheme, b)
+        q8 = sgq.quantize_int8(dev(w), scheme)
+        y8 = sgq.quantized_matmul(dev(x), q8, dev(b), layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+        assert rel_err(y8, want8) <= TOL_FP32, (M, K, N, scheme, rel_err(y8, want8))
+    check_status(sgq)
+
+
+def test_kn_decode_kernel_rejects_what_it_cannot_run(sgq):
+    w = torch.randn(64, 40, device="cuda")          # N = 40 is not a multiple of 16
+    q = sgq.quantize_int4(w, 32)
+    with pytest.raises(sgq.SgqError) as e:
+        sgq.quantized_matmul(torch.randn(1, 64, device="cuda"), q, None, layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV)
+    assert e.value.status == 4
+    sgq.quantized_matmul(torch.randn(1, 64, device="cuda"), q, None, layout=cases.LAYOUT_KN)      # AUTO: any-shape kernel
+    q24 = sgq.quantize_int4(torch.randn(64, 48, device="cuda"), 24)                                # group 24: not a multiple of 16
+    with pytest.raises(sgq.SgqError):
+        sgq.quantized_matmul(torch.randn(1, 64, device="cuda"), q24, None, layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV)
