@@ -341,14 +341,11 @@ def nanollama_case(torch, sgq, dev, *, reps: int, warm: int, rank: int = 0, worl
         toks = torch.empty(batch, n_new, dtype=torch.int64, device=dev)
         torch.argmax(logits, dim=-1, out=model.tok)
         toks[:, 0].copy_(model.tok)
-        if world == 1 and model._graph is None:
+        if model._graph is None:
             model.capture_decode_graph()          # first (warm-up) generation only
         e1.record()
         for s in range(1, n_new):
-            if world == 1:
-                model._graph.replay()
-            else:
-                model._greedy_step()
+            model._graph.replay()
             toks[:, s].copy_(model.tok)
         out_h.copy_(toks, non_blocking=True)
         e2.record()
@@ -381,7 +378,8 @@ def nanollama_case(torch, sgq, dev, *, reps: int, warm: int, rank: int = 0, worl
         "h2d_bytes": batch * prompt_len * 8, "d2h_bytes": batch * n_new * 8, "device_status_word": status,
         "batch": batch, "prompt_len": prompt_len, "new_tokens": n_new, "kv_cache": "fp32",
         "prefill_path": "tc_bf16 (auto)", "decode_path": "gemv (auto)",
-        "launch": "one CUDA graph replay per decode step" if world == 1 else "eager launches, NCCL all-gather after every sharded linear",
+        "launch": "one CUDA graph replay per decode step" + ("" if world == 1 else "; column slices exchanged by peer stores from this "
+                  "library's kernels + a barrier kernel per exchange (4 per block + logits), NCCL only in the prompt pass"),
     }
 
 

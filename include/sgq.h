@@ -182,6 +182,11 @@ SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int6
                                       int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
                                       void* const* signals, int rank, void* local_state, void* stream);
 
+/* The same exchange for a slice that some other kernel produced: src[M, n_local] (this GPU) is
+ * stored into y_ranks[r][m * ldy + n_offset + n] of every rank r.  Follow with sgq_peer_barrier. */
+SGQ_API int sgq_peer_scatter(const float* src, int64_t M, int64_t n_local, float* const* y_ranks, int world, int64_t ldy,
+                             int64_t n_offset, void* stream);
+
 /* Barrier between the GPUs of one box, in stream order, no host involvement.  signals: HOST array of
  * `world` device pointers, signals[r] = rank r's array of `world` 64-bit slots (zero-initialised,
  * writable by every rank: symmetric / peer-mapped memory).  local_epoch: one zero-initialised 64-bit

@@ -33,7 +33,7 @@ EXPORTS = [
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
     "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared", "sgq_set_stream_overlap",
-    "sgq_linear_int4_allgather", "sgq_peer_barrier",
+    "sgq_linear_int4_allgather", "sgq_peer_barrier", "sgq_peer_scatter",
 ]
 
 # every symbol include/sgq_decoder.h declares
@@ -75,6 +75,7 @@ def _load() -> C.CDLL:
     lib.sgq_set_stream_overlap.argtypes = [i32]
     lib.sgq_linear_int4_allgather.argtypes = [p, i64, i64, i64, p, p, p, C.POINTER(p), i32, i64, i64, p, sz, C.POINTER(p), i32, p, p]
     lib.sgq_peer_barrier.argtypes = [C.POINTER(p), i32, i32, p, p]
+    lib.sgq_peer_scatter.argtypes = [p, i64, i64, C.POINTER(p), i32, i64, i64, p]
     lib.sgq_prepared_x_bytes.restype = sz
     lib.sgq_prepared_x_bytes.argtypes = [i64, i64]
     lib.sgq_prepare_x.argtypes = [p, i64, i64, p, sz, p]

@@ -40,12 +40,59 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant_
         atomicCAS(&g_status_peer, 0u, (kDevErrPeerWait << 24) | 0x10000u);
 }
 
+// src[M, n_local] -> y_r[m * ldy + n] for every rank r (the pointers already include the column offset)
+__global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restrict__ src, int64_t M, int64_t n_local,
+                                                           const __grid_constant__ PeerOut peers, int64_t ldy, int vec) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = M * n_local;
+    if (vec) {
+        for (int64_t i = (blockIdx.x * 256ll + threadIdx.x) * 4; i < total; i += gridDim.x * 1024ll) {
+            const int64_t m = i / n_local, n = i - m * n_local;
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            for (int r = 0; r < peers.n; ++r) *reinterpret_cast<float4*>(peers.p[r] + m * ldy + n) = v;
+        }
+    } else {
+        for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
+            const int64_t m = i / n_local, n = i - m * n_local;
+            const float v = src[i];
+            for (int r = 0; r < peers.n; ++r) peers.p[r][m * ldy + n] = v;
+        }
+    }
+}
+
 }  // namespace
 }  // namespace sgq
 
 using namespace sgq;
 
 extern "C" {
+
+int sgq_peer_scatter(const float* src, int64_t M, int64_t n_local, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset,
+                     void* stream) {
+    if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
+    if (M < 0 || n_local < 0 || n_offset < 0 || ldy < n_offset + n_local) return bad(SGQ_ERR_BAD_SHAPE, "bad slice shape");
+    if (M * n_local == 0) return SGQ_OK;
+    if (!src || !y_ranks) return bad(SGQ_ERR_NULL_POINTER, "src or y_ranks is NULL");
+    PeerOut peers = {};
+    bool vec = aligned(src, 16) && (n_offset & 3) == 0 && (n_local & 3) == 0 && (ldy & 3) == 0;
+    for (int r = 0; r < world; ++r) {
+        if (!y_ranks[r]) return bad(SGQ_ERR_NULL_POINTER, "an output pointer is NULL");
+        peers.p[r] = y_ranks[r] + n_offset;
+        vec = vec && aligned(y_ranks[r], 16);
+    }
+    peers.n = world;
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    int64_t blocks = ceil_div(M * n_local, 1024);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    // 128-bit stores when every row on both sides is 16-byte aligned
+    SGQ_CUDA_TRY(launch_kernel(peer_scatter_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                               stream_overlap_enabled(), src, M, n_local, peers, ldy, vec ? 1 : 0));
+    return SGQ_OK;
+}
 
 int sgq_peer_barrier(void* const* signals, int rank, int world, void* local_epoch, void* stream) {
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return bad(SGQ_ERR_BAD_ARGUMENT, "bad rank/world (at most 8 GPUs)");

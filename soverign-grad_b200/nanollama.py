@@ -105,10 +105,45 @@ class _Linear:
         return linear_int4_prepared(planes, M, self.q, None, out)
 
 
+class _PeerSites:
+    """Full-width symmetric buffers of one decode step (attention output, wo output, SiLU gate output,
+    w_down output, logits) that every rank stores its column slice into, and one signal/epoch space for
+    the barriers.  One buffer per site is enough: a rank can run at most one exchange ahead of another,
+    and a site is reused only four exchanges later."""
+
+    def __init__(self, cfg: NanoLlamaConfig, M: int, device, group):
+        import ctypes as C
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        widths = {"attn": cfg.dim, "o": cfg.dim, "act": cfg.hidden, "d": cfg.dim, "logits": cfg.vocab}
+        offs, total = {}, 0
+        for k, w in widths.items():
+            offs[k] = total
+            total += (M * w + 63) // 64 * 64
+        self._buf = symm.empty(total, dtype=torch.float32, device=device)
+        self._sig = symm.empty(64, dtype=torch.int64, device=device)
+        self._buf.zero_()
+        self._sig.zero_()
+        h_buf, h_sig = symm.rendezvous(self._buf, self.group), symm.rendezvous(self._sig, self.group)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self.local = {k: self._buf[offs[k]: offs[k] + M * w].view(M, w) for k, w in widths.items()}
+        self.y_ranks = {k: (C.c_void_p * self.world)(*[int(p) + offs[k] * 4 for p in h_buf.buffer_ptrs]) for k in widths}
+        self.width = widths
+        self.signals = (C.c_void_p * self.world)(*[int(p) for p in h_sig.buffer_ptrs])
+        self.state = torch.zeros(2, dtype=torch.int64, device=device)
+        self._handles = (h_buf, h_sig)
+
+
 class NanoLlamaInt4:
     def __init__(self, cfg: NanoLlamaConfig, device, batch: int, *, seed: int = 0,
                  init: Optional[Callable[[str, int], torch.Tensor]] = None, rank: int = 0, world: int = 1, group=None,
-                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO, overlap: bool = True):
+                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO, overlap: bool = True,
+                 exchange: str = "peer"):
         if cfg.n_heads % world or cfg.hidden % (32 * world) or cfg.dim % (32 * world) or cfg.vocab % (32 * world):
             raise ValueError("heads, hidden, dim and vocab must split into equal 32-row slices per rank")
         self.cfg, self.device, self.batch = cfg, torch.device(device), batch
@@ -117,6 +152,11 @@ class NanoLlamaInt4:
         # consecutive kernels overlap (sgq_set_stream_overlap): legal here because no weight is ever
         # written by the kernel in front of the linear that reads it
         self.overlap = overlap
+        # world > 1, decode steps: "peer" = slices stored into every rank's buffers by this library's kernels +
+        # sgq_peer_barrier (graph-capturable); "nccl" = all-gather + interleave (eager).  The prompt pass always
+        # uses NCCL (one pass, large slices).
+        self.exchange = exchange if world > 1 else "none"
+        self._sites = None
         init = init or default_init(cfg, self.device, seed)
         dev = self.device
         self.ws = Workspace(dev)
@@ -171,10 +211,30 @@ class NanoLlamaInt4:
             self._bufs[M] = b
         return self._bufs[M]
 
-    def _gather(self, local: torch.Tensor, gathered: torch.Tensor, full: torch.Tensor) -> torch.Tensor:
+    def _peer(self, M: int):
+        """The symmetric buffers, if this pass exchanges through peer stores (decode steps of a sharded model)."""
+        if self.exchange != "peer" or M != self.batch:
+            return None
+        if self._sites is None:
+            self._sites = _PeerSites(self.cfg, M, self.device, self.group)
+        return self._sites
+
+    def _barrier(self, sites):
+        check(lib.sgq_peer_barrier(sites.signals, self.rank, self.world, _ptr(sites.state), _stream()), "sgq_peer_barrier")
+        self._count()
+
+    def _gather(self, local: torch.Tensor, gathered: torch.Tensor, full: torch.Tensor, site: Optional[str] = None) -> torch.Tensor:
         """[M, n_local] slices of every rank -> row-major [M, world * n_local]; identity on one GPU."""
         if self.world == 1:
             return local
+        sites = self._peer(local.shape[0]) if site else None
+        if sites is not None:
+            M, n_local = local.shape
+            check(lib.sgq_peer_scatter(_ptr(local), M, n_local, sites.y_ranks[site], self.world, sites.width[site],
+                                       self.rank * n_local, _stream()), "sgq_peer_scatter")
+            self._count()
+            self._barrier(sites)
+            return sites.local[site]
         import torch.distributed as dist
         M, n_local = local.shape
         dist.all_gather_into_tensor(gathered.view(self.world * M, n_local), local, group=self.group)
@@ -189,6 +249,24 @@ class NanoLlamaInt4:
         check(lib.sgqd_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(gamma), self.cfg.eps, h.shape[0], h.shape[1], _ptr(out),
                                    _ptr(planes), planes.numel() if planes is not None else 0, _stream()), "sgqd_add_rmsnorm")
         self._count()
+
+    def _linear_gathered(self, lin: _Linear, x, out, path, gathered, full, site: str):
+        """A column-sharded linear whose full-width output every rank needs: on the peer exchange the decode
+        kernel stores its slice into all ranks' buffers itself (fused all-gather), then the barrier."""
+        sites = self._peer(x.shape[0]) if self.world > 1 else None
+        if sites is None:
+            self._linear(lin, x, out, path)
+            return self._gather(out, gathered, full)
+        M, K = x.shape
+        need = int(lib.sgq_linear_workspace_bytes(4, M, K, lin.n_local, LAYOUT_NK, PATH_GEMV))
+        ws = self.ws.get(need) if need else None
+        check(lib.sgq_linear_int4_allgather(_ptr(x), M, K, lin.n_local, _ptr(lin.q.qdata), _ptr(lin.q.scales), None,
+                                            sites.y_ranks[site], self.world, sites.width[site], self.rank * lin.n_local,
+                                            _ptr(ws), ws.numel() if ws is not None else 0, None, self.rank, None, _stream()),
+              "sgq_linear_int4_allgather")
+        self._count(2 if M * (K // 8) > 1024 else 1)
+        self._barrier(sites)
+        return sites.local[site]
 
     def _linear(self, lin: _Linear, x, out, path, planes=None):
         """planes: x already in the decode kernel's prepared form (written by the operator before)."""
@@ -229,17 +307,19 @@ class NanoLlamaInt4:
                                              _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
                 self._count()
                 self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"])
-            attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"))
-            self._linear(L["wo"], attn, b["o"], path)
-            o = self._gather(b["o"], b.get("g_o"), b.get("o_full"))
+            attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"), "attn")
+            o = self._linear_gathered(L["wo"], attn, b["o"], path, b.get("g_o"), b.get("o_full"), "o")
             self._add_rmsnorm(h, o, L["ffn_norm"], n, p_dim)
             self._linear(L["gu"], n, b["gu"], path, p_dim)
             check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _ptr(p_hid),
                                     p_hid.numel() if p_hid is not None else 0, _stream()), "sgqd_silu_mul")
             self._count()
-            act = self._gather(b["act"], b.get("g_act"), b.get("act_full"))
-            self._linear(L["down"], act, b["d"], path, p_hid)
-            delta = self._gather(b["d"], b.get("g_o"), b.get("d_full"))
+            act = self._gather(b["act"], b.get("g_act"), b.get("act_full"), "act")
+            if self.world == 1:
+                self._linear(L["down"], act, b["d"], path, p_hid)
+                delta = b["d"]
+            else:
+                delta = self._linear_gathered(L["down"], act, b["d"], path, b.get("g_o"), b.get("d_full"), "d")
         self._add_rmsnorm(h, delta, self.final_norm, n, p_dim)
         self._final_planes = p_dim
         return n
@@ -265,8 +345,10 @@ class NanoLlamaInt4:
             self._bufs[key] = (f(M, self.voc_local), f(self.world, M, self.voc_local) if self.world > 1 else None,
                                f(M, self.cfg.vocab) if self.world > 1 else None)
         loc, g, full = self._bufs[key]
+        if self.world > 1:
+            return self._linear_gathered(self.lm_head, n_rows, loc, path, g, full, "logits")
         self._linear(self.lm_head, n_rows, loc, path, planes)
-        return self._gather(loc, g, full)
+        return loc
 
     @contextlib.contextmanager
     def _overlapped(self):
@@ -314,8 +396,8 @@ class NanoLlamaInt4:
 
     def capture_decode_graph(self):
         """Records one greedy decode step (token buffer -> next token buffer) into a CUDA graph."""
-        if self.world > 1:
-            raise RuntimeError("the sharded model launches its collectives eagerly")
+        if self.world > 1 and self.exchange != "peer":
+            raise RuntimeError("NCCL collectives are launched eagerly; use exchange='peer' to record the sharded step")
         saved_pos, saved_tok = self.pos.clone(), self.tok.clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -341,7 +423,7 @@ class NanoLlamaInt4:
         kept = [logits.clone()] if keep_logits else None
         torch.argmax(logits, dim=-1, out=self.tok)
         out[:, 0].copy_(self.tok)
-        use_graph = use_graph and self.world == 1 and not keep_logits
+        use_graph = use_graph and (self.world == 1 or self.exchange == "peer") and not keep_logits
         if use_graph and self._graph is None:
             self.capture_decode_graph()
         for s in range(1, n_new):

@@ -60,6 +60,26 @@ def worker(rank, world, port, out_dir):
                 y = lin(xr)
                 torch.cuda.synchronize()
                 assert torch.equal(y, want), ("peer", M, K, N, rep, fused)
+    # the sharded decoder (heads, SwiGLU columns, wo / w_down outputs and the vocabulary split by column) against
+    # the same model on one GPU: every output element is computed by the same instructions, so logits are equal
+    nl = importlib.import_module("sgq_b200.nanollama")
+    cfg = nl.NanoLlamaConfig(dim=256, n_layers=2, n_heads=2, hidden=512, vocab=512, max_seq=64)
+    prompt = torch.randint(0, cfg.vocab, (2, 9), generator=torch.Generator().manual_seed(3))
+    single = nl.NanoLlamaInt4(cfg, "cuda", 2, seed=11)
+    tok1, log1 = single.generate(prompt, 6, use_graph=False, keep_logits=True)
+    for exchange in ("peer", "nccl"):
+        sharded = nl.NanoLlamaInt4(cfg, "cuda", 2, seed=11, rank=rank, world=world, exchange=exchange)
+        tok2, log2 = sharded.generate(prompt, 6, use_graph=False, keep_logits=True)
+        assert torch.equal(tok2, tok1), exchange
+        for a, b2 in zip(log1, log2):
+            assert torch.equal(a, b2), exchange
+        if exchange == "peer":                       # the sharded decode step as one CUDA graph
+            tok3 = sharded.generate(prompt, 6, use_graph=True)
+            assert torch.equal(tok3, tok1)
+            tok4 = sharded.generate(prompt, 6, use_graph=True)
+            assert torch.equal(tok4, tok1)
+        torch.cuda.synchronize()
+        dist.barrier()
     assert sgq.device_status() == 0
     dist.barrier()
     if rank == 0:
