@@ -265,6 +265,22 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
     for M in (1, 16):
         guard(f"gemv_int8_tensor_M{M}_28672x8192", lambda M=M: gemv_int8(M, 28672, 8192))
 
+    def gemv_int4_large(M, N, K):
+        # config 5 shape: 147 MB of packed codes + scales, larger than L2 by itself
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        q = sgq.quantize_int4(w, GROUP)
+        del w
+        x = torch.randn(M, K, device=dev, generator=g)
+        y = torch.empty(M, N, device=dev)
+        ws = sgq.Workspace(dev)
+        f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV, out=y, workspace=ws)  # noqa: E731
+        ms = timer(f, 10, inner=10)
+        nbytes = gemv_bytes(M, K, N)
+        return {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"], "path": "gemv"}
+
+    for M in (1, 16):
+        guard(f"gemv_int4_g32_M{M}_28672x8192", lambda M=M: gemv_int4_large(M, 28672, 8192))
+
     def pack(shape, bits):
         # two inputs > L2 in total for the big shape; alternate so the small one also misses L2
         ws_ = [torch.randn(shape, device=dev, generator=g) * 0.02 for _ in range(3)]
