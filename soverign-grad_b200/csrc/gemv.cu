@@ -153,17 +153,27 @@ __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const floa
     }
 }
 
-// NSETS: sets of 8 digit columns; WPB: consumer warps per 256-k step (1 or 2);
+// Consumer organisation (template parameter WPB):
+//   1: 8 warps, one per 256-k step, every warp works on every stage (the compact two-CTAs-per-SM form);
+//   2: 16 warps, two per step (half a step each), every warp works on every stage;
+//   3: 16 warps in two sets of 8, one warp per step, the sets take ALTERNATE stages — two stages are
+//      in work at any time, so the latency bubbles of one set (barrier waits, the hand-off to the
+//      reducer at the end of a tile) are covered by the other.
+__host__ __device__ constexpr int consumer_warps(int wpb) { return wpb == 1 ? 8 : 16; }
+
+// NSETS: sets of 8 digit columns; WPB: see above;
 // PRE: the activation planes were prepared by gemv_prepare_x_kernel and are copied in by TMA.
 template <int NSETS, int WPB, bool PRE>
-__global__ void __launch_bounds__((kStepsPerStage * WPB + 2) * 32, WPB == 1 ? 2 : 1)
+__global__ void __launch_bounds__((consumer_warps(WPB) + 2) * 32, WPB == 1 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
                     float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages, int early_weights,
                     const __grid_constant__ PeerOut peers) {
-    constexpr int kWarps = kStepsPerStage * WPB;
+    constexpr int kWarps = consumer_warps(WPB);
     constexpr int kConsumerThreads = kWarps * 32;
-    constexpr int kGroupsPerWarp = 8 / WPB;
+    constexpr int kWarpsPerStep = WPB == 2 ? 2 : 1;
+    constexpr int kGroupsPerWarp = 8 / kWarpsPerStep;
+    constexpr int kStageSets = WPB == 3 ? 2 : 1;       // sets of warps that take alternate stages
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -193,7 +203,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], kWarps);
+            mbar_init(&empty[i], kWarps / kStageSets);
         }
         for (int i = 0; i < kPSlots; ++i) {
             mbar_init(&pfull[i], kWarps);
@@ -424,8 +434,9 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     SGQ_MARK(2);
 
     const int g = lane >> 2, t = lane & 3;
-    const int step_in_stage = warp / WPB;            // which 256-k step of a stage this warp works on
-    const int g0 = (warp % WPB) * kGroupsPerWarp;    // first of its groups inside the step
+    const int step_in_stage = (warp / kWarpsPerStep) & 7;          // which 256-k step of a stage this warp works on
+    const int g0 = (warp % kWarpsPerStep) * kGroupsPerWarp;        // first of its groups inside the step
+    const uint32_t my_set = (kStageSets == 2) ? static_cast<uint32_t>(warp >> 3) : 0u;
     // byte offset of this lane's word inside a step box, for each of its groups (swizzle: chunk ^ row)
     uint32_t woff[kGroupsPerWarp];
 #pragma unroll
@@ -440,6 +451,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
         for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
+            if (kStageSets == 2 && (seq & 1u) != my_set) continue;       // the other set's stage
             const int st = seq % nstages;
             const uint32_t ph = (seq / nstages) & 1u;
             if (alive && !mbar_wait(&full[st], ph)) {
@@ -563,15 +575,15 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
 #ifdef SGQ_FORCE_WPB
     for (int wpb = SGQ_FORCE_WPB; wpb >= 1; --wpb) {
 #else
-    for (int wpb = compact ? 1 : 2; wpb >= 1; --wpb) {
+    for (int wpb = compact ? 1 : 3; wpb >= 1; --wpb) {
 #endif
-        for (int st = kMaxStages; st >= (wpb == 2 ? 3 : 2); --st) {
-            const Smem L = smem_layout(st, K, p->nsets, kStepsPerStage * wpb);
+        for (int st = kMaxStages; st >= (wpb == 3 ? 4 : (wpb == 2 ? 3 : 2)); --st) {
+            const Smem L = smem_layout(st, K, p->nsets, consumer_warps(wpb));
             if (L.total + 1024 <= static_cast<uint32_t>(limit)) {
                 p->wpb = wpb;
                 p->nstages = st;
                 p->smem = L.total + 1024;
-                p->pre = have_workspace && (M * (K / 8) > 4 * kStepsPerStage * wpb * 32) && K <= 8LL * kPrepMaxChunks * kPrepThreads;
+                p->pre = have_workspace && (M * (K / 8) > 4 * consumer_warps(wpb) * 32) && K <= 8LL * kPrepMaxChunks * kPrepThreads;
                 return true;
             }
         }
@@ -602,7 +614,7 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap,
                                    a.x, static_cast<int>(a.M), a.K, p.ndigits, p.nsets, static_cast<uint8_t*>(a.workspace)));
     }
-    SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((kStepsPerStage * WPB + 2) * 32), p.smem, a.stream,
+    SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((consumer_warps(WPB) + 2) * 32), p.smem, a.stream,
                                overlap, map_w, map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
                                p.nstages, overlap ? 1 : 0, a.peers));
     return SGQ_OK;
@@ -612,9 +624,11 @@ template <int NSETS>
 int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                  bool planes_ready) {
     if (p.pre)
-        return p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid, planes_ready)
+        return p.wpb == 3 ? launch_variant<NSETS, 3, true>(a, p, map_w, map_s, grid, planes_ready)
+             : p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid, planes_ready)
                           : launch_variant<NSETS, 1, true>(a, p, map_w, map_s, grid, planes_ready);
-    return p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid, false)
+    return p.wpb == 3 ? launch_variant<NSETS, 3, false>(a, p, map_w, map_s, grid, false)
+         : p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid, false)
                       : launch_variant<NSETS, 1, false>(a, p, map_w, map_s, grid, false);
 }
 
