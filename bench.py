@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE config 2): INT4 g=32 weight-only decode, W[11008,4096] stored [N,K],
+Workload (benchmark configuration 2): INT4 g=32 weight-only decode, W[11008,4096] stored [N,K],
 X[1,4096] fp32, y = x * deq(W)^T.  One *step* = `--launches-per-step` forwards cycling through
 `--copies` distinct weight sets (10 x 28.2 MB = 282 MB > 126 MB L2, so every launch streams its
 weights from HBM).  Metric: achieved HBM GB/s = algorithmic bytes / time, whole job.
@@ -214,7 +214,7 @@ def eager_time(torch, fn, iters: int) -> float:
 
 def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
     """Secondary measurements (reported, not the headline): other batch sizes, the pack kernels and
-    the prefill GEMM of BASELINE config 3."""
+    the prefill GEMM of benchmark configuration 3."""
     out = {}
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(1)
@@ -329,7 +329,7 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
 
 def nanollama_case(torch, sgq, dev, *, reps: int, warm: int, rank: int = 0, world: int = 1, dist=None,
                    batch: int = 8, prompt_len: int = 512, n_new: int = 128):
-    """BASELINE config 4: NanoLLaMA-INT4 (dim 2048, 16 blocks, 16 heads, SwiGLU 5632, vocab 32000,
+    """benchmark configuration 4: NanoLLaMA-INT4 (dim 2048, 16 blocks, 16 heads, SwiGLU 5632, vocab 32000,
     random init), batch 8, uniform random token ids, 512-token prefill + 128 greedy decode steps.
     One generation = prefill (tcgen05 bf16 path) + first token + 127 decode steps (decode kernel, one
     CUDA graph replay per step on one GPU; eager with NCCL all-gathers when column-sharded).

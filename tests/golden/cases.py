@@ -73,5 +73,5 @@ def forward_inputs(name: str, M: int, K: int, N: int, layout: int):
 
 
 def config1_inputs():
-    """BASELINE config 1: X[128,1024]~N(0,1), W[1024,1024]~N(0,0.02), bias zeros, seed 0."""
+    """benchmark configuration 1: X[128,1024]~N(0,1), W[1024,1024]~N(0,0.02), bias zeros, seed 0."""
     return normal(0, (128, 1024)), normal(1, (1024, 1024), 0.02), np.zeros(1024, np.float32)

@@ -1,7 +1,7 @@
 """Regenerates tests/golden/*.npz from the compiled, UNMODIFIED reference.
 
 Run in a container that has the reference checkout:
-    make -C oracle ref REF=/root/reference && python tests/golden/make_golden.py
+    make -C oracle ref REF=<reference checkout> && python tests/golden/make_golden.py
 
 Every stored code/scale/output below is what the reference's own functions returned
 (sovereigngrad::quantization::* through oracle/ref_driver.cpp).  The reference keeps codes as
@@ -115,7 +115,7 @@ def main():
                     lin.close()
     np.savez_compressed(os.path.join(HERE, "forward.npz"), **f)
 
-    # BASELINE config 1 at full size: inputs are re-derivable from the seed; keep digests of the
+    # benchmark configuration 1 at full size: inputs are re-derivable from the seed; keep digests of the
     # codes and a strided sample of the output.
     x, w, b = cases.config1_inputs()
     c1 = {}

@@ -66,7 +66,7 @@ def test_golden_forward_simt(sgq, golden, name, M, K, N):
 
 
 def test_config1_forward(sgq, golden):
-    """BASELINE config 1 (X[128,1024], W[1024,1024], INT8 per tensor, the reference's CPU case)."""
+    """benchmark configuration 1 (X[128,1024], W[1024,1024], INT8 per tensor, the reference's CPU case)."""
     g = golden["config1"]
     x, w, b = cases.config1_inputs()
     xd, wd, bd = dev(x), dev(w), dev(b)
@@ -156,7 +156,7 @@ def test_decode_kernel_rejects_what_it_cannot_run(sgq):
 
 @pytest.mark.parametrize("M", [1, 4, 16])
 def test_config2_decode_full_size(sgq, port, M):
-    """BASELINE config 2: W[11008,4096] INT4 g=32, X[M,4096], M in {1,4,16}."""
+    """benchmark configuration 2: W[11008,4096] INT4 g=32, X[M,4096], M in {1,4,16}."""
     K, N = 4096, 11008
     x = cases.normal(100 + M, (M, K))
     w = cases.normal(7, (N, K), 0.02)
@@ -197,7 +197,7 @@ def test_tc_bf16_against_port(sgq, port, M, K, N):
     assert rel_err(y, model) <= 2e-4, ("layout/pipeline error, not rounding", rel_err(y, model))
     # Operands rounded to 8 significant bits: the bound is normwise (max |error| over max |output|).
     # With 1% x20 outliers and a short K one product can dominate an output, so the rms-floored
-    # elementwise ratio is only held to 2e-2 from K >= 1024 on (BASELINE's shapes have K >= 4096).
+    # elementwise ratio is only held to 2e-2 from K >= 1024 on (the benchmark's shapes have K >= 4096).
     assert norm_err(y, want) <= TOL_BF16, norm_err(y, want)
     assert rel_err(y, want) <= (TOL_BF16 if K >= 1024 else 8e-2), rel_err(y, want)
 
@@ -258,7 +258,7 @@ def test_tc_i8_exact(sgq, port, M, K, N):
 
 
 def test_config3_prefill_full_size(sgq, port):
-    """BASELINE config 3: X[2048,4096], W[4096,4096] (1% x20 outliers), INT4 g=32 on the bf16
+    """benchmark configuration 3: X[2048,4096], W[4096,4096] (1% x20 outliers), INT4 g=32 on the bf16
     tensor-core path.  Full-size check without a full-size CPU product: 16 sampled rows against
     the oracle, everything against the any-shape kernel."""
     M, K, N = 2048, 4096, 4096
@@ -305,7 +305,7 @@ def test_column_slices_reassemble(sgq):
 
 @pytest.mark.parametrize("M", [1, 16, 128, 1024, 8192])
 def test_config5_large_shapes(sgq, port, M):
-    """BASELINE config 5 at full size on one GPU: W[28672, 8192] as INT4 g=32 and INT8 per tensor,
+    """benchmark configuration 5 at full size on one GPU: W[28672, 8192] as INT4 g=32 and INT8 per tensor,
     X[M, 8192].  Too large for a CPU forward, so: 24 sampled output features against the port on the
     GPU's own codes (the quantizer is bit-exact, tested elsewhere), and Y(2x) = 2 Y(x) exactly (a
     power-of-two factor moves no digit, no bf16 mantissa and no fp32 product)."""

@@ -93,7 +93,7 @@ def test_int8_against_port(sgq, port, rows, cols):
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (11008, 4096)])
 def test_config3_pack_full_size(sgq, port, shape):
-    """BASELINE config 3: N(0,0.02) with 1% entries x20, INT8 per tensor and INT4 g=32, at full size:
+    """benchmark configuration 3: N(0,0.02) with 1% entries x20, INT8 per tensor and INT4 g=32, at full size:
     bytes and scales bit-exact against the oracle, plus a round-trip bound that needs no oracle."""
     w = cases.weight_with_outliers(42, shape)
     wd = dev(w)
