@@ -96,6 +96,82 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
     }
 }
 
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < THREADS / 32 ? red[threadIdx.x & 31] : 0.f;
+    return warp_sum(t);
+}
+
+// The same operator for rows that fit in registers (dim % 256 == 0, dim <= 2048 * CH): the row is read
+// once, normalised and, with PREP, converted to digit planes from registers — no pass re-reads memory.
+// The decode steps of a model take this form (a few rows, launch- and latency-bound).
+template <bool PREP, int CH>
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                                      const float* __restrict__ gamma, float eps, int64_t dim,
+                                                                      float* __restrict__ out, int ndigits, int nsets,
+                                                                      uint8_t* __restrict__ planes) {
+    __shared__ float red[kNormThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int chunks = static_cast<int>(dim / 8);
+    float* hr = h + blockIdx.x * dim;
+    const float* dr = delta ? delta + blockIdx.x * dim : nullptr;
+    float* orow = out + blockIdx.x * dim;
+    float v[CH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < CH; ++r) {
+        const int c = threadIdx.x + r * kNormThreads;
+        if (c < chunks) {
+            float4 a = *(reinterpret_cast<const float4*>(hr) + 2 * c), b = *(reinterpret_cast<const float4*>(hr) + 2 * c + 1);
+            if (dr) {
+                const float4 da = *(reinterpret_cast<const float4*>(dr) + 2 * c), db = *(reinterpret_cast<const float4*>(dr) + 2 * c + 1);
+                a.x += da.x; a.y += da.y; a.z += da.z; a.w += da.w;
+                b.x += db.x; b.y += db.y; b.z += db.z; b.w += db.w;
+                *(reinterpret_cast<float4*>(hr) + 2 * c) = a;
+                *(reinterpret_cast<float4*>(hr) + 2 * c + 1) = b;
+            }
+            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = fmaf(v[r][j], v[r][j], ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum<kNormThreads>(ss, red) / static_cast<float>(dim) + eps);
+    float amax = 0.f;
+#pragma unroll
+    for (int r = 0; r < CH; ++r) {
+        const int c = threadIdx.x + r * kNormThreads;
+        if (c < chunks) {
+            const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c), gb = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c + 1);
+            const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[r][j] = v[r][j] * inv * g[j];
+                amax = fmaxf(amax, fabsf(v[r][j]));
+            }
+            *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+            *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
+        }
+    }
+    if (PREP) {
+        const float all = block_max<kNormThreads>(amax, red);
+        const size_t groups = static_cast<size_t>(dim / 32);
+        uint8_t* corr = planes + groups * nsets * 256;
+        float P, invP;
+        row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
+        if (threadIdx.x == 0) reinterpret_cast<float*>(corr + groups * nsets * 32)[blockIdx.x] = invP;
+#pragma unroll
+        for (int r = 0; r < CH; ++r) {
+            const int c = threadIdx.x + r * kNormThreads;
+            if (c < chunks) digits_item(v[r], P, blockIdx.x, c, ndigits, nsets, planes, corr);      // chunks % 32 == 0: whole warps
+        }
+    }
+}
+
 // One block per token; thread items are (head, d) pairs with d < head_dim / 2.
 __global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ qkv, int t_new, int n_heads, int head_dim,
                                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -329,6 +405,51 @@ __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const fl
     prepare_row_block<kNormThreads>(orow, all, blockIdx.x, hidden, ndigits, nsets, planes);
 }
 
+// The register-resident form of the same (hidden % 256 == 0, hidden <= 8192): one pass over memory.
+constexpr int kSiluThreads = 512;
+__global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(const float* __restrict__ gu, int64_t hidden,
+                                                                           float* __restrict__ out, int ndigits, int nsets,
+                                                                           uint8_t* __restrict__ planes) {
+    __shared__ float red[kSiluThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int CH = 2;
+    const int chunks = static_cast<int>(hidden / 8);
+    const float* g = gu + blockIdx.x * 2 * hidden;
+    const float* u = g + hidden;
+    float* orow = out + blockIdx.x * hidden;
+    float v[CH][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int r = 0; r < CH; ++r) {
+        const int c = threadIdx.x + r * kSiluThreads;
+        if (c < chunks) {
+            const float4 ga = *(reinterpret_cast<const float4*>(g) + 2 * c), gb = *(reinterpret_cast<const float4*>(g) + 2 * c + 1);
+            const float4 ua = *(reinterpret_cast<const float4*>(u) + 2 * c), ub = *(reinterpret_cast<const float4*>(u) + 2 * c + 1);
+            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+            const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[r][j] = gg[j] / (1.0f + expf(-gg[j])) * uu[j];
+                amax = fmaxf(amax, fabsf(v[r][j]));
+            }
+            *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+            *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
+        }
+    }
+    const float all = block_max<kSiluThreads>(amax, red);
+    const size_t groups = static_cast<size_t>(hidden / 32);
+    uint8_t* corr = planes + groups * nsets * 256;
+    float P, invP;
+    row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
+    if (threadIdx.x == 0) reinterpret_cast<float*>(corr + groups * nsets * 32)[blockIdx.x] = invP;
+#pragma unroll
+    for (int r = 0; r < CH; ++r) {
+        const int c = threadIdx.x + r * kSiluThreads;
+        if (c < chunks) digits_item(v[r], P, blockIdx.x, c, ndigits, nsets, planes, corr);
+    }
+}
+
 int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
     // as many splits as keep every CTA resident at once (one wave), at least 32 keys each, at most
     // the portable cluster size
@@ -398,6 +519,19 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool ov = stream_overlap_enabled();
+    const bool in_regs = (dim % 256) == 0 && dim <= 8192 && aligned(h, 16) && aligned(out, 16) && aligned(gamma, 16) &&
+                         (!delta || aligned(delta, 16));
+    if (in_regs) {
+        uint8_t* pl = static_cast<uint8_t*>(prepared_out);
+        const dim3 grid(static_cast<unsigned>(rows)), block(kNormThreads);
+#define SGQ_NORM_ROW(PREPV, CHV) \
+    SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_row_kernel<PREPV, CHV>, grid, block, 0, s, ov, h, delta, gamma, eps, dim, out, L.ndigits, L.nsets, pl))
+        if (dim <= 2048) { if (pl) SGQ_NORM_ROW(true, 1); else SGQ_NORM_ROW(false, 1); }
+        else if (dim <= 4096) { if (pl) SGQ_NORM_ROW(true, 2); else SGQ_NORM_ROW(false, 2); }
+        else { if (pl) SGQ_NORM_ROW(true, 4); else SGQ_NORM_ROW(false, 4); }
+#undef SGQ_NORM_ROW
+        return SGQ_OK;
+    }
     if (prepared_out)
         SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
                                    gamma, eps, dim, out, L.ndigits, L.nsets, static_cast<uint8_t*>(prepared_out)));
@@ -456,6 +590,12 @@ int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out
     rc = check_device();
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (prepared_out && (hidden % 256) == 0 && hidden <= 8192) {
+        SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_row_kernel, dim3(static_cast<unsigned>(rows)), dim3(kSiluThreads), 0, s,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets,
+                                   static_cast<uint8_t*>(prepared_out)));
+        return SGQ_OK;
+    }
     if (prepared_out) {
         SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s,
                                    stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets,
