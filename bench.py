@@ -452,7 +452,7 @@ def run_ours(args):
     peaks = measured_peaks()
     if world > 1:
         args.no_overlap = True      # measured on 2 GPUs: the per-forward barrier leaves nothing to overlap (17.3 us serial, 19.2 us overlapped)
-    sgq.set_stream_overlap(not args.no_overlap)     # consecutive forwards overlap their prologue and first weight tiles
+    sgq.set_stream_overlap(0 if args.no_overlap else args.overlap_mode)     # consecutive forwards overlap their prologue and first weight tiles
     M, copies, lps = args.M, args.copies, args.launches_per_step
     if world > 1 and args.nccl and lps > 200:
         lps = 200
@@ -620,8 +620,8 @@ def run_ours(args):
                    "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
                    "path": sgq.PATH_NAMES[path], "bytes_per_launch": bytes_per_launch,
                    "launch": "one CUDA graph replay per step" if use_graph else "eager launches",
-                   "stream_overlap": "on: programmatic dependent launch, a forward's first weight tiles are fetched while the "
-                                     "previous forward finishes" if not args.no_overlap else "off"},
+                   "stream_overlap": (f"mode {args.overlap_mode}: programmatic dependent launch, a forward's first weight tiles are "
+                                      "fetched while the previous forward finishes") if not args.no_overlap else "off"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
                      "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_LAUNCH.get(M) if world == 1 else None,
@@ -660,6 +660,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--overlap-mode", type=int, default=1, choices=[1, 2],
+                    help="1: overlapped launches; 2: overlapped launches with the two-CTAs-per-SM form of the decode kernel")
     ap.add_argument("--nccl", action="store_true", help="N > 1: exchange output slices with an NCCL all-gather instead of peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -78,17 +78,18 @@ SGQ_API const char* sgq_last_error(void);
 SGQ_API int sgq_abi_version(void);
 
 /* Overlap of consecutive kernels in a stream (programmatic dependent launch; process-wide switch,
- * off by default, returns the previous setting; no counterpart in the reference).  When on, every
+ * off by default, returns the previous setting; no counterpart in the reference).  With 1, every
  * kernel of this library is launched so that it may start while the kernel before it in the same
  * stream is still finishing: its set-up, and for the decode kernel the first tiles of WEIGHTS and
  * SCALES, are fetched early; activations, workspaces and outputs are touched only after the
- * earlier kernel has completed.  The decode kernel then runs as two smaller CTAs per SM (so that the
- * next forward's CTA can sit beside the running one), which adds its fp32 partial sums in another
- * order: results equal those of the serial form to fp32 rounding, and are bit-identical from run
- * to run.  The one rule it adds: a weight, scale or
- * bias buffer must not be the output of the kernel launched immediately before the linear that
- * reads it in the same stream (quantize, then run something else or synchronise, then multiply).
- * It pays in launch-bound sequences: a decode step is ~130 kernels of 5-15 us. */
+ * earlier kernel has completed, so results are the same bits as without overlap.  With 2 the INT4
+ * decode kernel additionally runs as two smaller CTAs per SM, so that the next forward's CTA can sit
+ * beside the running one; that form adds its fp32 partial sums in another order (results equal to
+ * fp32 rounding, bit-identical run to run) and measured no faster than 1 on B200.  The one rule
+ * the switch adds: a weight, scale or bias buffer must not be the output of the kernel launched
+ * immediately before the linear that reads it in the same stream (quantize, then run something
+ * else or synchronise, then multiply).  It pays in launch-bound sequences: a decode step is ~130
+ * kernels of 3-17 us. */
 SGQ_API int sgq_set_stream_overlap(int enabled);
 
 /* Kernels that wait on hardware barriers (TMA / tensor-core pipelines) bound every wait; one that

@@ -95,10 +95,10 @@ def check(status: int, what: str = "sgq call") -> None:
         raise SgqError(status, f"{what} failed: {lib.sgq_status_string(status).decode()}", lib.sgq_last_error().decode())
 
 
-def set_stream_overlap(enabled: bool) -> bool:
+def set_stream_overlap(enabled) -> int:
     """Programmatic dependent launch for every kernel of the library (see sgq_set_stream_overlap in
     include/sgq.h for the one rule it adds).  Returns the previous setting."""
-    return bool(lib.sgq_set_stream_overlap(1 if enabled else 0))
+    return int(lib.sgq_set_stream_overlap(int(enabled)))
 
 
 def device_status(clear: bool = True) -> int:

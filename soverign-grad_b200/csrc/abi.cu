@@ -106,6 +106,7 @@ namespace {
 int g_stream_overlap = 0;
 }
 bool stream_overlap_enabled() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) != 0; }
+bool stream_overlap_compact() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) == 2; }
 
 int check_device() {
     if (device_info().major != 10) {
@@ -200,7 +201,7 @@ const char* sgq_last_error(void) { return g_error; }
 int sgq_abi_version(void) { return SGQ_ABI_VERSION; }
 
 int sgq_set_stream_overlap(int enabled) {
-    return __atomic_exchange_n(&g_stream_overlap, enabled ? 1 : 0, __ATOMIC_RELAXED);
+    return __atomic_exchange_n(&g_stream_overlap, enabled == 2 ? 2 : (enabled ? 1 : 0), __ATOMIC_RELAXED);
 }
 
 int sgq_device_status(unsigned int* word, int clear) {

@@ -707,7 +707,7 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
     LinearArgs probe = a;
     if (planes_ready) probe.x = static_cast<const float*>(a.workspace);      // x is not read: only its alignment rule is waived
-    const bool compact = stream_overlap_enabled();
+    const bool compact = stream_overlap_compact();
     if (!gemv_supported(probe) || !((compact && make_plan(a.M, a.K, have_ws, &p, true)) || make_plan(a.M, a.K, have_ws, &p)) ||
         (planes_ready && !have_ws)) {
         set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "

@@ -48,6 +48,7 @@ struct SmemOptIn {
 // serialization, so that a kernel's prologue, and for the decode kernel its first weight tiles,
 // overlap the tail of the kernel before it in the stream.
 bool stream_overlap_enabled();
+bool stream_overlap_compact();     // mode 2: the decode kernel also takes its two-CTAs-per-SM form
 
 #ifdef __CUDACC__
 // kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute when `overlap`.

@@ -142,7 +142,7 @@ class _PeerSites:
 class NanoLlamaInt4:
     def __init__(self, cfg: NanoLlamaConfig, device, batch: int, *, seed: int = 0,
                  init: Optional[Callable[[str, int], torch.Tensor]] = None, rank: int = 0, world: int = 1, group=None,
-                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO, overlap: bool = True,
+                 decode_path: int = PATH_AUTO, prefill_path: int = PATH_AUTO, overlap: int = 1,
                  exchange: str = "peer"):
         if cfg.n_heads % world or cfg.hidden % (32 * world) or cfg.dim % (32 * world) or cfg.vocab % (32 * world):
             raise ValueError("heads, hidden, dim and vocab must split into equal 32-row slices per rank")
@@ -352,7 +352,7 @@ class NanoLlamaInt4:
 
     @contextlib.contextmanager
     def _overlapped(self):
-        prev = set_stream_overlap(self.overlap)
+        prev = set_stream_overlap(int(self.overlap))
         try:
             yield
         finally:

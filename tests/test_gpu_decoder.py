@@ -240,14 +240,17 @@ def test_greedy_decode_matches_full_recompute(sgq, nl, port, prompt_len, n_new, 
 
 
 def test_overlapped_launches_agree_with_serial_ones(sgq, nl, port):
-    """Programmatic dependent launch on (the default of the model) and off: same tokens, and logits
-    equal up to fp32 summation order (an overlapped decode forward runs as two smaller CTAs per SM,
-    which add their partial sums in a different order)."""
-    _, _, tok_on, log_on, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=True)
-    _, _, tok_off, log_off, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=False)
+    """Programmatic dependent launch on (the default of the model) and off: the same bits; with the
+    two-CTAs-per-SM form of the decode kernel (mode 2): same tokens, logits equal up to fp32 summation
+    order (that form adds its partial sums in a different order)."""
+    _, _, tok_on, log_on, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=1)
+    _, _, tok_off, log_off, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=0)
+    _, _, tok_two, log_two, _ = tiny_model(nl, port, prompt_len=9, n_new=6, prefill_path=sgq.PATH_SIMT, overlap=2)
     np.testing.assert_array_equal(tok_on, tok_off)
-    for a, b in zip(log_on, log_off):
-        assert norm_err(a, b) <= 2e-5
+    np.testing.assert_array_equal(tok_two, tok_off)
+    for a, b, c in zip(log_on, log_off, log_two):
+        np.testing.assert_array_equal(a, b)
+        assert norm_err(c, b) <= 2e-5
     assert sgq.device_status() == 0
 
 
@@ -274,7 +277,9 @@ def test_overlap_switch_on_back_to_back_linears(sgq, M, K):
         inputs = []
         want = chain(inputs)
         outputs = inputs[1:] + [want]
-        sgq.set_stream_overlap(True)
+        sgq.set_stream_overlap(1)
+        assert torch.equal(chain(), want)                                 # overlapped launches alone change no bit
+        sgq.set_stream_overlap(2)                                         # ... the two-CTAs-per-SM form changes the summation order
         got = chain()
         again = chain()
         ws = sgq.Workspace(x0.device)      # every layer on the serial run's input, launched back to back
