@@ -50,7 +50,6 @@ constexpr int kABytes = BM * 128;     // 256 rows x 128 B (rows 128.. are the se
 constexpr int kBBytes = BN * 128;     // 256 rows x 128 B
 constexpr int kRawBytes = BN * 32;    // 256 rows x 64 nibbles (kBF16); the INT8 form is twice that, Cfg::kRawStageBytes
 constexpr int kDequantWarps = 16;     // two threads per row of the 256-row weight tile (one 32-k group each)
-constexpr int kDequantGroups = 1;
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kBProducerWarp = 6;     // loads B (kI8) or the raw nibbles (kBF16)
 constexpr int kDequantWarp0 = 7;
@@ -67,7 +66,7 @@ struct Cfg {
     static constexpr int kBStages = 3;
     static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
     static constexpr int kRawStageBytes = MODE == kBF16W8 ? BN * 64 : kRawBytes;
-    static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps * kDequantGroups;
+    static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps;
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kAOff = 0;
     static constexpr int kBOff = kAStages * kABytes;

@@ -9,7 +9,7 @@
 //     and a box [8 steps][16 rows][8] of fp32 scales, into a ring of stages guarded by
 //     full/empty mbarriers.  A step is 256 k of a 16-row tile.
 //   * Integer inner product.  Each activation row is turned once per CTA into fixed point
-//     relative to the power of two above its absmax (22 bits for M <= 5, 14 bits above), split
+//     relative to the power of two above its absmax (22 bits for M <= 2, 14 bits above: eight digit columns = one MMA then cover M = 4), split
 //     into balanced base-256 digits (int8).  The 4-bit codes become bytes with two LOP3s per
 //     eight codes ((w & 0x0F0F0F0F) ^ 0x08080808 = code + 8, exact), and a 32-k group of 16
 //     weight rows times up to 8 digit columns is ONE mma.sync m16n8k32 (u8 x s8 -> s32, exact).
@@ -23,7 +23,7 @@
 //
 // Error against the reference's single fp32 chain: the fixed-point step is 2^-22 (2^-14) of the
 // row's power-of-two bound per activation, everything up to the group sums is exact, the rest
-// is fp32 rounding: ~1e-6 (M <= 5) / ~4e-5 (M > 5) relative for Gaussian rows, inside 1e-3.
+// is fp32 rounding: ~1e-6 (M <= 2) / ~4e-5 (M > 2) relative for Gaussian rows, inside 1e-3.
 // Activations must be finite.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
@@ -60,10 +60,6 @@ extern "C" __attribute__((visibility("default"))) int sgq_debug_set_timeline(uns
 }
 #else
 #define SGQ_MARK(slot) do { } while (0)
-#endif
-
-#ifndef SGQ_EXP
-#define SGQ_EXP 0
 #endif
 
 namespace {
@@ -460,18 +456,14 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             if (seq < 5) SGQ_MARK(3 + 2 * seq);
             const int step = c0 + step_in_stage;
-            if (alive && step < spt && !(SGQ_EXP & 16)) {
+            if (alive && step < spt) {
                 const uint8_t* wbox = stages + st * kStageBytes + step_in_stage * kWStepBytes;
                 const uint8_t* sbox = stages + st * kStageBytes + kStageW + step_in_stage * kSStepBytes;
                 float sc_lo[kGroupsPerWarp], sc_hi[kGroupsPerWarp];   // scales of rows g and g+8
 #pragma unroll
                 for (int h = 0; h < kGroupsPerWarp / 4; ++h) {
-#if (SGQ_EXP & 128)
-                    const float4 a = make_float4(1.f, 2.f, 3.f, 4.f), b = a;
-#else
                     const float4 a = *reinterpret_cast<const float4*>(sbox + g * 32 + (g0 / 4 + h) * 16);
                     const float4 b = *reinterpret_cast<const float4*>(sbox + (g + 8) * 32 + (g0 / 4 + h) * 16);
-#endif
                     sc_lo[4 * h + 0] = a.x; sc_lo[4 * h + 1] = a.y; sc_lo[4 * h + 2] = a.z; sc_lo[4 * h + 3] = a.w;
                     sc_hi[4 * h + 0] = b.x; sc_hi[4 * h + 1] = b.y; sc_hi[4 * h + 2] = b.z; sc_hi[4 * h + 3] = b.w;
                 }
@@ -494,29 +486,15 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     a[3] = ((w_hi >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // row g+8
 #pragma unroll
                     for (int s = 0; s < NSETS; ++s) {
-#if (SGQ_EXP & 64)
-                        const uint2 xb = make_uint2(seq + i, seq * 3 + s);
-                        const int2 cc = make_int2(i, s);
-#else
                         const uint2 xb = *reinterpret_cast<const uint2*>(xg + i * (256 * NSETS) + s * 256);
                         const int2 cc = *reinterpret_cast<const int2*>(cg + i * (32 * NSETS) + s * 32);
-#endif
                         int d[4];
-#if (SGQ_EXP & 4)
-                        d[0] = a[0] + xb.x + cc.x; d[1] = a[1] + xb.y + cc.y; d[2] = a[2] + xb.x; d[3] = a[3] + xb.y;
-#else
                         mma_u8s8_16832(d, a, xb.x, xb.y, cc.x, cc.y);
-#endif
-#if (SGQ_EXP & 2)
-                        total[s][0] += __int_as_float(d[0]); total[s][1] += __int_as_float(d[1]);
-                        total[s][2] += __int_as_float(d[2]) * sc_lo[i]; total[s][3] += __int_as_float(d[3]) * sc_hi[i];
-#else
                         // d holds 12582912.0f + (exact group sum) as fp32 bits: one subtraction instead of a conversion
                         total[s][0] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[0]), kGroupSumBiasF), total[s][0]);
                         total[s][1] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[1]), kGroupSumBiasF), total[s][1]);
                         total[s][2] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[2]), kGroupSumBiasF), total[s][2]);
                         total[s][3] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[3]), kGroupSumBiasF), total[s][3]);
-#endif
                     }
                 }
             }
@@ -567,16 +545,12 @@ struct Plan {
 // latency and the tail of consecutive decode forwards hide behind each other.
 constexpr int kCompactSmem = 112 * 1024;
 bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact = false) {
-    p->ndigits = (M <= 5) ? 3 : 2;
+    p->ndigits = prepared_layout(M, K).ndigits;
     p->nsets = static_cast<int>((M * p->ndigits + 7) / 8);
     p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 288 + kMaxM * 4;
     const int limit = compact ? kCompactSmem : kSmemLimit;
     // two warps per step while at least 3 stages still fit, else one (smaller partial-sum buffers)
-#ifdef SGQ_FORCE_WPB
-    for (int wpb = SGQ_FORCE_WPB; wpb >= 1; --wpb) {
-#else
     for (int wpb = compact ? 1 : 3; wpb >= 1; --wpb) {
-#endif
         for (int st = kMaxStages; st >= (wpb == 3 ? 4 : (wpb == 2 ? 3 : 2)); --st) {
             const Smem L = smem_layout(st, K, p->nsets, consumer_warps(wpb));
             if (L.total + 1024 <= static_cast<uint32_t>(limit)) {

@@ -4,7 +4,7 @@
 // scale per row.  Shared by the decode kernel (conversion inside its CTAs), the stand-alone
 // conversion kernel, and the decoder operators that emit this format directly.
 //
-// Layout of a prepared buffer for M rows of K values (K % 256 == 0), with ndigits = 3 (M <= 5) or
+// Layout of a prepared buffer for M rows of K values (K % 256 == 0), with ndigits = 3 (M <= 2) or
 // 2 and nsets = ceil(M * ndigits / 8):
 //   [digit planes: (K/32) * nsets * 256 B][corrections: (K/32) * nsets * 32 B][inv scale: 16 fp32]
 #pragma once
@@ -29,7 +29,7 @@ struct PreparedLayout {
 
 inline PreparedLayout prepared_layout(int64_t M, int64_t K) {
     PreparedLayout L;
-    L.ndigits = (M <= 5) ? 3 : 2;
+    L.ndigits = (M <= 2) ? 3 : 2;        // 2 digits: M = 3, 4 still fit one set of 8 columns
     L.nsets = static_cast<int>((M * L.ndigits + 7) / 8);
     L.bytes = static_cast<size_t>(K / 32) * L.nsets * 288 + kPreparedMaxM * 4;
     return L;

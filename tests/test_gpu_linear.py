@@ -128,7 +128,7 @@ def test_decode_int8_kernel_against_port(sgq, port, M, K, N):
         assert rel_err(y, want) <= TOL_FP32, (M, K, N, scheme, rel_err(y, want))
         # the kernel's own arithmetic: x in fixed point (22 / 14 fractional bits below the power of two
         # above the row's absmax, round to nearest), exact integer dot products, then fp32 scaling
-        frac = 22 if M <= 5 else 14
+        frac = 22 if M <= 2 else 14
         e = np.floor(np.log2(np.abs(x).max(axis=1, keepdims=True).astype(np.float64))) + 1
         xq = np.rint(x.astype(np.float64) * 2.0 ** (frac - e))
         model = (xq @ wq.astype(np.float64).T) * 2.0 ** (e - frac) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
