@@ -454,8 +454,6 @@ def run_ours(args):
         args.no_overlap = True      # measured on 2 GPUs: the per-forward barrier leaves nothing to overlap (17.3 us serial, 19.2 us overlapped)
     sgq.set_stream_overlap(0 if args.no_overlap else args.overlap_mode)     # consecutive forwards overlap their prologue and first weight tiles
     M, copies, lps = args.M, args.copies, args.launches_per_step
-    if world > 1 and args.nccl and lps > 200:
-        lps = 200
     if args.only:
         # profiling aid: run one secondary case a few times, eagerly, and print it
         g0 = torch.Generator(device=dev).manual_seed(1234)
@@ -477,15 +475,28 @@ def run_ours(args):
     if world > 1:
         import importlib
         sh = importlib.import_module("sgq_b200.sharding")
-        if args.nccl or M > 16:
-            # one column-sharded layer per weight set: local slice through the C ABI, NCCL all-gather, interleave
-            sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
-        else:
+        exchange = None
+        if not (args.nccl or M > 16):
             # fused all-gather: the decode kernel stores its slice into every rank's output (peer stores), then one
             # barrier kernel; two alternating output sets, shared by all layers of this shape
-            exchange = sh.PeerExchange(M, world * N_DIM, dev)
+            ok = torch.ones(1, device=dev)
+            try:
+                exchange = sh.PeerExchange(M, world * N_DIM, dev)
+            except Exception as e:  # noqa: BLE001  (no peer mapping on this box: every rank falls back together)
+                sys.stderr.write(f"[bench] rank {rank}: peer exchange unavailable ({type(e).__name__}: {e}); using NCCL\n")
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok.item()) == 0.0:
+                exchange, args.nccl = None, True
+        if exchange is None:
+            # one column-sharded layer per weight set: local slice through the C ABI, NCCL all-gather, interleave
+            args.nccl = True
+            sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
+        else:
             # barrier as its own small kernel: measured faster than the in-kernel form (17.3 vs 19.6 us per forward at N=2)
             sharded = [sh.PeerShardedLinear(q, None, world * N_DIM, exchange, fused_barrier=False) for q in weights]
+    if world > 1 and args.nccl and lps > 200:
+        lps = 200                   # eager NCCL launches: keep a step short
     last = {}
 
     def forward(i):
