@@ -18,6 +18,7 @@
 #include <vector>
 
 #include "sovereigngrad/nn.hpp"
+#include "sovereigngrad/safetensors.hpp"
 
 using namespace sovereigngrad;
 namespace q = sovereigngrad::quantization;
@@ -143,6 +144,58 @@ static int run_cpu() {
     Tensor y = lin.forward(Tensor(std::vector<float>(16, 1.0f), {2, 8}));
     CHECK(y.shape() == (std::vector<int64_t>{2, 4}));
     std::puts("ok no cpu fallback");
+
+    // packed-weight checkpoint: an INT4 and an INT8 tensor as packed codes + scales + metadata
+    {
+        namespace st = safetensors;
+        const std::string path = "/tmp/sgq_host_test_ckpt.safetensors";
+        q::QuantizedTensor q4, q8;
+        q4.bits = 4; q4.group_size = 32; q4.original_shape = {8, 64}; q4.layout = q::WeightLayout::NK;
+        q4.scheme = q::QuantizationScheme::GroupedAsymmetric;
+        q4.qdata = Tensor::empty({8 * 64 / 2}, Device::CPU, DType::UInt8);
+        q4.scales = Tensor::empty({8 * 64 / 32}, Device::CPU);
+        for (int i = 0; i < 256; ++i) static_cast<uint8_t*>(q4.qdata.raw())[i] = static_cast<uint8_t>(i * 37 + 5);
+        for (int i = 0; i < 16; ++i) q4.scales.data()[i] = 0.001f * static_cast<float>(i + 1);
+        q8.bits = 8; q8.group_size = 15; q8.original_shape = {3, 5};
+        q8.scheme = q::QuantizationScheme::PerChannelSymmetric;
+        q8.qdata = Tensor::empty({3, 5}, Device::CPU, DType::Int8);
+        q8.scales = Tensor::empty({3}, Device::CPU);
+        for (int i = 0; i < 15; ++i) static_cast<int8_t*>(q8.qdata.raw())[i] = static_cast<int8_t>(i * 17 - 127);
+        for (int i = 0; i < 3; ++i) q8.scales.data()[i] = 0.5f + static_cast<float>(i);
+        st::StateDict sd;
+        st::Metadata md;
+        md["format"] = "sgq \"packed\" v1";
+        st::put_quantized("layers.0.w", q4, &sd, &md);
+        st::put_quantized("head", q8, &sd, &md);
+        sd["bias"] = Tensor(std::vector<float>{1.f, -2.f, 3.5f}, {3});
+        st::save_file(sd, path, md);
+        st::Metadata md2;
+        auto meta = st::inspect_file(path, &md2);
+        CHECK(meta.size() == 5 && meta.at("layers.0.w.qdata").dtype == "U8" && meta.at("head.qdata").dtype == "I8");
+        CHECK(meta.at("head.qdata").shape == (std::vector<int64_t>{3, 5}) && md2 == md);
+        CHECK(meta.at("layers.0.w.qdata").data_offset_end - meta.at("layers.0.w.qdata").data_offset_start == 256);   // 8x less than fp32 codes
+        st::Metadata md3;
+        st::StateDict back = st::load_file(path, Device::CPU, &md3);
+        q::QuantizedTensor r4 = st::get_quantized("layers.0.w", back, md3), r8 = st::get_quantized("head", back, md3);
+        CHECK(r4.bits == 4 && r4.group_size == 32 && r4.layout == q::WeightLayout::NK && r4.original_shape == q4.original_shape);
+        CHECK(std::memcmp(r4.qdata.raw(), q4.qdata.raw(), 256) == 0 && std::memcmp(r4.scales.raw(), q4.scales.raw(), 64) == 0);
+        CHECK(r8.bits == 8 && r8.scheme == q::QuantizationScheme::PerChannelSymmetric && r8.layout == q::WeightLayout::KN);
+        CHECK(std::memcmp(r8.qdata.raw(), q8.qdata.raw(), 15) == 0 && r8.scales.to_vector() == q8.scales.to_vector());
+        CHECK(back.at("bias").to_vector() == (std::vector<float>{1.f, -2.f, 3.5f}));
+        // equal inputs give equal files; malformed files are refused
+        st::save_file(sd, path + ".2", md);
+        std::ifstream fa(path, std::ios::binary), fb(path + ".2", std::ios::binary);
+        std::string ca((std::istreambuf_iterator<char>(fa)), std::istreambuf_iterator<char>());
+        std::string cb((std::istreambuf_iterator<char>(fb)), std::istreambuf_iterator<char>());
+        CHECK(ca == cb && ca.size() > 8);
+        { std::ofstream cut(path + ".3", std::ios::binary); cut.write(ca.data(), static_cast<std::streamsize>(ca.size() - 5)); }
+        CHECK(throws([&] { st::load_file(path + ".3"); }));
+        CHECK(throws([&] { st::load_file("/tmp/sgq_no_such_file.safetensors"); }));
+        md3.erase("head.bits");
+        CHECK(throws([&] { st::get_quantized("head", back, md3); }));
+        std::remove(path.c_str()); std::remove((path + ".2").c_str()); std::remove((path + ".3").c_str());
+        std::puts("ok packed checkpoint");
+    }
     return 0;
 }
 

@@ -25,7 +25,8 @@ def test_host_layer_on_cpu():
     ensure_built()
     r = subprocess.run([EXE, "cpu"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
-    for line in ("ok cpu pool statistics", "ok device pool on the stand-in backend", "ok tensor metadata", "ok no cpu fallback"):
+    for line in ("ok cpu pool statistics", "ok device pool on the stand-in backend", "ok tensor metadata", "ok no cpu fallback",
+                 "ok packed checkpoint"):
         assert line in r.stdout
 
 
