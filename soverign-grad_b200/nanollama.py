@@ -367,6 +367,10 @@ class NanoLlamaInt4:
         B, P = prompt.shape
         if B != self.batch or P > self.cfg.max_seq:
             raise ValueError("prompt shape does not fit the model's batch / max_seq")
+        # checked on the host: an out-of-range id must never reach the gather kernel (the reference's
+        # embedding returns zeros for such ids, src/ops.cpp:2624-2659; here it is an error)
+        if P and (int(prompt.min()) < 0 or int(prompt.max()) >= self.cfg.vocab):
+            raise ValueError("token id outside [0, vocab)")
         self._launches = 0
         self.reset()
         with self._overlapped():
