@@ -67,8 +67,12 @@ enum {
     SGQ_PATH_AUTO = 0,
     SGQ_PATH_SIMT = 1,    /* tiled fp32 SIMT kernel, any shape; one fused-multiply-add chain per
                              output in ascending k, i.e. the reference CPU rounding */
-    SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernels, fp32 accumulation ([N,K]: INT4 g=32 and
-                             INT8 on integer tensor-core tiles; [K,N], the reference module's layout: fp32) */
+    SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernels.  [N,K] (INT4 g=32, INT8): exact integer
+                             tensor-core dot products of the codes with block-scaled fixed-point activations (one
+                             scale per 32 k of a row, 16 bits, 24 for M = 1), fp32 scaling and accumulation; any
+                             activation distribution stays within 1e-3 of the reference's fp32 forward; a row with a
+                             NaN or Inf activation yields a NaN output row.  [K,N] (the reference module's layout):
+                             fp32 throughout */
     SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16, weights dequantized to bf16 in shared memory */
     SGQ_PATH_TC_I8 = 4    /* prefill, INT8 weights only: activations quantized per row, tcgen05 kind::i8 */
 };
@@ -158,7 +162,7 @@ SGQ_API int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, con
  * group 32, SGQ_PATH_GEMV) computes for that x.  The format is opaque, depends on (M, K) and is
  * only valid for the library build that wrote it.
  *   sgq_prepared_x_bytes  bytes of the prepared form of x[M, K]; 0 when there is none (it needs
- *                         1 <= M <= 16, K % 256 == 0 and planes that fit in shared memory)
+ *                         1 <= M <= 16 and K % 256 == 0)
  *   sgq_prepare_x         x[M, K] fp32 (16-byte aligned) -> prepared (256-byte aligned) */
 SGQ_API size_t sgq_prepared_x_bytes(int64_t M, int64_t K);
 SGQ_API int sgq_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, size_t prepared_bytes, void* stream);
@@ -193,9 +197,17 @@ SGQ_API int sgq_peer_scatter(const float* src, int64_t M, int64_t n_local, float
  * writable by every rank: symmetric / peer-mapped memory).  local_epoch: one zero-initialised 64-bit
  * counter in this GPU's own memory.  Every rank must call it the same number of times.  All peer
  * stores this GPU issued before the barrier are visible on their targets once the targets' barriers
- * return.  The wait is bounded (a few tenths of a second): if a rank never arrives the kernel gives
- * up and sgq_device_status() reports it. */
+ * return.  The wait is bounded (about half a second by default, see
+ * sgq_set_peer_wait_budget): if a rank never arrives the kernel gives up, returns, and
+ * sgq_device_status() reports SGQ_ERR_TIMEOUT; the outputs of that exchange are then incomplete and
+ * must not be used. */
 SGQ_API int sgq_peer_barrier(void* const* signals, int rank, int world, void* local_epoch, void* stream);
+
+/* Number of polls a device-side wait for another GPU spends before it gives up (process-wide, applies
+ * to launches made afterwards; returns the previous value; no counterpart in the reference).  A poll
+ * costs 0.1-0.4 us once a wait has lasted more than a few microseconds; the default 2^21 is about half
+ * a second.  Smaller values make a missing rank show up sooner (and let a test make a wait run out). */
+SGQ_API unsigned int sgq_set_peer_wait_budget(unsigned int polls);
 
 /* Decode forward for callers that cannot allocate device memory.  (No counterpart in the
  * reference: there every call allocates its temporaries through MemoryAllocator.)
@@ -210,8 +222,8 @@ SGQ_API int sgq_peer_barrier(void* const* signals, int rank, int world, void* lo
  * but the scratch is a fixed array inside the library's device image: 320 KiB on every GPU that
  * loads the library, held until the process exits.  Limits and rules:
  *  - shapes the decode kernel takes (M <= 16, K % 256 == 0, 16-byte aligned x/packed/scales) whose
- *    scratch need, sgq_linear_workspace_bytes(4, M, K, N, SGQ_LAYOUT_NK, SGQ_PATH_GEMV), is at most
- *    320 KiB (e.g. K = 8192 at M = 16); anything larger returns SGQ_ERR_WORKSPACE;
+ *    prepared activations, sgq_prepared_x_bytes(M, K), are at most 320 KiB (e.g. K = 8192 at
+ *    M = 16); anything larger returns SGQ_ERR_WORKSPACE;
  *  - the first call on each device looks up the array's device address (a runtime query, no
  *    allocation); make that first call outside any stream capture;
  *  - all calls on a device share the one array, whose contents are simply overwritten by the next

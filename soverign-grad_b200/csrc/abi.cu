@@ -104,7 +104,9 @@ bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void*
 
 namespace {
 int g_stream_overlap = 0;
+unsigned int g_peer_wait_budget = 1u << 21;     // about half a second with the back-off of the wait loop
 }
+unsigned int peer_wait_budget() { return __atomic_load_n(&g_peer_wait_budget, __ATOMIC_RELAXED); }
 bool stream_overlap_enabled() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) != 0; }
 bool stream_overlap_compact() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) == 2; }
 
@@ -202,6 +204,10 @@ int sgq_abi_version(void) { return SGQ_ABI_VERSION; }
 
 int sgq_set_stream_overlap(int enabled) {
     return __atomic_exchange_n(&g_stream_overlap, enabled == 2 ? 2 : (enabled ? 1 : 0), __ATOMIC_RELAXED);
+}
+
+unsigned int sgq_set_peer_wait_budget(unsigned int polls) {
+    return __atomic_exchange_n(&g_peer_wait_budget, polls < 16u ? 16u : polls, __ATOMIC_RELAXED);
 }
 
 int sgq_device_status(unsigned int* word, int clear) {
@@ -400,6 +406,7 @@ int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_lo
         }
         a.peers.rank = rank;
         a.peers.state = static_cast<unsigned long long*>(local_state);
+        a.peers.poll_budget = peer_wait_budget();
     }
     a.y = a.peers.p[0];
     a.ldy = ldy;

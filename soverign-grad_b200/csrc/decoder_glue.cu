@@ -23,17 +23,6 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// Block-wide maximum, known to every thread afterwards.  `red` holds THREADS / 32 floats.
-template <int THREADS>
-__device__ __forceinline__ float block_max(float v, float* red) {
-    v = warp_max(v);
-    __syncthreads();                                   // red may still be read by an earlier reduction
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = red[(threadIdx.x & 31) < THREADS / 32 ? (threadIdx.x & 31) : 0];
-    return warp_max(t);
-}
-
 // One block per row.  Pass 1 adds the delta into the residual stream and accumulates the sum of
 // squares; pass 2 re-reads the row (L1/L2) and scales it.  The reference sums the squares of a row
 // sequentially in fp32 (src/ops.cpp:1546-1550); a tree sum differs from it by a few ulps.
@@ -41,7 +30,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 template <bool PREP>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                   const float* __restrict__ gamma, float eps, int64_t dim,
-                                                                  float* out, int ndigits, int nsets, uint8_t* planes) {
+                                                                  float* out, int ndigits, int nsets, int colmul, uint8_t* planes) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float inv_rms_s;
     pdl_launch_dependents();
@@ -77,7 +66,6 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
     }
     __syncthreads();      // also orders this thread block's writes of h before the re-read below
     const float inv = inv_rms_s;
-    float amax = 0.f;
     if ((dim & 3) == 0) {
         for (int64_t i = threadIdx.x * 4; i < dim; i += kNormThreads * 4) {
             const float4 v = *reinterpret_cast<const float4*>(hr + i);
@@ -85,14 +73,13 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
             float4 o;
             o.x = v.x * inv * g.x; o.y = v.y * inv * g.y; o.z = v.z * inv * g.z; o.w = v.w * inv * g.w;
             *reinterpret_cast<float4*>(orow + i) = o;
-            if (PREP) amax = fmaxf(fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y))), fmaxf(fabsf(o.z), fabsf(o.w)));
         }
     } else {
         for (int64_t i = threadIdx.x; i < dim; i += kNormThreads) orow[i] = hr[i] * inv * gamma[i];
     }
     if (PREP) {
-        const float all = block_max<kNormThreads>(amax, red);      // its barriers also publish this block's stores of orow
-        prepare_row_block<kNormThreads>(orow, all, blockIdx.x, dim, ndigits, nsets, planes);
+        __syncthreads();                                           // publishes this block's stores of orow
+        prepare_row_block<kNormThreads>(orow, blockIdx.x, dim, ndigits, nsets, colmul, planes);
     }
 }
 
@@ -112,7 +99,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <bool PREP, int CH>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                       const float* __restrict__ gamma, float eps, int64_t dim,
-                                                                      float* __restrict__ out, int ndigits, int nsets,
+                                                                      float* __restrict__ out, int ndigits, int nsets, int colmul,
                                                                       uint8_t* __restrict__ planes) {
     __shared__ float red[kNormThreads / 32];
     pdl_launch_dependents();
@@ -141,7 +128,6 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __
         }
     }
     const float inv = 1.0f / sqrtf(block_sum<kNormThreads>(ss, red) / static_cast<float>(dim) + eps);
-    float amax = 0.f;
 #pragma unroll
     for (int r = 0; r < CH; ++r) {
         const int c = threadIdx.x + r * kNormThreads;
@@ -149,25 +135,17 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __
             const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c), gb = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * c + 1);
             const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[r][j] = v[r][j] * inv * g[j];
-                amax = fmaxf(amax, fabsf(v[r][j]));
-            }
+            for (int j = 0; j < 8; ++j) v[r][j] = v[r][j] * inv * g[j];
             *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
             *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
         }
     }
     if (PREP) {
-        const float all = block_max<kNormThreads>(amax, red);
-        const size_t groups = static_cast<size_t>(dim / 32);
-        uint8_t* corr = planes + groups * nsets * 256;
-        float P, invP;
-        row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
-        if (threadIdx.x == 0) reinterpret_cast<float*>(corr + groups * nsets * 32)[blockIdx.x] = invP;
+        float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(dim / 32) * nsets * 256);
 #pragma unroll
         for (int r = 0; r < CH; ++r) {
-            const int c = threadIdx.x + r * kNormThreads;
-            if (c < chunks) digits_item(v[r], P, blockIdx.x, c, ndigits, nsets, planes, corr);      // chunks % 32 == 0: whole warps
+            const int c = threadIdx.x + r * kNormThreads;       // chunks % 32 == 0: whole warps
+            if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 0.0625f, planes, scales);
         }
     }
 }
@@ -384,14 +362,12 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 
 // One block per row; also converts the row to the decode kernel's prepared-activation format.
 __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const float* __restrict__ gu, int64_t hidden, float* out,
-                                                                       int ndigits, int nsets, uint8_t* planes) {
-    __shared__ float red[kNormThreads / 32];
+                                                                       int ndigits, int nsets, int colmul, uint8_t* planes) {
     pdl_launch_dependents();
     pdl_wait();
     const float* g = gu + blockIdx.x * 2 * hidden;
     const float* u = g + hidden;
     float* orow = out + blockIdx.x * hidden;
-    float amax = 0.f;
     for (int64_t i = threadIdx.x * 4; i < hidden; i += kNormThreads * 4) {
         const float4 a = *reinterpret_cast<const float4*>(g + i);
         const float4 b = *reinterpret_cast<const float4*>(u + i);
@@ -399,18 +375,16 @@ __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const fl
         o.x = a.x / (1.0f + expf(-a.x)) * b.x; o.y = a.y / (1.0f + expf(-a.y)) * b.y;
         o.z = a.z / (1.0f + expf(-a.z)) * b.z; o.w = a.w / (1.0f + expf(-a.w)) * b.w;
         *reinterpret_cast<float4*>(orow + i) = o;
-        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(o.x), fabsf(o.y))), fmaxf(fabsf(o.z), fabsf(o.w)));
     }
-    const float all = block_max<kNormThreads>(amax, red);
-    prepare_row_block<kNormThreads>(orow, all, blockIdx.x, hidden, ndigits, nsets, planes);
+    __syncthreads();                                               // publishes this block's stores of orow
+    prepare_row_block<kNormThreads>(orow, blockIdx.x, hidden, ndigits, nsets, colmul, planes);
 }
 
 // The register-resident form of the same (hidden % 256 == 0, hidden <= 8192): one pass over memory.
 constexpr int kSiluThreads = 512;
 __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(const float* __restrict__ gu, int64_t hidden,
-                                                                           float* __restrict__ out, int ndigits, int nsets,
+                                                                           float* __restrict__ out, int ndigits, int nsets, int colmul,
                                                                            uint8_t* __restrict__ planes) {
-    __shared__ float red[kSiluThreads / 32];
     pdl_launch_dependents();
     pdl_wait();
     constexpr int CH = 2;
@@ -419,7 +393,6 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(cons
     const float* u = g + hidden;
     float* orow = out + blockIdx.x * hidden;
     float v[CH][8];
-    float amax = 0.f;
 #pragma unroll
     for (int r = 0; r < CH; ++r) {
         const int c = threadIdx.x + r * kSiluThreads;
@@ -429,24 +402,16 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(cons
             const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
             const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[r][j] = gg[j] / (1.0f + expf(-gg[j])) * uu[j];
-                amax = fmaxf(amax, fabsf(v[r][j]));
-            }
+            for (int j = 0; j < 8; ++j) v[r][j] = gg[j] / (1.0f + expf(-gg[j])) * uu[j];
             *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
             *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
         }
     }
-    const float all = block_max<kSiluThreads>(amax, red);
-    const size_t groups = static_cast<size_t>(hidden / 32);
-    uint8_t* corr = planes + groups * nsets * 256;
-    float P, invP;
-    row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
-    if (threadIdx.x == 0) reinterpret_cast<float*>(corr + groups * nsets * 32)[blockIdx.x] = invP;
+    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(hidden / 32) * nsets * 256);
 #pragma unroll
     for (int r = 0; r < CH; ++r) {
-        const int c = threadIdx.x + r * kSiluThreads;
-        if (c < chunks) digits_item(v[r], P, blockIdx.x, c, ndigits, nsets, planes, corr);
+        const int c = threadIdx.x + r * kSiluThreads;           // whole warps
+        if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 0.0625f, planes, scales);
     }
 }
 
@@ -525,7 +490,7 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
         uint8_t* pl = static_cast<uint8_t*>(prepared_out);
         const dim3 grid(static_cast<unsigned>(rows)), block(kNormThreads);
 #define SGQ_NORM_ROW(PREPV, CHV) \
-    SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_row_kernel<PREPV, CHV>, grid, block, 0, s, ov, h, delta, gamma, eps, dim, out, L.ndigits, L.nsets, pl))
+    SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_row_kernel<PREPV, CHV>, grid, block, 0, s, ov, h, delta, gamma, eps, dim, out, L.ndigits, L.nsets, L.colmul, pl))
         if (dim <= 2048) { if (pl) SGQ_NORM_ROW(true, 1); else SGQ_NORM_ROW(false, 1); }
         else if (dim <= 4096) { if (pl) SGQ_NORM_ROW(true, 2); else SGQ_NORM_ROW(false, 2); }
         else { if (pl) SGQ_NORM_ROW(true, 4); else SGQ_NORM_ROW(false, 4); }
@@ -534,10 +499,10 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
     }
     if (prepared_out)
         SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
-                                   gamma, eps, dim, out, L.ndigits, L.nsets, static_cast<uint8_t*>(prepared_out)));
+                                   gamma, eps, dim, out, L.ndigits, L.nsets, L.colmul, static_cast<uint8_t*>(prepared_out)));
     else
         SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
-                                   gamma, eps, dim, out, 0, 0, static_cast<uint8_t*>(nullptr)));
+                                   gamma, eps, dim, out, 0, 0, 1, static_cast<uint8_t*>(nullptr)));
     return SGQ_OK;
 }
 
@@ -592,13 +557,13 @@ int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (prepared_out && (hidden % 256) == 0 && hidden <= 8192) {
         SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_row_kernel, dim3(static_cast<unsigned>(rows)), dim3(kSiluThreads), 0, s,
-                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets, L.colmul,
                                    static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
     }
     if (prepared_out) {
         SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s,
-                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.ndigits, L.nsets, L.colmul,
                                    static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
     }

@@ -133,7 +133,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     using C = Cfg<MODE>;
     constexpr int NA = C::kAStages, NB = C::kBStages, NR = C::kRawStages ? C::kRawStages : 1;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by pointer arithmetic on the shared array itself: a round trip through an integer would make the
+    // compiler lose the address space and emit generic loads for every shared-memory access below
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
     uint64_t* a_full = bars;                 // [NA] A tile landed
     uint64_t* a_empty = a_full + NA;         // [NA] the MMAs reading it completed

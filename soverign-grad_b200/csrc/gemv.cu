@@ -3,28 +3,34 @@
 // HBM-bound: every packed byte and every scale is read exactly once.
 //   algorithmic bytes = N*K/2 (nibbles) + N*K/32*4 (scales) + M*K*4 (x) + M*N*4 (y).
 //
-// One persistent CTA per SM: 8 or 16 consumer warps + 1 TMA producer warp + 1 reducer warp.
-//   * The producer thread issues two TMA copies per stage: a 3-D box [8 steps][16 rows][128 B]
-//     of packed weights (128-byte swizzle: the per-row word reads below are bank-conflict free)
-//     and a box [8 steps][16 rows][8] of fp32 scales, into a ring of stages guarded by
-//     full/empty mbarriers.  A step is 256 k of a 16-row tile.
-//   * Integer inner product.  Each activation row is turned once per CTA into fixed point
-//     relative to the power of two above its absmax (22 bits for M <= 2, 14 bits above: eight digit columns = one MMA then cover M = 4), split
-//     into balanced base-256 digits (int8).  The 4-bit codes become bytes with two LOP3s per
-//     eight codes ((w & 0x0F0F0F0F) ^ 0x08080808 = code + 8, exact), and a 32-k group of 16
-//     weight rows times up to 8 digit columns is ONE mma.sync m16n8k32 (u8 x s8 -> s32, exact).
-//     The +8 offset is cancelled exactly by starting the accumulator at -8 * sum(digits).
-//   * The exact group sums are converted to fp32, multiplied by the group's fp32 scale and
-//     accumulated in fp32:  y[m,n] = 2^-p_m * sum_j 256^j * sum_g scale[n,g] * S[n,g,m,j].
-//   * A consumer warp that finishes its share of a tile drops its partial sums into a small
-//     ring in shared memory and moves on; a dedicated reducer warp adds the partials in warp
-//     order (fixed order -> run-to-run deterministic), recombines digits, adds bias, stores y.
-//     Consumer warps never wait for one another, only for data and for ring slots.
+// One persistent CTA per SM (two smaller ones in the compact form): consumer warps + 1 TMA
+// producer warp + 1 reducer warp.
+//   * The producer thread issues three TMA copies per stage: a 3-D box [8 steps][16 rows][128 B]
+//     of packed weights (128-byte swizzle: the ldmatrix reads below are bank-conflict free) and two
+//     2-D boxes [16 rows][32 fp32] of scales (128-byte rows again: a 32-byte-wide box would cost the
+//     copy engine four times as many requests), into a ring of stages guarded by full/empty
+//     mbarriers.  A step is 256 k of a 16-row tile.
+//   * Integer inner product.  The activations arrive as block-scaled int8 digit planes
+//     (gemv_prepare.cuh).  A word of eight 4-bit codes becomes two words of signed bytes holding
+//     16 * code with one shift and two masks ((w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0: a nibble in
+//     the high half of a byte IS the two's-complement value times 16), and a 32-k group of 16
+//     weight rows times 8 digit columns is ONE mma.sync m16n8k32 (s8 x s8 -> s32, exact).
+//   * The exact group sums are turned into fp32 by the magic-number start value of the
+//     accumulator, multiplied by the product of the group's fp32 weight scale and the group's
+//     activation scale, and accumulated in fp32:
+//       y[m,n] = sum_j 256^j * sum_g (scale[n,g] * sx[m,g]) * (16 S[n,g,m,j]),  sx carrying the 1/16.
+//   * Consumer warps work in groups; every group owns whole tiles (all stages of a 16-row tile)
+//     and the groups take alternate tiles, so the latency bubbles of one group (barrier waits, the
+//     hand-off at the end of a tile) are covered by the others.  A warp that finishes its share
+//     of a tile drops its partial sums into a ring in shared memory and moves on; the reducer
+//     warp adds the partials in warp order (fixed order -> run-to-run deterministic), recombines
+//     digits, adds bias, stores y.  Consumer warps never wait for one another.
+//   * Activation planes too large for shared memory (e.g. K = 8192 at M = 16) are processed in
+//     phases over K: the planes of one K range are resident while ALL tiles of the CTA stream their
+//     weights of that range; later phases add into y.  The weights are still read exactly once.
 //
-// Error against the reference's single fp32 chain: the fixed-point step is 2^-22 (2^-14) of the
-// row's power-of-two bound per activation, everything up to the group sums is exact, the rest
-// is fp32 rounding: ~1e-6 (M <= 2) / ~4e-5 (M > 2) relative for Gaussian rows, inside 1e-3.
-// Activations must be finite.
+// Error against the reference's single fp32 chain: see gemv_prepare.cuh (group-scaled 16-bit
+// activations, 24-bit for one row); everything up to the group sums is exact, the rest is fp32.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
 #include "sm100_ptx.cuh"
@@ -42,55 +48,40 @@ cudaError_t read_status_gemv(uint32_t* v, bool clear) {
     return e;
 }
 
-#ifdef SGQ_TIMELINE
-// Debug build only: per-warp timestamps (globaltimer, ns) of the kernel's phases.
-__device__ unsigned long long* g_timeline = nullptr;
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define SGQ_MARK(slot)                                                                                     \
-    do {                                                                                                   \
-        if (g_timeline && (threadIdx.x & 31) == 0)                                                         \
-            g_timeline[(blockIdx.x * 32 + (threadIdx.x >> 5)) * 16 + (slot)] = now_ns();                   \
-    } while (0)
-extern "C" __attribute__((visibility("default"))) int sgq_debug_set_timeline(unsigned long long* buf) {
-    return static_cast<int>(cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf)));
-}
-#else
-#define SGQ_MARK(slot) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kRows = 16;                  // rows of W per tile (mma M)
 constexpr int kStepK = 256;                // k per step (one 128-byte swizzle row per weight row)
 constexpr int kStepsPerStage = 8;
 constexpr int kWStepBytes = kRows * 128;   // 2048
-constexpr int kSStepBytes = kRows * 32;    // 16 rows x 8 fp32
+constexpr int kSChunkBytes = kRows * 128;  // 16 rows x 32 fp32: the scales of 4 steps
 constexpr int kStageW = kStepsPerStage * kWStepBytes;   // 16384
-constexpr int kStageS = kStepsPerStage * kSStepBytes;   // 4096
+constexpr int kStageS = 2 * kSChunkBytes;               // 4096
 constexpr int kStageBytes = kStageW + kStageS;          // 20480
 constexpr int kMaxStages = 8;
+constexpr int kMaxSlots = 8;               // ring of per-tile partial-sum buffers: two per warp group
 constexpr int kSmemLimit = 227 * 1024;
+constexpr int kCompactSmem = 113 * 1024;   // a CTA that leaves room for a second one on the same SM
 constexpr int kMaxM = 16;
-constexpr int kPSlots = 2;                 // ring of per-tile partial-sum buffers
+
+// Consumer organisation: NWARPS consumer warps in groups of `warps_per_tile(NWARPS)`; a group works
+// on one tile at a time (each warp a fixed share of the steps of every stage), the NWARPS /
+// warps_per_tile groups take alternate tiles.
+__host__ __device__ constexpr int warps_per_tile(int nwarps) { return nwarps == 16 ? 8 : 4; }
 
 struct Smem {
-    uint32_t stages_off, x_off, corr_off, partial_off, misc_off, total;   // from a 1024-byte aligned base
+    uint32_t x_off, sx_off, partial_off, misc_off, total;   // from a 1024-byte aligned base; stages first
 };
 
-// groups = K/32; x digits: 256 B per (group, set); corrections: 32 B per (group, set)
-__host__ __device__ inline Smem smem_layout(int nstages, int64_t K, int nsets, int nwarps) {
+// groups: 32-k groups of ONE phase
+__host__ __device__ inline Smem smem_layout(int nstages, uint32_t groups, int nsets, int nwarps) {
     Smem s;
-    const uint32_t groups = static_cast<uint32_t>(K / 32);
-    s.stages_off = 0;
     s.x_off = nstages * kStageBytes;
-    s.corr_off = s.x_off + groups * 256u * nsets;
-    s.partial_off = s.corr_off + groups * 32u * nsets;
-    s.misc_off = s.partial_off + kPSlots * nwarps * (512u * nsets + 16u);   // padded per-warp partial sums
-    s.total = s.misc_off + (2u * kMaxStages + 2u * kPSlots + 1u) * 8u + kMaxM * 8u + 16u;
+    s.sx_off = s.x_off + groups * 256u * nsets;
+    s.partial_off = s.sx_off + groups * 16u * nsets;
+    s.partial_off = (s.partial_off + 15u) & ~15u;
+    s.misc_off = s.partial_off + 2u * nwarps * (512u * nsets + 16u);        // slots x warps per tile x padded partial sums
+    s.total = s.misc_off + (2u * kMaxStages + 2u * kMaxSlots + 2u) * 8u;
     return s;
 }
 
@@ -98,147 +89,124 @@ __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
     atomicCAS(&g_status_gemv, 0u, (code << 24) | (detail & 0xFFFFFFu));
 }
 
-// D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col) + C
-__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                               int c0, int c1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col) + magic
+__device__ __forceinline__ void mma_s8s8_16832_magic(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c0), "r"(c1));
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(kMagicBits));
 }
 
-// Activation planes for batches too large to convert inside every CTA: one CTA per batch row,
-// written once to global scratch in exactly the shared-memory layout the main kernel uses:
-//   [digit planes: groups*nsets*256 B][corrections: groups*nsets*32 B][inv_p: 16 fp32]
-constexpr int kPrepThreads = 512;
-constexpr int kPrepMaxChunks = 8;   // per thread: K <= 8 * 512 * 8 = 32768
-__global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int M, int64_t K,
-                                                                     int ndigits, int nsets, uint8_t* __restrict__ planes) {
-    __shared__ float red[kPrepThreads / 32];
+// N consecutive floats (16-byte aligned for N = 4, 8-byte for N = 2) with the widest load that fits.
+template <int N>
+__device__ __forceinline__ void load_scales(float (&v)[N], const float* p) {
+    if constexpr (N == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else if constexpr (N == 2) {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        v[0] = q.x; v[1] = q.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = p[i];
+    }
+}
+
+// Four 8x8 matrices of 16-byte rows: lane l supplies the address of row (l & 7) of matrix (l >> 3);
+// lane (g, t) receives word t of row g of every matrix.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+
+// Activation planes converted once into global scratch, in the prepared layout.  One CTA per row.
+constexpr int kPrepThreads = 256;
+__global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int64_t K, int ndigits, int nsets,
+                                                                     int colmul, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
-    const int m = blockIdx.x, lane = threadIdx.x & 31;
+    const int m = blockIdx.x;
     const int chunks = static_cast<int>(K / 8);
-    const size_t groups = static_cast<size_t>(K / 32);
-    uint8_t* xs = planes;
-    uint8_t* corr = planes + groups * nsets * 256;
-    float* inv_p = reinterpret_cast<float*>(corr + groups * nsets * 32);
-    float v[kPrepMaxChunks][8];
-    float mx = 0.0f;
-#pragma unroll
-    for (int r = 0; r < kPrepMaxChunks; ++r) {
-        const int c = threadIdx.x + r * kPrepThreads;
-        if (c < chunks) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K) + 2 * c);
-            const float4 b = __ldg(reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K) + 2 * c + 1);
-            v[r][0] = a.x; v[r][1] = a.y; v[r][2] = a.z; v[r][3] = a.w; v[r][4] = b.x; v[r][5] = b.y; v[r][6] = b.z; v[r][7] = b.w;
-            mx = fmaxf(mx, absmax8(v[r]));
-        }
-    }
-    mx = warp_max(mx);
-    if (lane == 0) red[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    float all = red[lane < kPrepThreads / 32 ? lane : 0];
-    all = warp_max(all);
-    float P, invP;
-    row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
-    if (threadIdx.x == 0) inv_p[m] = invP;
-#pragma unroll
-    for (int r = 0; r < kPrepMaxChunks; ++r) {
-        const int c = threadIdx.x + r * kPrepThreads;
-        if (c < chunks) digits_item(v[r], P, m, c, ndigits, nsets, xs, corr);   // chunks % 32 == 0: whole warps
+    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(K / 32) * nsets * 256);
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
+    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {          // chunks % 32 == 0: whole warps, one block each
+        const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        convert_groups<kOrderNibble>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 0.0625f, planes, scales);
     }
 }
 
-// Consumer organisation (template parameter WPB):
-//   1: 8 warps, one per 256-k step, every warp works on every stage (the compact two-CTAs-per-SM form);
-//   2: 16 warps, two per step (half a step each), every warp works on every stage;
-//   3: 16 warps in two sets of 8, one warp per step, the sets take ALTERNATE stages — two stages are
-//      in work at any time, so the latency bubbles of one set (barrier waits, the hand-off to the
-//      reducer at the end of a tile) are covered by the other.
-__host__ __device__ constexpr int consumer_warps(int wpb) { return wpb == 1 ? 8 : 16; }
+enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2 };
 
-// NSETS: sets of 8 digit columns; WPB: see above;
-// PRE: the activation planes were prepared by gemv_prepare_x_kernel and are copied in by TMA.
-template <int NSETS, int WPB, bool PRE>
-__global__ void __launch_bounds__((consumer_warps(WPB) + 2) * 32, WPB == 1 ? 2 : 1)
+// NSETS: sets of 8 digit columns; NWARPS: consumer warps (16, or 8 in the compact two-CTAs-per-SM
+// form); HALF: only even columns carry data (one- and two-row batches), the odd accumulators are skipped.
+template <int NSETS, int NWARPS, bool HALF>
+__global__ void __launch_bounds__((NWARPS + 2) * 32, NWARPS == 8 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
-                    float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N, int64_t ldy, int nstages, int early_weights,
-                    const __grid_constant__ PeerOut peers) {
-    constexpr int kWarps = consumer_warps(WPB);
-    constexpr int kConsumerThreads = kWarps * 32;
-    constexpr int kWarpsPerStep = WPB == 2 ? 2 : 1;
-    constexpr int kGroupsPerWarp = 8 / kWarpsPerStep;
-    constexpr int kStageSets = WPB == 3 ? 2 : 1;       // sets of warps that take alternate stages
+                    float* __restrict__ y, int M, int ndigits, int colmul, int64_t K, int64_t N, int64_t ldy, int nstages,
+                    int nphases, int flags, const __grid_constant__ PeerOut peers) {
+    constexpr int WPT = warps_per_tile(NWARPS);
+    constexpr int kGroups = NWARPS / WPT;              // warp groups = tiles in work at any time
+    constexpr int kSlots = 2 * kGroups;
+    constexpr int GPW = 64 / WPT;                      // 32-k groups of a stage per warp (8 or 16)
+    constexpr int kConsumerThreads = NWARPS * 32;
+    constexpr int kPStride = 128 * NSETS + 4;          // floats per warp in a partial-sum slot (padded against bank conflicts)
+    static_assert(GPW % 8 == 0, "a warp takes whole steps");
+    static_assert(kSlots <= kMaxSlots, "partial-sum ring");
 
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const Smem L = smem_layout(nstages, K, NSETS, kWarps);
-    uint8_t* stages = smem + L.stages_off;
+    // aligned by pointer arithmetic on the shared array itself: a round trip through an integer would make the
+    // compiler lose the address space and emit generic loads for every shared-memory access below
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int spt = static_cast<int>(K / kStepK);      // steps per tile (K % 256 == 0)
+    const int sp = spt / nphases;                      // steps per tile and phase
+    const Smem L = smem_layout(nstages, static_cast<uint32_t>(sp) * 8u, NSETS, NWARPS);
+    uint8_t* stages = smem;
     uint8_t* xs = smem + L.x_off;
-    uint8_t* corr = smem + L.corr_off;
+    float* sxs = reinterpret_cast<float*>(smem + L.sx_off);
     float* partial = reinterpret_cast<float*>(smem + L.partial_off);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.misc_off);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* pfull = empty + kMaxStages;      // [kPSlots] every consumer warp has left its partial sums
-    uint64_t* pempty = pfull + kPSlots;        // [kPSlots] the reducer is done with the slot
-    uint64_t* xfull = pempty + kPSlots;        // [1] prepared activation planes have landed (PRE)
-    uint32_t* rowmax_bits = reinterpret_cast<uint32_t*>(xfull + 1);            // [16]
-    float* inv_p = reinterpret_cast<float*>(rowmax_bits + kMaxM);              // [16]
+    uint64_t* pfull = empty + kMaxStages;      // [kSlots] every warp of the tile's group has left its partial sums
+    uint64_t* pempty = pfull + kMaxSlots;      // [kSlots] the reducer is done with the slot
+    uint64_t* xfull = pempty + kMaxSlots;      // the activation planes of a phase have landed
+    uint64_t* xempty = xfull + 1;              // every consumer warp is done with the planes of a phase
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
-    const int spt = static_cast<int>(K / kStepK);   // steps per tile (K % 256 == 0)
+    const bool prepared = (flags & kFlagPrepared) != 0;
 
-    SGQ_MARK(0);
     pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
-    if (threadIdx.x == kWarps * 32) {   // the producer thread: start fetching both descriptors now
+    if (threadIdx.x == NWARPS * 32) {   // the producer thread: start fetching both descriptors now
         tma_prefetch_descriptor(&map_w);
         tma_prefetch_descriptor(&map_s);
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; ++i) {
             mbar_init(&full[i], 1);
-            mbar_init(&empty[i], kWarps / kStageSets);
+            mbar_init(&empty[i], WPT);
         }
-        for (int i = 0; i < kPSlots; ++i) {
-            mbar_init(&pfull[i], kWarps);
+        for (int i = 0; i < kSlots; ++i) {
+            mbar_init(&pfull[i], WPT);
             mbar_init(&pempty[i], 1);
         }
         mbar_init(xfull, 1);
+        mbar_init(xempty, NWARPS);
         mbar_fence_init();
         fence_proxy_async_smem();
     }
-    if (threadIdx.x < kMaxM) rowmax_bits[threadIdx.x] = 0;
     __syncthreads();
     // Everything above touches no global data.  From here on every thread except the producer
     // first waits for the kernels this launch depends on (they wrote x / the planes, and may still
     // be reading y); the producer decides for itself below, because weights are not their output.
-    if (warp != kWarps) pdl_wait();
-    SGQ_MARK(12);
-    // The first kPre items of every consumer thread are requested before anything else, so that
-    // their global-memory latency overlaps the producer's first TMA issues.
-    constexpr int kPre = PRE ? 1 : 4;
-    const int chunks = static_cast<int>(K / 8);   // 8-float chunks per activation row
-    const int items = chunks * M;
-    float4 pre_a[kPre], pre_b[kPre];
-#pragma unroll
-    for (int r = 0; r < kPre; ++r) {
-        const int it = threadIdx.x + r * kConsumerThreads;
-        if (!PRE && warp < kWarps && it < items) {
-            pre_a[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
-            pre_b[r] = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
-        } else {
-            pre_a[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-            pre_b[r] = pre_a[r];
-        }
-    }
+    if (warp != NWARPS) pdl_wait();
 
-    if (warp == kWarps) {
+    if (warp == NWARPS) {
         // ---------------- producer ----------------
         if (lane == 0) {
             // Weights and scales are parameters, not the output of the kernel before this one: with
-            // early_weights the first ring of stages is requested before the dependency wait, so the
+            // early weights the first ring of stages is requested before the dependency wait, so the
             // weight stream overlaps the tail of that kernel.  The activation planes are its output
             // and are copied only after the wait.
             bool synced = false;
@@ -246,100 +214,129 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (synced) return;
                 synced = true;
                 pdl_wait();
-                SGQ_MARK(4);
-                if (PRE) {
-                    fence_proxy_async_all();        // the planes were written through the generic proxy
-                    // digit planes + corrections, contiguous in both places, in pieces of <= 32 KiB
-                    const uint32_t bytes = L.partial_off - L.x_off;
-                    mbar_arrive_expect_tx(xfull, bytes);
-                    for (uint32_t off = 0; off < bytes; off += 32768u)
-                        bulk_copy_g2s(xs + off, planes + off, (bytes - off < 32768u) ? bytes - off : 32768u, xfull);
-                }
+                if (prepared) fence_proxy_async_all();      // the planes were written through the generic proxy
             };
-            if (!early_weights) dependency_sync();
+            auto copy_planes = [&](int ph) {
+                // digit planes and group scales of this phase: two contiguous ranges, in pieces of <= 32 KiB
+                const uint32_t dbytes = static_cast<uint32_t>(sp) * 8u * 256u * NSETS;
+                const uint32_t sbytes = static_cast<uint32_t>(sp) * 8u * 16u * NSETS;
+                const uint8_t* dsrc = planes + static_cast<size_t>(ph) * dbytes;
+                const uint8_t* ssrc = planes + static_cast<size_t>(K / 32) * 256u * NSETS + static_cast<size_t>(ph) * sbytes;
+                mbar_arrive_expect_tx(xfull, dbytes + sbytes);
+                for (uint32_t off = 0; off < dbytes; off += 32768u)
+                    bulk_copy_g2s(xs + off, dsrc + off, (dbytes - off < 32768u) ? dbytes - off : 32768u, xfull);
+                bulk_copy_g2s(sxs, ssrc, sbytes, xfull);
+            };
+            if (!(flags & kFlagEarlyWeights)) dependency_sync();
             uint32_t seq = 0;
-            bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
-                    if (seq == static_cast<uint32_t>(nstages)) dependency_sync();   // the ring is full: nothing more to request early
-                    const int st = seq % nstages;
-                    const uint32_t ph = (seq / nstages) & 1u;
-                    if (!mbar_wait(&empty[st], ph ^ 1u)) {
-                        report(kDevErrEmptyWait, seq);
-                        ok = false;
+            bool ok = true, planes_sent = false;
+            for (int ph = 0; ph < nphases && ok; ++ph) {
+                if (ph > 0) {
+                    if (!mbar_wait(xempty, (ph - 1) & 1u)) {
+                        report(kDevErrEmptyWait, 0x400000u | ph);
                         break;
                     }
-                    // steps past K/256 are out of range in the third dimension: zero-filled, still counted
-                    mbar_arrive_expect_tx(&full[st], kStageBytes);
-                    uint8_t* sw = stages + st * kStageBytes;
-                    tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
-                    tma_load_3d(sw + kStageW, &map_s, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
-                    if (seq == 0) SGQ_MARK(1);
-                    if (seq == 6) SGQ_MARK(2);
+                    copy_planes(ph);
+                }
+                for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                    for (int c0 = 0; c0 < sp; c0 += kStepsPerStage, ++seq) {
+                        if (ph == 0 && !planes_sent && seq == static_cast<uint32_t>(nstages)) {
+                            // the ring is full: nothing more to request early
+                            dependency_sync();
+                            if (prepared) copy_planes(0);
+                            planes_sent = true;
+                        }
+                        const int st = seq % nstages;
+                        const uint32_t par = (seq / nstages) & 1u;
+                        if (!mbar_wait(&empty[st], par ^ 1u)) {
+                            report(kDevErrEmptyWait, seq);
+                            ok = false;
+                            break;
+                        }
+                        // steps past the end of K are out of range in the third dimension: zero-filled, still counted
+                        mbar_arrive_expect_tx(&full[st], kStageBytes);
+                        uint8_t* sw = stages + st * kStageBytes;
+                        const int32_t step0 = ph * sp + c0;
+                        tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), step0);
+                        // scales of steps step0 .. step0+3 and step0+4 .. step0+7 (columns past K/32 are zero-filled)
+                        tma_load_2d(sw + kStageW, &map_s, &full[st], step0 * 8, static_cast<int32_t>(tile * kRows));
+                        tma_load_2d(sw + kStageW + kSChunkBytes, &map_s, &full[st], step0 * 8 + 32, static_cast<int32_t>(tile * kRows));
+                    }
+                }
+                if (ph == 0 && !planes_sent) {
+                    dependency_sync();
+                    if (prepared) copy_planes(0);
+                    planes_sent = true;
                 }
             }
             dependency_sync();
-            SGQ_MARK(3);
         }
         return;
     }
 
-    constexpr int kPStride = 128 * NSETS + 4;   // floats per warp in a partial-sum slot (padded against bank conflicts)
-    if (warp == kWarps + 1) {
+    const int stages_per_tile = (sp + kStepsPerStage - 1) / kStepsPerStage;
+    const int64_t my_tiles = (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;      // per phase
+
+    if (warp == NWARPS + 1) {
         // ---------------- reducer ----------------
-        // lane -> output pairs (tile row r, batch row m); per digit column the kWarps partial sums
-        // are added in warp order, then digits are recombined: y = 2^-p * sum_j 256^j v_j + bias.
+        // lane -> output pairs (tile row r, batch row m); per digit column the partial sums of the
+        // tile's warps are added in warp order, then digits are recombined: y = sum_j 256^j v_j + bias.
         uint32_t tcount = 0;
         const int pairs = kRows * M;
-        for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-            const int slot = tcount % kPSlots;
-            const uint32_t pph = (tcount / kPSlots) & 1u;
-            if (!mbar_wait(&pfull[slot], pph)) {
-                report(kDevErrFullWait, 0x800000u | tcount);
-                break;
-            }
-            if (tcount < 6) SGQ_MARK(2 * tcount);
-            float* pbuf = partial + slot * (kWarps * kPStride);
-            // Step 1: add the warps' partial sums fragment-wise, in warp order (fixed order -> the same
-            // bits every run): lane L owns the float4 every consumer lane L wrote, so these are
-            // conflict-free 128-bit reads.  The sum goes back into warp 0's part of the slot.
-#pragma unroll
-            for (int s = 0; s < NSETS; ++s) {
-                float4 sum = *reinterpret_cast<const float4*>(pbuf + (s * 32 + lane) * 4);
-#pragma unroll
-                for (int w = 1; w < kWarps; ++w) {
-                    const float4 v = *reinterpret_cast<const float4*>(pbuf + w * kPStride + (s * 32 + lane) * 4);
-                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        bool ok = true;
+        for (int ph = 0; ph < nphases && ok; ++ph) {
+            for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
+                const int slot = tcount % kSlots;
+                const uint32_t pph = (tcount / kSlots) & 1u;
+                if (!mbar_wait(&pfull[slot], pph)) {
+                    report(kDevErrFullWait, 0x800000u | tcount);
+                    ok = false;
+                    break;
                 }
-                *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) = sum;
-            }
-            __syncwarp();
-            // Step 2: one value per (output, digit): recombine the digits, scale, add bias, store.
-            for (int p = lane; p < pairs; p += 32) {
-                const int r = p & 15, m = p >> 4;
-                const int gg = r & 7, hi = r >> 3;
-                float acc = 0.0f, weight = 1.0f;
-                for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
-                    const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
-                    const float v = pbuf[(set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1)];
-                    acc = __fmaf_rn(weight, v, acc);
+                float* pbuf = partial + slot * (WPT * kPStride);
+                // Step 1: add the warps' partial sums fragment-wise, in warp order (fixed order -> the same
+                // bits every run): lane L owns the float4 every consumer lane L wrote, so these are
+                // conflict-free 128-bit reads.  The sum goes back into the first warp's part of the slot.
+#pragma unroll
+                for (int s = 0; s < NSETS; ++s) {
+                    float4 sum = *reinterpret_cast<const float4*>(pbuf + (s * 32 + lane) * 4);
+#pragma unroll
+                    for (int w = 1; w < WPT; ++w) {
+                        const float4 v = *reinterpret_cast<const float4*>(pbuf + w * kPStride + (s * 32 + lane) * 4);
+                        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                    }
+                    *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) = sum;
                 }
-                const int64_t n = tile * kRows + r;
-                if (n < N) {
-                    float v = acc * (PRE ? __ldg(reinterpret_cast<const float*>(planes + (L.partial_off - L.x_off)) + m)
-                                         : inv_p[m]);
-                    if (bias) v += bias[n];
-                    if (peers.n == 0) {
-                        y[static_cast<int64_t>(m) * ldy + n] = v;
-                    } else {
-                        // fused all-gather: the slice goes into every GPU's full-width output (plain peer stores)
-                        for (int r2 = 0; r2 < peers.n; ++r2) peers.p[r2][static_cast<int64_t>(m) * ldy + n] = v;
+                __syncwarp();
+                // Step 2: one value per (output, digit): recombine the digits, add bias, store.
+                for (int p = lane; p < pairs; p += 32) {
+                    const int r = p & 15, m = p >> 4;
+                    const int gg = r & 7, hi = r >> 3;
+                    float acc = 0.0f, weight = 1.0f;
+                    for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
+                        const int col = (m * ndigits + j) * colmul, set = col >> 3, cc = col & 7;
+                        const float v = pbuf[(set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1)];
+                        acc = __fmaf_rn(weight, v, acc);
+                    }
+                    const int64_t n = tile * kRows + r;
+                    if (n < N) {
+                        float v = acc;
+                        if (ph == 0) {
+                            if (bias) v += bias[n];
+                        } else {
+                            v += y[static_cast<int64_t>(m) * ldy + n];        // written by this same lane in the phase before
+                        }
+                        if (peers.n == 0) {
+                            y[static_cast<int64_t>(m) * ldy + n] = v;
+                        } else {
+                            // fused all-gather: the slice goes into every GPU's full-width output (plain peer stores)
+                            for (int r2 = 0; r2 < peers.n; ++r2) peers.p[r2][static_cast<int64_t>(m) * ldy + n] = v;
+                        }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pempty[slot]);
             }
-            __syncwarp();
-            if (tcount < 6) SGQ_MARK(2 * tcount + 1);
-            if (lane == 0) mbar_arrive(&pempty[slot]);
         }
         if (peers.n > 0 && peers.sig[0] != nullptr) {
             // Barrier fused into the tail: this CTA's slices are out; the last CTA of the launch to get
@@ -353,7 +350,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (ticket == gridDim.x - 1) {
                 if (lane == 0) *counter = 0;          // re-armed for the next launch, which counts only at its own end
                 int late = 0;
-                if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late) && lane == 0)
+                if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late, peers.poll_budget) && lane == 0)
                     report(kDevErrPeerWait, 0x10000u);
             }
         }
@@ -362,202 +359,185 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     // ---------------- consumers ----------------
     bool alive = true;   // false after a wait ran out: skip the math but keep every barrier balanced
-    if (PRE) {
-        if (!mbar_wait(xfull, 0)) {
-            report(kDevErrFullWait, 0x400000u);
-            alive = false;
-        }
-    } else {
-        // Activations -> int8 digits, inside the CTA (small batches: every item was requested at the top).
-        auto unpack = [](const float4& a, const float4& b, float (&v)[8]) {
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        };
-        auto load_item = [&](int it, float (&v)[8]) {
-            unpack(__ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it)),
-                   __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1), v);
-        };
-        // pass 1: absmax per row (the bit pattern of |x| orders like the value).  items % 32 == 0 and
-        // chunks % 4 == 0, so whole warps are in or out and 4 neighbouring lanes share a row.
-        auto absmax_item = [&](int it, const float (&v)[8]) {
-            float mx = absmax8(v);
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            if ((lane & 3) == 0) atomicMax(&rowmax_bits[it / chunks], __float_as_uint(mx));
-        };
-#pragma unroll
-        for (int r = 0; r < kPre; ++r) {
-            const int it = threadIdx.x + r * kConsumerThreads;
-            if (it < items) {
-                float v[8];
-                unpack(pre_a[r], pre_b[r], v);
-                absmax_item(it, v);
-            }
-        }
-        for (int it = threadIdx.x + kPre * kConsumerThreads; it < items; it += kConsumerThreads) {
-            float v[8];
-            load_item(it, v);
-            absmax_item(it, v);
-        }
-        // Columns >= M*ndigits of the digit planes stay uninitialised: they only feed accumulator
-        // columns that nobody reads (integer MMA: no NaN can spread).
-        named_barrier_sync(1, kConsumerThreads);
-        const int frac_bits = (ndigits == 3) ? 22 : 14;
-        // pass 2: fixed point + digits.  Four neighbouring lanes own the four t-chunks of one group.
-        auto convert_item = [&](int it, const float (&v)[8]) {
+    if (!prepared) {
+        // Activations -> digit planes inside the CTA (small batches, one phase).  A warp converts 256 k
+        // per iteration; M * K / 8 is a multiple of 32, so whole warps are in or out.
+        const int chunks = static_cast<int>(K / 8);
+        const int items = chunks * M;
+        for (int it = threadIdx.x; it < items; it += kConsumerThreads) {
             const int m = it / chunks, c = it - m * chunks;
-            float P, invP;
-            row_scale(rowmax_bits[m], frac_bits, &P, &invP);
-            if (c == 0) inv_p[m] = invP;
-            digits_item(v, P, m, c, ndigits, NSETS, xs, corr);
-        };
-#pragma unroll
-        for (int r = 0; r < kPre; ++r) {
-            const int it = threadIdx.x + r * kConsumerThreads;
-            if (it < items) {
-                float v[8];
-                unpack(pre_a[r], pre_b[r], v);
-                convert_item(it, v);
-            }
+            const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            convert_groups<kOrderNibble>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, NSETS, colmul, 0.0625f, xs, sxs);
         }
-        for (int it = threadIdx.x + kPre * kConsumerThreads; it < items; it += kConsumerThreads) {
-            float v[8];
-            load_item(it, v);
-            convert_item(it, v);
-        }
+        named_barrier_sync(1, kConsumerThreads);
     }
-    SGQ_MARK(1);
-    named_barrier_sync(1, kConsumerThreads);
-    SGQ_MARK(2);
 
     const int g = lane >> 2, t = lane & 3;
-    const int step_in_stage = (warp / kWarpsPerStep) & 7;          // which 256-k step of a stage this warp works on
-    const int g0 = (warp % kWarpsPerStep) * kGroupsPerWarp;        // first of its groups inside the step
-    const uint32_t my_set = (kStageSets == 2) ? static_cast<uint32_t>(warp >> 3) : 0u;
-    // byte offset of this lane's word inside a step box, for each of its groups (swizzle: chunk ^ row)
-    uint32_t woff[kGroupsPerWarp];
+    const int my_group = warp / WPT, wj = warp % WPT;
+    // ldmatrix row address of this lane inside a step box, for group pair (2i, 2i+1): matrix (lane >> 3)
+    // = (rows 0-7 | rows 8-15) x (group 2i | 2i+1); 128-byte swizzle: 16-byte chunk index ^ (row & 7)
+    const uint32_t lm_row = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const uint32_t lm_sel = lane >> 4;
+    uint32_t lm_off[4];
 #pragma unroll
-    for (int i = 0; i < kGroupsPerWarp; ++i) woff[i] = g * 128 + (((g0 + i) ^ g) << 4) + t * 4;
+    for (int i = 0; i < 4; ++i) lm_off[i] = lm_row * 128 + (((2 * i + lm_sel) ^ (lane & 7)) << 4);
+    const uint32_t stages_u32 = smem_u32(stages);
 
     uint32_t seq = 0, tcount = 0;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-        float total[NSETS][4];
-#pragma unroll
-        for (int s = 0; s < NSETS; ++s)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
-
-        for (int c0 = 0; c0 < spt; c0 += kStepsPerStage, ++seq) {
-            if (kStageSets == 2 && (seq & 1u) != my_set) continue;       // the other set's stage
-            const int st = seq % nstages;
-            const uint32_t ph = (seq / nstages) & 1u;
-            if (alive && !mbar_wait(&full[st], ph)) {
-                report(kDevErrFullWait, seq);
-                alive = false;
-            }
-            if (seq < 5) SGQ_MARK(3 + 2 * seq);
-            const int step = c0 + step_in_stage;
-            if (alive && step < spt) {
-                const uint8_t* wbox = stages + st * kStageBytes + step_in_stage * kWStepBytes;
-                const uint8_t* sbox = stages + st * kStageBytes + kStageW + step_in_stage * kSStepBytes;
-                float sc_lo[kGroupsPerWarp], sc_hi[kGroupsPerWarp];   // scales of rows g and g+8
-#pragma unroll
-                for (int h = 0; h < kGroupsPerWarp / 4; ++h) {
-                    const float4 a = *reinterpret_cast<const float4*>(sbox + g * 32 + (g0 / 4 + h) * 16);
-                    const float4 b = *reinterpret_cast<const float4*>(sbox + (g + 8) * 32 + (g0 / 4 + h) * 16);
-                    sc_lo[4 * h + 0] = a.x; sc_lo[4 * h + 1] = a.y; sc_lo[4 * h + 2] = a.z; sc_lo[4 * h + 3] = a.w;
-                    sc_hi[4 * h + 0] = b.x; sc_hi[4 * h + 1] = b.y; sc_hi[4 * h + 2] = b.z; sc_hi[4 * h + 3] = b.w;
-                }
-                const size_t group0 = static_cast<size_t>(step) * 8 + g0;
-                const uint8_t* xg = xs + group0 * (256 * NSETS) + lane * 8;
-                const uint8_t* cg = corr + group0 * (32 * NSETS) + t * 8;
-                uint32_t wl[kGroupsPerWarp], wh[kGroupsPerWarp];
-#pragma unroll
-                for (int i = 0; i < kGroupsPerWarp; ++i) {
-                    wl[i] = *reinterpret_cast<const uint32_t*>(wbox + woff[i]);
-                    wh[i] = *reinterpret_cast<const uint32_t*>(wbox + 1024 + woff[i]);
-                }
-#pragma unroll
-                for (int i = 0; i < kGroupsPerWarp; ++i) {
-                    const uint32_t w_lo = wl[i], w_hi = wh[i];
-                    uint32_t a[4];
-                    a[0] = (w_lo & 0x0F0F0F0Fu) ^ 0x08080808u;          // row g,   k = 8t + {0,2,4,6}: code + 8
-                    a[1] = (w_hi & 0x0F0F0F0Fu) ^ 0x08080808u;          // row g+8
-                    a[2] = ((w_lo >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // row g,   k = 8t + {1,3,5,7}
-                    a[3] = ((w_hi >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // row g+8
-#pragma unroll
-                    for (int s = 0; s < NSETS; ++s) {
-                        const uint2 xb = *reinterpret_cast<const uint2*>(xg + i * (256 * NSETS) + s * 256);
-                        const int2 cc = *reinterpret_cast<const int2*>(cg + i * (32 * NSETS) + s * 32);
-                        int d[4];
-                        mma_u8s8_16832(d, a, xb.x, xb.y, cc.x, cc.y);
-                        // d holds 12582912.0f + (exact group sum) as fp32 bits: one subtraction instead of a conversion
-                        total[s][0] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[0]), kGroupSumBiasF), total[s][0]);
-                        total[s][1] = __fmaf_rn(sc_lo[i], __fsub_rn(__int_as_float(d[1]), kGroupSumBiasF), total[s][1]);
-                        total[s][2] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[2]), kGroupSumBiasF), total[s][2]);
-                        total[s][3] = __fmaf_rn(sc_hi[i], __fsub_rn(__int_as_float(d[3]), kGroupSumBiasF), total[s][3]);
-                    }
-                }
-            }
-            // everything loaded from the stage has been consumed once the accumulators are final
-            uint32_t fold = 0;
-#pragma unroll
-            for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
-            const uint32_t landed = loads_landed(fold);
-            if (seq < 5) SGQ_MARK(4 + 2 * seq);
-            if (lane == 0) mbar_arrive_after(&empty[st], landed);
+    for (int ph = 0; ph < nphases; ++ph) {
+        if (prepared && alive && !mbar_wait(xfull, ph & 1u)) {
+            report(kDevErrFullWait, 0x400000u | ph);
+            alive = false;
         }
-        if (tile == blockIdx.x) SGQ_MARK(13);
-
-        // ---- hand the tile's partial sums to the reducer warp ----
-        {
-            const int slot = tcount % kPSlots;
-            const uint32_t pph = (tcount / kPSlots) & 1u;
-            if (alive && !mbar_wait(&pempty[slot], pph ^ 1u)) {
-                report(kDevErrEmptyWait, 0x800000u | tcount);
-                alive = false;
+        for (int64_t ti = 0; ti < my_tiles; ++ti, ++tcount) {
+            if (static_cast<int>(tcount % kGroups) != my_group) {       // another group's tile
+                seq += stages_per_tile;
+                continue;
             }
-            float* pbuf = partial + slot * (kWarps * kPStride) + warp * kPStride;
+            float total[NSETS][4];
 #pragma unroll
             for (int s = 0; s < NSETS; ++s)
-                *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) =
-                    make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&pfull[slot]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
+
+            for (int c0 = 0; c0 < sp; c0 += kStepsPerStage, ++seq) {
+                const int st = seq % nstages;
+                const uint32_t par = (seq / nstages) & 1u;
+                if (alive && !mbar_wait(&full[st], par)) {
+                    report(kDevErrFullWait, seq);
+                    alive = false;
+                }
+#pragma unroll
+                for (int u = 0; u < GPW / 8; ++u) {
+                    const int step_in_stage = wj * (GPW / 8) + u;
+                    const int step = c0 + step_in_stage;                 // within the phase
+                    if (alive && step < sp) {
+                        const uint32_t wbox = stages_u32 + st * kStageBytes + step_in_stage * kWStepBytes;
+                        // scales: [2 chunks of 4 steps][16 rows][128 B], 16-byte units swizzled by the row like the weights
+                        const uint8_t* sbox = stages + st * kStageBytes + kStageW + (step_in_stage >> 2) * kSChunkBytes + g * 128;
+                        const int su = (step_in_stage & 3) * 2;
+                        const uint8_t* xg = xs + static_cast<size_t>(step) * 8 * (256 * NSETS);
+                        const float* sg = sxs + (static_cast<size_t>(step) * 8 * 4 + t) * NSETS;      // this lane's group scales
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {                 // four 32-k groups at a time
+                            const float4 sc_lo = *reinterpret_cast<const float4*>(sbox + (((su + hh) ^ g) << 4));          // scales of row g
+                            const float4 sc_hi = *reinterpret_cast<const float4*>(sbox + 1024 + (((su + hh) ^ g) << 4));   // and of row g + 8
+                            uint32_t wv[2][4];                           // [pair of groups]{rows 0-7, rows 8-15} x 2
+                            ldmatrix_x4(wv[0], wbox + lm_off[2 * hh]);
+                            ldmatrix_x4(wv[1], wbox + lm_off[2 * hh + 1]);
+                            // All MMAs of the four groups are issued before any of their results is used, so that the
+                            // tensor-pipe latency of one group is covered by the issue of the others.
+                            int d[4][NSETS][4];
+                            float sxv[4][NSETS];                         // activation scales: columns 2t, 2t+1 of every set
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t w_lo = wv[i >> 1][(i & 1) * 2], w_hi = wv[i >> 1][(i & 1) * 2 + 1];
+                                uint32_t a[4];
+                                a[0] = (w_lo << 4) & 0xF0F0F0F0u;        // row g,   k = 8t + {0,2,4,6}: 16 * code as s8
+                                a[1] = (w_hi << 4) & 0xF0F0F0F0u;        // row g+8
+                                a[2] = w_lo & 0xF0F0F0F0u;               // row g,   k = 8t + {1,3,5,7}
+                                a[3] = w_hi & 0xF0F0F0F0u;               // row g+8
+                                const uint8_t* xgi = xg + (4 * hh + i) * (256 * NSETS);
+                                load_scales<NSETS>(sxv[i], sg + (4 * hh + i) * (4 * NSETS));
+#pragma unroll
+                                for (int pr = 0; pr < (NSETS + 1) / 2; ++pr) {
+                                    if (2 * pr + 1 < NSETS) {            // a full pair of sets: one 128-bit load per lane
+                                        const uint4 q = *reinterpret_cast<const uint4*>(xgi + pr * 512 + lane * 16);
+                                        mma_s8s8_16832_magic(d[i][2 * pr], a, q.x, q.y);
+                                        mma_s8s8_16832_magic(d[i][2 * pr + 1], a, q.z, q.w);
+                                    } else {
+                                        const uint2 q = *reinterpret_cast<const uint2*>(xgi + pr * 512 + lane * 8);
+                                        mma_s8s8_16832_magic(d[i][2 * pr], a, q.x, q.y);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float s_lo = i == 0 ? sc_lo.x : i == 1 ? sc_lo.y : i == 2 ? sc_lo.z : sc_lo.w;
+                                const float s_hi = i == 0 ? sc_hi.x : i == 1 ? sc_hi.y : i == 2 ? sc_hi.z : sc_hi.w;
+#pragma unroll
+                                for (int s = 0; s < NSETS; ++s) {
+                                    // d holds 12582912.0f + 16 * (exact group sum) as fp32 bits
+                                    const float f_lo = __fmul_rn(s_lo, sxv[i][s]), f_hi = __fmul_rn(s_hi, sxv[i][s]);
+                                    total[s][0] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s][0]), kMagicF), total[s][0]);
+                                    total[s][2] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s][2]), kMagicF), total[s][2]);
+                                    if (!HALF) {
+                                        total[s][1] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s][1]), kMagicF), total[s][1]);
+                                        total[s][3] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s][3]), kMagicF), total[s][3]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+                // everything loaded from the stage has been consumed once the accumulators are final
+                uint32_t fold = 0;
+#pragma unroll
+                for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
+                const uint32_t landed = loads_landed(fold);
+                if (lane == 0) mbar_arrive_after(&empty[st], landed);
+            }
+
+            // ---- hand the tile's partial sums to the reducer warp ----
+            {
+                const int slot = tcount % kSlots;
+                const uint32_t pph = (tcount / kSlots) & 1u;
+                if (alive && !mbar_wait(&pempty[slot], pph ^ 1u)) {
+                    report(kDevErrEmptyWait, 0x800000u | tcount);
+                    alive = false;
+                }
+                float* pbuf = partial + slot * (WPT * kPStride) + wj * kPStride;
+#pragma unroll
+                for (int s = 0; s < NSETS; ++s)
+                    *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) =
+                        make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pfull[slot]);
+            }
         }
-        if (tile == blockIdx.x) SGQ_MARK(14);
+        if (nphases > 1) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xempty);
+        }
     }
-    SGQ_MARK(15);
 }
 
 struct Plan {
-    int ndigits, nsets, wpb, nstages;
+    PreparedLayout L;
+    int nwarps, nstages, nphases;
     bool pre;          // activation planes prepared by a separate launch into the workspace
     uint32_t smem;
     size_t planes_bytes;
 };
 
-// In-CTA conversion is used while every consumer thread can hold all its items in registers
-// (4 items of 8 activations per thread); larger batches are converted once by a pre-kernel.
-//
-// compact: a CTA that leaves room for a second one on the same SM (half the shared memory, 10
-// warps).  With overlapped launches the CTA of the NEXT kernel then sits beside the one still
-// running and streams its first weight stages in the meantime, so the pipeline fill, the launch
-// latency and the tail of consecutive decode forwards hide behind each other.
-constexpr int kCompactSmem = 112 * 1024;
+// Finds the fewest K phases (1, 2, 4, ...) whose activation planes fit in shared memory next to at
+// least `min_stages` pipeline stages.  A phase covers whole stages (steps per phase % 8 == 0) unless
+// there is only one.  compact: a CTA that leaves room for a second one on the same SM (half the
+// shared memory, 10 warps); with overlapped launches the CTA of the NEXT kernel then sits beside the
+// one still running and streams its first weight stages in the meantime.
 bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact = false) {
-    p->ndigits = prepared_layout(M, K).ndigits;
-    p->nsets = static_cast<int>((M * p->ndigits + 7) / 8);
-    p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 288 + kMaxM * 4;
+    if (M < 1 || M > kMaxM || K < kStepK || (K % kStepK) != 0) return false;
+    p->L = prepared_layout(M, K);
+    p->planes_bytes = p->L.bytes;
+    p->nwarps = compact ? 8 : 16;
     const int limit = compact ? kCompactSmem : kSmemLimit;
-    // two warps per step while at least 3 stages still fit, else one (smaller partial-sum buffers)
-    for (int wpb = compact ? 1 : 3; wpb >= 1; --wpb) {
-        for (int st = kMaxStages; st >= (wpb == 3 ? 4 : (wpb == 2 ? 3 : 2)); --st) {
-            const Smem L = smem_layout(st, K, p->nsets, consumer_warps(wpb));
-            if (L.total + 1024 <= static_cast<uint32_t>(limit)) {
-                p->wpb = wpb;
+    const int spt = static_cast<int>(K / kStepK);
+    for (int nph = 1; nph <= spt; nph *= 2) {
+        if (spt % nph) break;
+        const int sp = spt / nph;
+        if (nph > 1 && (sp % kStepsPerStage) != 0) break;
+        if (nph > 1 && !have_workspace) break;             // phases need the planes in global memory
+        const int min_stages = nph > 1 ? 3 : 2;
+        for (int st = kMaxStages; st >= min_stages; --st) {
+            const Smem S = smem_layout(st, static_cast<uint32_t>(sp) * 8u, p->L.nsets, p->nwarps);
+            if (S.total + 1024 <= static_cast<uint32_t>(limit)) {
                 p->nstages = st;
-                p->smem = L.total + 1024;
-                p->pre = have_workspace && (M * (K / 8) > 4 * consumer_warps(wpb) * 32) && K <= 8LL * kPrepMaxChunks * kPrepThreads;
+                p->nphases = nph;
+                p->smem = S.total + 1024;
+                // in-CTA conversion while it is a few items per thread; larger batches are converted once by a pre-kernel
+                p->pre = have_workspace && (nph > 1 || M * (K / 8) > 4 * p->nwarps * 32);
                 return true;
             }
         }
@@ -565,68 +545,61 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
     return false;
 }
 
-// Rows of the batch one launch can take: the largest m <= M whose activation planes fit in shared
-// memory next to the pipeline stages (0: not even one row fits).  Larger batches run as several
-// launches over row blocks; each streams the weights again, which is still far better than the
-// any-shape kernel.
-int64_t rows_per_launch(int64_t M, int64_t K) {
+// Rows of the batch one launch can take without a workspace: the largest m <= M whose activation
+// planes fit in shared memory next to the pipeline stages (0: not even one row fits).  Larger
+// batches then run as several launches over row blocks; each streams the weights again, which is
+// still far better than the any-shape kernel.
+int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
     Plan p;
     for (int64_t m = M; m >= 1; --m)
-        if (make_plan(m, K, false, &p)) return m;
+        if (make_plan(m, K, have_workspace, &p)) return m;
     return 0;
 }
 
-template <int NSETS, int WPB, bool PRE>
+template <int NSETS, int NWARPS, bool HALF>
 int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                    bool planes_ready) {
     static SmemOptIn optin;
-    auto kernel = gemv_int4_nk_kernel<NSETS, WPB, PRE>;
-    SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
+    auto kernel = gemv_int4_nk_kernel<NSETS, NWARPS, HALF>;
+    SGQ_CUDA_TRY(optin.ensure(kernel, NWARPS == 8 ? kCompactSmem : kSmemLimit));
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
     const bool overlap = stream_overlap_enabled();
-    if (PRE && !planes_ready) {
+    if (p.pre && !planes_ready) {
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap,
-                                   a.x, static_cast<int>(a.M), a.K, p.ndigits, p.nsets, static_cast<uint8_t*>(a.workspace)));
+                                   a.x, a.K, p.L.ndigits, p.L.nsets, p.L.colmul, static_cast<uint8_t*>(a.workspace)));
     }
-    SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((consumer_warps(WPB) + 2) * 32), p.smem, a.stream,
-                               overlap, map_w, map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy,
-                               p.nstages, overlap ? 1 : 0, a.peers));
+    const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
+    SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
+                               map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.L.ndigits, p.L.colmul, a.K, a.N, a.ldy,
+                               p.nstages, p.nphases, flags, a.peers));
     return SGQ_OK;
 }
 
-template <int NSETS>
+template <int NSETS, bool HALF>
 int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                  bool planes_ready) {
-    if (p.pre)
-        return p.wpb == 3 ? launch_variant<NSETS, 3, true>(a, p, map_w, map_s, grid, planes_ready)
-             : p.wpb == 2 ? launch_variant<NSETS, 2, true>(a, p, map_w, map_s, grid, planes_ready)
-                          : launch_variant<NSETS, 1, true>(a, p, map_w, map_s, grid, planes_ready);
-    return p.wpb == 3 ? launch_variant<NSETS, 3, false>(a, p, map_w, map_s, grid, false)
-         : p.wpb == 2 ? launch_variant<NSETS, 2, false>(a, p, map_w, map_s, grid, false)
-                      : launch_variant<NSETS, 1, false>(a, p, map_w, map_s, grid, false);
+    return p.nwarps == 8 ? launch_variant<NSETS, 8, HALF>(a, p, map_w, map_s, grid, planes_ready)
+                         : launch_variant<NSETS, 16, HALF>(a, p, map_w, map_s, grid, planes_ready);
+}
+
+bool shape_ok(int64_t M, int64_t K, int64_t N) {
+    return M >= 1 && M <= kMaxM && K >= kStepK && (K % kStepK) == 0 && K < (1LL << 24) && N >= 1 && N < (1LL << 31);
 }
 
 }  // namespace
 
 bool gemv_supported(const LinearArgs& a) {
-    Plan p;
-    return a.bits == 4 && a.layout == SGQ_LAYOUT_NK && a.group == 32 && a.M >= 1 && a.M <= kMaxM && a.K >= 256 &&
-           (a.K % 256) == 0 && a.N >= 1 && a.N < (1LL << 31) && a.K < (1LL << 24) && aligned(a.wq, 16) &&
-           aligned(a.scales, 16) && aligned(a.x, 16) && rows_per_launch(a.M, a.K) >= 1;
+    return a.bits == 4 && a.layout == SGQ_LAYOUT_NK && a.group == 32 && shape_ok(a.M, a.K, a.N) && aligned(a.wq, 16) &&
+           aligned(a.scales, 16) && aligned(a.x, 16) && rows_per_launch(a.M, a.K, false) >= 1;
 }
 
 // Scratch for the prepared activation planes (batches converted by the pre-kernel); 0 when the
 // conversion happens inside the CTAs.
 size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
-    (void)N;
-    Plan p;
-    if (bits != 4 || layout != SGQ_LAYOUT_NK || M < 1 || M > kMaxM || K < 256 || (K % 256) != 0) return 0;
-    const int64_t rows = rows_per_launch(M, K);
-    if (rows < 1) return 0;
-    if (rows < M) M = rows;                          // the row blocks of a split batch reuse one scratch
+    if (bits != 4 || layout != SGQ_LAYOUT_NK || !shape_ok(M, K, N > 0 ? N : 1)) return 0;
+    Plan p, c;
     if (!make_plan(M, K, true, &p)) return 0;
-    Plan c;
-    const bool compact_pre = make_plan(M, K, true, &c, true) && c.pre;    // what an overlapped launch would want
+    const bool compact_pre = make_plan(M, K, true, &c, true) && c.pre;    // what an overlapped launch in compact form would want
     if (!p.pre && !compact_pre) return 0;
     return (p.planes_bytes + 255) / 256 * 256;
 }
@@ -642,27 +615,26 @@ int launch_linear_gemv_prepared(const LinearArgs& a) { return launch_gemv_impl(a
 
 size_t gemv_prepared_bytes(int64_t M, int64_t K) {
     Plan p;
-    if (M < 1 || M > kMaxM || K < 256 || (K % 256) != 0 || K >= (1LL << 24) || !make_plan(M, K, true, &p)) return 0;
+    if (!shape_ok(M, K, 1) || !make_plan(M, K, true, &p)) return 0;
     return (p.planes_bytes + 255) / 256 * 256;
 }
 
 int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s) {
     const PreparedLayout L = prepared_layout(M, K);
-    if (K > 8LL * kPrepMaxChunks * kPrepThreads) {
-        set_error("K too large for the conversion kernel");
-        return SGQ_ERR_UNSUPPORTED;
-    }
     SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M)), dim3(kPrepThreads), 0, s,
-                               stream_overlap_enabled(), x, static_cast<int>(M), K, L.ndigits, L.nsets,
-                               static_cast<uint8_t*>(prepared)));
+                               stream_overlap_enabled(), x, K, L.ndigits, L.nsets, L.colmul, static_cast<uint8_t*>(prepared)));
     return SGQ_OK;
 }
 
 namespace {
 int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     Plan p;
-    if (!planes_ready && a.bits == 4 && a.M >= 1 && a.M <= kMaxM && a.K >= 256 && (a.K % 256) == 0) {
-        const int64_t rows = rows_per_launch(a.M, a.K);
+    const size_t want = planes_ready ? gemv_prepared_bytes(a.M, a.K) : gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    // K phases add into y in place, which the fused all-gather (stores into other GPUs) cannot do
+    const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
+    const bool phases_ok = have_ws && a.peers.n == 0;
+    if (!planes_ready && a.bits == 4 && shape_ok(a.M, a.K, a.N)) {
+        const int64_t rows = rows_per_launch(a.M, a.K, phases_ok);
         if (rows >= 1 && rows < a.M) {               // planes of the whole batch do not fit: row blocks
             for (int64_t m0 = 0; m0 < a.M; m0 += rows) {
                 LinearArgs sub = a;
@@ -677,19 +649,23 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
             return SGQ_OK;
         }
     }
-    const size_t want = planes_ready ? gemv_prepared_bytes(a.M, a.K) : gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
-    const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
     LinearArgs probe = a;
     if (planes_ready) probe.x = static_cast<const float*>(a.workspace);      // x is not read: only its alignment rule is waived
     const bool compact = stream_overlap_compact();
-    if (!gemv_supported(probe) || !((compact && make_plan(a.M, a.K, have_ws, &p, true)) || make_plan(a.M, a.K, have_ws, &p)) ||
-        (planes_ready && !have_ws)) {
+    if (!gemv_supported(probe) || (planes_ready && !have_ws) ||
+        !((compact && make_plan(a.M, a.K, phases_ok, &p, true)) || make_plan(a.M, a.K, phases_ok, &p))) {
         set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "
                   "16-byte aligned x/packed/scales");
         return SGQ_ERR_UNSUPPORTED;
     }
-    if (planes_ready) p.pre = true;
-    // packed weights as (128 B, N rows, K/256 steps); scales as (8 fp32, N rows, K/256 steps)
+    if (planes_ready) {
+        if (a.peers.n != 0 && p.nphases > 1) {
+            set_error("prepared activations of this size cannot be combined with the fused all-gather");
+            return SGQ_ERR_UNSUPPORTED;
+        }
+        p.pre = true;
+    }
+    // packed weights as (128 B, N rows, K/256 steps); scales as (K/32 fp32, N rows) in boxes of 32 x 16
     CUtensorMap map_w, map_s;
     const uint64_t steps = static_cast<uint64_t>(a.K / kStepK);
     {
@@ -699,21 +675,18 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
         if (!make_tensor_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
             return SGQ_ERR_CUDA;
     }
-    {
-        const uint64_t dims[3] = {8, static_cast<uint64_t>(a.N), steps};
-        const uint64_t strides[2] = {static_cast<uint64_t>(a.K / 32) * 4, 32};
-        const uint32_t box[3] = {8, kRows, kStepsPerStage};
-        if (!make_tensor_map(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.scales, 3, dims, strides, box,
-                             CU_TENSOR_MAP_SWIZZLE_NONE))
-            return SGQ_ERR_CUDA;
-    }
+    if (!make_tensor_map_2d(&map_s, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.scales, static_cast<uint64_t>(a.K / 32),
+                            static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 32) * 4, 32, kRows, CU_TENSOR_MAP_SWIZZLE_128B))
+        return SGQ_ERR_CUDA;
     const int64_t ntiles = ceil_div(a.N, kRows);
-    const int grid = static_cast<int>(ntiles < sm_count() ? ntiles : sm_count());
-    switch (p.nsets) {
-        case 1: return launch_nsets<1>(a, p, map_w, map_s, grid, planes_ready);
-        case 2: return launch_nsets<2>(a, p, map_w, map_s, grid, planes_ready);
-        case 3: return launch_nsets<3>(a, p, map_w, map_s, grid, planes_ready);
-        default: return launch_nsets<4>(a, p, map_w, map_s, grid, planes_ready);
+    const int64_t ctas = static_cast<int64_t>(sm_count()) * (p.nwarps == 8 ? 2 : 1);
+    const int grid = static_cast<int>(ntiles < ctas ? ntiles : ctas);
+    if (p.L.colmul == 2) return launch_nsets<1, true>(a, p, map_w, map_s, grid, planes_ready);
+    switch (p.L.nsets) {
+        case 1: return launch_nsets<1, false>(a, p, map_w, map_s, grid, planes_ready);
+        case 2: return launch_nsets<2, false>(a, p, map_w, map_s, grid, planes_ready);
+        case 3: return launch_nsets<3, false>(a, p, map_w, map_s, grid, planes_ready);
+        default: return launch_nsets<4, false>(a, p, map_w, map_s, grid, planes_ready);
     }
 }
 }  // namespace
@@ -724,8 +697,8 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
 // owns every allocation, or a serving loop that must not touch the allocator (and its locks)
 // between tokens.  For them the activation planes live in this file-scope array instead of a
 // caller workspace.  Every GPU that loads the library reserves these bytes until the process
-// exits.  The size bounds the batches this entry point accepts: (K/32) * ceil(M*digits/8) * 288
-// + 64 bytes, e.g. K = 8192 with M = 16.
+// exits.  The size bounds the batches this entry point accepts: (K/32) * sets * 272 bytes with
+// sets = ceil(M/4), e.g. K = 8192 with M = 16.
 constexpr size_t kStaticPlanesBytes = 320 * 1024;
 static __device__ __align__(256) unsigned char g_static_planes[kStaticPlanesBytes];
 
@@ -751,12 +724,12 @@ int static_planes_address(void** out) {
 }  // namespace
 
 int launch_linear_gemv_static(LinearArgs a) {
-    // the limit is stated for the whole batch, whether or not it then runs as several row blocks
-    size_t need = gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
-    if (a.M >= 1 && a.M <= kMaxM && a.K >= 256 && (a.K % 256) == 0 && rows_per_launch(a.M, a.K) < a.M) {
-        const size_t whole = (prepared_layout(a.M, a.K).bytes + 255) / 256 * 256;
-        if (whole > need) need = whole;
+    if (!shape_ok(a.M, a.K, a.N)) {
+        set_error("decode path needs M<=16 and K%%256==0");
+        return SGQ_ERR_UNSUPPORTED;
     }
+    // the limit is stated for the whole batch: its prepared planes must fit the built-in scratch
+    const size_t need = (prepared_layout(a.M, a.K).bytes + 255) / 256 * 256;
     if (need > kStaticPlanesBytes) {
         set_error("this batch needs %zu bytes of activation scratch; the built-in scratch holds %zu "
                   "(use sgq_linear_int4 with a caller workspace)", need, kStaticPlanesBytes);
@@ -765,8 +738,8 @@ int launch_linear_gemv_static(LinearArgs a) {
     void* planes = nullptr;
     int rc = static_planes_address(&planes);
     if (rc != SGQ_OK) return rc;
-    a.workspace = need ? planes : nullptr;
-    a.workspace_bytes = need ? kStaticPlanesBytes : 0;
+    a.workspace = planes;
+    a.workspace_bytes = kStaticPlanesBytes;
     return launch_linear_gemv(a);
 }
 

@@ -8,17 +8,18 @@
 //   * a step is 128 k of a 16-row tile (one 128-byte swizzled row per weight row), a stage is 8
 //     steps; the bytes go to the tensor core as they are (mma.sync m16n8k32 s8 x s8 -> s32), with
 //     no unpacking and no offset;
-//   * there is no per-group scale, so the int32 accumulators run over the WHOLE of K (exact:
-//     |sum| <= K * 127 * 128 < 2^31 for K < 2^17) and are converted to fp32 once per output;
-//   * the activation digit planes (same fixed-point digits as gemv_prepare.cuh, laid out for the
-//     natural k order of an int8 B fragment) are written once by a conversion kernel and stream
-//     through the same pipeline stages as the weights, 32 groups at a time, from L2.  They are
-//     never resident as a whole, so K is not limited by shared memory (K = 8192 at M = 16 runs);
-//   * tile epilogue: every warp leaves its int32 partial sums in one of two shared-memory slots,
-//     one named barrier, then thread (m, row) adds the eight partials (integers: any order gives
-//     the same bits), recombines the digits, applies 2^-p, the weight scale and the bias.
+//   * there is no per-group weight scale; the exact int32 sum of every 32-k group is multiplied by
+//     the activation scale of that group (gemv_prepare.cuh) and added up in fp32, the weight scale
+//     is applied once per output;
+//   * the activation digit planes and group scales (laid out for the natural k order of an int8 B
+//     fragment) are written once by a conversion kernel and stream through the same pipeline
+//     stages as the weights, 32 groups at a time, from L2.  They are never resident as a whole,
+//     so K is not limited by shared memory (K = 8192 at M = 16 runs);
+//   * tile epilogue: every warp leaves its fp32 partial sums in one of two shared-memory slots,
+//     one named barrier, then thread (m, row) adds the eight partials in warp order (fixed order:
+//     the same bits every run), recombines the digits, applies the weight scale and the bias.
 //
-// y[m,n] = ((sum_j 256^j * S_j[m,n]) * 2^-p_m) * scale[n] + bias[n],  S_j exact integers.
+// y[m,n] = (sum_j 256^j * sum_g sx[m,g] * S_j[g,m,n]) * scale[n] + bias[n],  S_j exact integers.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
 #include "sm100_ptx.cuh"
@@ -58,58 +59,56 @@ __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
     atomicCAS(&g_status_gemv_i8, 0u, (code << 24) | (detail & 0xFFFFFFu));
 }
 
-// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col) + C
-__device__ __forceinline__ void mma_s8s8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col) + magic
+__device__ __forceinline__ void mma_s8s8_16832_magic(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(kMagicBits));
 }
 
-// Digit planes for the int8 kernel: [group K/32][set][col 8][t 4] x 8 bytes, the 8 bytes of (col, t)
-// being the digits of k = 32*group + 4t + {0,1,2,3} (b0) and 32*group + 16 + 4t + {0,1,2,3} (b1);
-// column col = m * ndigits + j.  Followed by 16 fp32: 2^-p of every row.
+// N consecutive floats (16-byte aligned for N = 4, 8-byte for N = 2) with the widest load that fits.
+template <int N>
+__device__ __forceinline__ void load_scales(float (&v)[N], const float* p) {
+    if constexpr (N == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else if constexpr (N == 2) {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        v[0] = q.x; v[1] = q.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = p[i];
+    }
+}
+
+// Four 8x8 matrices of 16-byte rows: lane l supplies the address of row (l & 7) of matrix (l >> 3);
+// lane (g, t) receives word t of row g of every matrix.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+
+// Digit planes and group scales for the int8 kernel (gemv_prepare.cuh, natural k order): one CTA per
+// row, one pass.  K is a multiple of 128: in the last warp-wide call of a row the lanes beyond the end
+// pass zeros and store nothing.
 __global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float* __restrict__ x, int64_t K, int ndigits, int nsets,
-                                                                   uint8_t* __restrict__ planes) {
-    __shared__ float red[kPrepThreads / 32];
+                                                                   int colmul, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
-    const int m = blockIdx.x, lane = threadIdx.x & 31;
-    const float* xr = x + static_cast<int64_t>(m) * K;
+    const int m = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
     const int chunks = static_cast<int>(K / 8);
-    float mx = 0.0f;
-    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(xr) + 2 * c);
-        const float4 b = __ldg(reinterpret_cast<const float4*>(xr) + 2 * c + 1);
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        mx = fmaxf(mx, absmax8(v));
-    }
-    mx = warp_max(mx);
-    if (lane == 0) red[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    float all = red[lane < kPrepThreads / 32 ? lane : 0];
-    all = warp_max(all);
-    float P, invP;
-    row_scale(__float_as_uint(all), ndigits == 3 ? 22 : 14, &P, &invP);
-    const size_t groups = static_cast<size_t>(K / 32);
-    if (threadIdx.x == 0) reinterpret_cast<float*>(planes + groups * nsets * 256)[m] = invP;
-    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(xr) + 2 * c);          // second read: L1/L2
-        const float4 b = __ldg(reinterpret_cast<const float4*>(xr) + 2 * c + 1);
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        uint32_t db[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) db[j] = digit_bytes(__float2int_rn(v[j] * P));
-        const int group = c >> 2, q = c & 3;           // chunk q of its group: k = 8q .. 8q+7
-        const int t0 = 2 * (q & 1), half = q >> 1;     // k < 16 -> b0, else b1; words of t0 and t0 + 1
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            if (j < ndigits) {
-                const int col = m * ndigits + j, set = col >> 3, cc = col & 7;
-                uint8_t* base = planes + (static_cast<size_t>(group) * nsets + set) * 256 + (cc * 4 + t0) * 8 + half * 4;
-                *reinterpret_cast<uint32_t*>(base) = gather_byte(db[0], db[1], db[2], db[3], j);
-                *reinterpret_cast<uint32_t*>(base + 8) = gather_byte(db[4], db[5], db[6], db[7], j);
-            }
+    const int padded = (chunks + 31) & ~31;
+    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(K / 32) * nsets * 256);
+    for (int c = threadIdx.x; c < padded; c += kPrepThreads) {
+        const bool in = c < chunks;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (in) {
+            const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
+        convert_groups<kOrderNatural>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 1.0f, planes, scales, in);
     }
 }
 
@@ -119,9 +118,10 @@ struct Smem {
 
 __host__ __device__ inline Smem smem_layout(int nstages, int nsets) {
     Smem s;
-    s.stage_bytes = kStageW + kGroupsPerStage * 256u * nsets;
+    s.stage_bytes = kStageW + kGroupsPerStage * (256u + 16u) * nsets;   // weights, digits, group scales
+    s.stage_bytes = (s.stage_bytes + 1023u) & ~1023u;      // the swizzled weight box of every stage starts on a 1024-byte boundary
     s.partial_off = nstages * s.stage_bytes;
-    s.misc_off = s.partial_off + 2u * kWarps * (512u * nsets + 16u);      // two slots of per-warp int32 partial sums (padded)
+    s.misc_off = s.partial_off + 2u * kWarps * (512u * nsets + 16u);      // two slots of per-warp fp32 partial sums (padded)
     s.total = s.misc_off + 2u * kMaxStages * 8u + 16u;
     return s;
 }
@@ -129,15 +129,17 @@ __host__ __device__ inline Smem smem_layout(int nstages, int nsets) {
 template <int NSETS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __restrict__ planes, const float* __restrict__ wscales,
-                    int scale_per_row, const float* __restrict__ bias, float* __restrict__ y, int M, int ndigits, int64_t K, int64_t N,
-                    int64_t ldy, int nstages) {
+                    int scale_per_row, const float* __restrict__ bias, float* __restrict__ y, int M, int ndigits, int colmul, int64_t K,
+                    int64_t N, int64_t ldy, int nstages) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by pointer arithmetic on the shared array itself: a round trip through an integer would make the
+    // compiler lose the address space and emit generic loads for every shared-memory access below
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const Smem L = smem_layout(nstages, NSETS);
-    int* partial = reinterpret_cast<int*>(smem + L.partial_off);
+    float* partial = reinterpret_cast<float*>(smem + L.partial_off);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.misc_off);
     uint64_t* empty = full + kMaxStages;
-    constexpr int kPStride = 128 * NSETS + 4;       // ints per warp in a partial-sum slot
+    constexpr int kPStride = 128 * NSETS + 4;       // floats per warp in a partial-sum slot
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
@@ -175,11 +177,15 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                     const int g0 = c0 * 4;                                              // first digit group of the stage
                     const int ng = (groups_total - g0 < kGroupsPerStage) ? groups_total - g0 : kGroupsPerStage;
                     const uint32_t pbytes = static_cast<uint32_t>(ng) * 256u * NSETS;
+                    const uint32_t sbytes = static_cast<uint32_t>(ng) * 16u * NSETS;                  // group scales of the stage
                     // steps past K/128 are out of range in the third dimension: zero-filled, still counted
-                    mbar_arrive_expect_tx(&full[st], kStageW + pbytes);
+                    mbar_arrive_expect_tx(&full[st], kStageW + pbytes + sbytes);
                     uint8_t* sw = smem + st * L.stage_bytes;
                     tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
                     bulk_copy_g2s(sw + kStageW, planes + static_cast<size_t>(g0) * 256u * NSETS, pbytes, &full[st]);
+                    bulk_copy_g2s(sw + kStageW + kGroupsPerStage * 256u * NSETS,
+                                  planes + static_cast<size_t>(groups_total) * 256u * NSETS + static_cast<size_t>(g0) * 16u * NSETS, sbytes,
+                                  &full[st]);
                 }
             }
         }
@@ -188,27 +194,25 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
 
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
-    uint32_t woff[4][2];                            // this lane's word in chunks 2i and 2i+1 of rows g and g+8 (swizzle: chunk ^ row)
+    // ldmatrix row address of this lane inside a step box for group i (bytes 32 i .. 32 i + 31 of every row):
+    // matrix (lane >> 3) = (rows 0-7 | rows 8-15) x (16-byte chunk 2i | 2i+1); 128-byte swizzle: chunk ^ (row & 7)
+    uint32_t lm_off[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        woff[i][0] = g * 128 + (((2 * i) ^ g) << 4) + t * 4;
-        woff[i][1] = g * 128 + (((2 * i + 1) ^ g) << 4) + t * 4;
-    }
-    const float* inv_p = reinterpret_cast<const float*>(planes + static_cast<size_t>(groups_total) * 256u * NSETS);
+    for (int i = 0; i < 4; ++i)
+        lm_off[i] = ((lane & 7) + 8 * ((lane >> 3) & 1)) * 128 + (((2 * i + (lane >> 4)) ^ (lane & 7)) << 4);
+    const uint32_t smem_u = smem_u32(smem);
     // epilogue role of this thread: output (row er of the tile, batch row em)
     const int em = threadIdx.x >> 4, er = threadIdx.x & 15;
-    float my_inv_p = 0.f;
-    if (em < M) my_inv_p = __ldg(inv_p + em);
     const float sw_all = scale_per_row ? 1.0f : __ldg(wscales);
 
     bool alive = true;
     uint32_t seq = 0, tcount = 0;
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-        int acc[NSETS][4];
+        float total[NSETS][4];
 #pragma unroll
         for (int s = 0; s < NSETS; ++s)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[s][i] = 0;
+            for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
         for (int c0 = 0; c0 < spt; c0 += kSteps, ++seq) {
             const int st = seq % nstages;
@@ -219,52 +223,71 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
             }
             const int step = c0 + warp;
             if (alive && step < spt) {
-                const uint8_t* wbox = smem + st * L.stage_bytes + warp * (kRows * 128);
-                const uint8_t* xg = smem + st * L.stage_bytes + kStageW + (warp * 4) * (256 * NSETS) + lane * 8;
+                const uint32_t wbox = smem_u + st * L.stage_bytes + warp * (kRows * 128);
+                const uint8_t* xg = smem + st * L.stage_bytes + kStageW + (warp * 4) * (256 * NSETS);
+                const float* sg = reinterpret_cast<const float*>(smem + st * L.stage_bytes + kStageW + kGroupsPerStage * 256 * NSETS) +
+                                  ((warp * 4) * 4 + t) * NSETS;                           // this lane's group scales
                 uint32_t a[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    a[i][0] = *reinterpret_cast<const uint32_t*>(wbox + woff[i][0]);             // row g,   k = 32i + 4t..
-                    a[i][1] = *reinterpret_cast<const uint32_t*>(wbox + 1024 + woff[i][0]);      // row g+8
-                    a[i][2] = *reinterpret_cast<const uint32_t*>(wbox + woff[i][1]);             // row g,   k = 32i + 16 + 4t..
-                    a[i][3] = *reinterpret_cast<const uint32_t*>(wbox + 1024 + woff[i][1]);      // row g+8
-                }
+                for (int i = 0; i < 4; ++i) ldmatrix_x4(a[i], wbox + lm_off[i]);    // rows g / g+8, k = 32i + 4t.. and 32i + 16 + 4t..
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
+                    const uint8_t* xgi = xg + i * (256 * NSETS);
+                    float sxv[NSETS];                                               // activation scales: columns 2t, 2t+1 of every set
+                    load_scales<NSETS>(sxv, sg + i * (4 * NSETS));
 #pragma unroll
-                    for (int s = 0; s < NSETS; ++s) {
-                        const uint2 xb = *reinterpret_cast<const uint2*>(xg + i * (256 * NSETS) + s * 256);
-                        mma_s8s8_16832(acc[s], a[i], xb.x, xb.y);
+                    for (int pr = 0; pr < (NSETS + 1) / 2; ++pr) {
+                        uint32_t xb[4];
+                        if (2 * pr + 1 < NSETS) {                    // a full pair of sets: one 128-bit load per lane
+                            const uint4 q = *reinterpret_cast<const uint4*>(xgi + pr * 512 + lane * 16);
+                            xb[0] = q.x; xb[1] = q.y; xb[2] = q.z; xb[3] = q.w;
+                        } else {
+                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + pr * 512 + lane * 8);
+                            xb[0] = q.x; xb[1] = q.y; xb[2] = 0; xb[3] = 0;
+                        }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int s = 2 * pr + h;
+                            if (s < NSETS) {
+                                int d[4];
+                                mma_s8s8_16832_magic(d, a[i], xb[2 * h], xb[2 * h + 1]);
+                                // d holds 12582912.0f + (exact group sum) as fp32 bits
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    total[s][e] = __fmaf_rn(sxv[s], __fsub_rn(__int_as_float(d[e]), kMagicF), total[s][e]);
+                            }
+                        }
                     }
                 }
             }
             // everything loaded from the stage has been consumed once the accumulators are final
             uint32_t fold = 0;
 #pragma unroll
-            for (int s = 0; s < NSETS; ++s) fold ^= static_cast<uint32_t>(acc[s][0] ^ acc[s][3]);
+            for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][3]);
             const uint32_t landed = loads_landed(fold);
             if (lane == 0) mbar_arrive_after(&empty[st], landed);
         }
 
         // ---- tile epilogue: partial sums -> shared memory, one barrier, one output per thread ----
-        int* pslot = partial + (tcount & 1u) * (kWarps * kPStride);
+        float* pslot = partial + (tcount & 1u) * (kWarps * kPStride);
 #pragma unroll
         for (int s = 0; s < NSETS; ++s)
-            *reinterpret_cast<int4*>(pslot + warp * kPStride + (s * 32 + lane) * 4) = make_int4(acc[s][0], acc[s][1], acc[s][2], acc[s][3]);
+            *reinterpret_cast<float4*>(pslot + warp * kPStride + (s * 32 + lane) * 4) =
+                make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
         named_barrier_sync(1, kConsumerThreads);
         if (em < M) {
             float v = 0.0f, weight = 1.0f;
             for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
-                const int col = em * ndigits + j, set = col >> 3, cc = col & 7;
-                const int* src = pslot + (set * 32 + (er & 7) * 4 + (cc >> 1)) * 4 + (er >> 3) * 2 + (cc & 1);
-                int sum = 0;
+                const int col = (em * ndigits + j) * colmul, set = col >> 3, cc = col & 7;
+                const float* src = pslot + (set * 32 + (er & 7) * 4 + (cc >> 1)) * 4 + (er >> 3) * 2 + (cc & 1);
+                float sum = src[0];
 #pragma unroll
-                for (int w = 0; w < kWarps; ++w) sum += src[w * kPStride];
-                v = __fmaf_rn(weight, static_cast<float>(sum), v);
+                for (int w = 1; w < kWarps; ++w) sum += src[w * kPStride];          // warp order: the same bits every run
+                v = __fmaf_rn(weight, sum, v);
             }
             const int64_t n = tile * kRows + er;
             if (n < N && alive) {
-                v = __fmul_rn(__fmul_rn(v, my_inv_p), scale_per_row ? __ldg(wscales + n) : sw_all);
+                v = __fmul_rn(v, scale_per_row ? __ldg(wscales + n) : sw_all);
                 if (bias) v = __fadd_rn(v, bias[n]);
                 y[static_cast<int64_t>(em) * ldy + n] = v;
             }
@@ -275,7 +298,7 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
 }
 
 struct Plan {
-    int ndigits, nsets, nstages;
+    int ndigits, nsets, colmul, nstages;
     uint32_t smem;
     size_t planes_bytes;
 };
@@ -284,7 +307,8 @@ bool make_plan(int64_t M, int64_t K, Plan* p) {
     const PreparedLayout L = prepared_layout(M, K);
     p->ndigits = L.ndigits;
     p->nsets = L.nsets;
-    p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * 256 + kMaxM * 4;
+    p->colmul = L.colmul;
+    p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * (256 + 16);
     for (int st = kMaxStages; st >= 2; --st) {
         const Smem S = smem_layout(st, p->nsets);
         if (S.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {
@@ -303,10 +327,10 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
     const bool overlap = stream_overlap_enabled();
     SGQ_CUDA_TRY(launch_kernel(prepare_x_i8_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap, a.x, a.K,
-                               p.ndigits, p.nsets, static_cast<uint8_t*>(a.workspace)));
+                               p.ndigits, p.nsets, p.colmul, static_cast<uint8_t*>(a.workspace)));
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), p.smem, a.stream, overlap, map_w,
                                static_cast<const uint8_t*>(a.workspace), a.scales, a.scheme == SGQ_PER_ROW ? 1 : 0, a.bias, a.y,
-                               static_cast<int>(a.M), p.ndigits, a.K, a.N, a.ldy, p.nstages));
+                               static_cast<int>(a.M), p.ndigits, p.colmul, a.K, a.N, a.ldy, p.nstages));
     return SGQ_OK;
 }
 

@@ -6,8 +6,9 @@
 // slot r of rank q is written only by rank r.  A barrier publishes this rank's epoch (a counter
 // kept in local device memory, +1 per barrier, so recorded launches stay valid) into slot `rank` of
 // every rank and waits until each of its own slots has reached the epoch.  Ranks must call the
-// barrier the same number of times.  The wait is bounded: if a peer never arrives the kernel
-// records kDevErrPeerWait in the status word and returns; the caller reads it on the host.
+// barrier the same number of times.  The wait is bounded (sgq_set_peer_wait_budget): if a peer
+// never arrives the kernel records kDevErrPeerWait in the status word and returns; the caller
+// reads it on the host (sgq_device_status).
 #include "sgq_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -31,12 +32,12 @@ struct PeerSignals {
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const __grid_constant__ PeerSignals sig, int rank, int world,
-                                                          unsigned long long* local_epoch) {
+                                                          unsigned long long* local_epoch, unsigned int poll_budget) {
     const int lane = threadIdx.x;
     pdl_launch_dependents();      // the next kernel may set itself up (and fetch weights); it still waits for this grid
     pdl_wait();                   // the kernel that stored the slices has finished and its stores are visible here
     int late = 0;
-    if (!peer_signal_and_wait(sig.p, rank, world, local_epoch, lane, &late) && lane == 0)
+    if (!peer_signal_and_wait(sig.p, rank, world, local_epoch, lane, &late, poll_budget) && lane == 0)
         atomicCAS(&g_status_peer, 0u, (kDevErrPeerWait << 24) | 0x10000u);
 }
 
@@ -105,7 +106,7 @@ int sgq_peer_barrier(void* const* signals, int rank, int world, void* local_epoc
     int rc = check_device();
     if (rc != SGQ_OK) return rc;
     SGQ_CUDA_TRY(launch_kernel(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), stream_overlap_enabled(),
-                               sig, rank, world, static_cast<unsigned long long*>(local_epoch)));
+                               sig, rank, world, static_cast<unsigned long long*>(local_epoch), peer_wait_budget()));
     return SGQ_OK;
 }
 

@@ -96,13 +96,19 @@ struct PeerOut {
     unsigned long long* sig[kMaxPeers];
     int rank;
     unsigned long long* state;
+    unsigned int poll_budget;   // polls after which a wait for a peer gives up (peer_wait_budget())
 };
+
+// Polls a device-side wait for another GPU may spend before it gives up (sgq_set_peer_wait_budget);
+// with the back-off below one poll is 0.1-0.4 us once a wait has lasted more than a few microseconds.
+unsigned int peer_wait_budget();
 
 #ifdef __CUDACC__
 // One warp: publish this GPU's next epoch to every rank and wait (bounded) until every rank has
 // published it here.  Returns false if a peer did not arrive in time.
 __device__ __forceinline__ bool peer_signal_and_wait(unsigned long long* const* sig, int rank, int world,
-                                                     unsigned long long* local_epoch, int lane, int* late_rank) {
+                                                     unsigned long long* local_epoch, int lane, int* late_rank,
+                                                     unsigned int poll_budget) {
     unsigned long long epoch = 0;
     if (lane == 0) {
         epoch = *local_epoch + 1;
@@ -119,7 +125,7 @@ __device__ __forceinline__ bool peer_signal_and_wait(unsigned long long* const* 
             unsigned long long v;
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
             if (v >= epoch) break;
-            if (++polls > (1u << 21)) {           // x >= 100 ns back-off: gives up after a few seconds at most
+            if (++polls > poll_budget) {          // bounded: the caller records the failure and returns
                 ok = false;
                 *late_rank = lane;
                 break;

@@ -79,14 +79,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: 2^22 polls, the later ones with a short sleep (about half a second at most).
-// false = gave up.
+// Bounded wait.  Every try_wait may suspend the warp for up to kWaitSliceNs (it wakes as soon as the
+// phase completes), so a waiting warp costs a handful of instructions per slice instead of spinning
+// through the issue slots the working warps need; after kWaitSlices slices (about 0.7 s) it gives
+// up.  false = gave up.
+constexpr uint32_t kWaitSliceNs = 20000;
+constexpr uint32_t kWaitSlices = 1u << 15;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 2048) __nanosleep(64);
-    }
-    return false;
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n"
+        "SGQ_WAIT_%=:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "@p bra SGQ_DONE_%=;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %4;\n\t"
+        "@q bra SGQ_WAIT_%=;\n"
+        "SGQ_DONE_%=:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitSliceNs), "r"(kWaitSlices)
+        : "memory");
+    return ok != 0;
 }
 
 // 2-D TMA tile load, global -> this CTA's shared memory, completion on an mbarrier.

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import cases
-from util import TOL_BF16, TOL_FP32, bf16_round, norm_err, rel_err
+from util import TOL_BF16, TOL_FP32, bf16_round, block_fixed_point, heavy_tailed_rows, norm_err, rel_err
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -126,12 +126,9 @@ def test_decode_int8_kernel_against_port(sgq, port, M, K, N):
         y = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
         check_status(sgq)
         assert rel_err(y, want) <= TOL_FP32, (M, K, N, scheme, rel_err(y, want))
-        # the kernel's own arithmetic: x in fixed point (22 / 14 fractional bits below the power of two
-        # above the row's absmax, round to nearest), exact integer dot products, then fp32 scaling
-        frac = 22 if M <= 2 else 14
-        e = np.floor(np.log2(np.abs(x).max(axis=1, keepdims=True).astype(np.float64))) + 1
-        xq = np.rint(x.astype(np.float64) * 2.0 ** (frac - e))
-        model = (xq @ wq.astype(np.float64).T) * 2.0 ** (e - frac) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
+        # the kernel's own arithmetic: block-scaled fixed-point activations (tests/util.py), exact integer
+        # dot products per 128-k step, then fp32 scaling
+        model = (block_fixed_point(x) @ wq.astype(np.float64).T) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
         assert rel_err(y, model) <= 2e-6, ("layout/pipeline error, not rounding", rel_err(y, model))
         y_auto = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws).cpu().numpy()
         assert np.array_equal(y_auto, y)                         # AUTO takes this kernel when a workspace is supplied
@@ -152,6 +149,70 @@ def test_decode_kernel_rejects_what_it_cannot_run(sgq):
     sgq.quantized_matmul(torch.randn(1, 96, device="cuda"), q, None, layout=cases.LAYOUT_NK)
     with pytest.raises(RuntimeError):             # inner dimensions must match, as in the reference
         sgq.quantized_matmul(torch.randn(1, 95, device="cuda"), q, None, layout=cases.LAYOUT_NK)
+
+
+HEAVY = [(M, f, ch) for M in (1, 2, 3, 4, 8, 16) for f, ch in ((30.0, 1), (100.0, 8), (300.0, 1), (300.0, 40))]
+
+
+@pytest.mark.parametrize("M,factor,channels", HEAVY)
+def test_decode_kernels_heavy_tailed_activations(sgq, port, M, factor, channels):
+    """Activation rows with a few channels at 30x / 100x / 300x the rest, as normalised decoder
+    activations have them: the 1e-3 bound of the decode kernels must not depend on the activation
+    distribution.  INT4 g=32 and INT8 (per tensor, per row), against the reference-order forward."""
+    K, N = 4096, 272
+    x = heavy_tailed_rows(M * 131 + int(factor) + channels, M, K, factor, channels)
+    w = cases.weight_with_outliers(K + N + M, (N, K))
+    b = (np.random.default_rng(M).standard_normal(N) * 0.1).astype(np.float32)
+    ws = sgq.Workspace(torch.device("cuda"))
+    packed, scales = port.quantize_int4(w, 32)
+    want = port.qlinear_int4(x, packed, scales, K, N, cases.LAYOUT_NK, 32, b)
+    q = sgq.quantize_int4(dev(w), 32)
+    y = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+    check_status(sgq)
+    assert rel_err(y, want) <= TOL_FP32, ("int4", M, factor, channels, rel_err(y, want))
+    codes = port.unpack_int4_codes(packed, N * K).reshape(N, K).astype(np.float64)
+    wd = codes * np.repeat(scales.reshape(N, K // 32).astype(np.float64), 32, axis=1)
+    model = block_fixed_point(x) @ wd.T + b[None, :]
+    assert rel_err(y, model) <= 5e-6, ("layout/pipeline error, not rounding", rel_err(y, model))
+    for scheme in (cases.PER_TENSOR, cases.PER_ROW):
+        wq, sw = port.quantize_int8(w, scheme)
+        want8 = port.qlinear_int8(x, wq, sw, K, N, cases.LAYOUT_NK, scheme, b)
+        q8 = sgq.quantize_int8(dev(w), scheme)
+        y8 = sgq.quantized_matmul(dev(x), q8, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws).cpu().numpy()
+        check_status(sgq)
+        assert rel_err(y8, want8) <= TOL_FP32, ("int8", scheme, M, factor, channels, rel_err(y8, want8))
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_decode_kernels_non_finite_and_vanishing_activations(sgq, M):
+    """A NaN or Inf activation makes its own output row NaN and leaves the other rows alone (the
+    reference's fp32 chain would give NaN or Inf there too); an all-zero row gives the bias; rows of
+    denormal-sized values are treated as zero."""
+    K, N = 1024, 64
+    g = torch.Generator(device="cuda").manual_seed(M)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    b = torch.randn(N, device="cuda", generator=g)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    clean = x.clone()
+    x[0, 5] = float("inf")
+    if M > 1:
+        x[1] = 0.0
+    if M > 2:
+        x[2] = 1e-38
+        x[M - 1, 700] = float("nan")
+    ws = sgq.Workspace(torch.device("cuda"))
+    for q in (sgq.quantize_int4(w, 32), sgq.quantize_int8(w, sgq.PER_ROW)):
+        y = sgq.quantized_matmul(x, q, b, layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws)
+        y_clean = sgq.quantized_matmul(clean, q, b, layout=cases.LAYOUT_NK, path=sgq.PATH_GEMV, workspace=ws)
+        check_status(sgq)
+        assert torch.isnan(y[0]).all()
+        if M > 1:
+            assert torch.equal(y[1], b)
+        if M > 2:
+            assert torch.equal(y[2], b)
+            assert torch.isnan(y[M - 1]).all()
+            for m in range(3, M - 1):
+                assert torch.equal(y[m], y_clean[m])
 
 
 @pytest.mark.parametrize("M", [1, 4, 16])

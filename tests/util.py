@@ -31,3 +31,36 @@ def bf16_round(a):
 
 TOL_FP32 = 1e-3   # fp32-dequant paths (SIMT, decode)
 TOL_BF16 = 2e-2   # bf16 / int8 tensor-core paths
+
+
+def block_fixed_point(x, ndigits=None):
+    """What the decode kernels make of fp32 activations x[M, K], as float64: every 32 consecutive k
+    of a row share one scale gmax / Q (Q = 32600 for two int8 digits, 8355000 for the three digits
+    of a single-row batch), values are rounded to the nearest multiple of it.  All steps in fp32 as
+    on the device: P = Q / gmax, q = rint(x * P), scale = gmax / Q."""
+    x = np.ascontiguousarray(x, np.float32)
+    M, K = x.shape
+    if ndigits is None:
+        ndigits = 3 if M == 1 else 2
+    Q = np.float32(8355000.0 if ndigits == 3 else 32600.0)
+    out = np.zeros((M, K), np.float64)
+    for b0 in range(0, K, 32):
+        blk = x[:, b0:b0 + 32]
+        bmax = np.max(np.abs(blk), axis=1, keepdims=True).astype(np.float32)
+        ok = bmax >= np.float32(1e-30)
+        safe = np.where(ok, bmax, np.float32(1.0))
+        P = (Q / safe).astype(np.float32)
+        sx = (safe / Q).astype(np.float32)
+        q = np.rint((blk * P).astype(np.float32)).astype(np.float64)
+        out[:, b0:b0 + 32] = np.where(ok, q * sx.astype(np.float64), 0.0)
+    return out
+
+
+def heavy_tailed_rows(seed, M, K, factor, channels):
+    """N(0,1) activation rows in which `channels` positions (the same for every row, as the outlier
+    channels of a normalised decoder activation are) are multiplied by `factor`."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    idx = rng.choice(K, size=channels, replace=False)
+    x[:, idx] *= np.float32(factor)
+    return x
