@@ -68,9 +68,10 @@ enum {
     SGQ_PATH_SIMT = 1,    /* tiled fp32 SIMT kernel, any shape; one fused-multiply-add chain per
                              output in ascending k, i.e. the reference CPU rounding */
     SGQ_PATH_GEMV = 2,    /* decode (M <= 16): weight-streaming kernels.  [N,K] (INT4 g=32, INT8): exact integer
-                             tensor-core dot products of the codes with block-scaled fixed-point activations (one
-                             scale per 32 k of a row, 16 bits, 24 for M = 1), fp32 scaling and accumulation; any
-                             activation distribution stays within 1e-3 of the reference's fp32 forward; a row with a
+                             tensor-core dot products of the codes with fixed-point activations (24 bits below the
+                             absmax of every 32 k of a row; from three rows on the last 8 bits only where one value
+                             dominates its 32), fp32 scaling and accumulation; any activation distribution stays
+                             within ~1e-4 of the reference's fp32 forward (bound 1e-3); a row with a
                              NaN or Inf activation yields a NaN output row.  [K,N] (the reference module's layout):
                              fp32 throughout */
     SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16, weights dequantized to bf16 in shared memory */
@@ -219,10 +220,10 @@ SGQ_API unsigned int sgq_set_peer_wait_budget(unsigned int polls);
  * more than 4 rows (the activation planes of the decode kernel).
  *
  * Same computation and results as sgq_linear_int4(..., SGQ_LAYOUT_NK, group 32, SGQ_PATH_GEMV),
- * but the scratch is a fixed array inside the library's device image: 320 KiB on every GPU that
+ * but the scratch is a fixed array inside the library's device image: 448 KiB on every GPU that
  * loads the library, held until the process exits.  Limits and rules:
  *  - shapes the decode kernel takes (M <= 16, K % 256 == 0, 16-byte aligned x/packed/scales) whose
- *    prepared activations, sgq_prepared_x_bytes(M, K), are at most 320 KiB (e.g. K = 8192 at
+ *    prepared activations, sgq_prepared_x_bytes(M, K), are at most 448 KiB (e.g. K = 8192 at
  *    M = 16); anything larger returns SGQ_ERR_WORKSPACE;
  *  - the first call on each device looks up the array's device address (a runtime query, no
  *    allocation); make that first call outside any stream capture;

@@ -36,9 +36,13 @@ def build_port() -> str:
     return so
 
 
-def build_ref(reference_dir: str = "/root/reference") -> str | None:
-    """Compile the unmodified reference when its sources are reachable; else keep what exists."""
+def build_ref(reference_dir: str | None = None) -> str | None:
+    """Compile the unmodified reference when its sources are reachable (reference_dir, else the
+    environment variable SGQ_REFERENCE_DIR, else a sibling directory `reference` of this
+    repository); else keep what exists."""
     so = os.path.join(_HERE, "_ref", "libsgref.so")
+    if reference_dir is None:
+        reference_dir = os.environ.get("SGQ_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
     if os.path.isdir(os.path.join(reference_dir, "src")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={reference_dir}"])
     return so if os.path.exists(so) else None

@@ -36,10 +36,6 @@ cudaError_t read_status_gemm(uint32_t* v, bool clear) {
     return e;
 }
 
-#ifndef SGQ_TC_EXP
-#define SGQ_TC_EXP 0   // debug builds only: 1 = MMA issuer ignores the operand barriers, loaders idle
-#endif
-
 namespace {
 
 enum Mode { kI8 = 0, kBF16 = 1, kBF16W8 = 2 };   // W8A8 | bf16 x INT4 g=32 | bf16 x INT8 codes (scale in the epilogue)
@@ -62,7 +58,7 @@ template <int MODE>
 struct Cfg {
     static constexpr int kBlockK = MODE == kI8 ? 128 : 64;          // elements per k-block
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
-    static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage         // the INT8 raw ring takes the room of one A stage
+    static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage
     static constexpr int kBStages = 3;
     static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
     static constexpr int kRawStageBytes = MODE == kBF16W8 ? BN * 64 : kRawBytes;
@@ -174,7 +170,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if (warp == 0) {
         // ------------------------------- A producer ---------------------------------
-        if (lane == 0 && !(SGQ_TC_EXP & 1)) {
+        if (lane == 0) {
             tma_prefetch_descriptor(&map_a);
             Ring<NA> ra;
             Walk w(blockIdx.x);
@@ -190,7 +186,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp == kBProducerWarp) {
         // ------------------------------- B / raw producer ---------------------------
-        if (lane == 0 && !(SGQ_TC_EXP & 1)) {
+        if (lane == 0) {
             tma_prefetch_descriptor(&map_b);
             Ring<NB> rb;
             Ring<NR> rr;
@@ -229,10 +225,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tcgen05_fence_after();
                 }
                 const int sa = ra.slot, sb = rb.slot;
-#if !(SGQ_TC_EXP & 1)
                 if (!mbar_wait(&a_full[sa], ra.phase)) { report(kDevErrFullWait, static_cast<uint32_t>(it)); break; }
                 if (!mbar_wait(&b_full[sb], rb.phase)) { report(kDevErrFullWait, 0x800000u | static_cast<uint32_t>(it)); break; }
-#endif
                 tcgen05_fence_after();
                 const uint64_t bdesc = umma_desc_sw128(smem_u32(smem + C::kBOff + sb * kBBytes));
 #pragma unroll
@@ -276,7 +270,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int64_t m = mrow0 + lane;
                 float sxm = 1.0f;
                 if (MODE == kI8 && m < p.M) sxm = p.sx[m];
-                for (int c = 0; c < ((SGQ_TC_EXP & 16) ? 0 : BN / 32); ++c) {
+                for (int c = 0; c < BN / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + half * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), v);
                     tmem_ld_wait();
@@ -422,7 +416,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         Ring<NR> rr;
         Ring<NB> rb;
-        bool alive = !(SGQ_TC_EXP & 1);
+        bool alive = true;
         for (int64_t it0 = 0; it0 < total_its && alive; it0 += kAhead) {
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
@@ -443,7 +437,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t sx2 = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sc))) * 0x00010001u;
                 uint8_t* brow = smem + C::kBOff + sb * kBBytes + r * 128;
 #pragma unroll
-                for (int w = 0; w < ((SGQ_TC_EXP & 32) ? 0 : 4); ++w) {
+                for (int w = 0; w < 4; ++w) {
                     uint32_t o[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -457,9 +451,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     // chunk (4h + w) of the row goes to chunk ((4h + w) ^ (r & 7)): the 128-byte swizzle the MMA expects
                     *reinterpret_cast<uint4*>(brow + (((4 * h + w) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
-#if !(SGQ_TC_EXP & 64)
                 fence_proxy_async_smem();
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&b_full[sb]);
                 rr.advance();

@@ -10,8 +10,10 @@
 //     2-D boxes [16 rows][32 fp32] of scales (128-byte rows again: a 32-byte-wide box would cost the
 //     copy engine four times as many requests), into a ring of stages guarded by full/empty
 //     mbarriers.  A step is 256 k of a 16-row tile.
-//   * Integer inner product.  The activations arrive as block-scaled int8 digit planes
-//     (gemv_prepare.cuh).  A word of eight 4-bit codes becomes two words of signed bytes holding
+//   * Integer inner product.  The activations arrive as group-scaled int8 digit planes
+//     (gemv_prepare.cuh: 24-bit fixed point per 32-k group; in batches of three rows or more the
+//     low digit sits in column sets of its own that are skipped, group by group, where it cannot
+//     matter).  A word of eight 4-bit codes becomes two words of signed bytes holding
 //     16 * code with one shift and two masks ((w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0: a nibble in
 //     the high half of a byte IS the two's-complement value times 16), and a 32-k group of 16
 //     weight rows times 8 digit columns is ONE mma.sync m16n8k32 (s8 x s8 -> s32, exact).
@@ -29,8 +31,9 @@
 //     phases over K: the planes of one K range are resident while ALL tiles of the CTA stream their
 //     weights of that range; later phases add into y.  The weights are still read exactly once.
 //
-// Error against the reference's single fp32 chain: see gemv_prepare.cuh (group-scaled 16-bit
-// activations, 24-bit for one row); everything up to the group sums is exact, the rest is fp32.
+// Error against the reference's single fp32 chain: see gemv_prepare.cuh (at most ~1e-4 of an
+// output's scale for any activation distribution, ~1e-6 for one or two rows); everything up to the
+// group sums is exact, the rest is fp32.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
 #include "sm100_ptx.cuh"
@@ -69,18 +72,23 @@ constexpr int kMaxM = 16;
 // warps_per_tile groups take alternate tiles.
 __host__ __device__ constexpr int warps_per_tile(int nwarps) { return nwarps == 16 ? 8 : 4; }
 
+// Partial-sum slots per warp group: two, so that a group can start its next tile while the reducer still
+// reads the last one; one where the sums of a tile are large (many column sets) and shared memory is short.
+__host__ __device__ constexpr int slots_per_group(int nmain) { return nmain <= 2 ? 2 : 1; }
+
 struct Smem {
-    uint32_t x_off, sx_off, partial_off, misc_off, total;   // from a 1024-byte aligned base; stages first
+    uint32_t x_off, sx_off, flag_off, partial_off, misc_off, total;   // from a 1024-byte aligned base; stages first
 };
 
-// groups: 32-k groups of ONE phase
-__host__ __device__ inline Smem smem_layout(int nstages, uint32_t groups, int nsets, int nwarps) {
+// groups: 32-k groups of ONE phase; nmain / nlow: column sets (gemv_prepare.cuh)
+__host__ __device__ inline Smem smem_layout(int nstages, uint32_t groups, int nmain, int nlow, int nwarps) {
     Smem s;
+    const uint32_t nsets = nmain + nlow;
     s.x_off = nstages * kStageBytes;
     s.sx_off = s.x_off + groups * 256u * nsets;
-    s.partial_off = s.sx_off + groups * 16u * nsets;
-    s.partial_off = (s.partial_off + 15u) & ~15u;
-    s.misc_off = s.partial_off + 2u * nwarps * (512u * nsets + 16u);        // slots x warps per tile x padded partial sums
+    s.flag_off = s.sx_off + groups * 32u * nsets;
+    s.partial_off = s.flag_off + (nlow ? groups * 16u : 0u);
+    s.misc_off = s.partial_off + slots_per_group(nmain) * nwarps * (512u * nmain + 16u);   // slots x warps per tile x padded partial sums
     s.total = s.misc_off + (2u * kMaxStages + 2u * kMaxSlots + 2u) * 8u;
     return s;
 }
@@ -121,37 +129,42 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 
 // Activation planes converted once into global scratch, in the prepared layout.  One CTA per row.
 constexpr int kPrepThreads = 256;
-__global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int64_t K, int ndigits, int nsets,
-                                                                     int colmul, uint8_t* __restrict__ planes) {
+__global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int64_t K, int mode, int nmain,
+                                                                     int nsets, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
-    const int m = blockIdx.x;
+    const int m = blockIdx.x, M = gridDim.x;
     const int chunks = static_cast<int>(K / 8);
-    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(K / 32) * nsets * 256);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
     const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
-    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {          // chunks % 32 == 0: whole warps, one block each
+    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {          // chunks % 32 == 0: whole warps
         const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        convert_groups<kOrderNibble>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 0.0625f, planes, scales);
+        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 0.0625f, pp.digits, pp.scales,
+                                     pp.flags);
     }
 }
 
 enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2 };
 
-// NSETS: sets of 8 digit columns; NWARPS: consumer warps (16, or 8 in the compact two-CTAs-per-SM
-// form); HALF: only even columns carry data (one- and two-row batches), the odd accumulators are skipped.
-template <int NSETS, int NWARPS, bool HALF>
+// NM / NL: main and low sets of 8 digit columns (gemv_prepare.cuh; NL > 0: batches of three rows or
+// more); NWARPS: consumer warps (16, or 8 in the compact two-CTAs-per-SM form); HALF: one row, only
+// even columns carry data and the odd accumulators are skipped.
+template <int NM, int NL, int NWARPS, bool HALF>
 __global__ void __launch_bounds__((NWARPS + 2) * 32, NWARPS == 8 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
-                    float* __restrict__ y, int M, int ndigits, int colmul, int64_t K, int64_t N, int64_t ldy, int nstages,
-                    int nphases, int flags, const __grid_constant__ PeerOut peers) {
+                    float* __restrict__ y, int M, int64_t K, int64_t N, int64_t ldy, int nstages, int nphases, int flags,
+                    const __grid_constant__ PeerOut peers) {
+    constexpr int NSETS = NM + NL;
+    constexpr int kMode = NL > 0 ? 2 : (HALF ? 0 : 1);
+    constexpr int kDigitsOut = NL > 0 ? 2 : 3;
     constexpr int WPT = warps_per_tile(NWARPS);
     constexpr int kGroups = NWARPS / WPT;              // warp groups = tiles in work at any time
-    constexpr int kSlots = 2 * kGroups;
+    constexpr int kSlots = slots_per_group(NM) * kGroups;
     constexpr int GPW = 64 / WPT;                      // 32-k groups of a stage per warp (8 or 16)
     constexpr int kConsumerThreads = NWARPS * 32;
-    constexpr int kPStride = 128 * NSETS + 4;          // floats per warp in a partial-sum slot (padded against bank conflicts)
+    constexpr int kPStride = 128 * NM + 4;             // floats per warp in a partial-sum slot (padded against bank conflicts)
     static_assert(GPW % 8 == 0, "a warp takes whole steps");
     static_assert(kSlots <= kMaxSlots, "partial-sum ring");
 
@@ -161,10 +174,11 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int spt = static_cast<int>(K / kStepK);      // steps per tile (K % 256 == 0)
     const int sp = spt / nphases;                      // steps per tile and phase
-    const Smem L = smem_layout(nstages, static_cast<uint32_t>(sp) * 8u, NSETS, NWARPS);
+    const Smem L = smem_layout(nstages, static_cast<uint32_t>(sp) * 8u, NM, NL, NWARPS);
     uint8_t* stages = smem;
     uint8_t* xs = smem + L.x_off;
     float* sxs = reinterpret_cast<float*>(smem + L.sx_off);
+    uint8_t* flg = smem + L.flag_off;
     float* partial = reinterpret_cast<float*>(smem + L.partial_off);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.misc_off);
     uint64_t* empty = full + kMaxStages;
@@ -176,6 +190,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
     const bool prepared = (flags & kFlagPrepared) != 0;
+    const int ring_slots = nstages / kGroups;          // stage slots per warp group (nstages >= kGroups)
 
     pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
     if (threadIdx.x == NWARPS * 32) {   // the producer thread: start fetching both descriptors now
@@ -217,18 +232,28 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (prepared) fence_proxy_async_all();      // the planes were written through the generic proxy
             };
             auto copy_planes = [&](int ph) {
-                // digit planes and group scales of this phase: two contiguous ranges, in pieces of <= 32 KiB
-                const uint32_t dbytes = static_cast<uint32_t>(sp) * 8u * 256u * NSETS;
-                const uint32_t sbytes = static_cast<uint32_t>(sp) * 8u * 16u * NSETS;
+                // digit planes, group scales and flags of this phase: contiguous ranges, in pieces of <= 32 KiB
+                const uint32_t pgroups = static_cast<uint32_t>(sp) * 8u;
+                const uint32_t dbytes = pgroups * 256u * NSETS, sbytes = pgroups * 32u * NSETS, fbytes = NL ? pgroups * 16u : 0u;
+                const size_t groups_all = static_cast<size_t>(K / 32);
                 const uint8_t* dsrc = planes + static_cast<size_t>(ph) * dbytes;
-                const uint8_t* ssrc = planes + static_cast<size_t>(K / 32) * 256u * NSETS + static_cast<size_t>(ph) * sbytes;
-                mbar_arrive_expect_tx(xfull, dbytes + sbytes);
+                const uint8_t* ssrc = planes + groups_all * 256u * NSETS + static_cast<size_t>(ph) * sbytes;
+                const uint8_t* fsrc = planes + groups_all * (256u + 32u) * NSETS + static_cast<size_t>(ph) * fbytes;
+                mbar_arrive_expect_tx(xfull, dbytes + sbytes + fbytes);
                 for (uint32_t off = 0; off < dbytes; off += 32768u)
                     bulk_copy_g2s(xs + off, dsrc + off, (dbytes - off < 32768u) ? dbytes - off : 32768u, xfull);
-                bulk_copy_g2s(sxs, ssrc, sbytes, xfull);
+                for (uint32_t off = 0; off < sbytes; off += 32768u)
+                    bulk_copy_g2s(reinterpret_cast<uint8_t*>(sxs) + off, ssrc + off, (sbytes - off < 32768u) ? sbytes - off : 32768u, xfull);
+                if (NL) bulk_copy_g2s(flg, fsrc, fbytes, xfull);
             };
             if (!(flags & kFlagEarlyWeights)) dependency_sync();
-            uint32_t seq = 0;
+            // Every warp group has its own part of the stage ring (ring_slots consecutive slots) and its own
+            // stage counter: a slot is then always filled for, and waited on by, the same group, use after
+            // use, so a waiting warp can never be a whole barrier phase ahead of the slot it looks at.
+            uint32_t gseq[kGroups];
+#pragma unroll
+            for (int q = 0; q < kGroups; ++q) gseq[q] = 0;
+            uint32_t tcount = 0;
             bool ok = true, planes_sent = false;
             for (int ph = 0; ph < nphases && ok; ++ph) {
                 if (ph > 0) {
@@ -238,16 +263,22 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                     copy_planes(ph);
                 }
-                for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                    for (int c0 = 0; c0 < sp; c0 += kStepsPerStage, ++seq) {
-                        if (ph == 0 && !planes_sent && seq == static_cast<uint32_t>(nstages)) {
-                            // the ring is full: nothing more to request early
+                for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
+                    const int q = tcount % kGroups;
+                    for (int c0 = 0; c0 < sp; c0 += kStepsPerStage) {
+                        uint32_t seq = 0;
+#pragma unroll
+                        for (int qq = 0; qq < kGroups; ++qq)
+                            if (qq == q) seq = gseq[qq]++;
+                        if (ph == 0 && !planes_sent && seq >= static_cast<uint32_t>(ring_slots)) {
+                            // this group's part of the ring is full: nothing more to request early, and the wait
+                            // below needs consumers that have their activations
                             dependency_sync();
                             if (prepared) copy_planes(0);
                             planes_sent = true;
                         }
-                        const int st = seq % nstages;
-                        const uint32_t par = (seq / nstages) & 1u;
+                        const int st = q * ring_slots + static_cast<int>(seq % ring_slots);
+                        const uint32_t par = (seq / ring_slots) & 1u;
                         if (!mbar_wait(&empty[st], par ^ 1u)) {
                             report(kDevErrEmptyWait, seq);
                             ok = false;
@@ -274,7 +305,6 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         return;
     }
 
-    const int stages_per_tile = (sp + kStepsPerStage - 1) / kStepsPerStage;
     const int64_t my_tiles = (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;      // per phase
 
     if (warp == NWARPS + 1) {
@@ -298,7 +328,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 // bits every run): lane L owns the float4 every consumer lane L wrote, so these are
                 // conflict-free 128-bit reads.  The sum goes back into the first warp's part of the slot.
 #pragma unroll
-                for (int s = 0; s < NSETS; ++s) {
+                for (int s = 0; s < NM; ++s) {
                     float4 sum = *reinterpret_cast<const float4*>(pbuf + (s * 32 + lane) * 4);
 #pragma unroll
                     for (int w = 1; w < WPT; ++w) {
@@ -313,8 +343,10 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const int r = p & 15, m = p >> 4;
                     const int gg = r & 7, hi = r >> 3;
                     float acc = 0.0f, weight = 1.0f;
-                    for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
-                        const int col = (m * ndigits + j) * colmul, set = col >> 3, cc = col & 7;
+#pragma unroll
+                    for (int j = 3 - kDigitsOut; j < 3; ++j, weight *= 256.0f) {
+                        int set, cc;
+                        digit_slot(kMode, NM, m, j, &set, &cc);
                         const float v = pbuf[(set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1)];
                         acc = __fmaf_rn(weight, v, acc);
                     }
@@ -369,7 +401,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
             const float4 b = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
             const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            convert_groups<kOrderNibble>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, NSETS, colmul, 0.0625f, xs, sxs);
+            convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, kMode, NM, NSETS, 0.0625f, xs, sxs, flg);
         }
         named_barrier_sync(1, kConsumerThreads);
     }
@@ -385,17 +417,14 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     for (int i = 0; i < 4; ++i) lm_off[i] = lm_row * 128 + (((2 * i + lm_sel) ^ (lane & 7)) << 4);
     const uint32_t stages_u32 = smem_u32(stages);
 
-    uint32_t seq = 0, tcount = 0;
+    uint32_t seq = 0, tcount = 0;         // seq: stages of THIS group so far
     for (int ph = 0; ph < nphases; ++ph) {
         if (prepared && alive && !mbar_wait(xfull, ph & 1u)) {
             report(kDevErrFullWait, 0x400000u | ph);
             alive = false;
         }
         for (int64_t ti = 0; ti < my_tiles; ++ti, ++tcount) {
-            if (static_cast<int>(tcount % kGroups) != my_group) {       // another group's tile
-                seq += stages_per_tile;
-                continue;
-            }
+            if (static_cast<int>(tcount % kGroups) != my_group) continue;       // another group's tile
             float total[NSETS][4];
 #pragma unroll
             for (int s = 0; s < NSETS; ++s)
@@ -403,8 +432,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
             for (int c0 = 0; c0 < sp; c0 += kStepsPerStage, ++seq) {
-                const int st = seq % nstages;
-                const uint32_t par = (seq / nstages) & 1u;
+                const int st = my_group * ring_slots + static_cast<int>(seq % ring_slots);
+                const uint32_t par = (seq / ring_slots) & 1u;
                 if (alive && !mbar_wait(&full[st], par)) {
                     report(kDevErrFullWait, seq);
                     alive = false;
@@ -419,53 +448,79 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const uint8_t* sbox = stages + st * kStageBytes + kStageW + (step_in_stage >> 2) * kSChunkBytes + g * 128;
                         const int su = (step_in_stage & 3) * 2;
                         const uint8_t* xg = xs + static_cast<size_t>(step) * 8 * (256 * NSETS);
-                        const float* sg = sxs + (static_cast<size_t>(step) * 8 * 4 + t) * NSETS;      // this lane's group scales
+                        const float* sg = sxs + (static_cast<size_t>(step) * 8 * 4 + t) * (2 * NSETS);   // this lane's group scales
+                        const uint8_t* fg = flg + static_cast<size_t>(step) * 8 * 16;
+                        constexpr int BG = NM <= 2 ? 4 : 2;              // 32-k groups whose MMAs are in flight together
 #pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {                 // four 32-k groups at a time
+                        for (int hb = 0; hb < 8 / BG; ++hb) {
+                            const int hh = (hb * BG) >> 2;               // which half of the step: 16-byte unit of the scales
                             const float4 sc_lo = *reinterpret_cast<const float4*>(sbox + (((su + hh) ^ g) << 4));          // scales of row g
                             const float4 sc_hi = *reinterpret_cast<const float4*>(sbox + 1024 + (((su + hh) ^ g) << 4));   // and of row g + 8
-                            uint32_t wv[2][4];                           // [pair of groups]{rows 0-7, rows 8-15} x 2
-                            ldmatrix_x4(wv[0], wbox + lm_off[2 * hh]);
-                            ldmatrix_x4(wv[1], wbox + lm_off[2 * hh + 1]);
-                            // All MMAs of the four groups are issued before any of their results is used, so that the
-                            // tensor-pipe latency of one group is covered by the issue of the others.
-                            int d[4][NSETS][4];
-                            float sxv[4][NSETS];                         // activation scales: columns 2t, 2t+1 of every set
+                            uint32_t wv[BG / 2][4];                      // [pair of groups]{rows 0-7, rows 8-15} x 2
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
+                            for (int pq = 0; pq < BG / 2; ++pq) ldmatrix_x4(wv[pq], wbox + lm_off[(hb * BG) / 2 + pq]);
+                            // The main-set MMAs of these groups are issued before any of their results is used, so
+                            // that the tensor-pipe latency of one group is covered by the issue of the others.
+                            int d[BG][NM][4];
+                            float2 sxv[BG][NM];                          // activation scales of columns 2t, 2t+1 of every main set
+                            uint32_t av[BG][4];
+#pragma unroll
+                            for (int i = 0; i < BG; ++i) {
+                                const int gi = hb * BG + i;              // group within the step
                                 const uint32_t w_lo = wv[i >> 1][(i & 1) * 2], w_hi = wv[i >> 1][(i & 1) * 2 + 1];
-                                uint32_t a[4];
-                                a[0] = (w_lo << 4) & 0xF0F0F0F0u;        // row g,   k = 8t + {0,2,4,6}: 16 * code as s8
-                                a[1] = (w_hi << 4) & 0xF0F0F0F0u;        // row g+8
-                                a[2] = w_lo & 0xF0F0F0F0u;               // row g,   k = 8t + {1,3,5,7}
-                                a[3] = w_hi & 0xF0F0F0F0u;               // row g+8
-                                const uint8_t* xgi = xg + (4 * hh + i) * (256 * NSETS);
-                                load_scales<NSETS>(sxv[i], sg + (4 * hh + i) * (4 * NSETS));
+                                av[i][0] = (w_lo << 4) & 0xF0F0F0F0u;    // row g,   k = 8t + {0,2,4,6}: 16 * code as s8
+                                av[i][1] = (w_hi << 4) & 0xF0F0F0F0u;    // row g+8
+                                av[i][2] = w_lo & 0xF0F0F0F0u;           // row g,   k = 8t + {1,3,5,7}
+                                av[i][3] = w_hi & 0xF0F0F0F0u;           // row g+8
+                                const uint8_t* xgi = xg + gi * (256 * NSETS);
+                                const float* sgi = sg + gi * (8 * NSETS);
 #pragma unroll
-                                for (int pr = 0; pr < (NSETS + 1) / 2; ++pr) {
-                                    if (2 * pr + 1 < NSETS) {            // a full pair of sets: one 128-bit load per lane
-                                        const uint4 q = *reinterpret_cast<const uint4*>(xgi + pr * 512 + lane * 16);
-                                        mma_s8s8_16832_magic(d[i][2 * pr], a, q.x, q.y);
-                                        mma_s8s8_16832_magic(d[i][2 * pr + 1], a, q.z, q.w);
-                                    } else {
-                                        const uint2 q = *reinterpret_cast<const uint2*>(xgi + pr * 512 + lane * 8);
-                                        mma_s8s8_16832_magic(d[i][2 * pr], a, q.x, q.y);
+                                for (int s2 = 0; s2 < NM; ++s2) sxv[i][s2] = *reinterpret_cast<const float2*>(sgi + 2 * s2);
+#pragma unroll
+                                for (int s2 = 0; s2 < NM; ++s2) {
+                                    if ((s2 & 1) == 0 && s2 + 1 < NM) {  // two main sets side by side: one 128-bit load per lane
+                                        const uint4 q = *reinterpret_cast<const uint4*>(xgi + (s2 >> 1) * 512 + lane * 16);
+                                        mma_s8s8_16832_magic(d[i][s2], av[i], q.x, q.y);
+                                        mma_s8s8_16832_magic(d[i][s2 + 1], av[i], q.z, q.w);
+                                    } else if ((s2 & 1) == 0) {
+                                        const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, s2, lane));
+                                        mma_s8s8_16832_magic(d[i][s2], av[i], q.x, q.y);
                                     }
                                 }
                             }
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float s_lo = i == 0 ? sc_lo.x : i == 1 ? sc_lo.y : i == 2 ? sc_lo.z : sc_lo.w;
-                                const float s_hi = i == 0 ? sc_hi.x : i == 1 ? sc_hi.y : i == 2 ? sc_hi.z : sc_hi.w;
+                            for (int i = 0; i < BG; ++i) {
+                                const int gi = hb * BG + i, gq = gi & 3;
+                                const float s_lo = gq == 0 ? sc_lo.x : gq == 1 ? sc_lo.y : gq == 2 ? sc_lo.z : sc_lo.w;
+                                const float s_hi = gq == 0 ? sc_hi.x : gq == 1 ? sc_hi.y : gq == 2 ? sc_hi.z : sc_hi.w;
 #pragma unroll
-                                for (int s = 0; s < NSETS; ++s) {
+                                for (int s2 = 0; s2 < NM; ++s2) {
                                     // d holds 12582912.0f + 16 * (exact group sum) as fp32 bits
-                                    const float f_lo = __fmul_rn(s_lo, sxv[i][s]), f_hi = __fmul_rn(s_hi, sxv[i][s]);
-                                    total[s][0] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s][0]), kMagicF), total[s][0]);
-                                    total[s][2] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s][2]), kMagicF), total[s][2]);
-                                    if (!HALF) {
-                                        total[s][1] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s][1]), kMagicF), total[s][1]);
-                                        total[s][3] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s][3]), kMagicF), total[s][3]);
+                                    const float f_lo = __fmul_rn(s_lo, sxv[i][s2].x), f_hi = __fmul_rn(s_hi, sxv[i][s2].x);
+                                    total[s2][0] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s2][0]), kMagicF), total[s2][0]);
+                                    total[s2][2] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s2][2]), kMagicF), total[s2][2]);
+                                    if (kMode == 2) {                    // columns 2t and 2t+1 belong to the same batch row: one scale
+                                        total[s2][1] = __fmaf_rn(f_lo, __fsub_rn(__int_as_float(d[i][s2][1]), kMagicF), total[s2][1]);
+                                        total[s2][3] = __fmaf_rn(f_hi, __fsub_rn(__int_as_float(d[i][s2][3]), kMagicF), total[s2][3]);
+                                    } else if (kMode == 1) {
+                                        const float e_lo = __fmul_rn(s_lo, sxv[i][s2].y), e_hi = __fmul_rn(s_hi, sxv[i][s2].y);
+                                        total[s2][1] = __fmaf_rn(e_lo, __fsub_rn(__int_as_float(d[i][s2][1]), kMagicF), total[s2][1]);
+                                        total[s2][3] = __fmaf_rn(e_hi, __fsub_rn(__int_as_float(d[i][s2][3]), kMagicF), total[s2][3]);
+                                    }
+                                }
+                                // low digits: only where a row of the set flagged this group (rare: one value dominating its group)
+#pragma unroll
+                                for (int l = 0; l < NL; ++l) {
+                                    const uint2 fl = *reinterpret_cast<const uint2*>(fg + gi * 16 + l * 8);
+                                    if ((fl.x | fl.y) != 0u) {           // the same for every lane of the warp
+                                        const uint2 q = *reinterpret_cast<const uint2*>(xg + gi * (256 * NSETS) + plane_offset(0, NSETS, NM + l, lane));
+                                        const float2 sl = *reinterpret_cast<const float2*>(sg + gi * (8 * NSETS) + 2 * (NM + l));
+                                        int dl[4];
+                                        mma_s8s8_16832_magic(dl, av[i], q.x, q.y);
+                                        total[NM + l][0] = __fmaf_rn(__fmul_rn(s_lo, sl.x), __fsub_rn(__int_as_float(dl[0]), kMagicF), total[NM + l][0]);
+                                        total[NM + l][1] = __fmaf_rn(__fmul_rn(s_lo, sl.y), __fsub_rn(__int_as_float(dl[1]), kMagicF), total[NM + l][1]);
+                                        total[NM + l][2] = __fmaf_rn(__fmul_rn(s_hi, sl.x), __fsub_rn(__int_as_float(dl[2]), kMagicF), total[NM + l][2]);
+                                        total[NM + l][3] = __fmaf_rn(__fmul_rn(s_hi, sl.y), __fsub_rn(__int_as_float(dl[3]), kMagicF), total[NM + l][3]);
                                     }
                                 }
                             }
@@ -488,9 +543,23 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     report(kDevErrEmptyWait, 0x800000u | tcount);
                     alive = false;
                 }
+                // Low-digit sums join the accumulator of digit 1 of their batch row (the main scales carry the
+                // factor 256 between the digits).  Low set l holds row 8l + 2t + e in column 2t + e of lane t; that
+                // row's digit-1 accumulator is column 2t' of main set (8l + 2t + e) / 4 in lane t' = 2 (t & 1) + e.
+#pragma unroll
+                for (int s = 0; s < NM && NL > 0; ++s) {
+                    const int l = s >> 1;
+                    const int src = (lane & ~3) | (2 * (s & 1) + (t >> 1));
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float v0 = __shfl_sync(0xffffffffu, total[NM + (l < NL ? l : 0)][0 + 2 * h], src);
+                        const float v1 = __shfl_sync(0xffffffffu, total[NM + (l < NL ? l : 0)][1 + 2 * h], src);
+                        total[s][2 * h] += (t & 1) ? v1 : v0;
+                    }
+                }
                 float* pbuf = partial + slot * (WPT * kPStride) + wj * kPStride;
 #pragma unroll
-                for (int s = 0; s < NSETS; ++s)
+                for (int s = 0; s < NM; ++s)
                     *reinterpret_cast<float4*>(pbuf + (s * 32 + lane) * 4) =
                         make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
                 __syncwarp();
@@ -529,9 +598,9 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
         const int sp = spt / nph;
         if (nph > 1 && (sp % kStepsPerStage) != 0) break;
         if (nph > 1 && !have_workspace) break;             // phases need the planes in global memory
-        const int min_stages = nph > 1 ? 3 : 2;
+        const int min_stages = 2;                          // one slot for each of the two warp groups
         for (int st = kMaxStages; st >= min_stages; --st) {
-            const Smem S = smem_layout(st, static_cast<uint32_t>(sp) * 8u, p->L.nsets, p->nwarps);
+            const Smem S = smem_layout(st, static_cast<uint32_t>(sp) * 8u, p->L.nmain, p->L.nlow, p->nwarps);
             if (S.total + 1024 <= static_cast<uint32_t>(limit)) {
                 p->nstages = st;
                 p->nphases = nph;
@@ -556,30 +625,30 @@ int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
     return 0;
 }
 
-template <int NSETS, int NWARPS, bool HALF>
+template <int NM, int NL, int NWARPS, bool HALF>
 int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                    bool planes_ready) {
     static SmemOptIn optin;
-    auto kernel = gemv_int4_nk_kernel<NSETS, NWARPS, HALF>;
+    auto kernel = gemv_int4_nk_kernel<NM, NL, NWARPS, HALF>;
     SGQ_CUDA_TRY(optin.ensure(kernel, NWARPS == 8 ? kCompactSmem : kSmemLimit));
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
     const bool overlap = stream_overlap_enabled();
     if (p.pre && !planes_ready) {
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap,
-                                   a.x, a.K, p.L.ndigits, p.L.nsets, p.L.colmul, static_cast<uint8_t*>(a.workspace)));
+                                   a.x, a.K, p.L.mode, p.L.nmain, p.L.nsets, static_cast<uint8_t*>(a.workspace)));
     }
     const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
-                               map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), p.L.ndigits, p.L.colmul, a.K, a.N, a.ldy,
-                               p.nstages, p.nphases, flags, a.peers));
+                               map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages, p.nphases, flags,
+                               a.peers));
     return SGQ_OK;
 }
 
-template <int NSETS, bool HALF>
+template <int NM, int NL, bool HALF>
 int launch_nsets(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                  bool planes_ready) {
-    return p.nwarps == 8 ? launch_variant<NSETS, 8, HALF>(a, p, map_w, map_s, grid, planes_ready)
-                         : launch_variant<NSETS, 16, HALF>(a, p, map_w, map_s, grid, planes_ready);
+    return p.nwarps == 8 ? launch_variant<NM, NL, 8, HALF>(a, p, map_w, map_s, grid, planes_ready)
+                         : launch_variant<NM, NL, 16, HALF>(a, p, map_w, map_s, grid, planes_ready);
 }
 
 bool shape_ok(int64_t M, int64_t K, int64_t N) {
@@ -622,7 +691,7 @@ size_t gemv_prepared_bytes(int64_t M, int64_t K) {
 int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s) {
     const PreparedLayout L = prepared_layout(M, K);
     SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M)), dim3(kPrepThreads), 0, s,
-                               stream_overlap_enabled(), x, K, L.ndigits, L.nsets, L.colmul, static_cast<uint8_t*>(prepared)));
+                               stream_overlap_enabled(), x, K, L.mode, L.nmain, L.nsets, static_cast<uint8_t*>(prepared)));
     return SGQ_OK;
 }
 
@@ -681,12 +750,13 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     const int64_t ntiles = ceil_div(a.N, kRows);
     const int64_t ctas = static_cast<int64_t>(sm_count()) * (p.nwarps == 8 ? 2 : 1);
     const int grid = static_cast<int>(ntiles < ctas ? ntiles : ctas);
-    if (p.L.colmul == 2) return launch_nsets<1, true>(a, p, map_w, map_s, grid, planes_ready);
-    switch (p.L.nsets) {
-        case 1: return launch_nsets<1, false>(a, p, map_w, map_s, grid, planes_ready);
-        case 2: return launch_nsets<2, false>(a, p, map_w, map_s, grid, planes_ready);
-        case 3: return launch_nsets<3, false>(a, p, map_w, map_s, grid, planes_ready);
-        default: return launch_nsets<4, false>(a, p, map_w, map_s, grid, planes_ready);
+    if (p.L.mode == 0) return launch_nsets<1, 0, true>(a, p, map_w, map_s, grid, planes_ready);
+    if (p.L.mode == 1) return launch_nsets<1, 0, false>(a, p, map_w, map_s, grid, planes_ready);
+    switch (p.L.nmain) {                 // three rows or more: ceil(M / 4) main sets, ceil(M / 8) low sets
+        case 1: return launch_nsets<1, 1, false>(a, p, map_w, map_s, grid, planes_ready);
+        case 2: return launch_nsets<2, 1, false>(a, p, map_w, map_s, grid, planes_ready);
+        case 3: return launch_nsets<3, 2, false>(a, p, map_w, map_s, grid, planes_ready);
+        default: return launch_nsets<4, 2, false>(a, p, map_w, map_s, grid, planes_ready);
     }
 }
 }  // namespace
@@ -697,9 +767,9 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
 // owns every allocation, or a serving loop that must not touch the allocator (and its locks)
 // between tokens.  For them the activation planes live in this file-scope array instead of a
 // caller workspace.  Every GPU that loads the library reserves these bytes until the process
-// exits.  The size bounds the batches this entry point accepts: (K/32) * sets * 272 bytes with
-// sets = ceil(M/4), e.g. K = 8192 with M = 16.
-constexpr size_t kStaticPlanesBytes = 320 * 1024;
+// exits.  The size bounds the batches this entry point accepts: (K/32) * (sets * 288 + 16) bytes
+// with sets = ceil(M/4) + ceil(M/8), e.g. K = 4096 with M = 16 or K = 8192 with M = 8.
+constexpr size_t kStaticPlanesBytes = 448 * 1024;
 static __device__ __align__(256) unsigned char g_static_planes[kStaticPlanesBytes];
 
 namespace {

@@ -9,8 +9,9 @@
 //     steps; the bytes go to the tensor core as they are (mma.sync m16n8k32 s8 x s8 -> s32), with
 //     no unpacking and no offset;
 //   * there is no per-group weight scale; the exact int32 sum of every 32-k group is multiplied by
-//     the activation scale of that group (gemv_prepare.cuh) and added up in fp32, the weight scale
-//     is applied once per output;
+//     the activation scale of that group (gemv_prepare.cuh: 24-bit fixed point per group, the low
+//     digit in column sets of its own that are skipped where it cannot matter) and added up in fp32,
+//     the weight scale is applied once per output;
 //   * the activation digit planes and group scales (laid out for the natural k order of an int8 B
 //     fragment) are written once by a conversion kernel and stream through the same pipeline
 //     stages as the weights, 32 groups at a time, from L2.  They are never resident as a whole,
@@ -89,18 +90,29 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
                  : "r"(smem_addr));
 }
 
+// total += (exact int32 sums of one 32-k group) * (activation scales of columns 2t and 2t+1)
+__device__ __forceinline__ void accumulate_group(float (&total)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, float2 sx) {
+    int d[4];
+    mma_s8s8_16832_magic(d, a, b0, b1);
+    // d holds 12582912.0f + (exact group sum) as fp32 bits
+    total[0] = __fmaf_rn(sx.x, __fsub_rn(__int_as_float(d[0]), kMagicF), total[0]);
+    total[1] = __fmaf_rn(sx.y, __fsub_rn(__int_as_float(d[1]), kMagicF), total[1]);
+    total[2] = __fmaf_rn(sx.x, __fsub_rn(__int_as_float(d[2]), kMagicF), total[2]);
+    total[3] = __fmaf_rn(sx.y, __fsub_rn(__int_as_float(d[3]), kMagicF), total[3]);
+}
+
 // Digit planes and group scales for the int8 kernel (gemv_prepare.cuh, natural k order): one CTA per
 // row, one pass.  K is a multiple of 128: in the last warp-wide call of a row the lanes beyond the end
 // pass zeros and store nothing.
-__global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float* __restrict__ x, int64_t K, int ndigits, int nsets,
-                                                                   int colmul, uint8_t* __restrict__ planes) {
+__global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float* __restrict__ x, int64_t K, int mode, int nmain,
+                                                                   int nsets, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
-    const int m = blockIdx.x;
+    const int m = blockIdx.x, M = gridDim.x;
     const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
     const int chunks = static_cast<int>(K / 8);
     const int padded = (chunks + 31) & ~31;
-    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(K / 32) * nsets * 256);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
     for (int c = threadIdx.x; c < padded; c += kPrepThreads) {
         const bool in = c < chunks;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -108,7 +120,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float*
             const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
-        convert_groups<kOrderNatural>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 1.0f, planes, scales, in);
+        convert_groups<kOrderNatural>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 1.0f, pp.digits, pp.scales, pp.flags, in);
     }
 }
 
@@ -116,30 +128,33 @@ struct Smem {
     uint32_t stage_bytes, partial_off, misc_off, total;
 };
 
-__host__ __device__ inline Smem smem_layout(int nstages, int nsets) {
+__host__ __device__ inline Smem smem_layout(int nstages, int nmain, int nlow) {
     Smem s;
-    s.stage_bytes = kStageW + kGroupsPerStage * (256u + 16u) * nsets;   // weights, digits, group scales
+    const uint32_t nsets = nmain + nlow;
+    s.stage_bytes = kStageW + kGroupsPerStage * ((256u + 32u) * nsets + (nlow ? 16u : 0u));   // weights, digits, group scales, flags
     s.stage_bytes = (s.stage_bytes + 1023u) & ~1023u;      // the swizzled weight box of every stage starts on a 1024-byte boundary
     s.partial_off = nstages * s.stage_bytes;
-    s.misc_off = s.partial_off + 2u * kWarps * (512u * nsets + 16u);      // two slots of per-warp fp32 partial sums (padded)
+    s.misc_off = s.partial_off + 2u * kWarps * (512u * nmain + 16u);      // two slots of per-warp fp32 partial sums (padded)
     s.total = s.misc_off + 2u * kMaxStages * 8u + 16u;
     return s;
 }
 
-template <int NSETS>
+template <int NM, int NL, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __restrict__ planes, const float* __restrict__ wscales,
-                    int scale_per_row, const float* __restrict__ bias, float* __restrict__ y, int M, int ndigits, int colmul, int64_t K,
-                    int64_t N, int64_t ldy, int nstages) {
+                    int scale_per_row, const float* __restrict__ bias, float* __restrict__ y, int M, int64_t K, int64_t N, int64_t ldy,
+                    int nstages) {
+    constexpr int NSETS = NM + NL;
+    constexpr int kDigitsOut = NL > 0 ? 2 : 3;
     extern __shared__ uint8_t smem_raw[];
     // aligned by pointer arithmetic on the shared array itself: a round trip through an integer would make the
     // compiler lose the address space and emit generic loads for every shared-memory access below
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const Smem L = smem_layout(nstages, NSETS);
+    const Smem L = smem_layout(nstages, NM, NL);
     float* partial = reinterpret_cast<float*>(smem + L.partial_off);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.misc_off);
     uint64_t* empty = full + kMaxStages;
-    constexpr int kPStride = 128 * NSETS + 4;       // floats per warp in a partial-sum slot
+    constexpr int kPStride = 128 * NM + 4;          // floats per warp in a partial-sum slot
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
@@ -177,15 +192,20 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                     const int g0 = c0 * 4;                                              // first digit group of the stage
                     const int ng = (groups_total - g0 < kGroupsPerStage) ? groups_total - g0 : kGroupsPerStage;
                     const uint32_t pbytes = static_cast<uint32_t>(ng) * 256u * NSETS;
-                    const uint32_t sbytes = static_cast<uint32_t>(ng) * 16u * NSETS;                  // group scales of the stage
+                    const uint32_t sbytes = static_cast<uint32_t>(ng) * 32u * NSETS;                  // group scales of the stage
+                    const uint32_t fbytes = NL ? static_cast<uint32_t>(ng) * 16u : 0u;                // and its low-digit flags
                     // steps past K/128 are out of range in the third dimension: zero-filled, still counted
-                    mbar_arrive_expect_tx(&full[st], kStageW + pbytes + sbytes);
+                    mbar_arrive_expect_tx(&full[st], kStageW + pbytes + sbytes + fbytes);
                     uint8_t* sw = smem + st * L.stage_bytes;
                     tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
                     bulk_copy_g2s(sw + kStageW, planes + static_cast<size_t>(g0) * 256u * NSETS, pbytes, &full[st]);
                     bulk_copy_g2s(sw + kStageW + kGroupsPerStage * 256u * NSETS,
-                                  planes + static_cast<size_t>(groups_total) * 256u * NSETS + static_cast<size_t>(g0) * 16u * NSETS, sbytes,
+                                  planes + static_cast<size_t>(groups_total) * 256u * NSETS + static_cast<size_t>(g0) * 32u * NSETS, sbytes,
                                   &full[st]);
+                    if (NL)
+                        bulk_copy_g2s(sw + kStageW + kGroupsPerStage * (256u + 32u) * NSETS,
+                                      planes + static_cast<size_t>(groups_total) * (256u + 32u) * NSETS + static_cast<size_t>(g0) * 16u, fbytes,
+                                      &full[st]);
                 }
             }
         }
@@ -226,36 +246,33 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                 const uint32_t wbox = smem_u + st * L.stage_bytes + warp * (kRows * 128);
                 const uint8_t* xg = smem + st * L.stage_bytes + kStageW + (warp * 4) * (256 * NSETS);
                 const float* sg = reinterpret_cast<const float*>(smem + st * L.stage_bytes + kStageW + kGroupsPerStage * 256 * NSETS) +
-                                  ((warp * 4) * 4 + t) * NSETS;                           // this lane's group scales
+                                  ((warp * 4) * 4 + t) * (2 * NSETS);                     // this lane's group scales
+                const uint8_t* fg = smem + st * L.stage_bytes + kStageW + kGroupsPerStage * (256 + 32) * NSETS + (warp * 4) * 16;
                 uint32_t a[4][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) ldmatrix_x4(a[i], wbox + lm_off[i]);    // rows g / g+8, k = 32i + 4t.. and 32i + 16 + 4t..
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint8_t* xgi = xg + i * (256 * NSETS);
-                    float sxv[NSETS];                                               // activation scales: columns 2t, 2t+1 of every set
-                    load_scales<NSETS>(sxv, sg + i * (4 * NSETS));
+                    const float* sgi = sg + i * (8 * NSETS);
 #pragma unroll
-                    for (int pr = 0; pr < (NSETS + 1) / 2; ++pr) {
-                        uint32_t xb[4];
-                        if (2 * pr + 1 < NSETS) {                    // a full pair of sets: one 128-bit load per lane
-                            const uint4 q = *reinterpret_cast<const uint4*>(xgi + pr * 512 + lane * 16);
-                            xb[0] = q.x; xb[1] = q.y; xb[2] = q.z; xb[3] = q.w;
-                        } else {
-                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + pr * 512 + lane * 8);
-                            xb[0] = q.x; xb[1] = q.y; xb[2] = 0; xb[3] = 0;
+                    for (int s2 = 0; s2 < NM; ++s2) {
+                        if ((s2 & 1) == 0 && s2 + 1 < NM) {          // two main sets side by side: one 128-bit load per lane
+                            const uint4 q = *reinterpret_cast<const uint4*>(xgi + (s2 >> 1) * 512 + lane * 16);
+                            accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
+                            accumulate_group(total[s2 + 1], a[i], q.z, q.w, *reinterpret_cast<const float2*>(sgi + 2 * s2 + 2));
+                        } else if ((s2 & 1) == 0) {
+                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, s2, lane));
+                            accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
                         }
+                    }
+                    // low digits: only where a row of the set flagged this group (rare: one value dominating its group)
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int s = 2 * pr + h;
-                            if (s < NSETS) {
-                                int d[4];
-                                mma_s8s8_16832_magic(d, a[i], xb[2 * h], xb[2 * h + 1]);
-                                // d holds 12582912.0f + (exact group sum) as fp32 bits
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    total[s][e] = __fmaf_rn(sxv[s], __fsub_rn(__int_as_float(d[e]), kMagicF), total[s][e]);
-                            }
+                    for (int l = 0; l < NL; ++l) {
+                        const uint2 fl = *reinterpret_cast<const uint2*>(fg + i * 16 + l * 8);
+                        if ((fl.x | fl.y) != 0u) {                   // the same for every lane of the warp
+                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, NM + l, lane));
+                            accumulate_group(total[NM + l], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * (NM + l)));
                         }
                     }
                 }
@@ -269,16 +286,32 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
         }
 
         // ---- tile epilogue: partial sums -> shared memory, one barrier, one output per thread ----
+        // Low-digit sums join the accumulator of digit 1 of their batch row (the main scales carry the factor
+        // 256 between the digits).  Low set l holds row 8l + 2t + e in column 2t + e of lane t; that row's
+        // digit-1 accumulator is column 2t' of main set (8l + 2t + e) / 4 in lane t' = 2 (t & 1) + e.
+#pragma unroll
+        for (int s = 0; s < NM && NL > 0; ++s) {
+            const int l = s >> 1;
+            const int src = (lane & ~3) | (2 * (s & 1) + (t >> 1));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float v0 = __shfl_sync(0xffffffffu, total[NM + (l < NL ? l : 0)][0 + 2 * h], src);
+                const float v1 = __shfl_sync(0xffffffffu, total[NM + (l < NL ? l : 0)][1 + 2 * h], src);
+                total[s][2 * h] += (t & 1) ? v1 : v0;
+            }
+        }
         float* pslot = partial + (tcount & 1u) * (kWarps * kPStride);
 #pragma unroll
-        for (int s = 0; s < NSETS; ++s)
+        for (int s = 0; s < NM; ++s)
             *reinterpret_cast<float4*>(pslot + warp * kPStride + (s * 32 + lane) * 4) =
                 make_float4(total[s][0], total[s][1], total[s][2], total[s][3]);
         named_barrier_sync(1, kConsumerThreads);
         if (em < M) {
             float v = 0.0f, weight = 1.0f;
-            for (int j = 0; j < ndigits; ++j, weight *= 256.0f) {
-                const int col = (em * ndigits + j) * colmul, set = col >> 3, cc = col & 7;
+#pragma unroll
+            for (int j = 3 - kDigitsOut; j < 3; ++j, weight *= 256.0f) {
+                int set, cc;
+                digit_slot(MODE, NM, em, j, &set, &cc);
                 const float* src = pslot + (set * 32 + (er & 7) * 4 + (cc >> 1)) * 4 + (er >> 3) * 2 + (cc & 1);
                 float sum = src[0];
 #pragma unroll
@@ -298,19 +331,17 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
 }
 
 struct Plan {
-    int ndigits, nsets, colmul, nstages;
+    PreparedLayout L;
+    int nstages;
     uint32_t smem;
     size_t planes_bytes;
 };
 
 bool make_plan(int64_t M, int64_t K, Plan* p) {
-    const PreparedLayout L = prepared_layout(M, K);
-    p->ndigits = L.ndigits;
-    p->nsets = L.nsets;
-    p->colmul = L.colmul;
-    p->planes_bytes = static_cast<size_t>(K / 32) * p->nsets * (256 + 16);
+    p->L = prepared_layout(M, K);
+    p->planes_bytes = p->L.bytes;
     for (int st = kMaxStages; st >= 2; --st) {
-        const Smem S = smem_layout(st, p->nsets);
+        const Smem S = smem_layout(st, p->L.nmain, p->L.nlow);
         if (S.total + 1024 <= static_cast<uint32_t>(kSmemLimit)) {
             p->nstages = st;
             p->smem = S.total + 1024;
@@ -320,17 +351,17 @@ bool make_plan(int64_t M, int64_t K, Plan* p) {
     return false;
 }
 
-template <int NSETS>
+template <int NM, int NL, int MODE>
 int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, int grid) {
     static SmemOptIn optin;
-    auto kernel = gemv_int8_nk_kernel<NSETS>;
+    auto kernel = gemv_int8_nk_kernel<NM, NL, MODE>;
     SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
     const bool overlap = stream_overlap_enabled();
     SGQ_CUDA_TRY(launch_kernel(prepare_x_i8_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap, a.x, a.K,
-                               p.ndigits, p.nsets, p.colmul, static_cast<uint8_t*>(a.workspace)));
+                               p.L.mode, p.L.nmain, p.L.nsets, static_cast<uint8_t*>(a.workspace)));
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), p.smem, a.stream, overlap, map_w,
                                static_cast<const uint8_t*>(a.workspace), a.scales, a.scheme == SGQ_PER_ROW ? 1 : 0, a.bias, a.y,
-                               static_cast<int>(a.M), p.ndigits, p.colmul, a.K, a.N, a.ldy, p.nstages));
+                               static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages));
     return SGQ_OK;
 }
 
@@ -368,11 +399,13 @@ int launch_linear_gemv_i8(const LinearArgs& a) {
         return SGQ_ERR_CUDA;
     const int64_t ntiles = ceil_div(a.N, kRows);
     const int grid = static_cast<int>(ntiles < sm_count() ? ntiles : sm_count());
-    switch (p.nsets) {
-        case 1: return launch_variant<1>(a, p, map_w, grid);
-        case 2: return launch_variant<2>(a, p, map_w, grid);
-        case 3: return launch_variant<3>(a, p, map_w, grid);
-        default: return launch_variant<4>(a, p, map_w, grid);
+    if (p.L.mode == 0) return launch_variant<1, 0, 0>(a, p, map_w, grid);
+    if (p.L.mode == 1) return launch_variant<1, 0, 1>(a, p, map_w, grid);
+    switch (p.L.nmain) {                 // three rows or more: ceil(M / 4) main sets, ceil(M / 8) low sets
+        case 1: return launch_variant<1, 1, 2>(a, p, map_w, grid);
+        case 2: return launch_variant<2, 1, 2>(a, p, map_w, grid);
+        case 3: return launch_variant<3, 2, 2>(a, p, map_w, grid);
+        default: return launch_variant<4, 2, 2>(a, p, map_w, grid);
     }
 }
 

@@ -4,25 +4,33 @@
 // stand-alone conversion kernels, and the decoder operators that emit this format directly.
 //
 // Arithmetic.  Every 32 consecutive k of a row (the span of one INT4 weight group) have their own
-// scale: with gmax the group's absmax, q = rint(x * (Q / gmax)) with Q = 32600 (two digits) or
-// 8355000 (three digits, single-row batches), q = d0 + 256 d1 (+ 65536 d2) with every digit in
-// [-128, 127].  The kernels form exact integer dot products per digit and group and multiply them
-// by gmax / Q in fp32.  The rounding error of one activation is at most gmax / (2 Q): relative to
-// the largest of its 32 neighbours, not to the largest value of the row, so a few huge channels
-// cost the rest of the row nothing (rms error of an output <= sqrt(32) * 0.29 / Q = 5e-5 of the
-// output's own scale with two digits, whatever the distribution of the activations).  A group
-// whose absmax is NaN or Inf gets a NaN scale (the output row becomes NaN); a group whose absmax is
-// below 1e-30 contributes zero.
+// scale: with gmax the group's absmax, q = rint(x * (Q / gmax)), Q = 8355000, and
+// q = d0 + 256 d1 + 65536 d2 with every digit in [-128, 127] (24 bits below the group's absmax:
+// finer than the rounding of the reference's own fp32 chain).  The kernels form exact integer dot
+// products per digit and group and multiply them by gmax / Q in fp32.
+//   Batches of one or two rows always use all three digits.  Larger batches keep the low digit d0
+// in separate MMA column sets and skip them, group by group, where the digit cannot matter: a
+// group is flagged (its low digit is used) when one value dominates it, 32 gmax^2 > 16 sum x^2;
+// in every other group gmax < 4 rms(group), so dropping d0 (which, the digits being balanced, is a
+// round-to-nearest to 16 bits) costs at most 1.53e-5 gmax < 6.2e-5 rms(group) per activation.
+// Hence no activation distribution can push the error of an output beyond ~1e-4 of the output's
+// own scale: a few huge channels cost the rest of the row nothing.  A group whose absmax is NaN or
+// Inf gets a NaN scale (the output row becomes NaN); a group whose absmax is below 1e-30
+// contributes zero.
 //
 // Layout of a prepared buffer for M rows of K values (K % 32 == 0):
 //   digit planes  [group K/32][set pair][fragment lane 32][sets of the pair x 8 bytes]
-//   group scales  [group K/32][t 4][set] fp32: the scale of the batch row whose digits sit in
-//                 columns 2t and 2t+1 of the set (a lane of an MMA holds exactly these two columns)
-// A "set" is one group of eight B-fragment columns (one MMA); column = (m * ndigits + j) * colmul
-// for digit j of row m; colmul = 2 when all columns then still fit one set (only even columns
-// carry data and the kernels skip the odd accumulators).  With two digits a row owns columns 2t and
-// 2t+1 of its set.  Sets are stored in pairs so that a lane fetches the fragments of two sets with
-// one 128-bit load; a last unpaired set uses 8 bytes per lane.
+//   group scales  [group K/32][t 4][set][2] fp32: the scales that belong to columns 2t and 2t+1 of
+//                 the set (a lane of an MMA holds exactly these two accumulator columns)
+//   flags         [group K/32][16] bytes (three rows or more): row m's low digit is needed
+// A "set" is one group of eight B-fragment columns (one MMA).  Column of digit j of row m:
+//   one row     set 0, column 2j (only even columns carry data; the kernels skip the odd accumulators)
+//   two rows    set 0, column 3m + j
+//   more rows   d1, d2: column 2m + j - 1 counted through the `nmain` main sets (a row owns columns 2t, 2t+1
+//               of its set; the scales of these sets carry a factor 256); d0: column m counted through
+//               the `nlow` low sets that follow the main sets.
+// Sets are stored in pairs so that a lane fetches the fragments of two sets with one 128-bit load; a
+// last unpaired set uses 8 bytes per lane.
 #pragma once
 
 #include "sgq_common.cuh"
@@ -37,23 +45,46 @@ constexpr int kPreparedMaxM = 16;
 constexpr int kMagicBits = 0x4B400000;
 constexpr float kMagicF = 12582912.0f;
 
-constexpr float kDigitRange2 = 32600.0f;     // |q| <= 32639 = 127 * 257 must hold after rounding
-constexpr float kDigitRange3 = 8355000.0f;   // |q| <= 8355711 = 127 * 65793
+constexpr float kDigitRange = 8355000.0f;    // |q| <= 8355711 = 127 * 65793 must hold after rounding
 
 struct PreparedLayout {
-    int ndigits, nsets, colmul;
-    size_t digit_bytes, scale_bytes, bytes;
+    int mode;                  // 0: one row, 1: two rows, 2: three rows or more (main and low sets)
+    int nmain, nlow, nsets;    // nsets = nmain + nlow
+    int ndigits_out;           // digits a kernel recombines per output: 3, or 2 when the low digit is folded in before
+    size_t digit_bytes, scale_bytes, flag_bytes, bytes;
 };
 
 inline PreparedLayout prepared_layout(int64_t M, int64_t K) {
     PreparedLayout L;
-    L.ndigits = (M == 1) ? 3 : 2;
-    L.colmul = (M * L.ndigits <= 4) ? 2 : 1;
-    L.nsets = static_cast<int>((M * L.ndigits * L.colmul + 7) / 8);
-    L.digit_bytes = static_cast<size_t>(K / 32) * L.nsets * 256;
-    L.scale_bytes = static_cast<size_t>(K / 32) * L.nsets * 16;
-    L.bytes = L.digit_bytes + L.scale_bytes;
+    L.mode = (M <= 1) ? 0 : (M == 2 ? 1 : 2);
+    L.nmain = L.mode == 2 ? static_cast<int>((M + 3) / 4) : 1;
+    L.nlow = L.mode == 2 ? static_cast<int>((M + 7) / 8) : 0;
+    L.nsets = L.nmain + L.nlow;
+    L.ndigits_out = L.mode == 2 ? 2 : 3;
+    const size_t groups = static_cast<size_t>(K / 32);
+    L.digit_bytes = groups * L.nsets * 256;
+    L.scale_bytes = groups * L.nsets * 32;
+    L.flag_bytes = L.mode == 2 ? groups * 16 : 0;
+    L.bytes = L.digit_bytes + L.scale_bytes + L.flag_bytes;
     return L;
+}
+
+// Set and column of digit j of row m.
+__host__ __device__ inline void digit_slot(int mode, int nmain, int m, int j, int* set, int* cc) {
+    if (mode == 0) {
+        *set = 0;
+        *cc = 2 * j;
+    } else if (mode == 1) {
+        *set = 0;
+        *cc = 3 * m + j;
+    } else if (j == 0) {
+        *set = nmain + (m >> 3);
+        *cc = m & 7;
+    } else {
+        const int cm = 2 * m + j - 1;
+        *set = cm >> 3;
+        *cc = cm & 7;
+    }
 }
 
 #ifdef __CUDACC__
@@ -86,15 +117,16 @@ __device__ __forceinline__ uint32_t gather_byte(uint32_t a, uint32_t b, uint32_t
 //                 as they lie in memory.
 enum { kOrderNibble = 0, kOrderNatural = 1 };
 
-// Converts 256 consecutive k (eight 32-k groups, the first being group `group0`) of row m.  Must be
-// called by all 32 lanes of a warp together, lane l holding the 8 consecutive activations
-// k = 32 * group0 + 8 l .. + 7 in v: four neighbouring lanes share a group.  `scale_mul` is folded
-// into the stored scales (the INT4 kernel feeds its codes to the tensor core as 16 * code and
-// passes 1/16).  A lane with store == false (beyond the end of a row) passes zeros and writes nothing.
+// Converts 256 consecutive k (eight 32-k groups, the first being group `group0`) of row m of an
+// M-row batch.  Must be called by all 32 lanes of a warp together, lane l holding the 8 consecutive
+// activations k = 32 * group0 + 8 l .. + 7 in v: four neighbouring lanes share a group.
+// `scale_mul` is folded into the stored scales (the INT4 kernel feeds its codes to the tensor core
+// as 16 * code and passes 1/16).  A lane with store == false (beyond the end of a row) passes zeros
+// and writes nothing.
 template <int ORDER>
-__device__ __forceinline__ void convert_groups(const float (&v)[8], int m, size_t group0, int ndigits, int nsets, int colmul,
+__device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M, size_t group0, int mode, int nmain, int nsets,
                                                float scale_mul, uint8_t* __restrict__ digits, float* __restrict__ scales,
-                                               bool store = true) {
+                                               uint8_t* __restrict__ flags, bool store = true) {
     const int lane = threadIdx.x & 31;
     uint32_t mb = 0;
 #pragma unroll
@@ -109,7 +141,6 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, size_
         mb = o > mb ? o : mb;
     }
     const float gmax = __uint_as_float(mb);
-    const float range = (ndigits == 3) ? kDigitRange3 : kDigitRange2;
     float P, sx;
     if (mb >= 0x7F800000u) {            // NaN or Inf somewhere in the group: the output row becomes NaN
         P = 0.0f;
@@ -118,51 +149,79 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, size_
         P = 0.0f;
         sx = 0.0f;
     } else {
-        P = __fdiv_rn(range, gmax);
-        sx = __fmul_rn(__fdiv_rn(gmax, range), scale_mul);
+        P = __fdiv_rn(kDigitRange, gmax);
+        sx = __fmul_rn(__fdiv_rn(gmax, kDigitRange), scale_mul);
     }
-    if (!store) return;
     uint32_t db[8];
+    float sq = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) db[j] = digit_bytes(__float2int_rn(__fmul_rn(v[j], P)));
+    for (int j = 0; j < 8; ++j) {
+        const int q = __float2int_rn(__fmul_rn(v[j], P));
+        const float qf = static_cast<float>(q);
+        sq = __fmaf_rn(qf, qf, sq);
+        db[j] = digit_bytes(q);
+    }
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    if (!store) return;
     const size_t group = group0 + (lane >> 2);
-    const int q = lane & 3;             // which quarter of the group this lane holds
+    const int q4 = lane & 3;            // which quarter of the group this lane holds
+    if (mode == 2 && q4 == 0) {
+        // one value dominates the group (32 gmax^2 > 16 sum x^2, in units of the scaled integers): keep the low digit
+        flags[group * 16 + m] = (P != 0.0f && sq < 2.0f * kDigitRange * kDigitRange) ? 1 : 0;
+        if (m == 0)
+            for (int z = M; z < 16; ++z) flags[group * 16 + z] = 0;        // rows this batch does not have
+    }
 #pragma unroll
     for (int j = 0; j < 3; ++j) {
-        if (j < ndigits) {
-            const int col = (m * ndigits + j) * colmul, set = col >> 3, cc = col & 7;
-            if (q == 0) scales[(group * 4 + (cc >> 1)) * nsets + set] = sx;
-            if (ORDER == kOrderNibble) {
-                const uint32_t b0 = gather_byte(db[0], db[2], db[4], db[6], j);
-                const uint32_t b1 = gather_byte(db[1], db[3], db[5], db[7], j);
-                *reinterpret_cast<uint2*>(digits + plane_offset(group, nsets, set, cc * 4 + q)) = make_uint2(b0, b1);
-            } else {
-                // k = 8q .. 8q+7: the first four go to fragment lane t0 = 2 (q & 1), the next four to t0 + 1,
-                // in b0 when k < 16 and in b1 otherwise
-                const int t0 = 2 * (q & 1), half = q >> 1;
-                *reinterpret_cast<uint32_t*>(digits + plane_offset(group, nsets, set, cc * 4 + t0) + half * 4) =
-                    gather_byte(db[0], db[1], db[2], db[3], j);
-                *reinterpret_cast<uint32_t*>(digits + plane_offset(group, nsets, set, cc * 4 + t0 + 1) + half * 4) =
-                    gather_byte(db[4], db[5], db[6], db[7], j);
-            }
+        int set, cc;
+        digit_slot(mode, nmain, m, j, &set, &cc);
+        if (q4 == 0) scales[((group * 4 + (cc >> 1)) * nsets + set) * 2 + (cc & 1)] = (mode == 2 && j > 0) ? sx * 256.0f : sx;
+        if (ORDER == kOrderNibble) {
+            const uint32_t b0 = gather_byte(db[0], db[2], db[4], db[6], j);
+            const uint32_t b1 = gather_byte(db[1], db[3], db[5], db[7], j);
+            *reinterpret_cast<uint2*>(digits + plane_offset(group, nsets, set, cc * 4 + q4)) = make_uint2(b0, b1);
+        } else {
+            // k = 8q .. 8q+7: the first four go to fragment lane t0 = 2 (q & 1), the next four to t0 + 1,
+            // in b0 when k < 16 and in b1 otherwise
+            const int t0 = 2 * (q4 & 1), half = q4 >> 1;
+            *reinterpret_cast<uint32_t*>(digits + plane_offset(group, nsets, set, cc * 4 + t0) + half * 4) =
+                gather_byte(db[0], db[1], db[2], db[3], j);
+            *reinterpret_cast<uint32_t*>(digits + plane_offset(group, nsets, set, cc * 4 + t0 + 1) + half * 4) =
+                gather_byte(db[4], db[5], db[6], db[7], j);
         }
     }
 }
 
-// Block-wide conversion of one row (row index m of the batch) whose K values lie at x_row in
+// Where the three parts of a prepared buffer of `groups` 32-k groups start.
+struct PreparedParts {
+    uint8_t* digits;
+    float* scales;
+    uint8_t* flags;
+};
+__host__ __device__ inline PreparedParts prepared_parts(uint8_t* base, size_t groups, int nsets) {
+    PreparedParts p;
+    p.digits = base;
+    p.scales = reinterpret_cast<float*>(base + groups * nsets * 256);
+    p.flags = base + groups * nsets * (256 + 32);
+    return p;
+}
+
+// Block-wide conversion of one row (row index m of an M-row batch) whose K values lie at x_row in
 // global memory (values this thread block wrote itself are visible after the caller's
 // __syncthreads).  THREADS must be a multiple of 32 and K a multiple of 256, so that whole warps
 // take part in every conversion call.  `planes` is the prepared buffer of the INT4 decode kernel.
 template <int THREADS>
-__device__ __forceinline__ void prepare_row_block(const float* x_row, int m, int64_t K, int ndigits, int nsets, int colmul,
+__device__ __forceinline__ void prepare_row_block(const float* x_row, int m, int M, int64_t K, int mode, int nmain, int nsets,
                                                   uint8_t* __restrict__ planes) {
     const int chunks = static_cast<int>(K / 8);
-    float* scales = reinterpret_cast<float*>(planes + static_cast<size_t>(K / 32) * nsets * 256);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
     for (int c = threadIdx.x; c < chunks; c += THREADS) {
         const float4 a = __ldcg(reinterpret_cast<const float4*>(x_row) + 2 * c);     // L2: coherent with this block's own stores
         const float4 b = __ldcg(reinterpret_cast<const float4*>(x_row) + 2 * c + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        convert_groups<kOrderNibble>(v, m, static_cast<size_t>(c >> 5) * 8, ndigits, nsets, colmul, 0.0625f, planes, scales);
+        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 0.0625f, pp.digits, pp.scales,
+                                     pp.flags);
     }
 }
 

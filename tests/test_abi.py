@@ -45,7 +45,7 @@ def test_decoder_argument_validation_needs_no_device(sgq):
     two = C.c_void_p(512)
     assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 100, two, two, 4096, None) == 4  # no prepared form for dim 100
     assert L.sgqd_add_rmsnorm(one, None, one, 1e-5, 2, 256, two, two, 16, None) == 5    # prepared buffer too small
-    assert int(L.sgq_prepared_x_bytes(8, 2048)) == (2048 // 32) * 2 * 272      # digits + group scales, 2 sets
+    assert int(L.sgq_prepared_x_bytes(8, 2048)) == (2048 // 32) * (3 * 288 + 16)      # digits + group scales of 2 main sets + 1 low set, flags
     assert L.sgq_linear_int4_prepared(one, 64, 8, 2048, 64, one, one, None, one, 64, None) == 5
     assert L.sgq_linear_int4_prepared(one, 1 << 20, 8, 2050, 64, one, one, None, one, 64, None) == 4
     assert L.sgqd_rope_kv_store(one, 1, 1, 2, 12, one, one, one, one, one, 8, None) == 2   # head_dim % 8
@@ -88,12 +88,13 @@ def test_workspace_queries(sgq):
     assert sgq.linear_workspace_bytes(4, 2048, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_SIMT) == 0
     assert sgq.linear_workspace_bytes(4, 0, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_AUTO) == 0
     assert int(sgq.lib.sgq_linear_w8a8_workspace_bytes(128, 1024, 1024)) == 128 * 1024 + 512
-    # INT8 decode kernel: digit planes (256 B) and scales (16 B) of the whole batch per 32-k group and set of 8 columns
-    assert sgq.linear_workspace_bytes(8, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * 4 * 272
+    # INT8 decode kernel: digit planes (256 B) and scales (32 B) of the whole batch per 32-k group and set of 8 columns
+    # (16 rows: 4 main sets + 2 low sets), 16 flag bytes per group
+    assert sgq.linear_workspace_bytes(8, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (6 * 288 + 16)
     assert sgq.linear_workspace_bytes(8, 4, 100, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == 0          # K % 128 != 0: no such path
     assert sgq.linear_workspace_bytes(8, 2048, 4096, 64, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2
     # an INT4 batch whose planes exceed shared memory is processed in phases over K: scratch for the whole batch
-    assert sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * 4 * 272
+    assert sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (6 * 288 + 16)
 
 
 def test_no_cpu_fallback(sgq):

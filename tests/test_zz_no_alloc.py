@@ -60,7 +60,7 @@ def test_noalloc_matches_workspace_entry_point(sgq, M, K, N):
 
 
 def test_noalloc_rejects_what_exceeds_the_builtin_scratch(sgq):
-    M, K, N = 16, 16384, 32                      # needs 16384/32 * 4 * 272 bytes > 320 KiB
+    M, K, N = 16, 16384, 32                      # needs 16384/32 * (6 * 288 + 16) bytes > 448 KiB
     one = torch.zeros(M * K, device="cuda")
     rc = sgq.lib.sgq_linear_int4_decode_noalloc(one.data_ptr(), M, K, N, one.data_ptr(), one.data_ptr(), None, one.data_ptr(), N, None)
     assert rc == 5                               # SGQ_ERR_WORKSPACE: too large for the built-in scratch
