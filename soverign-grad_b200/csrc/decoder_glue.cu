@@ -30,7 +30,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <bool PREP>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                   const float* __restrict__ gamma, float eps, int64_t dim,
-                                                                  float* out, int pmode, int nmain, int nsets, uint8_t* planes) {
+                                                                  float* out, int pmode, int nmain, int nlow, uint8_t* planes) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float inv_rms_s;
     pdl_launch_dependents();
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
     }
     if (PREP) {
         __syncthreads();                                           // publishes this block's stores of orow
-        prepare_row_block<kNormThreads>(orow, blockIdx.x, gridDim.x, dim, pmode, nmain, nsets, planes);
+        prepare_row_block<kNormThreads>(orow, blockIdx.x, gridDim.x, dim, pmode, nmain, nlow, planes);
     }
 }
 
@@ -99,7 +99,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <bool PREP, int CH>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                       const float* __restrict__ gamma, float eps, int64_t dim,
-                                                                      float* __restrict__ out, int pmode, int nmain, int nsets,
+                                                                      float* __restrict__ out, int pmode, int nmain, int nlow,
                                                                       uint8_t* __restrict__ planes) {
     __shared__ float red[kNormThreads / 32];
     pdl_launch_dependents();
@@ -141,11 +141,11 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_row_kernel(float* __
         }
     }
     if (PREP) {
-        const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(dim / 32), nsets);
+        const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(dim / 32), nmain, nlow);
 #pragma unroll
         for (int r = 0; r < CH; ++r) {
             const int c = threadIdx.x + r * kNormThreads;       // chunks % 32 == 0: whole warps
-            if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nsets, 0.0625f, pp.digits, pp.scales, pp.flags);
+            if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nlow, 0.0625f, pp);
         }
     }
 }
@@ -362,7 +362,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 
 // One block per row; also converts the row to the decode kernel's prepared-activation format.
 __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const float* __restrict__ gu, int64_t hidden, float* out,
-                                                                       int pmode, int nmain, int nsets, uint8_t* planes) {
+                                                                       int pmode, int nmain, int nlow, uint8_t* planes) {
     pdl_launch_dependents();
     pdl_wait();
     const float* g = gu + blockIdx.x * 2 * hidden;
@@ -377,13 +377,13 @@ __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const fl
         *reinterpret_cast<float4*>(orow + i) = o;
     }
     __syncthreads();                                               // publishes this block's stores of orow
-    prepare_row_block<kNormThreads>(orow, blockIdx.x, gridDim.x, hidden, pmode, nmain, nsets, planes);
+    prepare_row_block<kNormThreads>(orow, blockIdx.x, gridDim.x, hidden, pmode, nmain, nlow, planes);
 }
 
 // The register-resident form of the same (hidden % 256 == 0, hidden <= 8192): one pass over memory.
 constexpr int kSiluThreads = 512;
 __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(const float* __restrict__ gu, int64_t hidden,
-                                                                           float* __restrict__ out, int pmode, int nmain, int nsets,
+                                                                           float* __restrict__ out, int pmode, int nmain, int nlow,
                                                                            uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();
@@ -407,11 +407,11 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(cons
             *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
         }
     }
-    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(hidden / 32), nsets);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(hidden / 32), nmain, nlow);
 #pragma unroll
     for (int r = 0; r < CH; ++r) {
         const int c = threadIdx.x + r * kSiluThreads;           // whole warps
-        if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nsets, 0.0625f, pp.digits, pp.scales, pp.flags);
+        if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nlow, 0.0625f, pp);
     }
 }
 
@@ -490,7 +490,7 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
         uint8_t* pl = static_cast<uint8_t*>(prepared_out);
         const dim3 grid(static_cast<unsigned>(rows)), block(kNormThreads);
 #define SGQ_NORM_ROW(PREPV, CHV) \
-    SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_row_kernel<PREPV, CHV>, grid, block, 0, s, ov, h, delta, gamma, eps, dim, out, L.mode, L.nmain, L.nsets, pl))
+    SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_row_kernel<PREPV, CHV>, grid, block, 0, s, ov, h, delta, gamma, eps, dim, out, L.mode, L.nmain, L.nlow, pl))
         if (dim <= 2048) { if (pl) SGQ_NORM_ROW(true, 1); else SGQ_NORM_ROW(false, 1); }
         else if (dim <= 4096) { if (pl) SGQ_NORM_ROW(true, 2); else SGQ_NORM_ROW(false, 2); }
         else { if (pl) SGQ_NORM_ROW(true, 4); else SGQ_NORM_ROW(false, 4); }
@@ -499,7 +499,7 @@ int sgqd_add_rmsnorm(float* h, const float* delta, const float* gamma, float eps
     }
     if (prepared_out)
         SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
-                                   gamma, eps, dim, out, L.mode, L.nmain, L.nsets, static_cast<uint8_t*>(prepared_out)));
+                                   gamma, eps, dim, out, L.mode, L.nmain, L.nlow, static_cast<uint8_t*>(prepared_out)));
     else
         SGQ_CUDA_TRY(launch_kernel(add_rmsnorm_kernel<false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s, ov, h, delta,
                                    gamma, eps, dim, out, 0, 1, 1, static_cast<uint8_t*>(nullptr)));
@@ -557,13 +557,13 @@ int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (prepared_out && (hidden % 256) == 0 && hidden <= 8192) {
         SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_row_kernel, dim3(static_cast<unsigned>(rows)), dim3(kSiluThreads), 0, s,
-                                   stream_overlap_enabled(), gate_up, hidden, out, L.mode, L.nmain, L.nsets,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.mode, L.nmain, L.nlow,
                                    static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
     }
     if (prepared_out) {
         SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, s,
-                                   stream_overlap_enabled(), gate_up, hidden, out, L.mode, L.nmain, L.nsets,
+                                   stream_overlap_enabled(), gate_up, hidden, out, L.mode, L.nmain, L.nlow,
                                    static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
     }

@@ -77,17 +77,19 @@ __host__ __device__ constexpr int warps_per_tile(int nwarps) { return nwarps == 
 __host__ __device__ constexpr int slots_per_group(int nmain) { return nmain <= 2 ? 2 : 1; }
 
 struct Smem {
-    uint32_t x_off, sx_off, flag_off, partial_off, misc_off, total;   // from a 1024-byte aligned base; stages first
+    uint32_t x_off, sx_off, flag_off, low_off, partial_off, misc_off, total;   // from a 1024-byte aligned base; stages first
 };
 
-// groups: 32-k groups of ONE phase; nmain / nlow: column sets (gemv_prepare.cuh)
-__host__ __device__ inline Smem smem_layout(int nstages, uint32_t groups, int nmain, int nlow, int nwarps) {
+// groups: 32-k groups of ONE phase; nmain / nlow: column sets (gemv_prepare.cuh).  The main digit planes,
+// main scales and flags are always resident; the low parts only when the CTAs convert the activations
+// themselves (low_resident) — prepared activations keep them in global memory.
+__host__ __device__ inline Smem smem_layout(int nstages, uint32_t groups, int nmain, int nlow, int nwarps, bool low_resident) {
     Smem s;
-    const uint32_t nsets = nmain + nlow;
     s.x_off = nstages * kStageBytes;
-    s.sx_off = s.x_off + groups * 256u * nsets;
-    s.flag_off = s.sx_off + groups * 32u * nsets;
-    s.partial_off = s.flag_off + (nlow ? groups * 16u : 0u);
+    s.sx_off = s.x_off + groups * 256u * nmain;
+    s.flag_off = s.sx_off + groups * 32u * nmain;
+    s.low_off = s.flag_off + (nlow ? groups * 16u : 0u);
+    s.partial_off = s.low_off + (low_resident ? groups * (256u + 32u) * nlow : 0u);
     s.misc_off = s.partial_off + slots_per_group(nmain) * nwarps * (512u * nmain + 16u);   // slots x warps per tile x padded partial sums
     s.total = s.misc_off + (2u * kMaxStages + 2u * kMaxSlots + 2u) * 8u;
     return s;
@@ -127,21 +129,22 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
                  : "r"(smem_addr));
 }
 
-// Activation planes converted once into global scratch, in the prepared layout.  One CTA per row.
-constexpr int kPrepThreads = 256;
+// Activation planes converted once into global scratch, in the prepared layout.  grid (rows, ceil(K / 1024)):
+// a CTA converts 1024 consecutive k of one row, so that even a few rows spread over many SMs.
+constexpr int kPrepThreads = 128;
 __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int64_t K, int mode, int nmain,
-                                                                     int nsets, uint8_t* __restrict__ planes) {
+                                                                     int nlow, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
     const int m = blockIdx.x, M = gridDim.x;
     const int chunks = static_cast<int>(K / 8);
-    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nmain, nlow);
     const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
-    for (int c = threadIdx.x; c < chunks; c += kPrepThreads) {          // chunks % 32 == 0: whole warps
+    const int c = blockIdx.y * kPrepThreads + threadIdx.x;
+    if (c < chunks) {                                  // chunks % 32 == 0: whole warps
         const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 0.0625f, pp.digits, pp.scales,
-                                     pp.flags);
+        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nlow, 0.0625f, pp);
     }
 }
 
@@ -156,7 +159,6 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
                     float* __restrict__ y, int M, int64_t K, int64_t N, int64_t ldy, int nstages, int nphases, int flags,
                     const __grid_constant__ PeerOut peers) {
-    constexpr int NSETS = NM + NL;
     constexpr int kMode = NL > 0 ? 2 : (HALF ? 0 : 1);
     constexpr int kDigitsOut = NL > 0 ? 2 : 3;
     constexpr int WPT = warps_per_tile(NWARPS);
@@ -174,7 +176,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int spt = static_cast<int>(K / kStepK);      // steps per tile (K % 256 == 0)
     const int sp = spt / nphases;                      // steps per tile and phase
-    const Smem L = smem_layout(nstages, static_cast<uint32_t>(sp) * 8u, NM, NL, NWARPS);
+    const bool prepared = (flags & kFlagPrepared) != 0;
+    const Smem L = smem_layout(nstages, static_cast<uint32_t>(sp) * 8u, NM, NL, NWARPS, !prepared);
     uint8_t* stages = smem;
     uint8_t* xs = smem + L.x_off;
     float* sxs = reinterpret_cast<float*>(smem + L.sx_off);
@@ -189,7 +192,6 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
-    const bool prepared = (flags & kFlagPrepared) != 0;
     const int ring_slots = nstages / kGroups;          // stage slots per warp group (nstages >= kGroups)
 
     pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
@@ -232,13 +234,13 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (prepared) fence_proxy_async_all();      // the planes were written through the generic proxy
             };
             auto copy_planes = [&](int ph) {
-                // digit planes, group scales and flags of this phase: contiguous ranges, in pieces of <= 32 KiB
+                // main digit planes, main scales and flags of this phase: contiguous ranges, in pieces of <= 32 KiB
                 const uint32_t pgroups = static_cast<uint32_t>(sp) * 8u;
-                const uint32_t dbytes = pgroups * 256u * NSETS, sbytes = pgroups * 32u * NSETS, fbytes = NL ? pgroups * 16u : 0u;
+                const uint32_t dbytes = pgroups * 256u * NM, sbytes = pgroups * 32u * NM, fbytes = NL ? pgroups * 16u : 0u;
                 const size_t groups_all = static_cast<size_t>(K / 32);
                 const uint8_t* dsrc = planes + static_cast<size_t>(ph) * dbytes;
-                const uint8_t* ssrc = planes + groups_all * 256u * NSETS + static_cast<size_t>(ph) * sbytes;
-                const uint8_t* fsrc = planes + groups_all * (256u + 32u) * NSETS + static_cast<size_t>(ph) * fbytes;
+                const uint8_t* ssrc = planes + groups_all * 256u * (NM + NL) + static_cast<size_t>(ph) * sbytes;
+                const uint8_t* fsrc = planes + groups_all * (256u + 32u) * (NM + NL) + static_cast<size_t>(ph) * fbytes;
                 mbar_arrive_expect_tx(xfull, dbytes + sbytes + fbytes);
                 for (uint32_t off = 0; off < dbytes; off += 32768u)
                     bulk_copy_g2s(xs + off, dsrc + off, (dbytes - off < 32768u) ? dbytes - off : 32768u, xfull);
@@ -346,7 +348,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int j = 3 - kDigitsOut; j < 3; ++j, weight *= 256.0f) {
                         int set, cc;
-                        digit_slot(kMode, NM, m, j, &set, &cc);
+                        digit_slot(kMode, m, j, &set, &cc);
                         const float v = pbuf[(set * 32 + gg * 4 + (cc >> 1)) * 4 + hi * 2 + (cc & 1)];
                         acc = __fmaf_rn(weight, v, acc);
                     }
@@ -396,12 +398,18 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // per iteration; M * K / 8 is a multiple of 32, so whole warps are in or out.
         const int chunks = static_cast<int>(K / 8);
         const int items = chunks * M;
+        PreparedParts pp;
+        pp.dmain = xs;
+        pp.smain = sxs;
+        pp.flags = flg;
+        pp.dlow = smem + L.low_off;
+        pp.slow = reinterpret_cast<float*>(smem + L.low_off + static_cast<uint32_t>(sp) * 8u * 256u * NL);
         for (int it = threadIdx.x; it < items; it += kConsumerThreads) {
             const int m = it / chunks, c = it - m * chunks;
             const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it));
             const float4 b = __ldg(reinterpret_cast<const float4*>(x) + 2 * static_cast<int64_t>(it) + 1);
             const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, kMode, NM, NSETS, 0.0625f, xs, sxs, flg);
+            convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, kMode, NM, NL, 0.0625f, pp);
         }
         named_barrier_sync(1, kConsumerThreads);
     }
@@ -419,15 +427,24 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     uint32_t seq = 0, tcount = 0;         // seq: stages of THIS group so far
     for (int ph = 0; ph < nphases; ++ph) {
+        // Low digit planes and scales of this phase: in global memory behind the prepared buffer, or in shared
+        // memory when this CTA converted the activations itself (generic pointers: the loads work on either).
+        const uint8_t* lowd = smem + L.low_off;
+        const float* lows = reinterpret_cast<const float*>(smem + L.low_off + static_cast<uint32_t>(sp) * 8u * 256u * NL);
+        if (prepared && NL > 0) {
+            const size_t groups_all = static_cast<size_t>(K / 32), g0 = static_cast<size_t>(ph) * sp * 8;
+            lowd = planes + groups_all * 256u * NM + g0 * 256u * NL;
+            lows = reinterpret_cast<const float*>(planes + groups_all * (256u * (NM + NL) + 32u * NM)) + g0 * 8u * NL;
+        }
         if (prepared && alive && !mbar_wait(xfull, ph & 1u)) {
             report(kDevErrFullWait, 0x400000u | ph);
             alive = false;
         }
         for (int64_t ti = 0; ti < my_tiles; ++ti, ++tcount) {
             if (static_cast<int>(tcount % kGroups) != my_group) continue;       // another group's tile
-            float total[NSETS][4];
+            float total[NM + NL][4];
 #pragma unroll
-            for (int s = 0; s < NSETS; ++s)
+            for (int s = 0; s < NM + NL; ++s)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
@@ -447,8 +464,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         // scales: [2 chunks of 4 steps][16 rows][128 B], 16-byte units swizzled by the row like the weights
                         const uint8_t* sbox = stages + st * kStageBytes + kStageW + (step_in_stage >> 2) * kSChunkBytes + g * 128;
                         const int su = (step_in_stage & 3) * 2;
-                        const uint8_t* xg = xs + static_cast<size_t>(step) * 8 * (256 * NSETS);
-                        const float* sg = sxs + (static_cast<size_t>(step) * 8 * 4 + t) * (2 * NSETS);   // this lane's group scales
+                        const uint8_t* xg = xs + static_cast<size_t>(step) * 8 * (256 * NM);
+                        const float* sg = sxs + (static_cast<size_t>(step) * 8 * 4 + t) * (2 * NM);      // this lane's group scales
                         const uint8_t* fg = flg + static_cast<size_t>(step) * 8 * 16;
                         constexpr int BG = NM <= 2 ? 4 : 2;              // 32-k groups whose MMAs are in flight together
 #pragma unroll
@@ -472,8 +489,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 av[i][1] = (w_hi << 4) & 0xF0F0F0F0u;    // row g+8
                                 av[i][2] = w_lo & 0xF0F0F0F0u;           // row g,   k = 8t + {1,3,5,7}
                                 av[i][3] = w_hi & 0xF0F0F0F0u;           // row g+8
-                                const uint8_t* xgi = xg + gi * (256 * NSETS);
-                                const float* sgi = sg + gi * (8 * NSETS);
+                                const uint8_t* xgi = xg + gi * (256 * NM);
+                                const float* sgi = sg + gi * (8 * NM);
 #pragma unroll
                                 for (int s2 = 0; s2 < NM; ++s2) sxv[i][s2] = *reinterpret_cast<const float2*>(sgi + 2 * s2);
 #pragma unroll
@@ -483,7 +500,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                         mma_s8s8_16832_magic(d[i][s2], av[i], q.x, q.y);
                                         mma_s8s8_16832_magic(d[i][s2 + 1], av[i], q.z, q.w);
                                     } else if ((s2 & 1) == 0) {
-                                        const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, s2, lane));
+                                        const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NM, s2, lane));
                                         mma_s8s8_16832_magic(d[i][s2], av[i], q.x, q.y);
                                     }
                                 }
@@ -513,8 +530,9 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 for (int l = 0; l < NL; ++l) {
                                     const uint2 fl = *reinterpret_cast<const uint2*>(fg + gi * 16 + l * 8);
                                     if ((fl.x | fl.y) != 0u) {           // the same for every lane of the warp
-                                        const uint2 q = *reinterpret_cast<const uint2*>(xg + gi * (256 * NSETS) + plane_offset(0, NSETS, NM + l, lane));
-                                        const float2 sl = *reinterpret_cast<const float2*>(sg + gi * (8 * NSETS) + 2 * (NM + l));
+                                        const size_t grp = static_cast<size_t>(step) * 8 + gi;       // group within the phase
+                                        const uint2 q = *reinterpret_cast<const uint2*>(lowd + plane_offset(grp, NL, l, lane));
+                                        const float2 sl = *reinterpret_cast<const float2*>(lows + ((grp * 4 + t) * NL + l) * 2);
                                         int dl[4];
                                         mma_s8s8_16832_magic(dl, av[i], q.x, q.y);
                                         total[NM + l][0] = __fmaf_rn(__fmul_rn(s_lo, sl.x), __fsub_rn(__int_as_float(dl[0]), kMagicF), total[NM + l][0]);
@@ -530,7 +548,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 // everything loaded from the stage has been consumed once the accumulators are final
                 uint32_t fold = 0;
 #pragma unroll
-                for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
+                for (int s = 0; s < NM + NL; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
                 const uint32_t landed = loads_landed(fold);
                 if (lane == 0) mbar_arrive_after(&empty[st], landed);
             }
@@ -586,7 +604,7 @@ struct Plan {
 // there is only one.  compact: a CTA that leaves room for a second one on the same SM (half the
 // shared memory, 10 warps); with overlapped launches the CTA of the NEXT kernel then sits beside the
 // one still running and streams its first weight stages in the meantime.
-bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact = false) {
+bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact = false, bool allow_phases = true) {
     if (M < 1 || M > kMaxM || K < kStepK || (K % kStepK) != 0) return false;
     p->L = prepared_layout(M, K);
     p->planes_bytes = p->L.bytes;
@@ -597,16 +615,17 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
         if (spt % nph) break;
         const int sp = spt / nph;
         if (nph > 1 && (sp % kStepsPerStage) != 0) break;
-        if (nph > 1 && !have_workspace) break;             // phases need the planes in global memory
+        if (nph > 1 && (!have_workspace || !allow_phases)) break;      // phases need the planes in global memory
         const int min_stages = 2;                          // one slot for each of the two warp groups
         for (int st = kMaxStages; st >= min_stages; --st) {
-            const Smem S = smem_layout(st, static_cast<uint32_t>(sp) * 8u, p->L.nmain, p->L.nlow, p->nwarps);
+            // in-CTA conversion while it is a few items per thread; larger batches are converted once by a pre-kernel
+            const bool pre = have_workspace && (nph > 1 || M * (K / 8) > 2 * p->nwarps * 32);
+            const Smem S = smem_layout(st, static_cast<uint32_t>(sp) * 8u, p->L.nmain, p->L.nlow, p->nwarps, !pre);
             if (S.total + 1024 <= static_cast<uint32_t>(limit)) {
                 p->nstages = st;
                 p->nphases = nph;
                 p->smem = S.total + 1024;
-                // in-CTA conversion while it is a few items per thread; larger batches are converted once by a pre-kernel
-                p->pre = have_workspace && (nph > 1 || M * (K / 8) > 4 * p->nwarps * 32);
+                p->pre = pre;
                 return true;
             }
         }
@@ -620,7 +639,15 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
 // still far better than the any-shape kernel.
 int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
     Plan p;
-    for (int64_t m = M; m >= 1; --m)
+    // the whole batch in one pass over K — unless it is a wide batch that leaves the pipeline fewer than four stages
+    if (make_plan(M, K, have_workspace, &p, false, false) && (M <= 8 || p.nstages >= 4)) return M;
+    if (M > 8) {
+        // two or more launches of at most 8 rows each: measured faster than K phases over wide column sets
+        const int64_t blocks = (M + 7) / 8, rows = (M + blocks - 1) / blocks;
+        if (make_plan(rows, K, have_workspace, &p, false, false)) return rows;
+    }
+    if (make_plan(M, K, have_workspace, &p)) return M;                           // K phases
+    for (int64_t m = M - 1; m >= 1; --m)
         if (make_plan(m, K, have_workspace, &p)) return m;
     return 0;
 }
@@ -634,8 +661,8 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
     const bool overlap = stream_overlap_enabled();
     if (p.pre && !planes_ready) {
-        SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap,
-                                   a.x, a.K, p.L.mode, p.L.nmain, p.L.nsets, static_cast<uint8_t*>(a.workspace)));
+        SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M), static_cast<unsigned>(ceil_div(a.K / 8, kPrepThreads))), dim3(kPrepThreads), 0, a.stream, overlap,
+                                   a.x, a.K, p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace)));
     }
     const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
@@ -667,8 +694,9 @@ bool gemv_supported(const LinearArgs& a) {
 size_t gemv_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
     if (bits != 4 || layout != SGQ_LAYOUT_NK || !shape_ok(M, K, N > 0 ? N : 1)) return 0;
     Plan p, c;
-    if (!make_plan(M, K, true, &p)) return 0;
-    const bool compact_pre = make_plan(M, K, true, &c, true) && c.pre;    // what an overlapped launch in compact form would want
+    const int64_t rows = rows_per_launch(M, K, true);                     // row blocks reuse one scratch
+    if (rows < 1 || !make_plan(rows, K, true, &p)) return 0;
+    const bool compact_pre = make_plan(rows, K, true, &c, true) && c.pre;  // what an overlapped launch in compact form would want
     if (!p.pre && !compact_pre) return 0;
     return (p.planes_bytes + 255) / 256 * 256;
 }
@@ -690,8 +718,8 @@ size_t gemv_prepared_bytes(int64_t M, int64_t K) {
 
 int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s) {
     const PreparedLayout L = prepared_layout(M, K);
-    SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M)), dim3(kPrepThreads), 0, s,
-                               stream_overlap_enabled(), x, K, L.mode, L.nmain, L.nsets, static_cast<uint8_t*>(prepared)));
+    SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M), static_cast<unsigned>(ceil_div(K / 8, kPrepThreads))), dim3(kPrepThreads), 0, s,
+                               stream_overlap_enabled(), x, K, L.mode, L.nmain, L.nlow, static_cast<uint8_t*>(prepared)));
     return SGQ_OK;
 }
 

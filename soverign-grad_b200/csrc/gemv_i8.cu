@@ -12,10 +12,11 @@
 //     the activation scale of that group (gemv_prepare.cuh: 24-bit fixed point per group, the low
 //     digit in column sets of its own that are skipped where it cannot matter) and added up in fp32,
 //     the weight scale is applied once per output;
-//   * the activation digit planes and group scales (laid out for the natural k order of an int8 B
-//     fragment) are written once by a conversion kernel and stream through the same pipeline
-//     stages as the weights, 32 groups at a time, from L2.  They are never resident as a whole,
-//     so K is not limited by shared memory (K = 8192 at M = 16 runs);
+//   * the main activation digit planes, their scales and the low-digit flags (laid out for the
+//     natural k order of an int8 B fragment) are written once by a conversion kernel and stream
+//     through the same pipeline stages as the weights, 32 groups at a time, from L2.  They are
+//     never resident as a whole, so K is not limited by shared memory (K = 8192 at M = 16 runs);
+//     low digits are fetched from the prepared buffer itself, for flagged groups only;
 //   * tile epilogue: every warp leaves its fp32 partial sums in one of two shared-memory slots,
 //     one named barrier, then thread (m, row) adds the eight partials in warp order (fixed order:
 //     the same bits every run), recombines the digits, applies the weight scale and the bias.
@@ -105,14 +106,14 @@ __device__ __forceinline__ void accumulate_group(float (&total)[4], const uint32
 // row, one pass.  K is a multiple of 128: in the last warp-wide call of a row the lanes beyond the end
 // pass zeros and store nothing.
 __global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float* __restrict__ x, int64_t K, int mode, int nmain,
-                                                                   int nsets, uint8_t* __restrict__ planes) {
+                                                                   int nlow, uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
     const int m = blockIdx.x, M = gridDim.x;
     const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(m) * K);
     const int chunks = static_cast<int>(K / 8);
     const int padded = (chunks + 31) & ~31;
-    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nmain, nlow);
     for (int c = threadIdx.x; c < padded; c += kPrepThreads) {
         const bool in = c < chunks;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float*
             const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
-        convert_groups<kOrderNatural>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 1.0f, pp.digits, pp.scales, pp.flags, in);
+        convert_groups<kOrderNatural>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nlow, 1.0f, pp, in);
     }
 }
 
@@ -130,8 +131,7 @@ struct Smem {
 
 __host__ __device__ inline Smem smem_layout(int nstages, int nmain, int nlow) {
     Smem s;
-    const uint32_t nsets = nmain + nlow;
-    s.stage_bytes = kStageW + kGroupsPerStage * ((256u + 32u) * nsets + (nlow ? 16u : 0u));   // weights, digits, group scales, flags
+    s.stage_bytes = kStageW + kGroupsPerStage * ((256u + 32u) * nmain + (nlow ? 16u : 0u));   // weights, main digits and scales, flags
     s.stage_bytes = (s.stage_bytes + 1023u) & ~1023u;      // the swizzled weight box of every stage starts on a 1024-byte boundary
     s.partial_off = nstages * s.stage_bytes;
     s.misc_off = s.partial_off + 2u * kWarps * (512u * nmain + 16u);      // two slots of per-warp fp32 partial sums (padded)
@@ -144,7 +144,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __restrict__ planes, const float* __restrict__ wscales,
                     int scale_per_row, const float* __restrict__ bias, float* __restrict__ y, int M, int64_t K, int64_t N, int64_t ldy,
                     int nstages) {
-    constexpr int NSETS = NM + NL;
     constexpr int kDigitsOut = NL > 0 ? 2 : 3;
     extern __shared__ uint8_t smem_raw[];
     // aligned by pointer arithmetic on the shared array itself: a round trip through an integer would make the
@@ -191,21 +190,20 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                     }
                     const int g0 = c0 * 4;                                              // first digit group of the stage
                     const int ng = (groups_total - g0 < kGroupsPerStage) ? groups_total - g0 : kGroupsPerStage;
-                    const uint32_t pbytes = static_cast<uint32_t>(ng) * 256u * NSETS;
-                    const uint32_t sbytes = static_cast<uint32_t>(ng) * 32u * NSETS;                  // group scales of the stage
-                    const uint32_t fbytes = NL ? static_cast<uint32_t>(ng) * 16u : 0u;                // and its low-digit flags
+                    const uint32_t pbytes = static_cast<uint32_t>(ng) * 256u * NM;                    // main digit planes of the stage
+                    const uint32_t sbytes = static_cast<uint32_t>(ng) * 32u * NM;                     // their group scales
+                    const uint32_t fbytes = NL ? static_cast<uint32_t>(ng) * 16u : 0u;                // and the low-digit flags
                     // steps past K/128 are out of range in the third dimension: zero-filled, still counted
                     mbar_arrive_expect_tx(&full[st], kStageW + pbytes + sbytes + fbytes);
                     uint8_t* sw = smem + st * L.stage_bytes;
                     tma_load_3d(sw, &map_w, &full[st], 0, static_cast<int32_t>(tile * kRows), c0);
-                    bulk_copy_g2s(sw + kStageW, planes + static_cast<size_t>(g0) * 256u * NSETS, pbytes, &full[st]);
-                    bulk_copy_g2s(sw + kStageW + kGroupsPerStage * 256u * NSETS,
-                                  planes + static_cast<size_t>(groups_total) * 256u * NSETS + static_cast<size_t>(g0) * 32u * NSETS, sbytes,
-                                  &full[st]);
+                    const size_t G = static_cast<size_t>(groups_total);
+                    bulk_copy_g2s(sw + kStageW, planes + static_cast<size_t>(g0) * 256u * NM, pbytes, &full[st]);
+                    bulk_copy_g2s(sw + kStageW + kGroupsPerStage * 256u * NM, planes + G * 256u * (NM + NL) + static_cast<size_t>(g0) * 32u * NM,
+                                  sbytes, &full[st]);
                     if (NL)
-                        bulk_copy_g2s(sw + kStageW + kGroupsPerStage * (256u + 32u) * NSETS,
-                                      planes + static_cast<size_t>(groups_total) * (256u + 32u) * NSETS + static_cast<size_t>(g0) * 16u, fbytes,
-                                      &full[st]);
+                        bulk_copy_g2s(sw + kStageW + kGroupsPerStage * (256u + 32u) * NM,
+                                      planes + G * (256u + 32u) * (NM + NL) + static_cast<size_t>(g0) * 16u, fbytes, &full[st]);
                 }
             }
         }
@@ -224,13 +222,16 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
     // epilogue role of this thread: output (row er of the tile, batch row em)
     const int em = threadIdx.x >> 4, er = threadIdx.x & 15;
     const float sw_all = scale_per_row ? 1.0f : __ldg(wscales);
+    // low digit planes and scales: read from the prepared buffer, for flagged groups only
+    const uint8_t* low_digits = planes + static_cast<size_t>(groups_total) * 256u * NM;
+    const float* low_scales = reinterpret_cast<const float*>(planes + static_cast<size_t>(groups_total) * (256u * (NM + NL) + 32u * NM));
 
     bool alive = true;
     uint32_t seq = 0, tcount = 0;
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-        float total[NSETS][4];
+        float total[NM + NL][4];
 #pragma unroll
-        for (int s = 0; s < NSETS; ++s)
+        for (int s = 0; s < NM + NL; ++s)
 #pragma unroll
             for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
@@ -244,17 +245,18 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
             const int step = c0 + warp;
             if (alive && step < spt) {
                 const uint32_t wbox = smem_u + st * L.stage_bytes + warp * (kRows * 128);
-                const uint8_t* xg = smem + st * L.stage_bytes + kStageW + (warp * 4) * (256 * NSETS);
-                const float* sg = reinterpret_cast<const float*>(smem + st * L.stage_bytes + kStageW + kGroupsPerStage * 256 * NSETS) +
-                                  ((warp * 4) * 4 + t) * (2 * NSETS);                     // this lane's group scales
-                const uint8_t* fg = smem + st * L.stage_bytes + kStageW + kGroupsPerStage * (256 + 32) * NSETS + (warp * 4) * 16;
+                const uint8_t* xg = smem + st * L.stage_bytes + kStageW + (warp * 4) * (256 * NM);
+                const float* sg = reinterpret_cast<const float*>(smem + st * L.stage_bytes + kStageW + kGroupsPerStage * 256 * NM) +
+                                  ((warp * 4) * 4 + t) * (2 * NM);                        // this lane's group scales
+                const uint8_t* fg = smem + st * L.stage_bytes + kStageW + kGroupsPerStage * (256 + 32) * NM + (warp * 4) * 16;
+                const size_t grp0 = static_cast<size_t>(step) * 4;                        // first 32-k group of this step
                 uint32_t a[4][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) ldmatrix_x4(a[i], wbox + lm_off[i]);    // rows g / g+8, k = 32i + 4t.. and 32i + 16 + 4t..
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint8_t* xgi = xg + i * (256 * NSETS);
-                    const float* sgi = sg + i * (8 * NSETS);
+                    const uint8_t* xgi = xg + i * (256 * NM);
+                    const float* sgi = sg + i * (8 * NM);
 #pragma unroll
                     for (int s2 = 0; s2 < NM; ++s2) {
                         if ((s2 & 1) == 0 && s2 + 1 < NM) {          // two main sets side by side: one 128-bit load per lane
@@ -262,7 +264,7 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                             accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
                             accumulate_group(total[s2 + 1], a[i], q.z, q.w, *reinterpret_cast<const float2*>(sgi + 2 * s2 + 2));
                         } else if ((s2 & 1) == 0) {
-                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, s2, lane));
+                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NM, s2, lane));
                             accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
                         }
                     }
@@ -271,8 +273,9 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                     for (int l = 0; l < NL; ++l) {
                         const uint2 fl = *reinterpret_cast<const uint2*>(fg + i * 16 + l * 8);
                         if ((fl.x | fl.y) != 0u) {                   // the same for every lane of the warp
-                            const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NSETS, NM + l, lane));
-                            accumulate_group(total[NM + l], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * (NM + l)));
+                            const uint2 q = __ldg(reinterpret_cast<const uint2*>(low_digits + plane_offset(grp0 + i, NL, l, lane)));
+                            const float2 sl = __ldg(reinterpret_cast<const float2*>(low_scales + ((grp0 + i) * 4 + t) * NL * 2 + l * 2));
+                            accumulate_group(total[NM + l], a[i], q.x, q.y, sl);
                         }
                     }
                 }
@@ -280,7 +283,7 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
             // everything loaded from the stage has been consumed once the accumulators are final
             uint32_t fold = 0;
 #pragma unroll
-            for (int s = 0; s < NSETS; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][3]);
+            for (int s = 0; s < NM + NL; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][3]);
             const uint32_t landed = loads_landed(fold);
             if (lane == 0) mbar_arrive_after(&empty[st], landed);
         }
@@ -311,7 +314,7 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
 #pragma unroll
             for (int j = 3 - kDigitsOut; j < 3; ++j, weight *= 256.0f) {
                 int set, cc;
-                digit_slot(MODE, NM, em, j, &set, &cc);
+                digit_slot(MODE, em, j, &set, &cc);
                 const float* src = pslot + (set * 32 + (er & 7) * 4 + (cc >> 1)) * 4 + (er >> 3) * 2 + (cc & 1);
                 float sum = src[0];
 #pragma unroll
@@ -358,7 +361,7 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     SGQ_CUDA_TRY(optin.ensure(kernel, kSmemLimit));
     const bool overlap = stream_overlap_enabled();
     SGQ_CUDA_TRY(launch_kernel(prepare_x_i8_kernel, dim3(static_cast<unsigned>(a.M)), dim3(kPrepThreads), 0, a.stream, overlap, a.x, a.K,
-                               p.L.mode, p.L.nmain, p.L.nsets, static_cast<uint8_t*>(a.workspace)));
+                               p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace)));
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), p.smem, a.stream, overlap, map_w,
                                static_cast<const uint8_t*>(a.workspace), a.scales, a.scheme == SGQ_PER_ROW ? 1 : 0, a.bias, a.y,
                                static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages));

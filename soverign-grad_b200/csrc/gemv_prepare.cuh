@@ -18,17 +18,21 @@
 // Inf gets a NaN scale (the output row becomes NaN); a group whose absmax is below 1e-30
 // contributes zero.
 //
-// Layout of a prepared buffer for M rows of K values (K % 32 == 0):
-//   digit planes  [group K/32][set pair][fragment lane 32][sets of the pair x 8 bytes]
-//   group scales  [group K/32][t 4][set][2] fp32: the scales that belong to columns 2t and 2t+1 of
-//                 the set (a lane of an MMA holds exactly these two accumulator columns)
-//   flags         [group K/32][16] bytes (three rows or more): row m's low digit is needed
+// Layout of a prepared buffer for M rows of K values (K % 32 == 0), five parts one after the other:
+//   main digit planes  [group K/32][set pair][fragment lane 32][sets of the pair x 8 bytes]
+//   low digit planes   the same for the low sets (three rows or more)
+//   main scales        [group K/32][t 4][set][2] fp32: the scales that belong to columns 2t and 2t+1
+//                      of the set (a lane of an MMA holds exactly these two accumulator columns)
+//   low scales         the same for the low sets
+//   flags              [group K/32][16] bytes (three rows or more): row m's low digit is needed
+// The kernels keep the main parts and the flags in shared memory and fetch low digits and scales
+// from wherever the buffer lies, for the flagged groups only.
 // A "set" is one group of eight B-fragment columns (one MMA).  Column of digit j of row m:
 //   one row     set 0, column 2j (only even columns carry data; the kernels skip the odd accumulators)
 //   two rows    set 0, column 3m + j
 //   more rows   d1, d2: column 2m + j - 1 counted through the `nmain` main sets (a row owns columns 2t, 2t+1
 //               of its set; the scales of these sets carry a factor 256); d0: column m counted through
-//               the `nlow` low sets that follow the main sets.
+//               the `nlow` low sets.
 // Sets are stored in pairs so that a lane fetches the fragments of two sets with one 128-bit load; a
 // last unpaired set uses 8 bytes per lane.
 #pragma once
@@ -49,9 +53,9 @@ constexpr float kDigitRange = 8355000.0f;    // |q| <= 8355711 = 127 * 65793 mus
 
 struct PreparedLayout {
     int mode;                  // 0: one row, 1: two rows, 2: three rows or more (main and low sets)
-    int nmain, nlow, nsets;    // nsets = nmain + nlow
+    int nmain, nlow;
     int ndigits_out;           // digits a kernel recombines per output: 3, or 2 when the low digit is folded in before
-    size_t digit_bytes, scale_bytes, flag_bytes, bytes;
+    size_t off_dlow, off_smain, off_slow, off_flags, bytes;    // part offsets (the main digit planes start at 0)
 };
 
 inline PreparedLayout prepared_layout(int64_t M, int64_t K) {
@@ -59,27 +63,25 @@ inline PreparedLayout prepared_layout(int64_t M, int64_t K) {
     L.mode = (M <= 1) ? 0 : (M == 2 ? 1 : 2);
     L.nmain = L.mode == 2 ? static_cast<int>((M + 3) / 4) : 1;
     L.nlow = L.mode == 2 ? static_cast<int>((M + 7) / 8) : 0;
-    L.nsets = L.nmain + L.nlow;
     L.ndigits_out = L.mode == 2 ? 2 : 3;
     const size_t groups = static_cast<size_t>(K / 32);
-    L.digit_bytes = groups * L.nsets * 256;
-    L.scale_bytes = groups * L.nsets * 32;
-    L.flag_bytes = L.mode == 2 ? groups * 16 : 0;
-    L.bytes = L.digit_bytes + L.scale_bytes + L.flag_bytes;
+    L.off_dlow = groups * L.nmain * 256;
+    L.off_smain = L.off_dlow + groups * L.nlow * 256;
+    L.off_slow = L.off_smain + groups * L.nmain * 32;
+    L.off_flags = L.off_slow + groups * L.nlow * 32;
+    L.bytes = L.off_flags + (L.mode == 2 ? groups * 16 : 0);
     return L;
 }
 
-// Set and column of digit j of row m.
-__host__ __device__ inline void digit_slot(int mode, int nmain, int m, int j, int* set, int* cc) {
+// Main set and column of digit j of row m (three rows or more: j = 1, 2 only; the low digit j = 0 sits in
+// column m & 7 of low set m >> 3).
+__host__ __device__ inline void digit_slot(int mode, int m, int j, int* set, int* cc) {
     if (mode == 0) {
         *set = 0;
         *cc = 2 * j;
     } else if (mode == 1) {
         *set = 0;
         *cc = 3 * m + j;
-    } else if (j == 0) {
-        *set = nmain + (m >> 3);
-        *cc = m & 7;
     } else {
         const int cm = 2 * m + j - 1;
         *set = cm >> 3;
@@ -117,6 +119,24 @@ __device__ __forceinline__ uint32_t gather_byte(uint32_t a, uint32_t b, uint32_t
 //                 as they lie in memory.
 enum { kOrderNibble = 0, kOrderNatural = 1 };
 
+// Where the parts of a prepared buffer of `groups` 32-k groups start.
+struct PreparedParts {
+    uint8_t* dmain;
+    uint8_t* dlow;
+    float* smain;
+    float* slow;
+    uint8_t* flags;
+};
+__host__ __device__ inline PreparedParts prepared_parts(uint8_t* base, size_t groups, int nmain, int nlow) {
+    PreparedParts p;
+    p.dmain = base;
+    p.dlow = p.dmain + groups * nmain * 256;
+    p.smain = reinterpret_cast<float*>(p.dlow + groups * nlow * 256);
+    p.slow = p.smain + groups * nmain * 8;
+    p.flags = reinterpret_cast<uint8_t*>(p.slow + groups * nlow * 8);
+    return p;
+}
+
 // Converts 256 consecutive k (eight 32-k groups, the first being group `group0`) of row m of an
 // M-row batch.  Must be called by all 32 lanes of a warp together, lane l holding the 8 consecutive
 // activations k = 32 * group0 + 8 l .. + 7 in v: four neighbouring lanes share a group.
@@ -124,9 +144,8 @@ enum { kOrderNibble = 0, kOrderNatural = 1 };
 // as 16 * code and passes 1/16).  A lane with store == false (beyond the end of a row) passes zeros
 // and writes nothing.
 template <int ORDER>
-__device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M, size_t group0, int mode, int nmain, int nsets,
-                                               float scale_mul, uint8_t* __restrict__ digits, float* __restrict__ scales,
-                                               uint8_t* __restrict__ flags, bool store = true) {
+__device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M, size_t group0, int mode, int nmain, int nlow,
+                                               float scale_mul, const PreparedParts& pp, bool store = true) {
     const int lane = threadIdx.x & 31;
     uint32_t mb = 0;
 #pragma unroll
@@ -168,15 +187,26 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M
     const int q4 = lane & 3;            // which quarter of the group this lane holds
     if (mode == 2 && q4 == 0) {
         // one value dominates the group (32 gmax^2 > 16 sum x^2, in units of the scaled integers): keep the low digit
-        flags[group * 16 + m] = (P != 0.0f && sq < 2.0f * kDigitRange * kDigitRange) ? 1 : 0;
+        pp.flags[group * 16 + m] = (P != 0.0f && sq < 2.0f * kDigitRange * kDigitRange) ? 1 : 0;
         if (m == 0)
-            for (int z = M; z < 16; ++z) flags[group * 16 + z] = 0;        // rows this batch does not have
+            for (int z = M; z < 16; ++z) pp.flags[group * 16 + z] = 0;     // rows this batch does not have
     }
 #pragma unroll
     for (int j = 0; j < 3; ++j) {
-        int set, cc;
-        digit_slot(mode, nmain, m, j, &set, &cc);
-        if (q4 == 0) scales[((group * 4 + (cc >> 1)) * nsets + set) * 2 + (cc & 1)] = (mode == 2 && j > 0) ? sx * 256.0f : sx;
+        int set, cc, nsets;
+        uint8_t* digits;
+        if (mode == 2 && j == 0) {          // the low digit: its own sets, its own parts of the buffer
+            set = m >> 3;
+            cc = m & 7;
+            nsets = nlow;
+            digits = pp.dlow;
+            if (q4 == 0) pp.slow[((group * 4 + (cc >> 1)) * nsets + set) * 2 + (cc & 1)] = sx;
+        } else {
+            digit_slot(mode, m, j, &set, &cc);
+            nsets = nmain;
+            digits = pp.dmain;
+            if (q4 == 0) pp.smain[((group * 4 + (cc >> 1)) * nsets + set) * 2 + (cc & 1)] = (mode == 2) ? sx * 256.0f : sx;
+        }
         if (ORDER == kOrderNibble) {
             const uint32_t b0 = gather_byte(db[0], db[2], db[4], db[6], j);
             const uint32_t b1 = gather_byte(db[1], db[3], db[5], db[7], j);
@@ -193,35 +223,20 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M
     }
 }
 
-// Where the three parts of a prepared buffer of `groups` 32-k groups start.
-struct PreparedParts {
-    uint8_t* digits;
-    float* scales;
-    uint8_t* flags;
-};
-__host__ __device__ inline PreparedParts prepared_parts(uint8_t* base, size_t groups, int nsets) {
-    PreparedParts p;
-    p.digits = base;
-    p.scales = reinterpret_cast<float*>(base + groups * nsets * 256);
-    p.flags = base + groups * nsets * (256 + 32);
-    return p;
-}
-
 // Block-wide conversion of one row (row index m of an M-row batch) whose K values lie at x_row in
 // global memory (values this thread block wrote itself are visible after the caller's
 // __syncthreads).  THREADS must be a multiple of 32 and K a multiple of 256, so that whole warps
 // take part in every conversion call.  `planes` is the prepared buffer of the INT4 decode kernel.
 template <int THREADS>
-__device__ __forceinline__ void prepare_row_block(const float* x_row, int m, int M, int64_t K, int mode, int nmain, int nsets,
+__device__ __forceinline__ void prepare_row_block(const float* x_row, int m, int M, int64_t K, int mode, int nmain, int nlow,
                                                   uint8_t* __restrict__ planes) {
     const int chunks = static_cast<int>(K / 8);
-    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nsets);
+    const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nmain, nlow);
     for (int c = threadIdx.x; c < chunks; c += THREADS) {
         const float4 a = __ldcg(reinterpret_cast<const float4*>(x_row) + 2 * c);     // L2: coherent with this block's own stores
         const float4 b = __ldcg(reinterpret_cast<const float4*>(x_row) + 2 * c + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nsets, 0.0625f, pp.digits, pp.scales,
-                                     pp.flags);
+        convert_groups<kOrderNibble>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nlow, 0.0625f, pp);
     }
 }
 

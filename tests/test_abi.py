@@ -93,8 +93,9 @@ def test_workspace_queries(sgq):
     assert sgq.linear_workspace_bytes(8, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (6 * 288 + 16)
     assert sgq.linear_workspace_bytes(8, 4, 100, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == 0          # K % 128 != 0: no such path
     assert sgq.linear_workspace_bytes(8, 2048, 4096, 64, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2
-    # an INT4 batch whose planes exceed shared memory is processed in phases over K: scratch for the whole batch
-    assert sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (6 * 288 + 16)
+    # an INT4 batch of more than 8 rows whose planes exceed shared memory runs as blocks of at most 8 rows
+    # that share one scratch: 2 main sets + 1 low set
+    assert sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (3 * 288 + 16)
 
 
 def test_no_cpu_fallback(sgq):
