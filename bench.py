@@ -355,7 +355,7 @@ def nanollama_case(torch, sgq, dev, *, reps: int, warm: int, rank: int = 0, worl
         prompt_d.copy_(prompt_h, non_blocking=True)
         logits = model.prefill(prompt_d)
         toks = torch.empty(batch, n_new, dtype=torch.int64, device=dev)
-        torch.argmax(logits, dim=-1, out=model.tok)
+        model._argmax(logits)
         toks[:, 0].copy_(model.tok)
         if model._graph is None:
             model.capture_decode_graph()          # first (warm-up) generation only

@@ -16,6 +16,8 @@
  *                        KV cache and recomputes every row, models.hpp:262-300) + rotary_embedding
  *   sgqd_silu_mul        nn::SwiGLU gate                    include/sovereigngrad/nn.hpp:151-156
  *                        simd::vec_silu                     include/sovereigngrad/simd.hpp:103-108
+ *   sgqd_embedding       sovereigngrad::embedding           src/ops.cpp:2624-2659
+ *   sgqd_argmax_rows     greedy choice in NanoLLaMA::generate  include/sovereigngrad/models.hpp:291-298
  *
  * Conventions are those of sgq.h: device pointers owned by the caller, `stream` is a cudaStream_t
  * passed as void*, calls enqueue and return an sgq_status, nothing is allocated.
@@ -62,6 +64,16 @@ SGQ_API int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int6
  * prepared_out: as for sgqd_add_rmsnorm, the prepared form of out[rows, hidden]. */
 SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out,
                           size_t prepared_bytes, void* stream);
+
+/* out[i, :] = table[ids[i], :] for rows indices (ids: DEVICE int64).  An id outside [0, vocab) gives a row
+ * of zeros, as in the reference (src/ops.cpp:2643-2649); the table is never read out of bounds. */
+SGQ_API int sgqd_embedding(const float* table, int64_t vocab, int64_t dim, const int64_t* ids, int64_t rows, float* out,
+                           void* stream);
+
+/* out[r] = first index of the strict maximum of x[r, 0..n) (row stride ld), a DEVICE int64 per row: the
+ * reference's greedy choice keeps the first of equal candidates (models.hpp:291-298).  NaN never wins;
+ * a row of NaNs (or n == 0) gives 0. */
+SGQ_API int sgqd_argmax_rows(const float* x, int64_t rows, int64_t n, int64_t ld, int64_t* out, void* stream);
 
 #ifdef __cplusplus
 }

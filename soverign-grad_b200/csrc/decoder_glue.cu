@@ -415,6 +415,65 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(cons
     }
 }
 
+// Embedding lookup: one block per index.  An index outside [0, vocab) yields a row of zeros, as the
+// reference's lookup does (src/ops.cpp:2643-2649); nothing is ever read outside the table.
+__global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ table, int64_t vocab, int64_t dim,
+                                                        const int64_t* __restrict__ ids, float* __restrict__ out, int vec) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t id = ids[blockIdx.x];
+    const bool ok = id >= 0 && id < vocab;
+    float* o = out + blockIdx.x * dim;
+    const float* src = table + (ok ? id : 0) * dim;
+    if (vec) {
+        for (int64_t i = threadIdx.x * 4; i < dim; i += 1024)
+            *reinterpret_cast<float4*>(o + i) = ok ? __ldg(reinterpret_cast<const float4*>(src + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        for (int64_t i = threadIdx.x; i < dim; i += 256) o[i] = ok ? __ldg(src + i) : 0.f;
+    }
+}
+
+// First index of the strict maximum of every row (the reference's greedy choice keeps the first of equal
+// candidates: `if (p > best)`, include/sovereigngrad/models.hpp:291-298).  NaN never wins a comparison; a
+// row without any comparable value yields 0.
+constexpr int kArgmaxThreads = 512;
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const float* __restrict__ x, int64_t n, int64_t ld,
+                                                                    int64_t* __restrict__ out) {
+    __shared__ float sv[kArgmaxThreads / 32];
+    __shared__ long long si[kArgmaxThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* row = x + blockIdx.x * ld;
+    float best = -CUDART_INF_F;
+    long long idx = -1;                                   // -1: nothing seen yet (a -inf entry must still be able to win)
+    for (int64_t i = threadIdx.x; i < n; i += kArgmaxThreads) {
+        const float v = row[i];
+        if (v > best || (idx < 0 && v == best)) { best = v; idx = i; }
+    }
+    auto better = [](float v, long long i, float bv, long long bi) {
+        return i >= 0 && (bi < 0 || v > bv || (v == bv && i < bi));
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < kArgmaxThreads / 32 ? sv[threadIdx.x] : -CUDART_INF_F;
+        idx = threadIdx.x < kArgmaxThreads / 32 ? si[threadIdx.x] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const long long oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = idx < 0 ? 0 : idx;
+    }
+}
+
 int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
     // as many splits as keep every CTA resident at once (one wave), at least 32 keys each, at most
     // the portable cluster size
@@ -541,6 +600,29 @@ int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_he
                                 out, out_stride, s);
     return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0, out,
                            out_stride, s);
+}
+
+int sgqd_embedding(const float* table, int64_t vocab, int64_t dim, const int64_t* ids, int64_t rows, float* out, void* stream) {
+    if (vocab < 0 || dim < 0 || rows < 0 || rows > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad embedding shape");
+    if (rows * dim == 0) return SGQ_OK;
+    if (!table || !ids || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    const int vec = ((dim & 3) == 0 && aligned(table, 16) && aligned(out, 16)) ? 1 : 0;
+    SGQ_CUDA_TRY(launch_kernel(embedding_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                               stream_overlap_enabled(), table, vocab, dim, ids, out, vec));
+    return SGQ_OK;
+}
+
+int sgqd_argmax_rows(const float* x, int64_t rows, int64_t n, int64_t ld, int64_t* out, void* stream) {
+    if (rows < 0 || n < 0 || ld < n || rows > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad argmax shape");
+    if (rows == 0) return SGQ_OK;
+    if (!out || (n > 0 && !x)) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    SGQ_CUDA_TRY(launch_kernel(argmax_rows_kernel, dim3(static_cast<unsigned>(rows)), dim3(kArgmaxThreads), 0,
+                               static_cast<cudaStream_t>(stream), stream_overlap_enabled(), x, n, ld, out));
+    return SGQ_OK;
 }
 
 int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out, size_t prepared_bytes,

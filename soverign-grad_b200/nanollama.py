@@ -11,8 +11,8 @@ and greedy selection (models.hpp:286-298: first index of the strict maximum).
 
 What runs where: every Linear goes through sgq_linear_int4 (decode kernel for the M = batch steps,
 tcgen05 kernel for the prefill); RMSNorm, RoPE + KV-cache store, cache attention and the SiLU gate
-are the sgqd_* kernels of include/sgq_decoder.h; torch supplies device memory, the embedding gather,
-the prefill attention (fp32 math kernels) and argmax.  A decode step touches no host state — the
+the embedding lookup and the greedy argmax are the sgqd_* kernels of include/sgq_decoder.h; torch
+supplies device memory and the prompt's attention (fp32 math kernels).  A decode step touches no host state — the
 cache position lives in device memory — so one step is recorded into a CUDA graph and replayed.
 
 Sharding (world > 1): heads, SwiGLU columns, output features of wo / w_down and the vocabulary are
@@ -27,6 +27,7 @@ from typing import Callable, Optional
 import torch
 
 import contextlib
+import ctypes as C
 
 from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
                linear_int4_prepared, prepared_x_bytes, quantize_int4, quantized_matmul, set_stream_overlap)
@@ -276,9 +277,9 @@ class NanoLlamaInt4:
             return
         lin(x, out, path)
         M, K = x.shape
-        # the decode kernel converts activations inside its CTAs up to 2048 eight-value chunks; larger
+        # the decode kernel converts activations inside its CTAs up to 1024 eight-value chunks; larger
         # batches and the tensor-core path run a conversion kernel first
-        self._count(2 if (M > 16 or M * (K // 8) > 2048) else 1)
+        self._count(2 if (M > 16 or M * (K // 8) > 1024) else 1)
 
     # ---- one pass over t_new new tokens per sequence ---------------------------------------
     def _forward(self, tokens: torch.Tensor, t_new: int, path: int) -> torch.Tensor:
@@ -287,7 +288,8 @@ class NanoLlamaInt4:
         M = B * t_new
         b = self._buffers(M)
         h, n = b["h"], b["n"]
-        torch.index_select(self.embed, 0, tokens, out=h)                       # nn::Embedding lookup
+        # nn::Embedding lookup; an id outside the vocabulary gives a row of zeros, as in the reference
+        check(lib.sgqd_embedding(_ptr(self.embed), c.vocab, c.dim, _ptr(tokens), M, _ptr(h), _stream()), "sgqd_embedding")
         self._count()
         delta = None
         p_dim, p_hid = b["p_dim"], b["p_hid"]          # None for batches the decode kernel does not take
@@ -367,14 +369,10 @@ class NanoLlamaInt4:
         B, P = prompt.shape
         if B != self.batch or P > self.cfg.max_seq:
             raise ValueError("prompt shape does not fit the model's batch / max_seq")
-        # checked on the host: an out-of-range id must never reach the gather kernel (the reference's
-        # embedding returns zeros for such ids, src/ops.cpp:2624-2659; here it is an error)
-        if P and (int(prompt.min()) < 0 or int(prompt.max()) >= self.cfg.vocab):
-            raise ValueError("token id outside [0, vocab)")
         self._launches = 0
         self.reset()
         with self._overlapped():
-            n = self._forward(prompt.reshape(-1).to(self.device), P, self.prefill_path)
+            n = self._forward(prompt.reshape(-1).to(self.device, dtype=torch.int64).contiguous(), P, self.prefill_path)
             last = n.view(B, P, self.cfg.dim)[:, -1].contiguous()
             logits = self._logits(last, self.decode_path)
         self.pos.fill_(P)
@@ -385,7 +383,7 @@ class NanoLlamaInt4:
         advances the position and returns the logits of the next token [batch, vocab]."""
         self._launches = 0
         with self._overlapped():
-            n = self._forward(tokens, 1, self.decode_path)
+            n = self._forward(tokens.to(self.device, dtype=torch.int64).contiguous(), 1, self.decode_path)
             logits = self._logits(n, self.decode_path, self._final_planes)
         self.pos.add_(1)
         self._count()
@@ -393,10 +391,15 @@ class NanoLlamaInt4:
 
     def _greedy_step(self):
         logits = self.decode_step(self.tok)
-        torch.argmax(logits, dim=-1, out=self.tok)       # first index of the maximum (models.hpp:289-296)
-        self._count(2)
+        self._argmax(logits)
+        self._count()
         self.launches_per_decode_step = self._launches
         return logits
+
+    def _argmax(self, logits: torch.Tensor):
+        """Greedy choice into self.tok: first index of the strict maximum (models.hpp:291-298)."""
+        check(lib.sgqd_argmax_rows(_ptr(logits), logits.shape[0], logits.shape[1], logits.stride(0), _ptr(self.tok), _stream()),
+              "sgqd_argmax_rows")
 
     def capture_decode_graph(self):
         """Records one greedy decode step (token buffer -> next token buffer) into a CUDA graph."""
@@ -425,7 +428,7 @@ class NanoLlamaInt4:
         logits = self.prefill(prompt)
         out = torch.empty(B, n_new, dtype=torch.int64, device=self.device)
         kept = [logits.clone()] if keep_logits else None
-        torch.argmax(logits, dim=-1, out=self.tok)
+        self._argmax(logits)
         out[:, 0].copy_(self.tok)
         use_graph = use_graph and (self.world == 1 or self.exchange == "peer") and not keep_logits
         if use_graph and self._graph is None:
@@ -438,4 +441,9 @@ class NanoLlamaInt4:
                 if keep_logits:
                     kept.append(lg.clone())
             out[:, s].copy_(self.tok)
+        # A bounded device-side wait that ran out (a rank that never arrived at an exchange, a pipeline stall)
+        # leaves incomplete outputs behind: it must reach the caller as an error, not as tokens.
+        word = C.c_uint(0)
+        if lib.sgq_device_status(C.byref(word), 1) != 0:
+            raise RuntimeError(f"a device-side wait timed out during generation (status word 0x{word.value:08x}); the output is invalid")
         return (out, kept) if keep_logits else out

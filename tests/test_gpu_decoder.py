@@ -190,10 +190,48 @@ def test_attn_decode_position_out_of_range_stores_nothing(sgq):
     assert torch.equal(kc, k0) and torch.equal(vc, v0) and torch.isfinite(out).all()
 
 
+def test_embedding_lookup_and_out_of_range_ids(sgq):
+    """Rows of the table by index; an id outside [0, vocab) gives zeros as the reference's lookup does."""
+    vocab, dim = 37, 260
+    r = np.random.default_rng(3)
+    table = r.standard_normal((vocab, dim)).astype(np.float32)
+    ids = np.array([0, 36, 5, -1, 37, 10 ** 12, 5, -(10 ** 12)], np.int64)
+    out = torch.full((len(ids), dim), float("nan"), device="cuda")
+    td, idd = dev(table), dev(ids, torch.int64)
+    sgq.check(sgq.lib.sgqd_embedding(ptr(td), vocab, dim, ptr(idd), len(ids), ptr(out), stream()))
+    want = np.where(((ids >= 0) & (ids < vocab))[:, None], table[np.clip(ids, 0, vocab - 1)], 0.0).astype(np.float32)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    odd = torch.full((2, 7), float("nan"), device="cuda")                   # a width that is not a multiple of 4
+    t7 = dev(table[:, :7].copy())
+    sgq.check(sgq.lib.sgqd_embedding(ptr(t7), vocab, 7, ptr(idd), 2, ptr(odd), stream()))
+    np.testing.assert_array_equal(odd.cpu().numpy(), table[[0, 36], :7])
+
+
+def test_argmax_rows_first_strict_maximum(sgq):
+    """The reference's greedy choice: `if (p > best)` keeps the first of equal candidates."""
+    r = np.random.default_rng(4)
+    n = 32000
+    x = r.standard_normal((6, n)).astype(np.float32)
+    x[1, 700] = x[1, 31000] = 9.0                                           # a tie: the first index wins
+    x[2, :] = -np.inf
+    x[2, 123] = -1e30                                                       # everything else is -inf
+    x[3, :] = 0.25                                                          # all equal -> 0
+    x[4, 5] = np.nan
+    x[4, 6] = 50.0                                                          # NaN never wins
+    x[5, :] = -np.inf                                                       # nothing but -inf -> 0
+    out = torch.full((6,), -7, dtype=torch.int64, device="cuda")
+    xd = dev(x)
+    sgq.check(sgq.lib.sgqd_argmax_rows(ptr(xd), 6, n, n, ptr(out), stream()))
+    got = out.cpu().numpy()
+    assert got.tolist() == [int(np.argmax(x[0])), 700, 123, 0, 6, 0]
+    wide = dev(np.concatenate([x, x], axis=1))                              # row stride larger than the row
+    sgq.check(sgq.lib.sgqd_argmax_rows(ptr(wide), 6, 100, 2 * n, ptr(out), stream()))
+    assert out.cpu().numpy().tolist() == [int(np.nanargmax(x[i, :100])) if i not in (2, 3, 5) else 0 for i in range(6)]
+
+
 # ---- the whole model ------------------------------------------------------------------------------
-def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3, overlap=True):
-    cfg = nl.NanoLlamaConfig(dim=256, n_layers=2, n_heads=2, hidden=512, vocab=512, max_seq=64)
-    B = 2
+def tiny_model(nl, port, *, prompt_len, n_new, prefill_path, seed=3, overlap=True, cfg=None, B=2):
+    cfg = cfg or nl.NanoLlamaConfig(dim=256, n_layers=2, n_heads=2, hidden=512, vocab=512, max_seq=64)
     r = np.random.default_rng(seed)
     floats = {}
 
@@ -237,6 +275,27 @@ def test_greedy_decode_matches_full_recompute(sgq, nl, port, prompt_len, n_new, 
         decided = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.max(np.abs(ref))
         assert (tokens[decided, s] == no.greedy(ref)[decided]).all(), f"token of step {s}"
     assert sgq.device_status() == 0
+
+
+@pytest.mark.parametrize("prefill,tol", [("simt", TOL_FP32), ("tc_bf16", TOL_BF16)])
+def test_greedy_decode_at_benchmark_dimensions(sgq, nl, port, prefill, tol):
+    """The benchmarked model's own dimensions (dim 2048, 16 heads x 128, SwiGLU 5632, vocab 32000, batch 8)
+    with one block and a short prompt, so that the full-recompute numpy oracle stays affordable: every
+    step's logits within 1e-3 (fp32 prefill) / 2e-2 (bf16 tensor-core prefill) of the oracle."""
+    cfg = nl.NanoLlamaConfig(dim=2048, n_layers=1, n_heads=16, hidden=5632, vocab=32000, max_seq=32)
+    path = {"simt": sgq.PATH_SIMT, "tc_bf16": sgq.PATH_TC_BF16}[prefill]
+    prompt_len, n_new = 8, 3                                   # 8 sequences x 8 tokens = 64 rows: the tensor-core path's minimum
+    model, prompt, tokens, logits, want = tiny_model(nl, port, prompt_len=prompt_len, n_new=n_new, prefill_path=path, seed=5,
+                                                      cfg=cfg, B=8)
+    for s in range(n_new):
+        ref = want[:, prompt_len - 1 + s]
+        assert norm_err(logits[s], ref) <= tol, (f"step {s}", norm_err(logits[s], ref))
+        top2 = np.sort(ref, axis=-1)[:, -2:]
+        decided = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.max(np.abs(ref))
+        assert (tokens[decided, s] == no.greedy(ref)[decided]).all(), f"token of step {s}"
+    assert sgq.device_status() == 0
+    del model
+    torch.cuda.empty_cache()
 
 
 def test_overlapped_launches_agree_with_serial_ones(sgq, nl, port):
