@@ -11,8 +11,13 @@ weights from HBM).  Metric: achieved HBM GB/s = algorithmic bytes / time, whole 
 N > 1 (torchrun): weak scaling of a column-sharded layer — every rank holds its own
 [11008,4096] column slice (N_total = 11008 * ranks) and the full-width output is assembled on every
 rank per forward: the decode kernel stores its [M, 11008] slice into all ranks' outputs over NVLink
-peer mappings and a barrier kernel follows (`--nccl`: local forward + NCCL all-gather + interleave
-instead); value = bytes streamed by all ranks / max-over-ranks device time.
+peer mappings and signals; the next forward's kernel waits for all ranks' signals in its prologue
+(one NVLink round trip, no extra launch; one barrier kernel ends each step).  `--nccl`: local forward
++ NCCL all-gather + interleave instead.  value = bytes streamed by all ranks / max-over-ranks device
+time.  Before anything is timed the gathered output of one forward is compared, bit for bit, with the
+NCCL all-gather of the single-GPU results of the slices ("sharded_check").  `extra` then carries the
+column-sharded configurations: W[28672,8192] split over the ranks (strong scaling, M = 1 and 16) and
+the NanoLLaMA-INT4 generation with every linear split over the ranks.
 
 `--impl reference` times the reference's own CPU QuantizedLinear forward (oracle/_ref, the
 unmodified sources compiled for the host) on the same workload: one forward per step.
@@ -35,9 +40,22 @@ K_DIM, N_DIM, GROUP = 4096, 11008, 32
 METRIC, UNIT = "int4_g32_decode_gemv_hbm_gbs", "GB/s"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from the ncu capture summarised
-# in profiles/gemv_int4_nk_kernel__config2_M1.md (M = 1; the output is 44 KB and stays in L2)
-NCU_TRAFFIC_PER_LAUNCH = {1: 28258560.0}
+def ncu_traffic(kernel: str, m: int):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of `kernel` at batch m, as recorded by the
+    committed profiler summaries: a line `traffic_bytes_per_launch <kernel> M=<m>: <bytes>` in a file of the
+    profiles directory.  None when there is no such record."""
+    import glob
+    import re
+    pat = re.compile(r"traffic_bytes_per_launch\s+" + re.escape(kernel) + r"\s+M=" + str(m) + r":\s*([0-9.eE+]+)")
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*"))):
+        try:
+            with open(path) as f:
+                hit = pat.search(f.read())
+        except OSError:
+            continue
+        if hit:
+            return float(hit.group(1))
+    return None
 
 
 def gemv_bytes(M: int, K: int = K_DIM, N: int = N_DIM, bits: int = 4) -> int:
@@ -117,7 +135,10 @@ def host_cores():
         return os.cpu_count() or 1
 
 
-def reference_linear(M: int):
+def reference_linear(M: int, native_kn: bool = False):
+    """A timer for the reference's own CPU forward on all host cores.  Default: the weight as this benchmark
+    stores it, W[N,K] (the reference needs dequantize + transpose + matmul for it); native_kn: the reference
+    module's own layout W[K,N] (dequantize + matmul, src/quantization.cpp:199-206)."""
     import numpy as np
     import oracle
     ref = oracle.load_ref()
@@ -125,8 +146,14 @@ def reference_linear(M: int):
     w = (rng.standard_normal((N_DIM, K_DIM)) * 0.02).astype(np.float32)
     x = rng.standard_normal((M, K_DIM)).astype(np.float32)
     if ref is not None:
-        lin = ref.linear(w, oracle.LAYOUT_NK, 4, 0, GROUP, None)
+        ref.set_num_threads(host_cores())          # a launcher may have exported OMP_NUM_THREADS=1
+        if native_kn:
+            lin = ref.linear(np.ascontiguousarray(w.T), oracle.LAYOUT_KN, 4, 0, GROUP, None)
+        else:
+            lin = ref.linear(w, oracle.LAYOUT_NK, 4, 0, GROUP, None)
         return "reference", ref.num_threads(), (lambda iters: lin.time_forward(x, iters, with_bias=False))
+    if native_kn:
+        raise RuntimeError("the compiled reference is not available")
     port = oracle.Port()                                   # the reference was never compiled here
     packed, scales = port.quantize_int4(w, GROUP)
 
@@ -149,6 +176,15 @@ def run_reference(args):
     per = timer(args.steps)
     wall = time.perf_counter() - t0
     value = gemv_bytes(1) / per / 1e9
+    native = None
+    try:
+        _, _, timer_kn = reference_linear(1, native_kn=True)
+        timer_kn(1)
+        per_kn = timer_kn(max(2, min(args.steps, 10)))
+        native = {"value": gemv_bytes(1) / per_kn / 1e9, "unit": UNIT, "ms_per_forward": per_kn * 1e3,
+                  "what": "the same weight in the reference module's own [K,N] layout: dequantize + matmul, no transpose"}
+    except Exception as e:  # noqa: BLE001
+        native = {"error": f"{type(e).__name__}: {e}"[:200]}
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -157,7 +193,7 @@ def run_reference(args):
                                "(dequantize + fp32 matmul, as the reference does per call) per step",
                    "M": 1, "K": K_DIM, "N": N_DIM, "group": GROUP},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": f"{args.steps} forwards of the full workload, {wall:.1f} s"},
+                         "sample": f"{args.steps} forwards of the full workload, {wall:.1f} s", "native_layout_kn": native},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -327,6 +363,57 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
     return out
 
 
+def sharded_extras(torch, sgq, sh, dist, dev, rank: int, world: int, peaks):
+    """N > 1: the column-sharded configurations.  W[28672,8192] (benchmark configuration 5) split by rows over
+    the ranks (strong scaling: the same total work at every N), M = 1 and 16, full-width output assembled on
+    every rank per forward by the fused exchange; and the NanoLLaMA-INT4 generation (configuration 4) with every
+    linear split over the ranks.  Every rank takes part; times are the maximum over the ranks."""
+    out = {}
+    N, K = 28672, 8192
+    n0, n1 = sh.shard_bounds(N, world, rank)
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    slice_bytes = (n1 - n0) * K // 2 + (n1 - n0) * K // GROUP * 4
+    copies = max(2, min(12, int(300e6 // slice_bytes) + 1))          # rotate so that every forward streams from HBM
+    qs = [sgq.quantize_int4(torch.randn(n1 - n0, K, device=dev, generator=g) * 0.02, GROUP) for _ in range(copies)]
+    for M in (1, 16):
+        try:
+            ex = sh.PeerExchange(M, N, dev)
+            lins = [sh.PeerShardedLinear(q, None, N, ex, deferred=True) for q in qs]
+            x = torch.randn(M, K, device=dev, generator=g)
+            inner = 48
+            graph = make_graph(torch, lambda: ([lins[i % copies](x) for i in range(inner)], ex.barrier()))
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item()) / (10 * inner) * 1e3
+            nbytes = gemv_bytes(M, K, N)
+            out[f"sharded_int4_g32_M{M}_28672x8192"] = {
+                "us_per_forward": us, "aggregate_gbs": nbytes / us / 1e3, "n_local": n1 - n0, "weight_copies": copies,
+                "frac_of_measured_hbm_all_gpus": nbytes / us / 1e3 / (world * peaks["hbm_gbs"]), "scaling": "strong",
+                "exchange": "peer stores from the decode kernel, wait in the next forward's prologue"}
+            del ex, lins, graph
+        except Exception as e:  # noqa: BLE001
+            out[f"sharded_int4_g32_M{M}_28672x8192"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.synchronize()
+        dist.barrier()
+    del qs
+    torch.cuda.empty_cache()
+    try:
+        out["nanollama_int4_config4_sharded"] = nanollama_case(torch, sgq, dev, reps=2, warm=1, rank=rank, world=world, dist=dist)
+    except Exception as e:  # noqa: BLE001
+        out["nanollama_int4_config4_sharded"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    return out
+
+
 def nanollama_case(torch, sgq, dev, *, reps: int, warm: int, rank: int = 0, world: int = 1, dist=None,
                    batch: int = 8, prompt_len: int = 512, n_new: int = 128):
     """benchmark configuration 4: NanoLLaMA-INT4 (dim 2048, 16 blocks, 16 heads, SwiGLU 5632, vocab 32000,
@@ -450,8 +537,6 @@ def run_ours(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
-    if world > 1:
-        args.no_overlap = True      # measured on 2 GPUs: the per-forward barrier leaves nothing to overlap (17.3 us serial, 19.2 us overlapped)
     sgq.set_stream_overlap(0 if args.no_overlap else args.overlap_mode)     # consecutive forwards overlap their prologue and first weight tiles
     M, copies, lps = args.M, args.copies, args.launches_per_step
     if args.only:
@@ -493,8 +578,9 @@ def run_ours(args):
             args.nccl = True
             sharded = [sh.cuda_sharded_linear(q, None, world * N_DIM, path=path) for q in weights]
         else:
-            # barrier as its own small kernel: measured faster than the in-kernel form (17.3 vs 19.6 us per forward at N=2)
-            sharded = [sh.PeerShardedLinear(q, None, world * N_DIM, exchange, fused_barrier=False) for q in weights]
+            # deferred exchange: a forward stores its slices into every rank's output and signals; the NEXT forward
+            # waits for all ranks in its prologue (one NVLink round trip, no second launch)
+            sharded = [sh.PeerShardedLinear(q, None, world * N_DIM, exchange, deferred=True) for q in weights]
     if world > 1 and args.nccl and lps > 200:
         lps = 200                   # eager NCCL launches: keep a step short
     last = {}
@@ -505,12 +591,37 @@ def run_ours(args):
         else:
             sgq.quantized_matmul(x, weights[i % copies], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
 
+    def drain():
+        """Ends a sequence of deferred exchanges: after this barrier the last outputs are whole on every rank."""
+        if sharded and exchange is not None:
+            exchange.barrier()
+
+    # ---- N > 1: the gathered output must equal the single-GPU results of the slices, bit for bit
+    sharded_check = None
+    if world > 1:
+        forward(0)
+        drain()
+        torch.cuda.synchronize()
+        y_sharded = last["y"].clone()
+        sgq.quantized_matmul(x, weights[0], None, layout=sgq.LAYOUT_NK, path=path, out=y_local, workspace=ws)
+        parts = [torch.empty_like(y_local) for _ in range(world)]
+        dist.all_gather(parts, y_local)                  # NCCL as the checker only
+        ok = torch.tensor([1.0 if torch.equal(y_sharded, torch.cat(parts, dim=1)) else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        sharded_check = "ok" if float(ok.item()) == 1.0 else "MISMATCH"
+        if sharded_check != "ok":
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "sharded_check": sharded_check,
+                                  "error": "gathered output differs from the single-GPU results of the slices"}), flush=True)
+            dist.destroy_process_group()
+            sys.exit(3)
+
     # collectives are launched eagerly: capturing a thousand NCCL calls into one graph buys nothing
     # (the all-gather latency dominates a sharded decode forward) and is fragile across NCCL versions
     use_graph = not args.no_graph and (world == 1 or not args.nccl)
     if use_graph:
         try:
-            graph = make_graph(torch, lambda: [forward(i) for i in range(lps)])
+            graph = make_graph(torch, lambda: ([forward(i) for i in range(lps)], drain()))
         except Exception as e:  # noqa: BLE001  (e.g. a collective that cannot be captured)
             sys.stderr.write(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); launching eagerly\n")
             use_graph = False
@@ -522,6 +633,7 @@ def run_ours(args):
         else:
             for i in range(lps):
                 forward(s * lps + i)
+            drain()
 
     for s in range(args.warmup):
         step(s)
@@ -562,11 +674,13 @@ def run_ours(args):
         def e2e_forward(i):
             x.copy_(xh, non_blocking=True)
             forward(i)
+            if sharded and exchange is not None:
+                drain()                                  # the copy below reads this forward's gathered output
             yh.copy_(last["y"] if sharded else y_local, non_blocking=True)
         e2e_graph = None
         if use_graph:
             try:
-                e2e_graph = make_graph(torch, lambda: [e2e_forward(i) for i in range(lps)])
+                e2e_graph = make_graph(torch, lambda: ([e2e_forward(i) for i in range(lps)], drain()))
             except Exception as e:  # noqa: BLE001
                 sys.stderr.write(f"[bench] e2e graph capture failed ({type(e).__name__}: {e}); launching eagerly\n")
                 torch.cuda.synchronize()
@@ -577,6 +691,7 @@ def run_ours(args):
             else:
                 for i in range(lps):
                     e2e_forward(s * lps + i)
+                drain()
         for s in range(3):
             e2e_step(s)
         torch.cuda.synchronize()
@@ -598,6 +713,12 @@ def run_ours(args):
                "note": "weights are resident layer parameters; per forward x comes from pinned host memory and y returns to it"}
 
     status = sgq.device_status()
+    extra_sharded = None
+    if world > 1 and not args.no_extras and not args.nccl:
+        del sharded, weights
+        torch.cuda.empty_cache()
+        extra_sharded = sharded_extras(torch, sgq, sh, dist, dev, rank, world, peaks)
+        weights = []
     if rank != 0:
         if dist:
             dist.destroy_process_group()
@@ -615,6 +736,13 @@ def run_ours(args):
                    "sample": f"{iters} CPU forwards of the same W[11008,4096], M={M} workload "
                              f"({time.perf_counter() - t0:.1f} s); each dequantizes the whole weight, as the reference does",
                    "ms_per_forward": per * 1e3}
+            try:        # the same weight in the reference module's own [K,N] layout (no transpose before the matmul)
+                _, _, timer_kn = reference_linear(M, native_kn=True)
+                timer_kn(1)
+                per_kn = timer_kn(max(2, min(40, int(4.0 / max(t1, 1e-4)))))
+                cpu["native_layout_kn"] = {"value": gemv_bytes(M) / per_kn / 1e9, "unit": UNIT, "ms_per_forward": per_kn * 1e3}
+            except Exception as e:  # noqa: BLE001
+                cpu["native_layout_kn"] = {"error": f"{type(e).__name__}: {e}"[:200]}
         except Exception as e:  # noqa: BLE001
             cpu = {"error": f"{type(e).__name__}: {e}"[:200]}
 
@@ -625,7 +753,8 @@ def run_ours(args):
         "config": {"workload": f"config2: INT4 g=32 decode GEMV, W[{N_DIM},{K_DIM}] stored [N,K], X[{M},{K_DIM}] fp32"
                                + (f"; column-sharded, N_total={world * N_DIM}, "
                                   + ("NCCL all-gather of output slices per forward" if args.nccl else
-                                     "output slices stored into every GPU's output by the decode kernel (NVLink peer stores) + barrier kernel")
+                                     "output slices stored into every GPU's output by the decode kernel (NVLink peer stores), "
+                                     "signal at its end, wait in the next forward's prologue; one barrier kernel per step")
                                   if world > 1 else ""),
                    "M": M, "K": K_DIM, "N_per_gpu": N_DIM, "group": GROUP, "launches_per_step": lps, "weight_copies": copies,
                    "l2": f"rotating {copies} weight sets ({copies * gemv_bytes(0) / 1e6:.0f} MB) > 126 MB L2",
@@ -635,12 +764,16 @@ def run_ours(args):
                                       "fetched while the previous forward finishes") if not args.no_overlap else "off"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
-                     "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC_PER_LAUNCH.get(M) if world == 1 else None,
+                     "traffic": args.traffic if args.traffic is not None else ncu_traffic("gemv_int4_nk_kernel", M) if world == 1 else None,
                      "peak_source": peaks["source"], "kernel": "gemv_int4_nk_kernel",
                      "launch_us": launch_ms * 1e3},
-        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * (2 if world > 1 else 1), "clocks": clocks,
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches + (args.steps if world > 1 else 0), "clocks": clocks,
         "device_status_word": status,
     }
+    if sharded_check is not None:
+        line["sharded_check"] = sharded_check
+    if extra_sharded is not None:
+        line["extra"] = extra_sharded
     if world == 1 and not args.no_extras:
         line["extra"] = extras(torch, sgq, peaks, weights)
         del weights
@@ -664,7 +797,7 @@ def main():
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--copies", type=int, default=10)
     ap.add_argument("--launches-per-step", type=int, default=1000)
-    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report (from profiles/)")
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch to report instead of the recorded figure")
     ap.add_argument("--only", default=None, help="run just this secondary case (a key of `extra`), eagerly")
     ap.add_argument("--only-graph", action="store_true", help="with --only: time graph replays instead of a few eager launches")
     ap.add_argument("--no-extras", action="store_true")

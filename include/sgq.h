@@ -188,6 +188,22 @@ SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int6
                                       int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
                                       void* const* signals, int rank, void* local_state, void* stream);
 
+/* The same forward with the wait taken out of the producer.  The kernel stores its slices into every
+ * rank's output and, at its end, only SIGNALS (its epoch, one store per rank); it does not wait for
+ * the other ranks.  Instead every kernel launched through this entry point first waits, in its
+ * prologue, until all ranks have signalled the exchanges this GPU has already finished — one NVLink
+ * round trip that overlaps the kernel's own start-up and weight prefetch, and no extra launch.
+ * Consequences for the caller:
+ *  - the outputs of call i are whole on this GPU once a LATER call on the same signals (this entry
+ *    point or sgq_peer_barrier) has been enqueued behind it and has run; end a sequence with
+ *    sgq_peer_barrier before reading the last outputs;
+ *  - as with the other form, alternate between two sets of output buffers;
+ *  - signals, rank and local_state are required (same objects as for sgq_peer_barrier). */
+SGQ_API int sgq_linear_int4_allgather_deferred(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
+                                               const float* scales, const float* bias, float* const* y_ranks, int world,
+                                               int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
+                                               void* const* signals, int rank, void* local_state, void* stream);
+
 /* The same exchange for a slice that some other kernel produced: src[M, n_local] (this GPU) is
  * stored into y_ranks[r][m * ldy + n_offset + n] of every rank r.  Follow with sgq_peer_barrier. */
 SGQ_API int sgq_peer_scatter(const float* src, int64_t M, int64_t n_local, float* const* y_ranks, int world, int64_t ldy,

@@ -33,7 +33,7 @@ EXPORTS = [
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
     "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared", "sgq_set_stream_overlap",
-    "sgq_linear_int4_allgather", "sgq_peer_barrier", "sgq_peer_scatter", "sgq_set_peer_wait_budget",
+    "sgq_linear_int4_allgather", "sgq_linear_int4_allgather_deferred", "sgq_peer_barrier", "sgq_peer_scatter", "sgq_set_peer_wait_budget",
 ]
 
 # every symbol include/sgq_decoder.h declares
@@ -77,6 +77,7 @@ def _load() -> C.CDLL:
     lib.sgq_set_peer_wait_budget.argtypes = [C.c_uint]
     lib.sgq_set_peer_wait_budget.restype = C.c_uint
     lib.sgq_linear_int4_allgather.argtypes = [p, i64, i64, i64, p, p, p, C.POINTER(p), i32, i64, i64, p, sz, C.POINTER(p), i32, p, p]
+    lib.sgq_linear_int4_allgather_deferred.argtypes = lib.sgq_linear_int4_allgather.argtypes
     lib.sgq_peer_barrier.argtypes = [C.POINTER(p), i32, i32, p, p]
     lib.sgq_peer_scatter.argtypes = [p, i64, i64, C.POINTER(p), i32, i64, i64, p]
     lib.sgq_prepared_x_bytes.restype = sz

@@ -385,9 +385,9 @@ int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes, int64_
     return launch_linear_gemv_prepared(a);
 }
 
-int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed, const float* scales,
-                              const float* bias, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset, void* workspace,
-                              size_t workspace_bytes, void* const* signals, int rank, void* local_state, void* stream) {
+static int linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed, const float* scales,
+                                 const float* bias, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset, void* workspace,
+                                 size_t workspace_bytes, void* const* signals, int rank, void* local_state, void* stream, int deferred) {
     if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
     if (n_offset < 0 || ldy < n_offset + N_local) return bad(SGQ_ERR_BAD_SHAPE, "ldy < n_offset + N_local");
     if (!y_ranks) return bad(SGQ_ERR_NULL_POINTER, "y_ranks is NULL");
@@ -407,11 +407,29 @@ int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_lo
         a.peers.rank = rank;
         a.peers.state = static_cast<unsigned long long*>(local_state);
         a.peers.poll_budget = peer_wait_budget();
+        a.peers.deferred = deferred;
+    } else if (deferred) {
+        return bad(SGQ_ERR_NULL_POINTER, "the deferred exchange needs signals and local_state");
     }
     a.y = a.peers.p[0];
     a.ldy = ldy;
     // validate_linear wants ldy >= N for the single-output case; here rows are ldy apart and N_local wide
     return run_linear(a, SGQ_PATH_GEMV);
+}
+
+int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed, const float* scales,
+                              const float* bias, float* const* y_ranks, int world, int64_t ldy, int64_t n_offset, void* workspace,
+                              size_t workspace_bytes, void* const* signals, int rank, void* local_state, void* stream) {
+    return linear_int4_allgather(x, M, K, N_local, packed, scales, bias, y_ranks, world, ldy, n_offset, workspace, workspace_bytes,
+                                 signals, rank, local_state, stream, 0);
+}
+
+int sgq_linear_int4_allgather_deferred(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
+                                       const float* scales, const float* bias, float* const* y_ranks, int world, int64_t ldy,
+                                       int64_t n_offset, void* workspace, size_t workspace_bytes, void* const* signals, int rank,
+                                       void* local_state, void* stream) {
+    return linear_int4_allgather(x, M, K, N_local, packed, scales, bias, y_ranks, world, ldy, n_offset, workspace, workspace_bytes,
+                                 signals, rank, local_state, stream, 1);
 }
 
 int sgq_interleave_slices(const float* src, int64_t world, int64_t M, int64_t n_local, float* dst, int64_t ldd,

@@ -384,7 +384,9 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (ticket == gridDim.x - 1) {
                 if (lane == 0) *counter = 0;          // re-armed for the next launch, which counts only at its own end
                 int late = 0;
-                if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late, peers.poll_budget) && lane == 0)
+                if (peers.deferred)                   // the next kernel on these signals waits, in its prologue
+                    peer_signal(peers.sig, peers.rank, peers.n, peers.state, lane);
+                else if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late, peers.poll_budget) && lane == 0)
                     report(kDevErrPeerWait, 0x10000u);
             }
         }
@@ -393,6 +395,14 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     // ---------------- consumers ----------------
     bool alive = true;   // false after a wait ran out: skip the math but keep every barrier balanced
+    if (peers.n > 0 && peers.deferred && peers.sig[0] != nullptr) {
+        // Deferred exchange: the kernels before this one only signalled.  Before this kernel reads activations
+        // that other GPUs may have stored here, or stores into buffers other GPUs may still read, every rank
+        // must have finished the exchanges this GPU has finished (its own epoch, written by the kernel before).
+        if (!peer_wait_epoch(peers.sig[peers.rank], peers.n, peers.state, lane, peers.poll_budget)) {
+            if (lane == 0) report(kDevErrPeerWait, 0x20000u);
+        }
+    }
     if (!prepared) {
         // Activations -> digit planes inside the CTA (small batches, one phase).  A warp converts 256 k
         // per iteration; M * K / 8 is a multiple of 32, so whole warps are in or out.
@@ -739,7 +749,8 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
                 sub.x = a.x + m0 * a.K;
                 sub.y = a.y + m0 * a.ldy;
                 for (int r = 0; r < sub.peers.n; ++r) sub.peers.p[r] = a.peers.p[r] + m0 * a.ldy;
-                if (m0 + sub.M < a.M) sub.peers.sig[0] = nullptr;     // a fused barrier belongs to the last block only
+                // a fused barrier belongs to the last block only (the deferred form signals and waits per block)
+                if (m0 + sub.M < a.M && !a.peers.deferred) sub.peers.sig[0] = nullptr;
                 const int rc = launch_gemv_impl(sub, false);
                 if (rc != SGQ_OK) return rc;
             }

@@ -97,6 +97,8 @@ struct PeerOut {
     int rank;
     unsigned long long* state;
     unsigned int poll_budget;   // polls after which a wait for a peer gives up (peer_wait_budget())
+    int deferred;               // 1: the tail only signals; the wait for the other ranks happens in the prologue of the
+                                // next kernel that uses the same signals (a kernel launched with deferred = 1 itself)
 };
 
 // Polls a device-side wait for another GPU may spend before it gives up (sgq_set_peer_wait_budget);
@@ -104,6 +106,43 @@ struct PeerOut {
 unsigned int peer_wait_budget();
 
 #ifdef __CUDACC__
+// One warp: publish this GPU's next epoch to every rank (everything this GPU stored before, peer stores
+// included, is visible to a rank that then sees the epoch).  No waiting.
+__device__ __forceinline__ void peer_signal(unsigned long long* const* sig, int rank, int world, unsigned long long* local_epoch,
+                                            int lane) {
+    unsigned long long epoch = 0;
+    if (lane == 0) {
+        epoch = *local_epoch + 1;
+        *local_epoch = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    __threadfence_system();
+    if (lane < world) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(sig[lane] + rank), "l"(epoch) : "memory");
+}
+
+// One warp: wait (bounded) until every rank has published at least the epoch this GPU itself has reached,
+// i.e. until every rank has finished the exchanges this GPU has finished.  Returns false on a timeout.
+__device__ __forceinline__ bool peer_wait_epoch(const unsigned long long* mine, int world, const unsigned long long* local_epoch,
+                                                int lane, unsigned int poll_budget) {
+    unsigned long long epoch;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(epoch) : "l"(local_epoch) : "memory");
+    bool ok = true;
+    if (lane < world) {
+        unsigned int polls = 0;
+        for (;;) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine + lane) : "memory");
+            if (v >= epoch) break;
+            if (++polls > poll_budget) {
+                ok = false;
+                break;
+            }
+            if (polls > 64) __nanosleep(polls > 4096 ? 400 : 100);
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
 // One warp: publish this GPU's next epoch to every rank and wait (bounded) until every rank has
 // published it here.  Returns false if a peer did not arrive in time.
 __device__ __forceinline__ bool peer_signal_and_wait(unsigned long long* const* sig, int rank, int world,

@@ -146,9 +146,12 @@ class PeerShardedLinear:
     barrier between the ranks in its own tail (fused_barrier) or as a second small kernel.  No
     collective library on the data path."""
 
-    def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange, fused_barrier: bool = True):
+    def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange, fused_barrier: bool = True,
+                 deferred: bool = False):
         from . import Workspace
-        self.fused_barrier = fused_barrier
+        # deferred: the kernel only signals at its end and the NEXT forward on this exchange waits in its prologue
+        # (sgq_linear_int4_allgather_deferred); the caller ends a sequence with exchange.barrier()
+        self.fused_barrier, self.deferred = fused_barrier or deferred, deferred
         self.q, self.bias, self.n_total, self.ex = q_local, bias_local, n_total, exchange
         self.n_local = q_local.original_shape[0]
         self.n0, self.n1 = shard_bounds(n_total, exchange.world, exchange.rank)
@@ -162,11 +165,11 @@ class PeerShardedLinear:
         i = self.ex.next_buffer()
         need = linear_workspace_bytes(4, M, K, self.n_local, LAYOUT_NK, PATH_GEMV)
         ws = self.ws.get(need) if need else None
-        check(lib.sgq_linear_int4_allgather(_ptr(x), M, K, self.n_local, _ptr(self.q.qdata), _ptr(self.q.scales), _ptr(self.bias),
-                                            self.ex.y_ranks(i), self.ex.world, self.n_total, self.n0,
-                                            _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0,
-                                            self.ex._signals if self.fused_barrier else None, self.ex.rank, _ptr(self.ex._epoch),
-                                            _stream()),
+        fn = lib.sgq_linear_int4_allgather_deferred if self.deferred else lib.sgq_linear_int4_allgather
+        check(fn(_ptr(x), M, K, self.n_local, _ptr(self.q.qdata), _ptr(self.q.scales), _ptr(self.bias),
+                 self.ex.y_ranks(i), self.ex.world, self.n_total, self.n0,
+                 _ptr(ws) if ws is not None else None, ws.numel() if ws is not None else 0,
+                 self.ex._signals if self.fused_barrier else None, self.ex.rank, _ptr(self.ex._epoch), _stream()),
               "sgq_linear_int4_allgather")
         if not self.fused_barrier:
             self.ex.barrier()

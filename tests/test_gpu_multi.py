@@ -60,6 +60,17 @@ def worker(rank, world, port, out_dir):
                 y = lin(xr)
                 torch.cuda.synchronize()
                 assert torch.equal(y, want), ("peer", M, K, N, rep, fused)
+        # deferred form: a forward only signals, the next one waits in its prologue; a barrier ends the sequence
+        lin = sh.PeerShardedLinear(sh.slice_quantized(q_full, n0, n1), b[n0:n1].contiguous(), N, ex, deferred=True)
+        ys, wants = [], []
+        for rep in range(6):
+            xr = x * (rep + 1)
+            wants.append(sgq.quantized_matmul(xr, q_full, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_GEMV))
+            ys.append(lin(xr))           # a buffer is whole only after a later forward's wait or the barrier below
+        ex.barrier()
+        torch.cuda.synchronize()
+        assert torch.equal(ys[5], wants[5]), ("deferred, last", M, K, N)
+        assert torch.equal(ex.local[(ex.turn + 0) % 2], wants[4]), ("deferred, one before last", M, K, N)
     # the sharded decoder (heads, SwiGLU columns, wo / w_down outputs and the vocabulary split by column) against
     # the same model on one GPU: every output element is computed by the same instructions, so logits are equal
     nl = importlib.import_module("sgq_b200.nanollama")
