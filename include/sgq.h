@@ -155,6 +155,30 @@ SGQ_API int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, con
                     int layout, int scheme, const float* bias, float* y, int64_t ldy, int path, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Gradient with respect to the activations of a frozen quantized layer.  The reference attaches a
+ * MatmulNode when x requires a gradient (src/ops.cpp:451-453), so it can backpropagate through
+ * quantized_matmul_int4 / _int8 (src/quantization.cpp:189-206) into x; its backward is
+ * grad_output.matmul(deq(W)^T contiguous) (src/ops.cpp:367-370).  These entry points compute the same:
+ *   layout KN (y = x * W):    dx[m,k] = sum_n dy[m,n] * code(k,n) * scale(k,n)
+ *   layout NK (y = x * W^T):  dx[m,k] = sum_n dy[m,n] * code(n,k) * scale(n,k)
+ * dy: [M,N] fp32 row-major, dx: [M,K] with row stride ldx >= K; packed/codes/scales, group and scheme
+ * are the forward's own.  It is the forward of the same stored tensor read with the other layout flag,
+ * so every path of the forward is available (SGQ_PATH_SIMT reproduces the reference's fp32 chain;
+ * workspace as sgq_linear_backward_x_workspace_bytes says).  Weights get no gradient: they are codes. */
+SGQ_API int sgq_linear_int4_backward_x(const float* dy, int64_t M, int64_t K, int64_t N, const uint8_t* packed,
+                                       const float* scales, int layout, int64_t group, float* dx, int64_t ldx, int path,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+SGQ_API int sgq_linear_int8_backward_x(const float* dy, int64_t M, int64_t K, int64_t N, const int8_t* codes,
+                                       const float* scales, int layout, int scheme, float* dx, int64_t ldx, int path,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+SGQ_API size_t sgq_linear_backward_x_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int path);
+
+/* Dynamic quantization of activations: one scale per row (token) of x[M,K], the reference's per-channel
+ * quantizer applied to x (src/quantization.cpp:42-75): sx[m] = max(|x[m,:]|, 1e-8) / 127,
+ * xq = clamp(round_half_away(x * (127 / max)), -127, 127).  Bit-exact with the reference.  The same
+ * codes feed sgq_linear_w8a8. */
+SGQ_API int sgq_quantize_activations_int8(const float* x, int64_t M, int64_t K, int8_t* xq, float* sx, void* stream);
+
 /* Prepared activations: the decode kernel's own operand format (int8 digit planes of the
  * activations with one power-of-two scale per row).  (No counterpart in the reference.)  A decode
  * forward normally converts x on the fly; a caller that runs several linears on the same x, or

@@ -207,6 +207,10 @@ class Ref:
         L.sgref_linear_num_scales.argtypes = [C.c_void_p]
         L.sgref_linear_codes.argtypes = [C.c_void_p, _f32p, _f32p]
         L.sgref_linear_forward.argtypes = [C.c_void_p, _f32p, _i64, C.c_int, _f32p]
+        if hasattr(L, "sgref_linear_backward_x"):
+            L.sgref_linear_backward_x.argtypes = [C.c_void_p, _f32p, _i64, _f32p, _f32p]
+        if hasattr(L, "sgref_read_tensor"):
+            L.sgref_read_tensor.argtypes = [C.c_int, C.c_char_p, C.c_char_p, _f32p, _i64, C.POINTER(_i64)]
         L.sgref_linear_time.restype = C.c_double
         L.sgref_linear_time.argtypes = [C.c_void_p, _f32p, _i64, C.c_int, C.c_int]
         L.sgref_quantize_time.restype = C.c_double
@@ -339,6 +343,13 @@ class Ref:
             self.ref._check(self.ref.L.sgref_linear_forward(self.h, x, x.shape[0], 1 if with_bias else 0, y))
             return y
 
+        def backward_x(self, x, dy):
+            """Gradient with respect to x of sum(forward(x) * dy), by the reference's autograd."""
+            x, dy = _f32(x), _f32(dy)
+            dx = np.empty_like(x)
+            self.ref._check(self.ref.L.sgref_linear_backward_x(self.h, x, x.shape[0], dy, dx))
+            return dx
+
         def time_forward(self, x, iters, with_bias=False):
             x = _f32(x)
             t = self.ref.L.sgref_linear_time(self.h, x, x.shape[0], 1 if with_bias else 0, iters)
@@ -359,6 +370,13 @@ class Ref:
 
     def linear(self, *a, **kw):
         return Ref.Linear(self, *a, **kw)
+
+    def read_tensor(self, path, name, capacity, native=True):
+        """One fp32 tensor of a checkpoint file, read by the reference's own reader (native .sgrd or SafeTensors)."""
+        out = np.empty(capacity, np.float32)
+        n = _i64(0)
+        self._check(self.L.sgref_read_tensor(0 if native else 1, str(path).encode(), name.encode(), out, capacity, C.byref(n)))
+        return out[: n.value].copy()
 
     def time_quantize(self, x, bits, scheme=PER_TENSOR, group=32, iters=1):
         x = _f32(x)

@@ -16,13 +16,17 @@
 // the `cpu_baseline` / `--impl reference` legs of bench.py (timed baseline).
 #include "sovereigngrad/nn.hpp"
 #include "sovereigngrad/quantization.hpp"
+#include "sovereigngrad/safetensors.hpp"
+#include "sovereigngrad/serialization.hpp"
 #include "sovereigngrad/tensor.hpp"
 
 #include <chrono>
 #include <cstdint>
 #include <cstring>
 #include <exception>
+#include <stdexcept>
 #include <string>
+#include <unordered_map>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -215,6 +219,37 @@ int sgref_linear_forward(void* handle, const float* x, int64_t M, int with_bias,
     auto* h = static_cast<LinearHandle*>(handle);
     Tensor X = from_raw(x, {M, h->K});
     to_raw(forward(*h, X, with_bias != 0), y);
+    SGREF_CATCH
+}
+
+// dx[M,K] = gradient of sum(forward(x) * dy) with respect to x, through the reference's own autograd:
+// x.requires_grad makes matmul attach a MatmulNode (src/ops.cpp:451-453) whose backward computes
+// grad_output.matmul(B^T contiguous) (src/ops.cpp:367-370), B being the dequantized weight.
+int sgref_linear_backward_x(void* handle, const float* x, int64_t M, const float* dy, float* dx) {
+    SGREF_TRY
+    auto* h = static_cast<LinearHandle*>(handle);
+    Tensor X = from_raw(x, {M, h->K});
+    X.set_requires_grad(true);
+    Tensor Y = forward(*h, X, false);
+    Tensor DY = from_raw(dy, {M, h->N});
+    Tensor loss = sum(Y * DY);
+    loss.backward();
+    to_raw(X.grad(), dx);
+    SGREF_CATCH
+}
+
+// Reads one fp32 tensor out of a checkpoint with the reference's own readers: kind 0 = its native format
+// (serialization::load_checkpoint, src/serialization.cpp:49-107), kind 1 = SafeTensors
+// (safetensors::load_file, src/safetensors.cpp:236-287).  *numel receives the element count.
+int sgref_read_tensor(int kind, const char* path, const char* name, float* out, int64_t capacity, int64_t* numel) {
+    SGREF_TRY
+    std::unordered_map<std::string, Tensor> sd =
+        kind == 0 ? serialization::load_checkpoint(path, Device::CPU) : safetensors::load_file(path, Device::CPU);
+    auto it = sd.find(name);
+    if (it == sd.end()) throw std::runtime_error(std::string("tensor not in file: ") + name);
+    if (numel) *numel = it->second.numel();
+    if (it->second.numel() > capacity) throw std::runtime_error("output buffer too small");
+    to_raw(it->second, out);
     SGREF_CATCH
 }
 

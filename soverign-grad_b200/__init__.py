@@ -33,7 +33,9 @@ EXPORTS = [
     "sgq_linear_workspace_bytes", "sgq_linear_int4", "sgq_linear_int8",
     "sgq_linear_w8a8", "sgq_linear_w8a8_workspace_bytes", "sgq_interleave_slices", "sgq_linear_int4_decode_noalloc",
     "sgq_prepared_x_bytes", "sgq_prepare_x", "sgq_linear_int4_prepared", "sgq_set_stream_overlap",
-    "sgq_linear_int4_allgather", "sgq_linear_int4_allgather_deferred", "sgq_peer_barrier", "sgq_peer_scatter", "sgq_set_peer_wait_budget",
+    "sgq_linear_int4_allgather", "sgq_linear_int4_allgather_deferred", "sgq_peer_barrier", "sgq_peer_scatter",
+    "sgq_set_peer_wait_budget", "sgq_linear_int4_backward_x", "sgq_linear_int8_backward_x",
+    "sgq_linear_backward_x_workspace_bytes", "sgq_quantize_activations_int8",
 ]
 
 # every symbol include/sgq_decoder.h declares
@@ -68,6 +70,11 @@ def _load() -> C.CDLL:
     lib.sgq_linear_workspace_bytes.argtypes = [i32, i64, i64, i64, i32, i32]
     lib.sgq_linear_int4.argtypes = [p, i64, i64, i64, p, p, i32, i64, p, p, i64, i32, p, sz, p]
     lib.sgq_linear_int8.argtypes = [p, i64, i64, i64, p, p, i32, i32, p, p, i64, i32, p, sz, p]
+    lib.sgq_linear_int4_backward_x.argtypes = [p, i64, i64, i64, p, p, i32, i64, p, i64, i32, p, sz, p]
+    lib.sgq_linear_int8_backward_x.argtypes = [p, i64, i64, i64, p, p, i32, i32, p, i64, i32, p, sz, p]
+    lib.sgq_linear_backward_x_workspace_bytes.restype = sz
+    lib.sgq_linear_backward_x_workspace_bytes.argtypes = [i32, i64, i64, i64, i32, i32]
+    lib.sgq_quantize_activations_int8.argtypes = [p, i64, i64, p, p, p]
     lib.sgq_linear_w8a8_workspace_bytes.restype = sz
     lib.sgq_linear_w8a8_workspace_bytes.argtypes = [i64, i64, i64]
     lib.sgq_linear_w8a8.argtypes = [p, i64, i64, i64, p, p, i32, p, p, i64, p, p, p, p, sz, p]
@@ -263,6 +270,40 @@ def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: Optional[torch.T
                                  PER_TENSOR if per_tensor else PER_ROW, _ptr(b), _ptr(out), ldy, path, wsp, wsb, _stream())
     check(rc, "sgq_linear")
     return out
+
+
+def quantized_matmul_backward_x(dy: torch.Tensor, q: QuantizedTensor, *, layout: int = LAYOUT_KN, path: int = PATH_AUTO,
+                                workspace: Optional[Workspace] = None) -> torch.Tensor:
+    """Gradient with respect to x of quantized_matmul(x, q): what the reference's autograd computes through
+    quantized_matmul_int8 / _int4 when x requires a gradient (src/ops.cpp:367-370, 451-453)."""
+    dy = _f32_cuda(dy)
+    K, N = _weight_kn(q, layout)
+    M = dy.shape[0]
+    if dy.dim() != 2 or dy.shape[1] != N:
+        raise RuntimeError("Matrix inner dimensions must match for matmul!")
+    dx = torch.empty((M, K), dtype=torch.float32, device=dy.device)
+    need = int(lib.sgq_linear_backward_x_workspace_bytes(q.bits, M, K, N, layout, path))
+    ws = (workspace or Workspace(dy.device)).get(need) if need else None
+    wsp, wsb = (_ptr(ws), ws.numel()) if ws is not None else (None, 0)
+    if q.bits == 4:
+        rc = lib.sgq_linear_int4_backward_x(_ptr(dy), M, K, N, _ptr(q.qdata), _ptr(q.scales), layout, q.group_size, _ptr(dx), K, path,
+                                            wsp, wsb, _stream())
+    else:
+        per_tensor = q.scheme == PER_TENSOR or q.scales.numel() == 1
+        rc = lib.sgq_linear_int8_backward_x(_ptr(dy), M, K, N, _ptr(q.qdata), _ptr(q.scales), layout,
+                                            PER_TENSOR if per_tensor else PER_ROW, _ptr(dx), K, path, wsp, wsb, _stream())
+    check(rc, "sgq_linear_backward_x")
+    return dx
+
+
+def quantize_activations_int8(x: torch.Tensor):
+    """Per-row (per-token) INT8 quantization of activations: (codes int8 [M,K], scales fp32 [M])."""
+    x = _f32_cuda(x)
+    M, K = x.shape
+    xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    sx = torch.empty(M, dtype=torch.float32, device=x.device)
+    check(lib.sgq_quantize_activations_int8(_ptr(x), M, K, _ptr(xq), _ptr(sx), _stream()), "sgq_quantize_activations_int8")
+    return xq, sx
 
 
 def prepared_x_bytes(M: int, K: int) -> int:

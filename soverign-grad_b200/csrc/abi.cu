@@ -323,6 +323,32 @@ int sgq_linear_int8(const float* x, int64_t M, int64_t K, int64_t N, const int8_
     return run_linear(a, path);
 }
 
+// dx = dy * deq(W) (layout NK) or dy * deq(W)^T (layout KN): the forward of the same stored tensor read with the
+// other layout flag (the contraction then runs over the output features N and produces the K input features).
+int sgq_linear_int4_backward_x(const float* dy, int64_t M, int64_t K, int64_t N, const uint8_t* packed, const float* scales,
+                               int layout, int64_t group, float* dx, int64_t ldx, int path, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+    if (layout != SGQ_LAYOUT_KN && layout != SGQ_LAYOUT_NK) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown layout");
+    return sgq_linear_int4(dy, M, N, K, packed, scales, layout == SGQ_LAYOUT_KN ? SGQ_LAYOUT_NK : SGQ_LAYOUT_KN, group, nullptr, dx,
+                           ldx, path, workspace, workspace_bytes, stream);
+}
+
+int sgq_linear_int8_backward_x(const float* dy, int64_t M, int64_t K, int64_t N, const int8_t* codes, const float* scales,
+                               int layout, int scheme, float* dx, int64_t ldx, int path, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+    if (layout != SGQ_LAYOUT_KN && layout != SGQ_LAYOUT_NK) return bad(SGQ_ERR_BAD_ARGUMENT, "unknown layout");
+    return sgq_linear_int8(dy, M, N, K, codes, scales, layout == SGQ_LAYOUT_KN ? SGQ_LAYOUT_NK : SGQ_LAYOUT_KN, scheme, nullptr, dx,
+                           ldx, path, workspace, workspace_bytes, stream);
+}
+
+size_t sgq_linear_backward_x_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int path) {
+    return sgq_linear_workspace_bytes(bits, M, N, K, layout == SGQ_LAYOUT_KN ? SGQ_LAYOUT_NK : SGQ_LAYOUT_KN, path);
+}
+
+int sgq_quantize_activations_int8(const float* x, int64_t M, int64_t K, int8_t* xq, float* sx, void* stream) {
+    return sgq_quantize_int8(x, M, K, SGQ_PER_ROW, xq, sx, stream);
+}
+
 int sgq_linear_int4_decode_noalloc(const float* x, int64_t M, int64_t K, int64_t N, const uint8_t* packed,
                                    const float* scales, const float* bias, float* y, int64_t ldy, void* stream) {
     LinearArgs a{x, M, K, N, packed, scales, 4, SGQ_LAYOUT_NK, 32, SGQ_PER_TENSOR, bias, y, ldy, nullptr, 0,

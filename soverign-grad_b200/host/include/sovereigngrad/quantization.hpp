@@ -8,7 +8,8 @@
 //     codes_as_float() gives the reference's fp32 view.
 //   * tensors must live on Device::CUDA: the kernels are sm_100a only and there is no CPU path
 //     (the reference bounces every call through the host, src/quantization.cpp:12,40,110).
-//   * the forward is inference only (no autograd graph is recorded).
+//   * no autograd graph is recorded; the gradient the reference's graph would send into x
+//     (MatmulNode, src/ops.cpp:362-375) is available as quantized_matmul_backward_x().
 //   * `layout` says how a 2-D weight is stored: KN = [in, out] (the reference's own convention,
 //     y = x*W), NK = [out, in] (y = x*W^T).  It is recorded in the QuantizedTensor by
 //     quantize_*() callers through set_layout(); default KN.
@@ -51,6 +52,15 @@ Tensor quantized_matmul_int8(const Tensor& x, const QuantizedTensor& q_weight, c
                              ForwardPath path = ForwardPath::Auto);
 Tensor quantized_matmul_int4(const Tensor& x, const QuantizedTensor& q_weight, const Tensor& bias = Tensor(),
                              ForwardPath path = ForwardPath::Auto);
+
+// grad_x of quantized_matmul_int8 / _int4(x, q_weight): grad_output[M,N] * deq(W)^T, what the reference's
+// autograd computes when x requires a gradient (src/ops.cpp:367-370).  Weights are frozen codes.
+Tensor quantized_matmul_backward_x(const Tensor& grad_output, const QuantizedTensor& q_weight,
+                                   ForwardPath path = ForwardPath::Auto);
+
+// Dynamic activation quantization: one scale per row (token) of x[tokens, features] — the reference's
+// per-channel quantizer (src/quantization.cpp:42-75) applied to activations.
+QuantizedTensor quantize_activations_int8(const Tensor& x);
 
 }  // namespace quantization
 }  // namespace sovereigngrad

@@ -3,6 +3,8 @@
 #include <stdexcept>
 #include <string>
 
+#include <cuda_runtime_api.h>
+
 #include "sgq.h"
 
 namespace sovereigngrad {
@@ -29,7 +31,7 @@ bool per_tensor(const QuantizedTensor& q) {
     return q.scheme == QuantizationScheme::PerTensorSymmetric || q.scales.numel() == 1;   // src/quantization.cpp:91
 }
 
-// per-device scratch for the forward; grows on demand, protected by the pool's own locking
+// scratch for the forward; grows on demand, protected by the pool's own locking
 struct Workspace {
     Tensor buf;
     void* get(size_t bytes, size_t* have) {
@@ -40,7 +42,15 @@ struct Workspace {
         return buf.raw();
     }
 };
-thread_local Workspace g_workspace;   // one per calling thread: entry points are re-entrant
+// One per calling thread (entry points are re-entrant) AND per device: a thread that switches the
+// current device must never hand one GPU's kernels a scratch buffer that lives on another.
+constexpr int kMaxDevices = 64;
+thread_local Workspace g_workspaces[kMaxDevices];
+Workspace& workspace_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return g_workspaces[dev];
+}
 
 Tensor forward(const Tensor& x_in, const QuantizedTensor& q, const Tensor& bias, ForwardPath path) {
     require_cuda(x_in, "quantized_matmul");
@@ -64,7 +74,7 @@ Tensor forward(const Tensor& x_in, const QuantizedTensor& q, const Tensor& bias,
     Tensor y = Tensor::empty({M, N}, Device::CUDA);
     const int layout = kn ? SGQ_LAYOUT_KN : SGQ_LAYOUT_NK;
     size_t have = 0;
-    void* ws = g_workspace.get(sgq_linear_workspace_bytes(q.bits, M, K, N, layout, static_cast<int>(path)), &have);
+    void* ws = workspace_of_current_device().get(sgq_linear_workspace_bytes(q.bits, M, K, N, layout, static_cast<int>(path)), &have);
     int rc;
     if (q.bits == 4) {
         rc = sgq_linear_int4(x.data(), M, K, N, static_cast<const uint8_t*>(q.qdata.raw()), q.scales.data(), layout,
@@ -146,6 +156,37 @@ Tensor dequantize_int4(const QuantizedTensor& q) {
                               out.data(), nullptr),
           "dequantize_int4");
     return out;
+}
+
+Tensor quantized_matmul_backward_x(const Tensor& grad_in, const QuantizedTensor& q, ForwardPath path) {
+    require_cuda(grad_in, "quantized_matmul_backward_x");
+    require_cuda(q.qdata, "quantized_matmul_backward_x");
+    if (grad_in.shape().size() != 2 || q.original_shape.size() != 2)
+        throw std::runtime_error("matmul currently requires 2D tensors!");
+    const bool kn = q.layout == WeightLayout::KN;
+    const int64_t K = kn ? q.original_shape[0] : q.original_shape[1];
+    const int64_t N = kn ? q.original_shape[1] : q.original_shape[0];
+    const int64_t M = grad_in.shape()[0];
+    if (grad_in.shape()[1] != N) throw std::runtime_error("Matrix inner dimensions must match for matmul!");
+    Tensor dy = f32_contiguous(grad_in);
+    Tensor dx = Tensor::empty({M, K}, Device::CUDA);
+    const int layout = kn ? SGQ_LAYOUT_KN : SGQ_LAYOUT_NK;
+    size_t have = 0;
+    void* ws = workspace_of_current_device().get(
+        sgq_linear_backward_x_workspace_bytes(q.bits, M, K, N, layout, static_cast<int>(path)), &have);
+    const int rc = q.bits == 4
+        ? sgq_linear_int4_backward_x(dy.data(), M, K, N, static_cast<const uint8_t*>(q.qdata.raw()), q.scales.data(), layout,
+                                     q.group_size, dx.data(), K, static_cast<int>(path), ws, have, nullptr)
+        : sgq_linear_int8_backward_x(dy.data(), M, K, N, static_cast<const int8_t*>(q.qdata.raw()), q.scales.data(), layout,
+                                     per_tensor(q) ? SGQ_PER_TENSOR : SGQ_PER_ROW, dx.data(), K, static_cast<int>(path), ws, have,
+                                     nullptr);
+    check(rc, "quantized_matmul_backward_x");
+    return dx;
+}
+
+QuantizedTensor quantize_activations_int8(const Tensor& x) {
+    if (x.shape().size() != 2) throw std::runtime_error("quantize_activations_int8: expected [tokens, features]");
+    return quantize_int8(x, QuantizationScheme::PerChannelSymmetric);
 }
 
 Tensor quantized_matmul_int8(const Tensor& x, const QuantizedTensor& q, const Tensor& bias, ForwardPath path) {

@@ -30,4 +30,4 @@ def ref():
 @pytest.fixture(scope="session")
 def golden():
     d = os.path.join(ROOT, "tests", "golden")
-    return {n: np.load(os.path.join(d, n + ".npz")) for n in ("quantize", "forward", "config1")}
+    return {n: np.load(os.path.join(d, n + ".npz")) for n in ("quantize", "forward", "config1", "backward")}

@@ -64,6 +64,20 @@ FORWARD_CASES = [
 ]
 
 
+# (name, M, K, N): gradient with respect to x of a frozen quantized layer
+BACKWARD_CASES = [
+    ("bw_decode_1", 1, 256, 96),
+    ("bw_decode_4", 4, 512, 160),
+    ("bw_tails_17", 17, 130, 72),
+    ("bw_tile_40", 40, 160, 64),
+]
+
+
+def backward_seed(name: str, M: int, N: int) -> np.ndarray:
+    """The upstream gradient dy[M, N] of a backward case."""
+    return normal(sum(ord(c) for c in name) * 11 + 3, (M, N))
+
+
 def forward_inputs(name: str, M: int, K: int, N: int, layout: int):
     seed = sum(ord(c) for c in name) * 7 + layout
     x = normal(seed, (M, K))

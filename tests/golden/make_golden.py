@@ -66,11 +66,31 @@ def make_glue(ref):
     print("glue.npz", os.path.getsize(os.path.join(HERE, "glue.npz")), "bytes")
 
 
+def make_backward(ref):
+    """Gradient with respect to x through the reference's own autograd (MatmulNode, src/ops.cpp:362-375),
+    seeded with dy."""
+    bw = {}
+    for name, M, K, N in cases.BACKWARD_CASES:
+        for layout in (cases.LAYOUT_KN, cases.LAYOUT_NK):
+            x, w, _ = cases.forward_inputs(name, M, K, N, layout)
+            dy = cases.backward_seed(name, M, N)
+            for tag, bits, scheme, group in (("int4_g32", 4, 0, 32), ("int8_tensor", 8, cases.PER_TENSOR, 0),
+                                             ("int8_row", 8, cases.PER_ROW, 0)):
+                lin = ref.linear(w, layout, bits, scheme, group, None)
+                bw[f"{name}/L{layout}/{tag}/dx"] = lin.backward_x(x, dy)
+                lin.close()
+    np.savez_compressed(os.path.join(HERE, "backward.npz"), **bw)
+    print("backward.npz", os.path.getsize(os.path.join(HERE, "backward.npz")), "bytes")
+
+
 def main():
     ref = oracle.load_ref()
     assert ref is not None, "build oracle/_ref first (make -C oracle ref)"
     make_glue(ref)
     if sys.argv[1:] == ["glue"]:
+        return
+    if sys.argv[1:] == ["backward"]:
+        make_backward(ref)
         return
     q = {}
     for name, shape, gen in cases.QUANT_CASES:
@@ -114,6 +134,8 @@ def main():
                     f[f"{base}/{tag}/codes_sha256"] = np.frombuffer(sha(codes.astype(np.int8)).encode(), np.uint8)
                     lin.close()
     np.savez_compressed(os.path.join(HERE, "forward.npz"), **f)
+
+    make_backward(ref)
 
     # benchmark configuration 1 at full size: inputs are re-derivable from the seed; keep digests of the
     # codes and a strided sample of the output.

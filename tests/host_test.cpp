@@ -19,6 +19,7 @@
 
 #include "sovereigngrad/nn.hpp"
 #include "sovereigngrad/safetensors.hpp"
+#include "sovereigngrad/serialization.hpp"
 
 using namespace sovereigngrad;
 namespace q = sovereigngrad::quantization;
@@ -196,6 +197,93 @@ static int run_cpu() {
         std::remove(path.c_str()); std::remove((path + ".2").c_str()); std::remove((path + ".3").c_str());
         std::puts("ok packed checkpoint");
     }
+
+    // the reference's native ".sgrd" format: version 1 for fp32 state dicts, version 2 with packed tensors
+    {
+        namespace sz = serialization;
+        const std::string path = "/tmp/sgq_host_test_ckpt.sgrd";
+        sz::StateDict f32;
+        f32["linear.W"] = Tensor(std::vector<float>{1.f, 2.f, 3.f, 4.f, 5.f, 6.f}, {2, 3});
+        f32["linear.b"] = Tensor(std::vector<float>{-0.5f, 0.25f, 8.f}, {1, 3});
+        sz::save_checkpoint(f32, path);
+        {
+            std::ifstream f(path, std::ios::binary);
+            std::string c((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+            uint32_t version = 0;
+            std::memcpy(&version, c.data() + 4, 4);
+            CHECK(c.compare(0, 4, "SGRD") == 0 && version == 1);          // what the reference's reader accepts
+            // header 12 + (4 + 8 + 4 + 2*8 + 8 + 24) + (4 + 8 + 4 + 2*8 + 8 + 12)
+            CHECK(c.size() == 12 + 64 + 52);
+        }
+        sz::StateDict back = sz::load_checkpoint(path);
+        CHECK(back.size() == 2 && back.at("linear.W").shape() == (std::vector<int64_t>{2, 3}));
+        CHECK(back.at("linear.W").to_vector() == f32.at("linear.W").to_vector() && back.at("linear.b").to_vector() == f32.at("linear.b").to_vector());
+
+        q::QuantizedTensor q4;
+        q4.bits = 4; q4.group_size = 32; q4.original_shape = {4, 64}; q4.layout = q::WeightLayout::NK;
+        q4.scheme = q::QuantizationScheme::GroupedAsymmetric;
+        q4.qdata = Tensor::empty({4 * 64 / 2}, Device::CPU, DType::UInt8);
+        q4.scales = Tensor::empty({4 * 64 / 32}, Device::CPU);
+        for (int i = 0; i < 128; ++i) static_cast<uint8_t*>(q4.qdata.raw())[i] = static_cast<uint8_t>(i * 29 + 3);
+        for (int i = 0; i < 8; ++i) q4.scales.data()[i] = 0.002f * static_cast<float>(i + 1);
+        sz::StateDict packed = f32;
+        sz::put_quantized("layers.0.w", q4, &packed);
+        sz::save_checkpoint(packed, path + ".2");
+        {
+            std::ifstream f(path + ".2", std::ios::binary);
+            std::string c((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+            uint32_t version = 0;
+            std::memcpy(&version, c.data() + 4, 4);
+            CHECK(version == 2);
+        }
+        sz::StateDict pb = sz::load_checkpoint(path + ".2");
+        q::QuantizedTensor r4 = sz::get_quantized("layers.0.w", pb);
+        CHECK(r4.bits == 4 && r4.group_size == 32 && r4.layout == q::WeightLayout::NK && r4.original_shape == q4.original_shape);
+        CHECK(r4.scheme == q::QuantizationScheme::GroupedAsymmetric);
+        CHECK(std::memcmp(r4.qdata.raw(), q4.qdata.raw(), 128) == 0 && std::memcmp(r4.scales.raw(), q4.scales.raw(), 32) == 0);
+        CHECK(pb.at("linear.b").to_vector() == f32.at("linear.b").to_vector());
+        // equal inputs give equal files; malformed files are refused
+        sz::save_checkpoint(packed, path + ".3");
+        std::ifstream fa(path + ".2", std::ios::binary), fb(path + ".3", std::ios::binary);
+        std::string ca((std::istreambuf_iterator<char>(fa)), std::istreambuf_iterator<char>());
+        std::string cb((std::istreambuf_iterator<char>(fb)), std::istreambuf_iterator<char>());
+        CHECK(ca == cb);
+        { std::ofstream cut(path + ".4", std::ios::binary); cut.write(ca.data(), static_cast<std::streamsize>(ca.size() - 7)); }
+        CHECK(throws([&] { sz::load_checkpoint(path + ".4"); }));
+        { std::ofstream bad(path + ".5", std::ios::binary); bad.write("SGRX\1\0\0\0\0\0\0\0", 12); }
+        CHECK(throws([&] { sz::load_checkpoint(path + ".5"); }));
+        pb.erase("layers.0.w.qmeta");
+        CHECK(throws([&] { sz::get_quantized("layers.0.w", pb); }));
+        for (const char* suffix : {"", ".2", ".3", ".4", ".5"}) std::remove((path + suffix).c_str());
+        std::puts("ok sgrd checkpoint");
+    }
+    return 0;
+}
+
+// Writes, into `dir`, checkpoints whose fp32 tensors the REFERENCE's own readers must be able to read:
+// a version-1 .sgrd file, and a SafeTensors file that also carries a packed INT4 tensor.
+static int run_compat(const std::string& dir) {
+    namespace sz = serialization;
+    namespace st = safetensors;
+    sz::StateDict f32;
+    std::vector<float> w(6 * 5), b(5);
+    for (size_t i = 0; i < w.size(); ++i) w[i] = 0.125f * static_cast<float>(i) - 1.5f;
+    for (size_t i = 0; i < b.size(); ++i) b[i] = 1.0f / static_cast<float>(i + 1);
+    f32["linear.W"] = Tensor(w, {6, 5});
+    f32["linear.b"] = Tensor(b, {1, 5});
+    sz::save_checkpoint(f32, dir + "/f32.sgrd");
+    st::StateDict sd(f32.begin(), f32.end());
+    st::Metadata md;
+    q::QuantizedTensor q4;
+    q4.bits = 4; q4.group_size = 32; q4.original_shape = {2, 64}; q4.layout = q::WeightLayout::NK;
+    q4.scheme = q::QuantizationScheme::GroupedAsymmetric;
+    q4.qdata = Tensor::empty({64}, Device::CPU, DType::UInt8);
+    q4.scales = Tensor::empty({4}, Device::CPU);
+    for (int i = 0; i < 64; ++i) static_cast<uint8_t*>(q4.qdata.raw())[i] = static_cast<uint8_t>(i * 13 + 1);
+    for (int i = 0; i < 4; ++i) q4.scales.data()[i] = 0.01f * static_cast<float>(i + 1);
+    st::put_quantized("packed.w", q4, &sd, &md);
+    st::save_file(sd, dir + "/mixed.safetensors", md);
+    std::puts("ok compat files");
     return 0;
 }
 
@@ -244,6 +332,42 @@ static int run_gpu(const std::string& dir, int64_t M, int64_t K, int64_t N, int6
     dump(dir + "/y4_nk.bin", nk->forward(x));
     dump(dir + "/q4_nk_packed.bin", nk->q_weight.qdata);
 
+    // gradient into x through the frozen layers (upstream gradient: the forward's own output) and dynamic
+    // activation quantization
+    dump(dir + "/dx4.bin", q::quantized_matmul_backward_x(y4, ql4->q_weight));
+    dump(dir + "/dx8.bin", q::quantized_matmul_backward_x(y8, ql8->q_weight, q::ForwardPath::Simt));
+    dump(dir + "/dx4_nk.bin", q::quantized_matmul_backward_x(y4, nk->q_weight));
+    auto xa = q::quantize_activations_int8(x);
+    dump(dir + "/xa_codes.bin", xa.qdata);
+    dump(dir + "/xa_scales.bin", xa.scales);
+    CHECK(throws([&] { q::quantized_matmul_backward_x(Tensor({M, N + 1}, Device::CUDA), ql4->q_weight); }));
+
+    // packed checkpoints, both container formats: saved from device tensors, loaded straight into pool storage
+    // on the device, and the loaded layer computes the same bits
+    {
+        const size_t before = MemoryAllocator::instance().active_allocations(Device::CUDA);
+        serialization::StateDict sd;
+        serialization::put_quantized("proj", ql4->q_weight, &sd);
+        sd["proj.bias"] = ql4->bias;
+        serialization::save_checkpoint(sd, dir + "/packed.sgrd");
+        serialization::StateDict back = serialization::load_checkpoint(dir + "/packed.sgrd", Device::CUDA);
+        q::QuantizedTensor lq = serialization::get_quantized("proj", back);
+        CHECK(lq.qdata.device() == Device::CUDA && lq.scales.device() == Device::CUDA && back.at("proj.bias").device() == Device::CUDA);
+        CHECK(MemoryAllocator::instance().active_allocations(Device::CUDA) > before);      // it lives in the device pool
+        Tensor y_loaded = q::quantized_matmul_int4(x, lq, back.at("proj.bias"));
+        CHECK(y_loaded.to_vector() == y4.to_vector());
+        safetensors::StateDict sd2;
+        safetensors::Metadata md;
+        safetensors::put_quantized("proj", ql8->q_weight, &sd2, &md);
+        safetensors::save_file(sd2, dir + "/packed.safetensors", md);
+        safetensors::Metadata md2;
+        safetensors::StateDict back2 = safetensors::load_file(dir + "/packed.safetensors", Device::CUDA, &md2);
+        q::QuantizedTensor lq8 = safetensors::get_quantized("proj", back2, md2);
+        CHECK(lq8.qdata.device() == Device::CUDA);
+        CHECK(q::quantized_matmul_int8(x, lq8, lin.b).to_vector() == y8.to_vector());
+        std::puts("ok packed checkpoints on the device");
+    }
+
     // the tolerance checks of the reference's test (element 0 only, src/test_suite.cpp:719-722)
     Tensor fy = lin.forward(x);
     const float d8 = std::abs((fy - y8).to_vector()[0]), d4 = std::abs((fy - y4).to_vector()[0]);
@@ -263,12 +387,13 @@ static int run_gpu(const std::string& dir, int64_t M, int64_t K, int64_t N, int6
 int main(int argc, char** argv) {
     try {
         if (argc >= 2 && std::string(argv[1]) == "cpu") return run_cpu();
+        if (argc >= 3 && std::string(argv[1]) == "compat") return run_compat(argv[2]);
         if (argc >= 7 && std::string(argv[1]) == "gpu")
             return run_gpu(argv[2], std::atoll(argv[3]), std::atoll(argv[4]), std::atoll(argv[5]), std::atoll(argv[6]));
     } catch (const std::exception& e) {
         std::fprintf(stderr, "exception: %s\n", e.what());
         return 2;
     }
-    std::fprintf(stderr, "usage: sgq_host_test cpu | gpu <dir> M K N group\n");
+    std::fprintf(stderr, "usage: sgq_host_test cpu | compat <dir> | gpu <dir> M K N group\n");
     return 64;
 }

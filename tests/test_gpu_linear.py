@@ -446,3 +446,39 @@ def test_kn_decode_kernel_rejects_what_it_cannot_run(sgq):
     q24 = sgq.quantize_int4(torch.randn(64, 48, device="cuda"), 24)                                # group 24: not a multiple of 16
     with pytest.raises(sgq.SgqError):
         sgq.quantized_matmul(torch.randn(1, 64, device="cuda"), q24, None, layout=cases.LAYOUT_KN, path=sgq.PATH_GEMV)
+
+
+@pytest.mark.parametrize("name,M,K,N", cases.BACKWARD_CASES, ids=[c[0] for c in cases.BACKWARD_CASES])
+def test_backward_x_against_reference_autograd(sgq, golden, name, M, K, N):
+    """Gradient with respect to x through a frozen quantized layer: the any-shape kernel reproduces what the
+    compiled reference's autograd returned (fixtures), the fast paths stay within 1e-3 of it."""
+    g = golden["backward"]
+    ws = sgq.Workspace(torch.device("cuda"))
+    for layout in (cases.LAYOUT_KN, cases.LAYOUT_NK):
+        _, w, _ = cases.forward_inputs(name, M, K, N, layout)
+        dy = dev(cases.backward_seed(name, M, N))
+        single_chain = (M % 32) < 8 and M < 32 or K % 8 == 0
+        for tag in ("int4_g32", "int8_tensor", "int8_row"):
+            q = quantize(sgq, dev(w), tag)
+            want = g[f"{name}/L{layout}/{tag}/dx"]
+            dx = sgq.quantized_matmul_backward_x(dy, q, layout=layout, path=sgq.PATH_SIMT).cpu().numpy()
+            if single_chain:
+                assert np.array_equal(dx, want), (name, layout, tag)
+            else:
+                assert rel_err(dx, want) <= 1e-6
+            dx_auto = sgq.quantized_matmul_backward_x(dy, q, layout=layout, path=sgq.PATH_AUTO, workspace=ws).cpu().numpy()
+            assert rel_err(dx_auto, want) <= TOL_FP32, (name, layout, tag, rel_err(dx_auto, want))
+    check_status(sgq)
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (8, 4096), (37, 1000), (2048, 4096)])
+def test_quantize_activations_int8_bit_exact(sgq, port, M, K):
+    """Dynamic per-row (per-token) activation quantization = the reference's per-channel quantizer applied to x."""
+    x = (cases.normal(M + K, (M, K)) * np.random.default_rng(M).uniform(0.05, 40.0, (M, 1))).astype(np.float32)
+    x[0, 0] = 0.0
+    if M > 1:
+        x[1, :] = 0.0                                  # an all-zero row: scale 1e-8 / 127
+    xq, sx = sgq.quantize_activations_int8(dev(x))
+    codes, scales = port.quantize_int8(x, cases.PER_ROW)
+    assert np.array_equal(xq.cpu().numpy(), codes)
+    assert sx.cpu().numpy().tobytes() == np.asarray(scales, np.float32).tobytes()

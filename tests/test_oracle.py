@@ -165,3 +165,32 @@ def test_integer_subpath_is_self_consistent(port):
         assert eq(acc, xq.astype(np.int64) @ wq.astype(np.int64).T)
         sw = ws[0] if scheme == cases.PER_TENSOR else ws[None, :]
         assert eq(y, (acc.astype(np.float32) * sx[:, None]) * sw)
+
+
+@pytest.mark.parametrize("name,M,K,N", cases.BACKWARD_CASES, ids=[c[0] for c in cases.BACKWARD_CASES])
+def test_backward_x_is_the_forward_read_with_the_other_layout(port, ref, golden, name, M, K, N):
+    """The reference backpropagates through a frozen quantized layer into x (MatmulNode, src/ops.cpp:362-375):
+    dx = dy * deq(W)^T.  That is the forward of the same stored tensor with the layout flag flipped; the port
+    computes it that way and must reproduce what the compiled reference's autograd returned (fixtures), bit for
+    bit wherever the reference's matmul runs one fused-multiply-add chain per output."""
+    g = golden["backward"]
+    for layout in (cases.LAYOUT_KN, cases.LAYOUT_NK):
+        x, w, _ = cases.forward_inputs(name, M, K, N, layout)
+        dy = cases.backward_seed(name, M, N)
+        single_chain = (M % 32) < 8 and M < 32 or K % 8 == 0
+        packed, scales = port.quantize_int4(w, 32)
+        got = {"int4_g32": port.qlinear_int4(dy, packed, scales, N, K, 1 - layout, 32, None)}
+        for tag, scheme in (("int8_tensor", cases.PER_TENSOR), ("int8_row", cases.PER_ROW)):
+            wq, sw = port.quantize_int8(w, scheme)
+            got[tag] = port.qlinear_int8(dy, wq, sw, N, K, 1 - layout, scheme, None)
+        for tag, dx in got.items():
+            want = g[f"{name}/L{layout}/{tag}/dx"]
+            if single_chain:
+                assert np.array_equal(dx, want), (name, layout, tag)
+            else:
+                assert np.max(np.abs(dx - want)) <= 1e-6 * np.max(np.abs(want))
+            if ref is not None:
+                lin = ref.linear(w, layout, 4 if tag.startswith("int4") else 8,
+                                 cases.PER_ROW if tag == "int8_row" else cases.PER_TENSOR, 32, None)
+                assert np.array_equal(lin.backward_x(x, dy), want), "fixture is not what the compiled reference returns"
+                lin.close()
