@@ -14,6 +14,7 @@
  *   sgqd_attn_decode     nn::CausalSelfAttention            include/sovereigngrad/nn.hpp:503-560
  *                        (last row of the causal softmax(q k^T / sqrt(d)) v; the reference has no
  *                        KV cache and recomputes every row, models.hpp:262-300) + rotary_embedding
+ *   sgqd_attn_prefill    causal attention with online softmax  src/cuda_kernels.cu:1323-1394
  *   sgqd_silu_mul        nn::SwiGLU gate                    include/sovereigngrad/nn.hpp:151-156
  *                        simd::vec_silu                     include/sovereigngrad/simd.hpp:103-108
  *   sgqd_embedding       sovereigngrad::embedding           src/ops.cpp:2624-2659
@@ -59,6 +60,16 @@ SGQ_API int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t
 SGQ_API int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
                              const float* cos_table, const float* sin_table, float* k_cache, float* v_cache,
                              int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* stream);
+
+/* Causal attention of t_new NEW tokens per sequence (the prompt pass), after sgqd_rope_kv_store has rotated
+ * q in place and appended the rotated keys and the values: token i of sequence b (row b * t_new + i of qkv,
+ * position *pos0 + i) attends to cache positions 0 .. *pos0 + i,
+ *   out[b * t_new + i, h*head_dim + d] = sum_{t <= pos0 + i} softmax_t(q . k_t / sqrt(head_dim)) v_t[d],
+ * computed with an online softmax over tiles of 32 keys like the reference's attention
+ * (src/cuda_kernels.cu:1323-1394).  head_dim must be 64 or 128; batch * n_heads <= 65535. */
+SGQ_API int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,
+                              const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
+                              int64_t out_stride, void* stream);
 
 /* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up.
  * prepared_out: as for sgqd_add_rmsnorm, the prepared form of out[rows, hidden]. */

@@ -415,6 +415,133 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(cons
     }
 }
 
+// Causal attention of a block of new tokens (the prompt pass): token i of a sequence, at position *pos0 + i,
+// attends to the cache positions 0 .. *pos0 + i, which sgqd_rope_kv_store has filled (the new tokens included);
+// q comes from the rotated qkv rows.  Online softmax over tiles of keys, as the reference's attention does
+// (src/cuda_kernels.cu:1323-1394).  grid (ceil(t_new / 128), batch * heads), 256 threads.  Eight threads share
+// a query row, each owning an eighth of the head dimension (16-byte chunk c of a row belongs to thread c % 8,
+// so the eight threads read 128 consecutive bytes: no bank conflicts), and every thread carries FOUR queries, so
+// that a key or value fetched from shared memory is used four times.  K and V tiles of 16 keys go through
+// shared memory and are read by all 128 queries of the block.
+constexpr int kPrefillTPQ = 8, kPrefillQPT = 4, kPrefillKeys = 16;
+constexpr int kPrefillQ = 256 / kPrefillTPQ * kPrefillQPT;        // 128 queries per block
+template <int HD>
+__global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int t_new, int n_heads,
+                                                           const float* __restrict__ kc, const float* __restrict__ vc,
+                                                           int64_t max_seq, const int32_t* __restrict__ pos0,
+                                                           float* __restrict__ out, int64_t out_stride) {
+    constexpr int TPQ = kPrefillTPQ, QPT = kPrefillQPT, KT = kPrefillKeys;
+    constexpr int NC = HD / (4 * TPQ);         // 16-byte chunks of a row per thread
+    constexpr int LD = HD + 4;                 // padded row of a shared tile (keeps rows 16-byte aligned)
+    __shared__ __align__(16) float ks[KT * LD];
+    __shared__ __align__(16) float vs[KT * LD];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int bh = blockIdx.y, b = bh / n_heads, h = bh - b * n_heads;
+    const int q0 = blockIdx.x * kPrefillQ;
+    const int part = threadIdx.x % TPQ, qrow = threadIdx.x / TPQ;          // queries q0 + qrow + 32 u, u = 0..3
+    int64_t p0 = static_cast<int64_t>(*pos0);
+    p0 = p0 < 0 ? 0 : p0;
+    const float scale = rsqrtf(static_cast<float>(HD));
+    float q[QPT][NC * 4], o[QPT][NC * 4], m[QPT], l[QPT];
+    bool live[QPT];
+#pragma unroll
+    for (int u = 0; u < QPT; ++u) {
+        const int qi = q0 + qrow + 32 * u;
+        live[u] = qi < t_new;
+        m[u] = -CUDART_INF_F;
+        l[u] = 0.f;
+        const float* qr = qkv + (static_cast<int64_t>(b) * t_new + (live[u] ? qi : 0)) * qkv_stride + h * HD + part * 4;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {         // registers 4c .. 4c+3 = head dimensions 4 * (part + TPQ * c) .. + 3
+            const float4 v = live[u] ? *reinterpret_cast<const float4*>(qr + 4 * TPQ * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            q[u][4 * c] = v.x * scale; q[u][4 * c + 1] = v.y * scale; q[u][4 * c + 2] = v.z * scale; q[u][4 * c + 3] = v.w * scale;
+            o[u][4 * c] = o[u][4 * c + 1] = o[u][4 * c + 2] = o[u][4 * c + 3] = 0.f;
+        }
+    }
+    const int last_q = (q0 + kPrefillQ - 1 < t_new - 1) ? q0 + kPrefillQ - 1 : t_new - 1;
+    int64_t nk = p0 + last_q + 1;              // keys this block needs
+    nk = nk > max_seq ? max_seq : nk;
+    const float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD;
+    const float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD;
+    for (int64_t j0 = 0; j0 < nk; j0 += KT) {
+        __syncthreads();                       // the tile of the last round has been read by everyone
+        for (int it = threadIdx.x; it < KT * (HD / 4); it += 256) {
+            const int r = it / (HD / 4), c = (it - r * (HD / 4)) * 4;
+            const int64_t j = (j0 + r < nk) ? j0 + r : nk - 1;                         // clamped: masked below
+            *reinterpret_cast<float4*>(ks + r * LD + c) = __ldg(reinterpret_cast<const float4*>(kb + j * HD + c));
+            *reinterpret_cast<float4*>(vs + r * LD + c) = __ldg(reinterpret_cast<const float4*>(vb + j * HD + c));
+        }
+        __syncthreads();
+        float sc[QPT][KT];
+#pragma unroll
+        for (int jj = 0; jj < KT; ++jj) {
+            float dot[QPT];
+#pragma unroll
+            for (int u = 0; u < QPT; ++u) dot[u] = 0.f;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const float4 kv = *reinterpret_cast<const float4*>(ks + jj * LD + (part + TPQ * c) * 4);
+#pragma unroll
+                for (int u = 0; u < QPT; ++u)
+                    dot[u] = fmaf(q[u][4 * c], kv.x, fmaf(q[u][4 * c + 1], kv.y, fmaf(q[u][4 * c + 2], kv.z, fmaf(q[u][4 * c + 3], kv.w, dot[u]))));
+            }
+#pragma unroll
+            for (int u = 0; u < QPT; ++u) {
+                float d = dot[u];
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                const int64_t jmax = p0 + q0 + qrow + 32 * u;                           // last key of this query
+                sc[u][jj] = (live[u] && j0 + jj <= jmax && j0 + jj < nk) ? d : -CUDART_INF_F;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QPT; ++u) {
+            float tmax = -CUDART_INF_F;
+#pragma unroll
+            for (int jj = 0; jj < KT; ++jj) tmax = fmaxf(tmax, sc[u][jj]);
+            const float m_new = fmaxf(m[u], tmax);
+            // a query whose every key so far is masked keeps m = -inf: its weights and its rescaling are zero
+            const float alpha = (m_new == -CUDART_INF_F) ? 0.f : expf(m[u] - m_new);
+            l[u] *= alpha;
+#pragma unroll
+            for (int d = 0; d < NC * 4; ++d) o[u][d] *= alpha;
+#pragma unroll
+            for (int jj = 0; jj < KT; ++jj) {
+                sc[u][jj] = (m_new == -CUDART_INF_F) ? 0.f : expf(sc[u][jj] - m_new);   // the score becomes its weight; 0 for masked keys
+                l[u] += sc[u][jj];
+            }
+            m[u] = m_new;
+        }
+#pragma unroll
+        for (int jj = 0; jj < KT; ++jj) {
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const float4 vv = *reinterpret_cast<const float4*>(vs + jj * LD + (part + TPQ * c) * 4);
+#pragma unroll
+                for (int u = 0; u < QPT; ++u) {
+                    o[u][4 * c] = fmaf(sc[u][jj], vv.x, o[u][4 * c]);
+                    o[u][4 * c + 1] = fmaf(sc[u][jj], vv.y, o[u][4 * c + 1]);
+                    o[u][4 * c + 2] = fmaf(sc[u][jj], vv.z, o[u][4 * c + 2]);
+                    o[u][4 * c + 3] = fmaf(sc[u][jj], vv.w, o[u][4 * c + 3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < QPT; ++u) {
+        if (!live[u]) continue;
+        const int qi = q0 + qrow + 32 * u;
+        const float inv = l[u] > 0.f ? 1.0f / l[u] : 0.f;
+        float* orow = out + (static_cast<int64_t>(b) * t_new + qi) * out_stride + h * HD + part * 4;
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+            *reinterpret_cast<float4*>(orow + 4 * TPQ * c) =
+                make_float4(o[u][4 * c] * inv, o[u][4 * c + 1] * inv, o[u][4 * c + 2] * inv, o[u][4 * c + 3] * inv);
+    }
+}
+
 // Embedding lookup: one block per index.  An index outside [0, vocab) yields a row of zeros, as the
 // reference's lookup does (src/ops.cpp:2643-2649); nothing is ever read outside the table.
 __global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ table, int64_t vocab, int64_t dim,
@@ -600,6 +727,30 @@ int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_he
                                 out, out_stride, s);
     return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0, out,
                            out_stride, s);
+}
+
+int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,
+                      const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride,
+                      void* stream) {
+    if (batch < 0 || t_new < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 65535 || t_new > 0x3fffffff)
+        return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
+    if (head_dim != 64 && head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+    if (qkv_stride < 3 * n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride too small");
+    if (batch * t_new == 0) return SGQ_OK;
+    if (!qkv || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (!aligned(qkv, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(out, 16) || (qkv_stride & 3) || (out_stride & 3))
+        return bad(SGQ_ERR_ALIGNMENT, "rows and caches must be 16-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    const dim3 grid(static_cast<unsigned>(ceil_div(t_new, kPrefillQ)), static_cast<unsigned>(batch * n_heads));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_dim == 128)
+        SGQ_CUDA_TRY(launch_kernel(attn_prefill_kernel<128>, grid, dim3(256), 0, s, stream_overlap_enabled(), qkv, qkv_stride,
+                                   static_cast<int>(t_new), static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride));
+    else
+        SGQ_CUDA_TRY(launch_kernel(attn_prefill_kernel<64>, grid, dim3(256), 0, s, stream_overlap_enabled(), qkv, qkv_stride,
+                                   static_cast<int>(t_new), static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride));
+    return SGQ_OK;
 }
 
 int sgqd_embedding(const float* table, int64_t vocab, int64_t dim, const int64_t* ids, int64_t rows, float* out, void* stream) {

@@ -11,8 +11,8 @@ and greedy selection (models.hpp:286-298: first index of the strict maximum).
 
 What runs where: every Linear goes through sgq_linear_int4 (decode kernel for the M = batch steps,
 tcgen05 kernel for the prefill); RMSNorm, RoPE + KV-cache store, cache attention and the SiLU gate
-the embedding lookup and the greedy argmax are the sgqd_* kernels of include/sgq_decoder.h; torch
-supplies device memory and the prompt's attention (fp32 math kernels).  A decode step touches no host state — the
+the prompt's causal attention, the embedding lookup and the greedy argmax are the sgqd_* kernels of
+include/sgq_decoder.h; torch supplies device memory only.  A decode step touches no host state — the
 cache position lives in device memory — so one step is recorded into a CUDA graph and replayed.
 
 Sharding (world > 1): heads, SwiGLU columns, output features of wo / w_down and the vocabulary are
@@ -327,17 +327,10 @@ class NanoLlamaInt4:
         return n
 
     def _prefill_attention(self, qkv, kc, vc, T: int, out):
-        """Causal attention of a prompt that starts at position 0: q from the rotated qkv rows, k and v
-        from the cache rows just written.  torch fp32 math kernels (exact fp32 matmuls, no TF32)."""
-        B, Hl, hd = self.batch, self.h_local, self.cfg.head_dim
-        q = qkv.view(B, T, 3, Hl, hd)[:, :, 0].permute(0, 2, 1, 3)                       # [B, Hl, T, hd]
-        k, v = kc[:, :, :T], vc[:, :, :T]
-        scores = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / hd ** 0.5)
-        mask = torch.ones(T, T, dtype=torch.bool, device=self.device).triu_(1)
-        scores.masked_fill_(mask, float("-inf"))
-        ctx = torch.matmul(torch.softmax(scores, dim=-1), v)                              # [B, Hl, T, hd]
-        out.view(B, T, Hl, hd).copy_(ctx.permute(0, 2, 1, 3))
-        self._count(6)
+        """Causal attention of the prompt: q from the rotated qkv rows, k and v from the cache rows just written."""
+        check(lib.sgqd_attn_prefill(_ptr(qkv), 3 * self.dim_local, self.batch, T, self.h_local, self.cfg.head_dim, _ptr(kc), _ptr(vc),
+                                    self.cfg.max_seq, _ptr(self.pos), _ptr(out), self.dim_local, _stream()), "sgqd_attn_prefill")
+        self._count()
 
     def _logits(self, n_rows: torch.Tensor, path: int, planes=None) -> torch.Tensor:
         M = n_rows.shape[0]

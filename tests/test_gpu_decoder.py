@@ -190,6 +190,30 @@ def test_attn_decode_position_out_of_range_stores_nothing(sgq):
     assert torch.equal(kc, k0) and torch.equal(vc, v0) and torch.isfinite(out).all()
 
 
+@pytest.mark.parametrize("B,H,hd,T,pos0", [(2, 3, 128, 70, 0), (1, 2, 64, 33, 0), (2, 2, 128, 5, 41), (1, 1, 128, 130, 7)])
+def test_attn_prefill(sgq, B, H, hd, T, pos0):
+    """Causal attention of a block of new tokens at positions pos0 .. pos0 + T - 1 over a cache that already holds
+    them (and pos0 older entries), against the float64 oracle."""
+    max_seq = pos0 + T + 3
+    r = np.random.default_rng(T * 7 + hd + pos0)
+    dim = H * hd
+    qkv = r.standard_normal((B * T, 3 * dim)).astype(np.float32)
+    kc = (r.standard_normal((B, H, max_seq, hd)) * 1.2).astype(np.float32)
+    vc = r.standard_normal((B, H, max_seq, hd)).astype(np.float32)
+    out = torch.full((B * T, dim), float("nan"), device="cuda")
+    pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    qt, kt, vt = dev(qkv), dev(kc), dev(vc)
+    sgq.check(sgq.lib.sgqd_attn_prefill(ptr(qt), 3 * dim, B, T, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, stream()))
+    q = qkv[:, :dim].reshape(B, T, H, hd).transpose(0, 2, 1, 3).astype(np.float64)              # [B, H, T, hd]
+    S = pos0 + T
+    k, v = kc[:, :, :S].astype(np.float64), vc[:, :, :S].astype(np.float64)
+    scores = np.einsum("bhtd,bhsd->bhts", q, k) / np.sqrt(hd)
+    mask = np.arange(S)[None, :] > (pos0 + np.arange(T))[:, None]
+    scores = np.where(mask, -np.inf, scores)
+    want = np.einsum("bhts,bhsd->bhtd", no.softmax(scores), v).transpose(0, 2, 1, 3).reshape(B * T, dim)
+    assert norm_err(out.cpu().numpy(), want) <= 5e-6
+
+
 def test_embedding_lookup_and_out_of_range_ids(sgq):
     """Rows of the table by index; an id outside [0, vocab) gives zeros as the reference's lookup does."""
     vocab, dim = 37, 260
