@@ -354,10 +354,26 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
                 "frac_of_nominal_bf16_2250": tf / 2250.0, "path": sgq.PATH_NAMES[path],
                 "includes": "activation conversion/quantization kernel + GEMM"}
 
+    def int8_tensor_peak():
+        # Denominator for the W8A8 lines: the vendor library's int8 x int8 -> int32 GEMM (cuBLASLt through
+        # torch._int_mm) on 8192^3, timed the same way; a library call used only as a measured peak.
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8).t()
+        f = lambda: torch._int_mm(a, b)  # noqa: E731
+        ms = timer(f, 5, inner=4)
+        return {"ms": ms, "tops": 2.0 * n ** 3 / ms / 1e9, "what": "torch._int_mm (cuBLASLt s8*s8->s32), 8192^3"}
+
+    guard("int8_tensor_peak_measured", int8_tensor_peak)
+    i8_peak = (out.get("int8_tensor_peak_measured") or {}).get("tops")
+
     for N in (4096, 11008):
         guard(f"prefill_bf16_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16))
         guard(f"prefill_bf16_int8w_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16, bits=8))
         guard(f"prefill_i8_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_I8))
+        r = out.get(f"prefill_i8_2048x4096x{N}")
+        if i8_peak and r and "tflops" in r:
+            r["frac_of_measured_int8"] = r["tflops"] / i8_peak
     status = sgq.device_status()
     out["device_status_word"] = status
     return out
