@@ -336,23 +336,21 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
         guard(f"pack_int4_g32_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 4))
         guard(f"pack_int8_tensor_{shape[0]}x{shape[1]}", lambda s=shape: pack(s, 8))
 
-    def gemm(N, path, bits=None):
-        M, K = 2048, 4096
+    def gemm(N, path, bits=None, layout=None, M=2048, K=4096):
+        layout = sgq.LAYOUT_NK if layout is None else layout
         x = torch.randn(M, K, device=dev, generator=g)
-        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        w = torch.randn((N, K) if layout == sgq.LAYOUT_NK else (K, N), device=dev, generator=g) * 0.02
         bits = bits or (8 if path == sgq.PATH_TC_I8 else 4)
         q = sgq.quantize_int4(w, GROUP) if bits == 4 else sgq.quantize_int8(w, sgq.PER_TENSOR)
         y = torch.empty(M, N, device=dev)
         ws = sgq.Workspace(dev)
-        if path == sgq.PATH_TC_I8:
-            f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
-        else:
-            f = lambda: sgq.quantized_matmul(x, q, None, layout=sgq.LAYOUT_NK, path=path, out=y, workspace=ws)  # noqa: E731
+        f = lambda: sgq.quantized_matmul(x, q, None, layout=layout, path=path, out=y, workspace=ws)  # noqa: E731
         ms = timer(f, 5, inner=4)
         tf = 2.0 * M * N * K / ms / 1e9
         return {"ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                 "frac_of_nominal_bf16_2250": tf / 2250.0, "path": sgq.PATH_NAMES[path],
-                "includes": "activation conversion/quantization kernel + GEMM"}
+                "includes": "activation conversion/quantization kernel + GEMM"
+                            + (" + per-forward expansion of the [K,N] weight to bf16 [N,K]" if layout == sgq.LAYOUT_KN else "")}
 
     def int8_tensor_peak():
         # Denominator for the W8A8 lines: the vendor library's int8 x int8 -> int32 GEMM (cuBLASLt through
@@ -371,9 +369,12 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
         guard(f"prefill_bf16_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16))
         guard(f"prefill_bf16_int8w_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16, bits=8))
         guard(f"prefill_i8_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_I8))
+        guard(f"prefill_bf16_layout_kn_2048x4096x{N}", lambda N=N: gemm(N, sgq.PATH_TC_BF16, layout=sgq.LAYOUT_KN))
         r = out.get(f"prefill_i8_2048x4096x{N}")
         if i8_peak and r and "tflops" in r:
             r["frac_of_measured_int8"] = r["tflops"] / i8_peak
+    # configuration 5's largest prefill: 3.85 TFLOP per forward, a 470 MB expanded weight
+    guard("prefill_bf16_8192x8192x28672", lambda: gemm(28672, sgq.PATH_TC_BF16, M=8192, K=8192))
     status = sgq.device_status()
     out["device_status_word"] = status
     return out

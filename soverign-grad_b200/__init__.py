@@ -239,9 +239,11 @@ def _weight_kn(q: QuantizedTensor, layout: int):
 
 def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: Optional[torch.Tensor] = None, *, layout: int = LAYOUT_KN,
                      path: int = PATH_AUTO, out: Optional[torch.Tensor] = None, workspace: Optional[Workspace] = None,
-                     ldy: Optional[int] = None) -> torch.Tensor:
+                     ldy: Optional[int] = None, workspace_limit: Optional[int] = None) -> torch.Tensor:
     """quantization::quantized_matmul_int8 / _int4 (src/quantization.cpp:189-206) in one launch.
-    layout=LAYOUT_KN is the reference's own convention (weight [K,N], y = x*W)."""
+    layout=LAYOUT_KN is the reference's own convention (weight [K,N], y = x*W).  workspace_limit caps the scratch
+    bytes offered to the library (the bf16 tensor-core path then dequantizes [N,K] weights tile by tile in shared
+    memory instead of expanding them into the scratch first)."""
     x = _f32_cuda(x)
     if x.dim() != 2:
         raise RuntimeError("matmul currently requires 2D tensors!")
@@ -258,10 +260,14 @@ def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: Optional[torch.T
     elif ldy is None:
         ldy = out.stride(0)
     need = linear_workspace_bytes(q.bits, M, K, N, layout, path)
+    if workspace_limit is not None:
+        need = min(need, workspace_limit)
     ws = None
     if need:
         ws = (workspace or Workspace(x.device)).get(need)
     wsp, wsb = (_ptr(ws), ws.numel()) if ws is not None else (None, 0)
+    if workspace_limit is not None:
+        wsb = min(wsb, workspace_limit)
     if q.bits == 4:
         rc = lib.sgq_linear_int4(_ptr(x), M, K, N, _ptr(q.qdata), _ptr(q.scales), layout, q.group_size, _ptr(b), _ptr(out),
                                  ldy, path, wsp, wsb, _stream())

@@ -140,12 +140,41 @@ int validate_linear(const LinearArgs& a, int path) {
     return SGQ_OK;
 }
 
+// would AUTO send this (decode-sized) problem to one of the streaming decode kernels?
+bool decode_path_ready(const LinearArgs& a) {
+    return gemv_supported(a) ||
+           (gemv_i8_supported(a) && a.workspace && aligned(a.workspace, 256) && a.workspace_bytes >= gemv_i8_workspace_bytes(a.M, a.K)) ||
+           (kn_decode_supported(a) && a.workspace && aligned(a.workspace, 256) &&
+            a.workspace_bytes >= kn_decode_workspace_bytes(a.bits, a.M, a.K, a.N));
+}
+
+constexpr int64_t kDecodeRows = 16;       // rows one decode launch sequence takes
+constexpr int64_t kTensorCoreRows = 64;   // from here on AUTO prefers the tensor-core kernels
+
 int run_linear(LinearArgs a, int path) {
     int rc = validate_linear(a, path);
     if (rc != SGQ_OK) return rc;
     if (a.M == 0 || a.N == 0) return SGQ_OK;
     if ((rc = check_device()) != SGQ_OK) return rc;
     if (a.K == 0) return launch_linear_simt(a);  // y = bias
+    if (path == SGQ_PATH_AUTO && a.M > kDecodeRows && a.M < kTensorCoreRows) {
+        // Batches between the decode kernels' 16 rows and the tensor-core kernels' 64: blocks of 16 rows on the
+        // decode kernels (each block streams the weights once; same fp32 contract as a decode batch) rather
+        // than the any-shape kernel.  The blocks run one after the other on the stream and share the workspace.
+        LinearArgs blk = a;
+        blk.M = kDecodeRows;
+        if (decode_path_ready(blk)) {
+            for (int64_t m0 = 0; m0 < a.M; m0 += kDecodeRows) {
+                LinearArgs sub = a;
+                sub.M = a.M - m0 < kDecodeRows ? a.M - m0 : kDecodeRows;
+                sub.x = a.x + m0 * a.K;
+                sub.y = a.y + m0 * a.ldy;
+                if (!decode_path_ready(sub)) return launch_linear_simt(a);      // (cannot happen: fewer rows need less)
+                if ((rc = run_linear(sub, SGQ_PATH_GEMV)) != SGQ_OK) return rc;
+            }
+            return SGQ_OK;
+        }
+    }
     if (path == SGQ_PATH_AUTO) {
         if (gemv_supported(a) || (gemv_i8_supported(a) && a.workspace && aligned(a.workspace, 256) &&
                                   a.workspace_bytes >= gemv_i8_workspace_bytes(a.M, a.K)) ||
@@ -153,7 +182,7 @@ int run_linear(LinearArgs a, int path) {
              a.workspace_bytes >= kn_decode_workspace_bytes(a.bits, a.M, a.K, a.N)))
             path = SGQ_PATH_GEMV;
         else if (a.M >= 64 && tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
-                 a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
+                 a.workspace && a.workspace_bytes >= tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
                  aligned(a.wq, 16) && aligned(a.scales, 16) && aligned(a.x, 16))
             path = SGQ_PATH_TC_BF16;
         else
@@ -298,6 +327,7 @@ size_t sgq_linear_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int
         case SGQ_PATH_TC_BF16: return tc_bf16_workspace_bytes(bits, M, K, N, layout);
         case SGQ_PATH_TC_I8: return tc_i8_workspace_bytes(M, K, N);
         default: {  // AUTO: enough for whichever path AUTO may take
+            if (M > 16 && M < 64) M = 16;       // runs as blocks of 16 rows that share the scratch
             size_t a = layout == SGQ_LAYOUT_KN ? kn_decode_workspace_bytes(bits, M, K, N)
                                                : (bits == 8 ? gemv_i8_workspace_bytes(M, K) : gemv_workspace_bytes(bits, M, K, N, layout));
             size_t b = M >= 64 ? tc_bf16_workspace_bytes(bits, M, K, N, layout) : 0;

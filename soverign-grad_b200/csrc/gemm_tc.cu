@@ -38,7 +38,11 @@ cudaError_t read_status_gemm(uint32_t* v, bool clear) {
 
 namespace {
 
-enum Mode { kI8 = 0, kBF16 = 1, kBF16W8 = 2 };   // W8A8 | bf16 x INT4 g=32 | bf16 x INT8 codes (scale in the epilogue)
+// W8A8 | bf16 x INT4 g=32 | bf16 x INT8 codes (scale in the epilogue) | bf16 x bf16 weights already expanded in
+// global memory (the [K,N] layouts: a kernel in front dequantizes and transposes them once per forward)
+enum Mode { kI8 = 0, kBF16 = 1, kBF16W8 = 2, kBF16Plain = 3 };
+// both operands arrive by TMA in their final shared-memory form: no dequant warps, no raw ring
+__host__ __device__ constexpr bool direct_b(int mode) { return mode == kI8 || mode == kBF16Plain; }
 
 constexpr int BM = 256, BN = 256;     // two UMMA_M = 128 halves per tile
 constexpr int kHalfM = 128;
@@ -60,9 +64,9 @@ struct Cfg {
     static constexpr int kUmmaK = MODE == kI8 ? 32 : 16;            // elements per instruction (32 bytes)
     static constexpr int kAStages = MODE == kBF16W8 ? 2 : 3;         // the INT8 raw ring takes the room of one A stage
     static constexpr int kBStages = 3;
-    static constexpr int kRawStages = MODE == kI8 ? 0 : 3;
+    static constexpr int kRawStages = direct_b(MODE) ? 0 : 3;
     static constexpr int kRawStageBytes = MODE == kBF16W8 ? BN * 64 : kRawBytes;
-    static constexpr int kWarps = MODE == kI8 ? 7 : 7 + kDequantWarps;
+    static constexpr int kWarps = direct_b(MODE) ? 7 : 7 + kDequantWarps;
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kAOff = 0;
     static constexpr int kBOff = kAStages * kABytes;
@@ -153,7 +157,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], MODE == kI8 ? 1 : kDequantWarps); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], direct_b(MODE) ? 1 : kDequantWarps); mbar_init(&b_empty[i], 1); }
         for (int i = 0; i < NR; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kDequantWarps); }
         for (int i = 0; i < 2; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 4); }
         mbar_fence_init();
@@ -195,7 +199,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t seen_tile = 0;
             for (int64_t it = 0; it < total_its; ++it, rb.advance(), rr.advance(), w.advance(1, kblocks, gridDim.x)) {
                 if (w.tcount != seen_tile) { seen_tile = w.tcount; n0 = static_cast<int32_t>((w.tile / m_tiles) * BN); }
-                if (MODE == kI8) {
+                if (direct_b(MODE)) {
                     const int s = rb.slot;
                     if (!mbar_wait(&b_empty[s], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | static_cast<uint32_t>(it)); break; }
                     mbar_arrive_expect_tx(&b_full[s], kBBytes);
@@ -259,7 +263,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // row segments.
         uint8_t* stage_out = smem + C::kOutOff + (warp - kEpilogueWarp0) * 2048;
         const int cq = lane & 7, rq = lane >> 3;                  // after the transpose: columns 4cq..4cq+3, rows rq + 4i
-        constexpr bool kScaleN = MODE == kI8 || MODE == kBF16W8;       // weight scale applied per output column here
+        // weight scale applied per output column here (expanded INT8 codes: when the caller left it to the epilogue)
+        const bool kScaleN = MODE == kI8 || MODE == kBF16W8 || (MODE == kBF16Plain && p.sw != nullptr);
         const float sw_all = (kScaleN && !p.sw_per_row) ? p.sw[0] : 1.0f;
         for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
@@ -468,10 +473,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
-// x fp32 [M,K] -> bf16 [M,K]; inside every aligned group of 8 the order is k+{0,4,1,5,2,6,3,7},
-// the order in which the dequant warps emit the 8 nibbles of a packed word.
-// kCodeBytes (INT8 weights): inside every aligned group of 8 the order is k+{0,2,1,3,4,6,5,7} instead.
-template <bool kCodeBytes>
+// x fp32 [M,K] -> bf16 [M,K].  ORDER 0: inside every aligned group of 8 the order is k+{0,4,1,5,2,6,3,7},
+// the order in which the dequant warps emit the 8 nibbles of a packed word.  ORDER 1 (INT8 weights):
+// k+{0,2,1,3,4,6,5,7}.  ORDER 2: natural order (weights expanded to bf16 in global memory).
+template <int ORDER>
 __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __restrict__ x, uint4* __restrict__ out,
                                                              int64_t chunks) {
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -483,8 +488,104 @@ __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __rest
             return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
                    (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
         };
-        out[i] = kCodeBytes ? make_uint4(pk(a.x, a.z), pk(a.y, a.w), pk(b.x, b.z), pk(b.y, b.w))
-                            : make_uint4(pk(a.x, b.x), pk(a.y, b.y), pk(a.z, b.z), pk(a.w, b.w));
+        out[i] = ORDER == 1   ? make_uint4(pk(a.x, a.z), pk(a.y, a.w), pk(b.x, b.z), pk(b.y, b.w))
+                 : ORDER == 0 ? make_uint4(pk(a.x, b.x), pk(a.y, b.y), pk(a.z, b.z), pk(a.w, b.w))
+                              : make_uint4(pk(a.x, a.y), pk(a.z, a.w), pk(b.x, b.y), pk(b.z, b.w));
+    }
+}
+
+// Weights stored [K,N] (the reference module's layout) -> bf16 [N,K] in global memory, dequantized with the
+// reference's code * scale product in fp32 and rounded once.  A CTA transposes a tile of 64 k x 128 n through
+// shared memory: a thread reads 32 consecutive n of one k (INT4: one 16-byte load = one quantization group,
+// which runs along n in this layout; INT8: two loads), and the tile leaves as 128-byte rows of one n each.
+// N % 32 == 0 (groups never straddle rows), K % 64 == 0.  INT8 scales: [1] or one per ROW OF THE STORED TENSOR,
+// i.e. per k.
+constexpr int kTrK = 64, kTrN = 128, kTrStride = kTrK + 8;      // bf16 elements per shared-memory row (16-byte multiple)
+template <int BITS>
+__global__ void __launch_bounds__(256) dequant_kn_to_nk_bf16_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales,
+                                                                   int per_row, int64_t K, int64_t N,
+                                                                   __nv_bfloat16* __restrict__ out) {
+    __shared__ __align__(16) __nv_bfloat16 tile[kTrN * kTrStride];
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kTrN, k0 = static_cast<int64_t>(blockIdx.y) * kTrK;
+    const int kk = threadIdx.x >> 2, nq = threadIdx.x & 3;
+    const int64_t k = k0 + kk, n = n0 + 32 * nq;
+    if (n < N) {        // K % 64 == 0: k is always in range
+        const int64_t e = k * N + n;                                  // flat element index of the first of 32
+        if (BITS == 4) {
+            const uint4 w = *reinterpret_cast<const uint4*>(wq + e / 2);
+            const float sc = scales[e / 32];
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int code = static_cast<int>(words[i] << (28 - 4 * j)) >> 28;      // nibble j, sign-extended
+                    tile[(32 * nq + 8 * i + j) * kTrStride + kk] = __float2bfloat16_rn(__fmul_rn(static_cast<float>(code), sc));
+                }
+            }
+        } else {
+            const float sc = per_row ? scales[k] : scales[0];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 w = *reinterpret_cast<const uint4*>(wq + e + 16 * h);
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int code = static_cast<int>(words[i] << (24 - 8 * j)) >> 24;
+                        tile[(32 * nq + 16 * h + 4 * i + j) * kTrStride + kk] =
+                            __float2bfloat16_rn(__fmul_rn(static_cast<float>(code), sc));
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i, r = idx >> 3, c = idx & 7;
+        if (n0 + r < N)
+            *reinterpret_cast<uint4*>(out + (n0 + r) * K + k0 + 8 * c) = *reinterpret_cast<const uint4*>(tile + r * kTrStride + 8 * c);
+    }
+}
+
+// Weights stored [N,K] -> bf16 [N,K] in global memory, eight elements per thread (one packed word, or eight code
+// bytes).  INT4 g=32: code * scale in fp32, rounded once.  INT8: the codes themselves (exact in bf16); their scale
+// (per tensor or per output row) is applied by the GEMM's epilogue in fp32.
+// The same launch converts the activations (x fp32 [M,K] -> bf16, natural order): both operands of the GEMM
+// behind it are ready after one kernel.
+template <int BITS>
+__global__ void __launch_bounds__(256) expand_nk_bf16_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales,
+                                                            int64_t chunks, uint4* __restrict__ out, const float* __restrict__ x,
+                                                            int64_t xchunks, uint4* __restrict__ xout) {
+    auto pk = [](float lo, float hi) {
+        return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+               (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+    };
+    int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+    for (int64_t j = i; j < xchunks; j += stride) {
+        const float4 a = reinterpret_cast<const float4*>(x)[2 * j];
+        const float4 b = reinterpret_cast<const float4*>(x)[2 * j + 1];
+        xout[j] = make_uint4(pk(a.x, a.y), pk(a.z, a.w), pk(b.x, b.y), pk(b.z, b.w));
+    }
+    for (; i < chunks; i += stride) {
+        float v[8];
+        if (BITS == 4) {
+            const uint32_t w = reinterpret_cast<const uint32_t*>(wq)[i];
+            const float sc = scales[i >> 2];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(static_cast<float>(static_cast<int>(w << (28 - 4 * j)) >> 28), sc);
+        } else {
+            const uint2 w = reinterpret_cast<const uint2*>(wq)[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[j] = static_cast<float>(static_cast<int>(w.x << (24 - 8 * j)) >> 24);
+                v[4 + j] = static_cast<float>(static_cast<int>(w.y << (24 - 8 * j)) >> 24);
+            }
+        }
+        out[i] = make_uint4(pk(v[0], v[1]), pk(v[2], v[3]), pk(v[4], v[5]), pk(v[6], v[7]));
     }
 }
 
@@ -506,25 +607,38 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
 }  // namespace
 
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group) {
-    return ((bits == 4 && group == 32) || bits == 8) && layout == SGQ_LAYOUT_NK && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 &&
-           M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31);
+    if (!(((bits == 4 && group == 32) || bits == 8) && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 && M < (1LL << 31) &&
+          N < (1LL << 31) && K < (1LL << 31)))
+        return false;
+    // [K,N]: quantization groups run along N and must not straddle rows of the stored tensor
+    return layout == SGQ_LAYOUT_NK || (layout == SGQ_LAYOUT_KN && (N % 32) == 0);
 }
 
+// bf16 activations plus the whole weight expanded to bf16 [N,K]: the faster form (a GEMM whose operands both
+// arrive by TMA), and the only one for weights stored [K,N]
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
-    (void)bits; (void)N; (void)layout;
+    (void)bits; (void)layout;
+    return round_up(static_cast<size_t>(M) * static_cast<size_t>(K) * 2, 256) +
+           round_up(static_cast<size_t>(N) * static_cast<size_t>(K) * 2, 256);
+}
+
+// the least the path runs with: weights stored [N,K] can be dequantized tile by tile in shared memory instead
+size_t tc_bf16_min_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
+    if (layout == SGQ_LAYOUT_KN) return tc_bf16_workspace_bytes(bits, M, K, N, layout);
     return round_up(static_cast<size_t>(M) * static_cast<size_t>(K) * 2, 256);
 }
 
 int launch_linear_tc_bf16(const LinearArgs& a) {
     if (!tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group)) {
-        set_error("bf16 tensor-core path needs INT4 g=32 or INT8 weights stored [N,K] and K%%64==0");
+        set_error("bf16 tensor-core path needs INT4 g=32 or INT8 weights, K%%64==0, and N%%32==0 when stored [K,N]");
         return SGQ_ERR_UNSUPPORTED;
     }
     if (!aligned(a.x, 16) || !aligned(a.wq, 16) || !aligned(a.scales, 8)) {
         set_error("bf16 tensor-core path needs 16-byte aligned x and packed weights, 8-byte aligned scales");
         return SGQ_ERR_ALIGNMENT;
     }
-    const size_t need = tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    const size_t need = tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    const bool expand = a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
     if (!a.workspace || a.workspace_bytes < need) {
         set_error("bf16 tensor-core path needs %zu workspace bytes, got %zu", need, a.workspace ? a.workspace_bytes : 0);
         return SGQ_ERR_WORKSPACE;
@@ -533,11 +647,15 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
     int64_t blocks = ceil_div(chunks, 256);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     const int cgrid = static_cast<int>(blocks < cap ? blocks : cap);
-    if (a.bits == 8)
-        convert_x_bf16_kernel<true><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
-    else
-        convert_x_bf16_kernel<false><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
-    SGQ_LAUNCH_CHECK("convert_x_bf16_kernel");
+    if (!(expand && a.layout == SGQ_LAYOUT_NK)) {       // (that form converts x in its weight-expansion launch below)
+        if (expand)
+            convert_x_bf16_kernel<2><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
+        else if (a.bits == 8)
+            convert_x_bf16_kernel<1><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
+        else
+            convert_x_bf16_kernel<0><<<cgrid, 256, 0, a.stream>>>(a.x, static_cast<uint4*>(a.workspace), chunks);
+        SGQ_LAUNCH_CHECK("convert_x_bf16_kernel");
+    }
 
     CUtensorMap ma, mb;
     if (!make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.workspace, static_cast<uint64_t>(a.K),
@@ -545,6 +663,42 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
         return SGQ_ERR_CUDA;
     Params p{};
     p.bias = a.bias; p.y = a.y; p.ldy = a.ldy; p.M = a.M; p.N = a.N; p.K = a.K;
+    if (expand) {
+        // expand the stored weight to bf16 [N,K] behind the activations in the workspace, then a GEMM whose
+        // operands both arrive by TMA
+        __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(a.workspace) +
+                                                             round_up(static_cast<size_t>(a.M) * static_cast<size_t>(a.K) * 2, 256));
+        if (a.layout == SGQ_LAYOUT_KN) {
+            const dim3 tgrid(static_cast<unsigned>(ceil_div(a.N, kTrN)), static_cast<unsigned>(a.K / kTrK));
+            if (a.bits == 4)
+                dequant_kn_to_nk_bf16_kernel<4><<<tgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 0, a.K, a.N, wt);
+            else
+                dequant_kn_to_nk_bf16_kernel<8><<<tgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales,
+                                                                            a.scheme == SGQ_PER_ROW ? 1 : 0, a.K, a.N, wt);
+            SGQ_LAUNCH_CHECK("dequant_kn_to_nk_bf16_kernel");
+        } else {
+            const int64_t wchunks = a.N * a.K / 8;
+            const int64_t wblocks = ceil_div(wchunks > chunks ? wchunks : chunks, 256);
+            const int wgrid = static_cast<int>(wblocks < cap ? wblocks : cap);
+            if (a.bits == 4)
+                expand_nk_bf16_kernel<4><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, wchunks,
+                                                                     reinterpret_cast<uint4*>(wt), a.x, chunks,
+                                                                     static_cast<uint4*>(a.workspace));
+            else
+                expand_nk_bf16_kernel<8><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, wchunks,
+                                                                     reinterpret_cast<uint4*>(wt), a.x, chunks,
+                                                                     static_cast<uint4*>(a.workspace));
+            SGQ_LAUNCH_CHECK("expand_nk_bf16_kernel");
+            if (a.bits == 8) {          // codes are exact in bf16: their scale goes to the epilogue
+                p.sw = a.scales;
+                p.sw_per_row = (a.scheme == SGQ_PER_ROW) ? 1 : 0;
+            }
+        }
+        if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, wt, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
+                                static_cast<uint64_t>(a.K) * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+            return SGQ_ERR_CUDA;
+        return launch_tc<kBF16Plain>(ma, mb, p, a.stream);
+    }
     if (a.bits == 8) {
         if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
                                 static_cast<uint64_t>(a.K), 64, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
