@@ -90,6 +90,7 @@ struct Params {
     // kBF16
     const float* wscales;   // [N, K/32]
     int vec_store;          // y is 16-byte aligned with ldy % 4 == 0: 128-bit stores
+    int split_last;         // the tiles of the last, partial round are taken as two 128-row halves by two CTAs
 };
 
 __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
@@ -112,17 +113,21 @@ struct Ring {
 };
 
 // Walks this CTA's (tile, k-block) sequence: tiles blockIdx.x, +gridDim.x, ...; kb = 0..kblocks-1.
+// When the last round is split, the CTA's item number `switch_at` is `last_tile` instead.
 struct Walk {
     int64_t tile;
     int kb;
     uint32_t tcount = 0;   // tiles completed so far
-    __device__ __forceinline__ Walk(int64_t first_tile) : tile(first_tile), kb(0) {}
+    int64_t switch_at, last_tile;
+    __device__ __forceinline__ Walk(int64_t first_tile, int64_t switch_at_ = -1, int64_t last_tile_ = 0)
+        : tile(switch_at_ == 0 ? last_tile_ : first_tile), kb(0), switch_at(switch_at_), last_tile(last_tile_) {}
     __device__ __forceinline__ void advance(int stride, int kblocks, int64_t tile_stride) {
         kb += stride;
         while (kb >= kblocks) {
             kb -= kblocks;
             tile += tile_stride;
             ++tcount;
+            if (static_cast<int64_t>(tcount) == switch_at) tile = last_tile;
         }
     }
 };
@@ -152,7 +157,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int64_t tiles = m_tiles * n_tiles;
     const int kblocks = static_cast<int>((p.K + C::kBlockK - 1) / C::kBlockK);
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; `it` counts its k-blocks across tiles
-    const int64_t my_tiles = (tiles > blockIdx.x) ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    int64_t my_tiles = (tiles > blockIdx.x) ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // Split last round (both operands by TMA only): when the tiles left for the last round fill at most half of the
+    // CTAs, each of them goes to two CTAs as two 128-row halves (one accumulator each), and the round takes half the
+    // time.  The CTA's items are then `rounds` whole tiles and, for the first 2 * last CTAs, one half tile.
+    const int64_t rounds = tiles / gridDim.x, last = tiles - rounds * gridDim.x;
+    const bool split = direct_b(MODE) && p.split_last && last > 0 && 2 * last <= gridDim.x;
+    int64_t switch_at = -1, last_tile = 0;
+    int half_row0 = 0;                     // row offset of this CTA's half inside the split tile
+    if (split) {
+        const bool mine = blockIdx.x < 2 * last;
+        my_tiles = rounds + (mine ? 1 : 0);
+        if (mine) {
+            switch_at = rounds;
+            last_tile = rounds * gridDim.x + blockIdx.x / 2;
+            half_row0 = static_cast<int>(blockIdx.x & 1) * kHalfM;
+        }
+    }
     const int64_t total_its = my_tiles * kblocks;
 
     if (threadIdx.x == 0) {
@@ -177,11 +198,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) {
             tma_prefetch_descriptor(&map_a);
             Ring<NA> ra;
-            Walk w(blockIdx.x);
-            int32_t m0 = static_cast<int32_t>((w.tile % m_tiles) * BM);
+            Walk w(blockIdx.x, switch_at, last_tile);
+            auto row0 = [&]() {       // a half tile loads the box that starts at its own 128 rows (the rest is not used)
+                return static_cast<int32_t>((w.tile % m_tiles) * BM + (static_cast<int64_t>(w.tcount) == switch_at ? half_row0 : 0));
+            };
+            int32_t m0 = row0();
             uint32_t seen_tile = 0;
             for (int64_t it = 0; it < total_its; ++it, ra.advance(), w.advance(1, kblocks, gridDim.x)) {
-                if (w.tcount != seen_tile) { seen_tile = w.tcount; m0 = static_cast<int32_t>((w.tile % m_tiles) * BM); }
+                if (w.tcount != seen_tile) { seen_tile = w.tcount; m0 = row0(); }
                 const int s = ra.slot;
                 if (!mbar_wait(&a_empty[s], ra.phase ^ 1u)) { report(kDevErrEmptyWait, static_cast<uint32_t>(it)); break; }
                 mbar_arrive_expect_tx(&a_full[s], kABytes);
@@ -194,7 +218,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tma_prefetch_descriptor(&map_b);
             Ring<NB> rb;
             Ring<NR> rr;
-            Walk w(blockIdx.x);
+            Walk w(blockIdx.x, switch_at, last_tile);
             int32_t n0 = static_cast<int32_t>((w.tile / m_tiles) * BN);
             uint32_t seen_tile = 0;
             for (int64_t it = 0; it < total_its; ++it, rb.advance(), rr.advance(), w.advance(1, kblocks, gridDim.x)) {
@@ -219,10 +243,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t idesc = (MODE == kI8) ? umma_idesc(2u, 1u, kHalfM, BN) : umma_idesc(1u, 1u, kHalfM, BN);
             Ring<NA> ra;
             Ring<NB> rb;
-            Walk w(blockIdx.x);
+            Walk w(blockIdx.x, switch_at, last_tile);
             for (int64_t it = 0; it < total_its; ++it, ra.advance(), rb.advance(), w.advance(1, kblocks, gridDim.x)) {
                 const int kb = w.kb;
                 const uint32_t tcount = w.tcount;
+                const int halves = static_cast<int64_t>(tcount) == switch_at ? 1 : 2;      // a half tile uses the first accumulator
                 if (kb == 0) {
                     // both accumulators are reused by every tile: wait until the epilogue has drained them
                     if (!mbar_wait(&tmem_empty[0], (tcount & 1u) ^ 1u)) { report(kDevErrMmaWait, tcount); break; }
@@ -235,6 +260,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint64_t bdesc = umma_desc_sw128(smem_u32(smem + C::kBOff + sb * kBBytes));
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
+                    if (half >= halves) break;
                     const uint32_t tmem_d = tmem_base + half * BN;
                     const uint64_t adesc = umma_desc_sw128(smem_u32(smem + C::kAOff + sa * kABytes + half * (kHalfM * 128)));
 #pragma unroll
@@ -266,11 +292,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // weight scale applied per output column here (expanded INT8 codes: when the caller left it to the epilogue)
         const bool kScaleN = MODE == kI8 || MODE == kBF16W8 || (MODE == kBF16Plain && p.sw != nullptr);
         const float sw_all = (kScaleN && !p.sw_per_row) ? p.sw[0] : 1.0f;
-        for (int64_t tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++tcount) {
-            const int64_t m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (; static_cast<int64_t>(tcount) < my_tiles && alive; ++tcount) {
+            const bool half_item = static_cast<int64_t>(tcount) == switch_at;
+            const int64_t tile = half_item ? last_tile : blockIdx.x + static_cast<int64_t>(tcount) * gridDim.x;
+            const int64_t m0 = (tile % m_tiles) * BM + (half_item ? half_row0 : 0), n0 = (tile / m_tiles) * BN;
             if (!mbar_wait(&tmem_full[0], tcount & 1u)) { report(kDevErrMmaWait, 0x800000u | tcount); alive = false; break; }
             tcgen05_fence_after();
-            for (int half = 0; half < 2; ++half) {
+            for (int half = 0; half < (half_item ? 1 : 2); ++half) {
                 const int64_t mrow0 = m0 + half * kHalfM + quarter * 32;   // first row of this warp's block
                 const int64_t m = mrow0 + lane;
                 float sxm = 1.0f;
@@ -596,7 +624,16 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
     using C = Cfg<MODE>;
     p.vec_store = (aligned(p.y, 16) && (p.ldy % 4) == 0) ? 1 : 0;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
-    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    p.split_last = 0;
+    if (direct_b(MODE)) {
+        // the tiles of the last, partial round as half tiles on twice as many CTAs, where they fit
+        const int64_t sms = sm_count(), last = tiles % sms;
+        if (last > 0 && 2 * last <= sms) {
+            p.split_last = 1;
+            if (tiles < sms) grid = static_cast<int>(2 * tiles);
+        }
+    }
     static SmemOptIn optin;   // one per MODE instantiation
     SGQ_CUDA_TRY(optin.ensure(linear_tc_kernel<MODE>, C::kSmemBytes));
     linear_tc_kernel<MODE><<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
