@@ -8,10 +8,11 @@
 //   * a step is 128 k of a 16-row tile (one 128-byte swizzled row per weight row), a stage is 8
 //     steps; the bytes go to the tensor core as they are (mma.sync m16n8k32 s8 x s8 -> s32), with
 //     no unpacking and no offset;
-//   * there is no per-group weight scale; the exact int32 sum of every 32-k group is multiplied by
-//     the activation scale of that group (gemv_prepare.cuh: 24-bit fixed point per group, the low
-//     digit in column sets of its own that are skipped where it cannot matter) and added up in fp32,
-//     the weight scale is applied once per output;
+//   * there is no per-group weight scale, and the activations are scaled per 128 k (gemv_prepare.cuh
+//     with blocks of four groups: 24-bit fixed point below the block's absmax, the low digit in column
+//     sets of its own that are skipped where it cannot matter): the exact sums of a step's four groups
+//     add up in one int32 accumulator, are multiplied by the step's activation scale and added up in
+//     fp32; the weight scale is applied once per output;
 //   * the main activation digit planes, their scales and the low-digit flags (laid out for the
 //     natural k order of an int8 B fragment) are written once by a conversion kernel and stream
 //     through the same pipeline stages as the weights, 32 groups at a time, from L2.  They are
@@ -21,7 +22,7 @@
 //     one named barrier, then thread (m, row) adds the eight partials in warp order (fixed order:
 //     the same bits every run), recombines the digits, applies the weight scale and the bias.
 //
-// y[m,n] = (sum_j 256^j * sum_g sx[m,g] * S_j[g,m,n]) * scale[n] + bias[n],  S_j exact integers.
+// y[m,n] = (sum_j 256^j * sum_b sx[m,b] * S_j[b,m,n]) * scale[n] + bias[n],  S_j exact integers per 128-k block b.
 #include "sgq_common.cuh"
 #include "gemv_prepare.cuh"
 #include "sm100_ptx.cuh"
@@ -91,11 +92,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
                  : "r"(smem_addr));
 }
 
-// total += (exact int32 sums of one 32-k group) * (activation scales of columns 2t and 2t+1)
-__device__ __forceinline__ void accumulate_group(float (&total)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, float2 sx) {
-    int d[4];
-    mma_s8s8_16832_magic(d, a, b0, b1);
-    // d holds 12582912.0f + (exact group sum) as fp32 bits
+// D += A * B: the groups of a 128-k step add up in the same int32 accumulator (four groups of at most 32 * 127 * 127
+// stay inside the range in which the fp32 view of the magic start value is exact)
+__device__ __forceinline__ void mma_s8s8_16832_acc(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// total += (exact int32 sums of one 128-k step, as 12582912.0f + sum in fp32 bits) * (activation scales of columns 2t, 2t+1)
+__device__ __forceinline__ void scale_step(float (&total)[4], const int (&d)[4], float2 sx) {
     total[0] = __fmaf_rn(sx.x, __fsub_rn(__int_as_float(d[0]), kMagicF), total[0]);
     total[1] = __fmaf_rn(sx.y, __fsub_rn(__int_as_float(d[1]), kMagicF), total[1]);
     total[2] = __fmaf_rn(sx.x, __fsub_rn(__int_as_float(d[2]), kMagicF), total[2]);
@@ -121,7 +127,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_x_i8_kernel(const float*
             const float4 a = __ldg(xr + 2 * c), b = __ldg(xr + 2 * c + 1);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
-        convert_groups<kOrderNatural>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nlow, 1.0f, pp, in);
+        convert_groups<kOrderNatural, 4>(v, m, M, static_cast<size_t>(c >> 5) * 8, mode, nmain, nlow, 1.0f, pp, in);
     }
 }
 
@@ -253,30 +259,42 @@ gemv_int8_nk_kernel(const __grid_constant__ CUtensorMap map_w, const uint8_t* __
                 uint32_t a[4][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) ldmatrix_x4(a[i], wbox + lm_off[i]);    // rows g / g+8, k = 32i + 4t.. and 32i + 16 + 4t..
+                // The four 32-k groups of the step share their activation scales (gemv_prepare.cuh, blocks of four)
+                // and the weights have no group scale: their exact sums add up in int32, one scaling per step.
+                int d[NM][4];
+#pragma unroll
+                for (int s2 = 0; s2 < NM; ++s2)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) d[s2][c] = kMagicBits;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint8_t* xgi = xg + i * (256 * NM);
-                    const float* sgi = sg + i * (8 * NM);
 #pragma unroll
                     for (int s2 = 0; s2 < NM; ++s2) {
                         if ((s2 & 1) == 0 && s2 + 1 < NM) {          // two main sets side by side: one 128-bit load per lane
                             const uint4 q = *reinterpret_cast<const uint4*>(xgi + (s2 >> 1) * 512 + lane * 16);
-                            accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
-                            accumulate_group(total[s2 + 1], a[i], q.z, q.w, *reinterpret_cast<const float2*>(sgi + 2 * s2 + 2));
+                            mma_s8s8_16832_acc(d[s2], a[i], q.x, q.y);
+                            mma_s8s8_16832_acc(d[s2 + 1], a[i], q.z, q.w);
                         } else if ((s2 & 1) == 0) {
                             const uint2 q = *reinterpret_cast<const uint2*>(xgi + plane_offset(0, NM, s2, lane));
-                            accumulate_group(total[s2], a[i], q.x, q.y, *reinterpret_cast<const float2*>(sgi + 2 * s2));
+                            mma_s8s8_16832_acc(d[s2], a[i], q.x, q.y);
                         }
                     }
-                    // low digits: only where a row of the set flagged this group (rare: one value dominating its group)
+                }
 #pragma unroll
-                    for (int l = 0; l < NL; ++l) {
-                        const uint2 fl = *reinterpret_cast<const uint2*>(fg + i * 16 + l * 8);
-                        if ((fl.x | fl.y) != 0u) {                   // the same for every lane of the warp
+                for (int s2 = 0; s2 < NM; ++s2) scale_step(total[s2], d[s2], *reinterpret_cast<const float2*>(sg + 2 * s2));
+                // low digits: only where a row of the set flagged this step (rare: one value dominating its 128)
+#pragma unroll
+                for (int l = 0; l < NL; ++l) {
+                    const uint2 fl = *reinterpret_cast<const uint2*>(fg + l * 8);
+                    if ((fl.x | fl.y) != 0u) {                       // the same for every lane of the warp
+                        int dl[4] = {kMagicBits, kMagicBits, kMagicBits, kMagicBits};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
                             const uint2 q = __ldg(reinterpret_cast<const uint2*>(low_digits + plane_offset(grp0 + i, NL, l, lane)));
-                            const float2 sl = __ldg(reinterpret_cast<const float2*>(low_scales + ((grp0 + i) * 4 + t) * NL * 2 + l * 2));
-                            accumulate_group(total[NM + l], a[i], q.x, q.y, sl);
+                            mma_s8s8_16832_acc(dl, a[i], q.x, q.y);
                         }
+                        scale_step(total[NM + l], dl, __ldg(reinterpret_cast<const float2*>(low_scales + (grp0 * 4 + t) * NL * 2 + l * 2)));
                     }
                 }
             }

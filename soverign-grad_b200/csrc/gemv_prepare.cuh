@@ -143,9 +143,14 @@ __host__ __device__ inline PreparedParts prepared_parts(uint8_t* base, size_t gr
 // `scale_mul` is folded into the stored scales (the INT4 kernel feeds its codes to the tensor core
 // as 16 * code and passes 1/16).  A lane with store == false (beyond the end of a row) passes zeros
 // and writes nothing.
-template <int ORDER>
+// BLOCK = 4: four consecutive groups (128 k, 16 lanes) share one scale and one low-digit flag, both stored with
+// every group of the four (the INT8 decode kernel, which has no per-group weight scale, then adds the exact sums
+// of the four groups in int32 and scales once); the rule for the low digit is the same with the block in the
+// place of the group: it is dropped where the block's absmax is below 4 rms(block).
+template <int ORDER, int BLOCK = 1>
 __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M, size_t group0, int mode, int nmain, int nlow,
                                                float scale_mul, const PreparedParts& pp, bool store = true) {
+    static_assert(BLOCK == 1 || BLOCK == 4, "scale blocks of one or four groups");
     const int lane = threadIdx.x & 31;
     uint32_t mb = 0;
 #pragma unroll
@@ -158,6 +163,12 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M
         mb = o > mb ? o : mb;
         o = __shfl_xor_sync(0xffffffffu, mb, 2);
         mb = o > mb ? o : mb;
+        if (BLOCK == 4) {
+            o = __shfl_xor_sync(0xffffffffu, mb, 4);
+            mb = o > mb ? o : mb;
+            o = __shfl_xor_sync(0xffffffffu, mb, 8);
+            mb = o > mb ? o : mb;
+        }
     }
     const float gmax = __uint_as_float(mb);
     float P, sx;
@@ -182,12 +193,16 @@ __device__ __forceinline__ void convert_groups(const float (&v)[8], int m, int M
     }
     sq += __shfl_xor_sync(0xffffffffu, sq, 1);
     sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    if (BLOCK == 4) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+    }
     if (!store) return;
     const size_t group = group0 + (lane >> 2);
     const int q4 = lane & 3;            // which quarter of the group this lane holds
     if (mode == 2 && q4 == 0) {
         // one value dominates the group (32 gmax^2 > 16 sum x^2, in units of the scaled integers): keep the low digit
-        pp.flags[group * 16 + m] = (P != 0.0f && sq < 2.0f * kDigitRange * kDigitRange) ? 1 : 0;
+        pp.flags[group * 16 + m] = (P != 0.0f && sq < (2.0f * BLOCK) * kDigitRange * kDigitRange) ? 1 : 0;
         if (m == 0)
             for (int z = M; z < 16; ++z) pp.flags[group * 16 + z] = 0;     // rows this batch does not have
     }

@@ -135,8 +135,9 @@ def test_decode_int8_kernel_against_port(sgq, port, M, K, N):
         assert rel_err(y, want) <= TOL_FP32, (M, K, N, scheme, rel_err(y, want))
         # the kernel's own arithmetic: block-scaled fixed-point activations (tests/util.py), exact integer
         # dot products per 128-k step, then fp32 scaling
-        model = (block_fixed_point(x) @ wq.astype(np.float64).T) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
-        assert rel_err(y, model) <= (2e-6 if M <= 2 else 5e-5), ("layout/pipeline error, not rounding", rel_err(y, model))
+        model = (block_fixed_point(x, 128) @ wq.astype(np.float64).T) * np.asarray(sw, np.float64).reshape(1, -1) + b[None, :]
+        # (three rows or more: a block right at the threshold of the low-digit rule may fall either side of it in fp32)
+        assert rel_err(y, model) <= (2e-6 if M <= 2 else 1e-4), ("layout/pipeline error, not rounding", rel_err(y, model))
         y_auto = sgq.quantized_matmul(dev(x), q, dev(b), layout=cases.LAYOUT_NK, path=sgq.PATH_AUTO, workspace=ws).cpu().numpy()
         assert np.array_equal(y_auto, y)                         # AUTO takes this kernel when a workspace is supplied
     with pytest.raises(sgq.SgqError) as err:                     # no workspace: refused, never silently rerouted

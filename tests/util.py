@@ -33,19 +33,19 @@ TOL_FP32 = 1e-3   # fp32-dequant paths (SIMT, decode)
 TOL_BF16 = 2e-2   # bf16 / int8 tensor-core paths
 
 
-def block_fixed_point(x):
-    """What the decode kernels make of fp32 activations x[M, K], as float64: every 32 consecutive k
-    of a row share one scale gmax / Q, Q = 8355000 (24 bits: three int8 digits); values are rounded
-    to the nearest multiple of it.  In batches of three rows or more the lowest digit is dropped
-    (rounding to the nearest multiple of 256 scale units) except in groups that one value
-    dominates, 32 gmax^2 > 16 sum x^2.  All steps in fp32 as on the device: P = Q / gmax,
+def block_fixed_point(x, block=32):
+    """What the decode kernels make of fp32 activations x[M, K], as float64: every `block` consecutive k
+    of a row (32 for INT4 weights, 128 for INT8) share one scale gmax / Q, Q = 8355000 (24 bits: three
+    int8 digits); values are rounded to the nearest multiple of it.  In batches of three rows or more the
+    lowest digit is dropped (rounding to the nearest multiple of 256 scale units) except in blocks that
+    one value dominates, gmax > 4 rms(block).  All steps in fp32 as on the device: P = Q / gmax,
     q = rint(x * P), scale = gmax / Q."""
     x = np.ascontiguousarray(x, np.float32)
     M, K = x.shape
     Q = np.float32(8355000.0)
     out = np.zeros((M, K), np.float64)
-    for b0 in range(0, K, 32):
-        blk = x[:, b0:b0 + 32]
+    for b0 in range(0, K, block):
+        blk = x[:, b0:b0 + block]
         gmax = np.max(np.abs(blk), axis=1, keepdims=True).astype(np.float32)
         ok = gmax >= np.float32(1e-30)
         safe = np.where(ok, gmax, np.float32(1.0))
@@ -53,9 +53,9 @@ def block_fixed_point(x):
         sx = (safe / Q).astype(np.float32)
         q = np.rint((blk * P).astype(np.float32)).astype(np.float64)
         if M >= 3:
-            keep_low = (q ** 2).sum(axis=1, keepdims=True) < 2.0 * float(Q) ** 2
+            keep_low = (q ** 2).sum(axis=1, keepdims=True) < 2.0 * (block // 32) * float(Q) ** 2
             q = np.where(keep_low, q, np.floor((q + 128.0) / 256.0) * 256.0)     # balanced digits: the low one lies in [-128, 127]
-        out[:, b0:b0 + 32] = np.where(ok, q * sx.astype(np.float64), 0.0)
+        out[:, b0:b0 + block] = np.where(ok, q * sx.astype(np.float64), 0.0)
     return out
 
 
