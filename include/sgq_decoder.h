@@ -56,10 +56,15 @@ SGQ_API int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t
  * rotates q and k, appends k and v to the caches at position *pos0, and writes
  *   out[b, h*head_dim + d] = sum_{t <= pos0} softmax_t(q . k_t / sqrt(head_dim)) v_t[d].
  * Do not call sgqd_rope_kv_store for the same token.  If *pos0 is outside [0, max_seq) nothing is
- * stored and the query attends to the cache contents only.  head_dim must be 64 or 128. */
+ * stored and the query attends to the cache contents only.  head_dim must be 64 or 128.
+ * prepared_out (optional, prepared_bytes >= sgq_prepared_x_bytes(batch, n_heads * head_dim)): the rows
+ * out[b, 0 .. n_heads*head_dim) additionally in the decode kernel's prepared form, bit-identical to
+ * sgq_prepare_x on `out`, so that the linear behind the attention (sgq_linear_int4_prepared) needs no
+ * conversion launch. */
 SGQ_API int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
                              const float* cos_table, const float* sin_table, float* k_cache, float* v_cache,
-                             int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* stream);
+                             int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, void* prepared_out,
+                             size_t prepared_bytes, void* stream);
 
 /* Causal attention of t_new NEW tokens per sequence (the prompt pass), after sgqd_rope_kv_store has rotated
  * q in place and appended the rotated keys and the values: token i of sequence b (row b * t_new + i of qkv,

@@ -93,7 +93,7 @@ def _load() -> C.CDLL:
     lib.sgq_linear_int4_prepared.argtypes = [p, sz, i64, i64, i64, p, p, p, p, i64, p]
     lib.sgqd_add_rmsnorm.argtypes = [p, p, p, C.c_float, i64, i64, p, p, sz, p]
     lib.sgqd_rope_kv_store.argtypes = [p, i64, i64, i64, i64, p, p, p, p, p, i64, p]
-    lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, p, p, i64, p, p, i64, p]
+    lib.sgqd_attn_decode.argtypes = [p, i64, i64, i64, i64, p, p, p, p, i64, p, p, i64, p, C.c_size_t, p]
     lib.sgqd_silu_mul.argtypes = [p, i64, i64, p, p, sz, p]
     lib.sgqd_attn_prefill.argtypes = [p, i64, i64, i64, i64, i64, p, p, i64, p, p, i64, p]
     lib.sgqd_embedding.argtypes = [p, i64, i64, p, i64, p, p]

@@ -211,13 +211,15 @@ template <int HD>
 __global__ void __launch_bounds__(kAttnWarps * 32, kAttnCtasPerSm)
 attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_heads, const float* __restrict__ cos_t,
                    const float* __restrict__ sin_t, float* __restrict__ kc, float* __restrict__ vc, int64_t max_seq,
-                   const int32_t* __restrict__ pos0, float* __restrict__ out, int64_t out_stride) {
+                   const int32_t* __restrict__ pos0, float* __restrict__ out, int64_t out_stride, int batch, int pmode, int nmain,
+                   int nlow, uint8_t* __restrict__ planes) {
     constexpr int VEC = HD / 32;
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
     __shared__ float sm_acc[kAttnWarps][HD];
     __shared__ float sm_part[HD + 2];                      // this CTA's (max, sum, weighted value), read by rank 0
+    __shared__ __align__(16) float sm_out[HD];             // rank 0: the finished head, for the prepared form
     const int bh = blockIdx.x, split = blockIdx.y, S = gridDim.y;
     const int b = bh / n_heads, h = bh - b * n_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -331,19 +333,36 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
         if (threadIdx.x == 0) { sm_part[0] = M; sm_part[1] = L; }
     }
     cluster.sync();                                        // every CTA's partial result is in its shared memory
-    if (cluster.block_rank() == 0 && threadIdx.x < HD) {
-        float MM = -CUDART_INF_F;
-        for (int r = 0; r < S; ++r) MM = fmaxf(MM, cluster.map_shared_rank(sm_part, r)[0]);
-        float LL = 0.f, AA = 0.f;
-        for (int r = 0; r < S; ++r) {
-            const float* rp = cluster.map_shared_rank(sm_part, r);
-            const float ms = rp[0];
-            const float wgt = (ms == -CUDART_INF_F) ? 0.f : expf(ms - MM);
-            LL = fmaf(rp[1], wgt, LL);
-            AA = fmaf(rp[2 + threadIdx.x], wgt, AA);
+    if (cluster.block_rank() == 0) {
+        if (threadIdx.x < HD) {
+            float MM = -CUDART_INF_F;
+            for (int r = 0; r < S; ++r) MM = fmaxf(MM, cluster.map_shared_rank(sm_part, r)[0]);
+            float LL = 0.f, AA = 0.f;
+            for (int r = 0; r < S; ++r) {
+                const float* rp = cluster.map_shared_rank(sm_part, r);
+                const float ms = rp[0];
+                const float wgt = (ms == -CUDART_INF_F) ? 0.f : expf(ms - MM);
+                LL = fmaf(rp[1], wgt, LL);
+                AA = fmaf(rp[2 + threadIdx.x], wgt, AA);
+            }
+            // LL > 0 whenever there is at least one key; an out-of-range position with an empty cache yields 0
+            const float o = LL > 0.f ? AA / LL : 0.f;
+            out[static_cast<int64_t>(b) * out_stride + h * HD + threadIdx.x] = o;
+            sm_out[threadIdx.x] = o;
         }
-        // LL > 0 whenever there is at least one key; an out-of-range position with an empty cache yields 0
-        out[static_cast<int64_t>(b) * out_stride + h * HD + threadIdx.x] = LL > 0.f ? AA / LL : 0.f;
+        if (planes != nullptr) {
+            // the same values as prepared activations of the [batch, n_heads * HD] matrix (gemv_prepare.cuh): a head is
+            // HD / 32 whole groups of row b, so the linear behind the attention needs no conversion launch
+            __syncthreads();
+            if (warp == 0) {
+                const bool in = lane < HD / 8;
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = in ? sm_out[lane * 8 + j] : 0.f;
+                const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(n_heads) * (HD / 32), nmain, nlow);
+                convert_groups<kOrderNibble>(v, b, batch, static_cast<size_t>(h) * (HD / 32), pmode, nmain, nlow, 0.0625f, pp, in);
+            }
+        }
     }
     cluster.sync();                                        // keep shared memory alive until rank 0 has read it
 }
@@ -615,7 +634,8 @@ int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
 
 template <int HD>
 int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads, const float* cos_t, const float* sin_t, float* kc,
-                float* vc, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, cudaStream_t s) {
+                float* vc, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, const PreparedLayout& L,
+                uint8_t* planes, cudaStream_t s) {
     const int S = attn_splits(batch, n_heads, max_seq);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(batch * n_heads), static_cast<unsigned>(S), 1);
@@ -632,7 +652,7 @@ int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads
     cfg.attrs = attr;
     cfg.numAttrs = stream_overlap_enabled() ? 2 : 1;
     SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0, out,
-                                    out_stride));
+                                    out_stride, static_cast<int>(batch), L.mode, L.nmain, L.nlow, planes));
     return SGQ_OK;
 }
 
@@ -711,7 +731,7 @@ int sgqd_rope_kv_store(float* qkv, int64_t batch, int64_t t_new, int64_t n_heads
 
 int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim, const float* cos_table,
                      const float* sin_table, float* k_cache, float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
-                     int64_t out_stride, void* stream) {
+                     int64_t out_stride, void* prepared_out, size_t prepared_bytes, void* stream) {
     if (batch < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
     if (head_dim != 64 && head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
     if (qkv_stride < 3 * n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride too small");
@@ -719,14 +739,18 @@ int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_he
     if (!qkv || !cos_table || !sin_table || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
     if (!aligned(qkv, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || (qkv_stride & 3))
         return bad(SGQ_ERR_ALIGNMENT, "qkv rows and caches must be 16-byte aligned");
-    int rc = check_device();
+    PreparedLayout L = {};
+    int rc = check_prepared(prepared_out, prepared_bytes, batch, n_heads * head_dim, &L);
+    if (rc != SGQ_OK) return rc;
+    rc = check_device();
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint8_t* pl = static_cast<uint8_t*>(prepared_out);
     if (head_dim == 128)
         return launch_attn<128>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0,
-                                out, out_stride, s);
+                                out, out_stride, L, pl, s);
     return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0, out,
-                           out_stride, s);
+                           out_stride, L, pl, s);
 }
 
 int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,

@@ -299,10 +299,15 @@ class NanoLlamaInt4:
             self._add_rmsnorm(h, delta, L["attn_norm"], n, p_dim)
             self._linear(L["qkv"], n, b["qkv"], path, p_dim)
             kc, vc = self.k_cache[li], self.v_cache[li]
+            p_attn = None
             if t_new == 1:       # rotary embedding, cache append and attention of the new token in one kernel
+                # unsharded: the kernel also emits the prepared form of its output for the output projection
+                # (the planes of the normed hidden state have been consumed by the q/k/v projection by then)
+                p_attn = p_dim if self.world == 1 else None
                 check(lib.sgqd_attn_decode(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(self.cos),
                                            _ptr(self.sin), _ptr(kc), _ptr(vc), c.max_seq, _ptr(self.pos), _ptr(b["attn"]),
-                                           self.dim_local, _stream()), "sgqd_attn_decode")
+                                           self.dim_local, _ptr(p_attn), p_attn.numel() if p_attn is not None else 0, _stream()),
+                      "sgqd_attn_decode")
                 self._count()
             else:
                 check(lib.sgqd_rope_kv_store(_ptr(b["qkv"]), B, t_new, self.h_local, c.head_dim, _ptr(self.cos), _ptr(self.sin),
@@ -310,7 +315,11 @@ class NanoLlamaInt4:
                 self._count()
                 self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"])
             attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"), "attn")
-            o = self._linear_gathered(L["wo"], attn, b["o"], path, b.get("g_o"), b.get("o_full"), "o")
+            if p_attn is not None:
+                self._linear(L["wo"], attn, b["o"], path, p_attn)
+                o = b["o"]
+            else:
+                o = self._linear_gathered(L["wo"], attn, b["o"], path, b.get("g_o"), b.get("o_full"), "o")
             self._add_rmsnorm(h, o, L["ffn_norm"], n, p_dim)
             self._linear(L["gu"], n, b["gu"], path, p_dim)
             check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _ptr(p_hid),

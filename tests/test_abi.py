@@ -49,9 +49,9 @@ def test_decoder_argument_validation_needs_no_device(sgq):
     assert L.sgq_linear_int4_prepared(one, 64, 8, 2048, 64, one, one, None, one, 64, None) == 5
     assert L.sgq_linear_int4_prepared(one, 1 << 20, 8, 2050, 64, one, one, None, one, 64, None) == 4
     assert L.sgqd_rope_kv_store(one, 1, 1, 2, 12, one, one, one, one, one, 8, None) == 2   # head_dim % 8
-    assert L.sgqd_attn_decode(one, 768, 1, 2, 96, one, one, one, one, 8, one, one, 256, None) == 4    # head_dim 96
-    assert L.sgqd_attn_decode(one, 100, 1, 2, 128, one, one, one, one, 8, one, one, 256, None) == 2   # stride too small
-    assert L.sgqd_attn_decode(None, 768, 1, 2, 128, one, one, one, one, 8, one, one, 256, None) == 1
+    assert L.sgqd_attn_decode(one, 768, 1, 2, 96, one, one, one, one, 8, one, one, 256, None, 0, None) == 4    # head_dim 96
+    assert L.sgqd_attn_decode(one, 100, 1, 2, 128, one, one, one, one, 8, one, one, 256, None, 0, None) == 2   # stride too small
+    assert L.sgqd_attn_decode(None, 768, 1, 2, 128, one, one, one, one, 8, one, one, 256, None, 0, None) == 1
     assert L.sgqd_silu_mul(None, 2, 8, None, None, 0, None) == 1
 
 

@@ -156,9 +156,13 @@ def test_attn_decode(sgq, B, H, hd, length, max_seq):
     pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
     out = torch.empty(B, dim, device="cuda")
     qt, kt, vt, ct, st = dev(qkv), dev(kc), dev(vc), dev(cos), dev(sin)
+    nb = sgq.prepared_x_bytes(B, dim)                         # 0 where (B, dim) has no prepared form
+    planes = torch.zeros(max(nb, 1), dtype=torch.uint8, device="cuda")
     for _ in range(2):                                         # a second call over the already appended row changes nothing
         sgq.check(sgq.lib.sgqd_attn_decode(ptr(qt), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out),
-                                           dim, stream()))
+                                           dim, ptr(planes) if nb else None, nb, stream()))
+    if nb:       # the prepared form the kernel emits is the one sgq_prepare_x makes of its fp32 output
+        assert torch.equal(planes[:nb], sgq.prepare_x(out, torch.zeros(nb, dtype=torch.uint8, device="cuda"))[:nb])
     q = no.rope(qkv[:, :dim].reshape(B, H, 1, hd), cos, sin, [pos0])
     k_new = no.rope(qkv[:, dim:2 * dim].reshape(B, H, 1, hd), cos, sin, [pos0])
     v_new = qkv[:, 2 * dim:].reshape(B, H, 1, hd)
@@ -185,7 +189,7 @@ def test_attn_decode_position_out_of_range_stores_nothing(sgq):
     out = torch.empty(B, H * hd, device="cuda")
     pos = torch.tensor([max_seq], dtype=torch.int32, device="cuda")
     sgq.check(sgq.lib.sgqd_attn_decode(ptr(qkv), 3 * H * hd, B, H, hd, ptr(cos), ptr(sin), ptr(kc), ptr(vc), max_seq, ptr(pos), ptr(out),
-                                       H * hd, stream()))
+                                       H * hd, None, 0, stream()))
     torch.cuda.synchronize()
     assert torch.equal(kc, k0) and torch.equal(vc, v0) and torch.isfinite(out).all()
 
