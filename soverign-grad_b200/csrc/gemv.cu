@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const floa
     }
 }
 
-enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2 };
+enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2, kFlagSplitStages = 4 };
 
 // NM / NL: main and low sets of 8 digit columns (gemv_prepare.cuh; NL > 0: batches of three rows or
 // more); NWARPS: consumer warps (16, or 8 in the compact two-CTAs-per-SM form); HALF: one row, only
@@ -193,6 +193,10 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t ntiles = (N + kRows - 1) / kRows;
     const int ring_slots = nstages / kGroups;          // stage slots per warp group (nstages >= kGroups)
+    // Split form (no CTA has more than one tile, so one warp group would idle): the stages of the tile alternate
+    // between the groups, each group leaves its partial sums in a slot of its own and the reducer adds both.
+    const bool split = (flags & kFlagSplitStages) != 0;
+    constexpr int kSPG = kSlots / kGroups;             // partial-sum slots per group
 
     pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
     if (threadIdx.x == NWARPS * 32) {   // the producer thread: start fetching both descriptors now
@@ -266,8 +270,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     copy_planes(ph);
                 }
                 for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++tcount) {
-                    const int q = tcount % kGroups;
                     for (int c0 = 0; c0 < sp; c0 += kStepsPerStage) {
+                        const int q = split ? (c0 / kStepsPerStage) % kGroups : static_cast<int>(tcount % kGroups);
                         uint32_t seq = 0;
 #pragma unroll
                         for (int qq = 0; qq < kGroups; ++qq)
@@ -318,9 +322,11 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         bool ok = true;
         for (int ph = 0; ph < nphases && ok; ++ph) {
             for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tcount) {
-                const int slot = tcount % kSlots;
-                const uint32_t pph = (tcount / kSlots) & 1u;
-                if (!mbar_wait(&pfull[slot], pph)) {
+                // whole tiles: tile t is group t % kGroups' and uses slot t % kSlots; split: both groups, slots
+                // (t % kSPG) * kGroups + group
+                const int slot = split ? static_cast<int>(tcount % kSPG) * kGroups : static_cast<int>(tcount % kSlots);
+                const uint32_t pph = split ? (tcount / kSPG) & 1u : (tcount / kSlots) & 1u;
+                if (!mbar_wait(&pfull[slot], pph) || (split && !mbar_wait(&pfull[slot + 1], pph))) {
                     report(kDevErrFullWait, 0x800000u | tcount);
                     ok = false;
                     break;
@@ -333,7 +339,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int s = 0; s < NM; ++s) {
                     float4 sum = *reinterpret_cast<const float4*>(pbuf + (s * 32 + lane) * 4);
 #pragma unroll
-                    for (int w = 1; w < WPT; ++w) {
+                    for (int w = 1; w < (split ? 2 * WPT : WPT); ++w) {       // split: the second group's slot lies right behind
                         const float4 v = *reinterpret_cast<const float4*>(pbuf + w * kPStride + (s * 32 + lane) * 4);
                         sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
                     }
@@ -369,7 +375,10 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&pempty[slot]);
+                if (lane == 0) {
+                    mbar_arrive(&pempty[slot]);
+                    if (split) mbar_arrive(&pempty[slot + 1]);
+                }
             }
         }
         if (peers.n > 0 && peers.sig[0] != nullptr) {
@@ -451,14 +460,15 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             alive = false;
         }
         for (int64_t ti = 0; ti < my_tiles; ++ti, ++tcount) {
-            if (static_cast<int>(tcount % kGroups) != my_group) continue;       // another group's tile
+            if (!split && static_cast<int>(tcount % kGroups) != my_group) continue;       // another group's tile
             float total[NM + NL][4];
 #pragma unroll
             for (int s = 0; s < NM + NL; ++s)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) total[s][i] = 0.0f;
 
-            for (int c0 = 0; c0 < sp; c0 += kStepsPerStage, ++seq) {
+            for (int c0 = 0; c0 < sp; c0 += kStepsPerStage) {
+                if (split && (c0 / kStepsPerStage) % kGroups != my_group) continue;       // the other group's stage
                 const int st = my_group * ring_slots + static_cast<int>(seq % ring_slots);
                 const uint32_t par = (seq / ring_slots) & 1u;
                 if (alive && !mbar_wait(&full[st], par)) {
@@ -561,12 +571,13 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int s = 0; s < NM + NL; ++s) fold ^= __float_as_uint(total[s][0]) ^ __float_as_uint(total[s][2]);
                 const uint32_t landed = loads_landed(fold);
                 if (lane == 0) mbar_arrive_after(&empty[st], landed);
+                ++seq;
             }
 
             // ---- hand the tile's partial sums to the reducer warp ----
             {
-                const int slot = tcount % kSlots;
-                const uint32_t pph = (tcount / kSlots) & 1u;
+                const int slot = split ? static_cast<int>(tcount % kSPG) * kGroups + my_group : static_cast<int>(tcount % kSlots);
+                const uint32_t pph = split ? (tcount / kSPG) & 1u : (tcount / kSlots) & 1u;
                 if (alive && !mbar_wait(&pempty[slot], pph ^ 1u)) {
                     report(kDevErrEmptyWait, 0x800000u | tcount);
                     alive = false;
@@ -674,7 +685,10 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M), static_cast<unsigned>(ceil_div(a.K / 8, kPrepThreads))), dim3(kPrepThreads), 0, a.stream, overlap,
                                    a.x, a.K, p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace)));
     }
-    const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
+    // no CTA with more than one tile, tiles of two stages or more, one phase: the stages alternate between the warp groups
+    const int64_t ntiles = ceil_div(a.N, kRows);
+    const bool split = ntiles <= grid && p.nphases == 1 && a.K / kStepK > kStepsPerStage;
+    const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0) | (split ? kFlagSplitStages : 0);
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
                                map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages, p.nphases, flags,
                                a.peers));
