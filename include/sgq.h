@@ -74,12 +74,13 @@ enum {
                              within ~1e-4 of the reference's fp32 forward (bound 1e-3); a row with a
                              NaN or Inf activation yields a NaN output row.  [K,N] (the reference module's layout):
                              fp32 throughout */
-    SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16 on bf16 activations and bf16 weights (INT4 g=32 or INT8, K % 64 == 0).
+    SGQ_PATH_TC_BF16 = 3, /* prefill: tcgen05 kind::f16 on bf16 activations and bf16 weights (INT4 with any group that is a
+                             multiple of 8, or INT8; K % 64 == 0).
                              With the scratch sgq_linear_workspace_bytes() asks for, a launch in front expands the weight
                              to bf16 [N,K] (INT4: code * scale in fp32, rounded once; INT8 stored [N,K]: the exact codes,
                              scale applied in fp32 afterwards) and both operands reach the tensor cores by TMA; weights
                              stored [K,N] (N % 32 == 0) are transposed by that launch.  With scratch for the activations
-                             only (M * K * 2 bytes, rounded up to 256), weights stored [N,K] are dequantized tile by tile in
+                             only (M * K * 2 bytes, rounded up to 256), INT4 g=32 and INT8 weights stored [N,K] are dequantized tile by tile in
                              shared memory instead (slower).  Bound 2e-2 of the largest output. */
     SGQ_PATH_TC_I8 = 4    /* prefill, INT8 weights only: activations quantized per row, tcgen05 kind::i8 */
 };

@@ -182,7 +182,7 @@ int run_linear(LinearArgs a, int path) {
              a.workspace_bytes >= kn_decode_workspace_bytes(a.bits, a.M, a.K, a.N)))
             path = SGQ_PATH_GEMV;
         else if (a.M >= 64 && tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
-                 a.workspace && a.workspace_bytes >= tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout) &&
+                 a.workspace && a.workspace_bytes >= tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout, a.group) &&
                  aligned(a.wq, 16) && aligned(a.scales, 16) && aligned(a.x, 16))
             path = SGQ_PATH_TC_BF16;
         else

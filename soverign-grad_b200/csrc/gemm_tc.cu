@@ -531,7 +531,7 @@ __global__ void __launch_bounds__(256) convert_x_bf16_kernel(const float* __rest
 constexpr int kTrK = 64, kTrN = 128, kTrStride = kTrK + 8;      // bf16 elements per shared-memory row (16-byte multiple)
 template <int BITS>
 __global__ void __launch_bounds__(256) dequant_kn_to_nk_bf16_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales,
-                                                                   int per_row, int64_t K, int64_t N,
+                                                                   int per_row, int64_t group, int64_t K, int64_t N,
                                                                    __nv_bfloat16* __restrict__ out) {
     __shared__ __align__(16) __nv_bfloat16 tile[kTrN * kTrStride];
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kTrN, k0 = static_cast<int64_t>(blockIdx.y) * kTrK;
@@ -541,10 +541,10 @@ __global__ void __launch_bounds__(256) dequant_kn_to_nk_bf16_kernel(const uint8_
         const int64_t e = k * N + n;                                  // flat element index of the first of 32
         if (BITS == 4) {
             const uint4 w = *reinterpret_cast<const uint4*>(wq + e / 2);
-            const float sc = scales[e / 32];
             const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
+                const float sc = scales[(e + 8 * i) / group];           // group % 8 == 0: a word never straddles groups
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int code = static_cast<int>(words[i] << (28 - 4 * j)) >> 28;      // nibble j, sign-extended
@@ -585,8 +585,8 @@ __global__ void __launch_bounds__(256) dequant_kn_to_nk_bf16_kernel(const uint8_
 // behind it are ready after one kernel.
 template <int BITS>
 __global__ void __launch_bounds__(256) expand_nk_bf16_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales,
-                                                            int64_t chunks, uint4* __restrict__ out, const float* __restrict__ x,
-                                                            int64_t xchunks, uint4* __restrict__ xout) {
+                                                            int64_t group, int64_t chunks, uint4* __restrict__ out,
+                                                            const float* __restrict__ x, int64_t xchunks, uint4* __restrict__ xout) {
     auto pk = [](float lo, float hi) {
         return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
                (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(256) expand_nk_bf16_kernel(const uint8_t* __re
         float v[8];
         if (BITS == 4) {
             const uint32_t w = reinterpret_cast<const uint32_t*>(wq)[i];
-            const float sc = scales[i >> 2];
+            const float sc = scales[(8 * i) / group];       // group % 8 == 0: a word never straddles groups
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(static_cast<float>(static_cast<int>(w << (28 - 4 * j)) >> 28), sc);
         } else {
@@ -644,8 +644,10 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
 }  // namespace
 
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group) {
-    if (!(((bits == 4 && group == 32) || bits == 8) && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 && M < (1LL << 31) &&
-          N < (1LL << 31) && K < (1LL << 31)))
+    // INT4: any group that is a multiple of 8 (the weight is expanded word by word); 32 also has the form that
+    // dequantizes in shared memory
+    if (!(((bits == 4 && group >= 8 && (group % 8) == 0) || bits == 8) && M >= 1 && N >= 1 && K >= 64 && (K % 64) == 0 &&
+          M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31)))
         return false;
     // [K,N]: quantization groups run along N and must not straddle rows of the stored tensor
     return layout == SGQ_LAYOUT_NK || (layout == SGQ_LAYOUT_KN && (N % 32) == 0);
@@ -660,21 +662,21 @@ size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int la
 }
 
 // the least the path runs with: weights stored [N,K] can be dequantized tile by tile in shared memory instead
-size_t tc_bf16_min_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
-    if (layout == SGQ_LAYOUT_KN) return tc_bf16_workspace_bytes(bits, M, K, N, layout);
+size_t tc_bf16_min_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group) {
+    if (layout == SGQ_LAYOUT_KN || (bits == 4 && group != 32)) return tc_bf16_workspace_bytes(bits, M, K, N, layout);
     return round_up(static_cast<size_t>(M) * static_cast<size_t>(K) * 2, 256);
 }
 
 int launch_linear_tc_bf16(const LinearArgs& a) {
     if (!tc_bf16_supported(a.bits, a.M, a.K, a.N, a.layout, a.group)) {
-        set_error("bf16 tensor-core path needs INT4 g=32 or INT8 weights, K%%64==0, and N%%32==0 when stored [K,N]");
+        set_error("bf16 tensor-core path needs INT4 (group a multiple of 8) or INT8 weights, K%%64==0, and N%%32==0 when stored [K,N]");
         return SGQ_ERR_UNSUPPORTED;
     }
     if (!aligned(a.x, 16) || !aligned(a.wq, 16) || !aligned(a.scales, 8)) {
         set_error("bf16 tensor-core path needs 16-byte aligned x and packed weights, 8-byte aligned scales");
         return SGQ_ERR_ALIGNMENT;
     }
-    const size_t need = tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
+    const size_t need = tc_bf16_min_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout, a.group);
     const bool expand = a.workspace && a.workspace_bytes >= tc_bf16_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
     if (!a.workspace || a.workspace_bytes < need) {
         set_error("bf16 tensor-core path needs %zu workspace bytes, got %zu", need, a.workspace ? a.workspace_bytes : 0);
@@ -708,21 +710,21 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
         if (a.layout == SGQ_LAYOUT_KN) {
             const dim3 tgrid(static_cast<unsigned>(ceil_div(a.N, kTrN)), static_cast<unsigned>(a.K / kTrK));
             if (a.bits == 4)
-                dequant_kn_to_nk_bf16_kernel<4><<<tgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 0, a.K, a.N, wt);
+                dequant_kn_to_nk_bf16_kernel<4><<<tgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 0, a.group, a.K, a.N, wt);
             else
                 dequant_kn_to_nk_bf16_kernel<8><<<tgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales,
-                                                                            a.scheme == SGQ_PER_ROW ? 1 : 0, a.K, a.N, wt);
+                                                                            a.scheme == SGQ_PER_ROW ? 1 : 0, 32, a.K, a.N, wt);
             SGQ_LAUNCH_CHECK("dequant_kn_to_nk_bf16_kernel");
         } else {
             const int64_t wchunks = a.N * a.K / 8;
             const int64_t wblocks = ceil_div(wchunks > chunks ? wchunks : chunks, 256);
             const int wgrid = static_cast<int>(wblocks < cap ? wblocks : cap);
             if (a.bits == 4)
-                expand_nk_bf16_kernel<4><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, wchunks,
+                expand_nk_bf16_kernel<4><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, a.group, wchunks,
                                                                      reinterpret_cast<uint4*>(wt), a.x, chunks,
                                                                      static_cast<uint4*>(a.workspace));
             else
-                expand_nk_bf16_kernel<8><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, wchunks,
+                expand_nk_bf16_kernel<8><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 32, wchunks,
                                                                      reinterpret_cast<uint4*>(wt), a.x, chunks,
                                                                      static_cast<uint4*>(a.workspace));
             SGQ_LAUNCH_CHECK("expand_nk_bf16_kernel");

@@ -210,7 +210,7 @@ size_t kn_decode_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N);
 int launch_linear_kn_decode(const LinearArgs& a);
 bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);      // preferred (weights expanded)
-size_t tc_bf16_min_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout);  // least the path runs with
+size_t tc_bf16_min_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout, int64_t group);  // least the path runs with
 int launch_linear_tc_bf16(const LinearArgs& a);
 bool tc_i8_supported(int64_t M, int64_t K, int64_t N);
 size_t tc_i8_workspace_bytes(int64_t M, int64_t K, int64_t N);

@@ -62,8 +62,7 @@ def test_golden_forward_simt(sgq, golden, name, M, K, N):
                 m = cls.from_float(wd, bd, **kw)
                 assert m.q_weight.scales.cpu().numpy().tobytes() == g[f"{name}/L{layout}/{tag}/scales"].tobytes()
                 y = m(xd).cpu().numpy()                       # AUTO path
-                group32 = tag != "module_int4_g16"
-                if M >= 64 and K % 64 == 0 and N % 32 == 0 and group32:
+                if M >= 64 and K % 64 == 0 and N % 32 == 0:
                     # prefill-sized batches go to the tensor cores in this layout too (bf16 operands)
                     assert norm_err(y, g[f"{name}/L{layout}/{tag}/y"]) <= TOL_BF16
                 else:
@@ -339,6 +338,28 @@ def test_tc_bf16_kn_layout_against_port(sgq, port, M, K, N):
         model8 = bf16_round(x).astype(np.float64) @ bf16_round(wd8).astype(np.float64) + b[None, :]
         assert rel_err(y8, model8) <= 2e-5, (scheme, rel_err(y8, model8))
         assert norm_err(y8, want8) <= TOL_BF16, (scheme, norm_err(y8, want8))
+
+
+@pytest.mark.parametrize("group", [8, 16, 64, 128, 96])
+def test_tc_bf16_other_group_sizes(sgq, port, group):
+    """INT4 groups other than 32 (any multiple of 8, also ones that straddle rows) on the tensor cores, both layouts:
+    the weight is expanded word by word, so the group size only selects the scale."""
+    M, K, N = 128, 256, 160
+    rng = np.random.default_rng(group)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    for layout, shape in ((cases.LAYOUT_NK, (N, K)), (cases.LAYOUT_KN, (K, N))):
+        w = cases.weight_with_outliers(group + layout, shape)
+        packed, scales = port.quantize_int4(w, group)
+        want = port.qlinear_int4(x, packed, scales, K, N, layout, group, b)
+        q = sgq.quantize_int4(dev(w), group)
+        y = sgq.quantized_matmul(dev(x), q, dev(b), layout=layout, path=sgq.PATH_TC_BF16).cpu().numpy()
+        check_status(sgq)
+        wd = port.dequantize_int4(packed, scales, shape, group).astype(np.float64)
+        wb = bf16_round(wd).astype(np.float64)
+        model = bf16_round(x).astype(np.float64) @ (wb.T if layout == cases.LAYOUT_NK else wb) + b[None, :]
+        assert rel_err(y, model) <= 2e-5, (group, layout, rel_err(y, model))
+        assert norm_err(y, want) <= TOL_BF16, (group, layout, norm_err(y, want))
 
 
 def test_tc_bf16_kn_layout_rejects_ragged_groups(sgq):
