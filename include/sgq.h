@@ -222,8 +222,11 @@ SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int6
                                       void* const* signals, int rank, void* local_state, void* stream);
 
 /* The same forward with the wait taken out of the producer.  The kernel stores its slices into every
- * rank's output and, at its end, only SIGNALS (its epoch, one store per rank); it does not wait for
- * the other ranks.  Instead every kernel launched through this entry point first waits, in its
+ * rank's output and only SIGNALS: every thread block, when its own slices are out, adds one to this
+ * rank's slot on every rank (a system-scope release reduction: no separate fence, no election of a
+ * last block), so the slots count arrivals and local_state counts what this rank has sent; it does
+ * not wait for the other ranks.  (Every rank must therefore run the same sequence of launches on the
+ * same signals, as for the barrier.)  Instead every kernel launched through this entry point first waits, in its
  * prologue, until all ranks have signalled the exchanges this GPU has already finished — one NVLink
  * round trip that overlaps the kernel's own start-up and weight prefetch, and no extra launch.
  * Consequences for the caller:

@@ -381,7 +381,11 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
             }
         }
-        if (peers.n > 0 && peers.sig[0] != nullptr) {
+        if (peers.n > 0 && peers.sig[0] != nullptr && peers.deferred) {
+            // Deferred exchange: this CTA's slices are out; it counts itself with every rank and is done.  The next
+            // kernel on these signals waits, in its prologue, until every rank's count has reached its own.
+            peer_arrive(peers.sig, peers.rank, peers.n, peers.state, lane);
+        } else if (peers.n > 0 && peers.sig[0] != nullptr) {
             // Barrier fused into the tail: this CTA's slices are out; the last CTA of the launch to get
             // here tells every rank and waits for every rank, so the kernel ends when all outputs are whole.
             __syncwarp();
@@ -393,9 +397,7 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (ticket == gridDim.x - 1) {
                 if (lane == 0) *counter = 0;          // re-armed for the next launch, which counts only at its own end
                 int late = 0;
-                if (peers.deferred)                   // the next kernel on these signals waits, in its prologue
-                    peer_signal(peers.sig, peers.rank, peers.n, peers.state, lane);
-                else if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late, peers.poll_budget) && lane == 0)
+                if (!peer_signal_and_wait(peers.sig, peers.rank, peers.n, peers.state, lane, &late, peers.poll_budget) && lane == 0)
                     report(kDevErrPeerWait, 0x10000u);
             }
         }

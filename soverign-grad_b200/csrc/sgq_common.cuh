@@ -106,18 +106,17 @@ struct PeerOut {
 unsigned int peer_wait_budget();
 
 #ifdef __CUDACC__
-// One warp: publish this GPU's next epoch to every rank (everything this GPU stored before, peer stores
-// included, is visible to a rank that then sees the epoch).  No waiting.
-__device__ __forceinline__ void peer_signal(unsigned long long* const* sig, int rank, int world, unsigned long long* local_epoch,
+// The signal slots count: slot [d][r] is the number of signals rank r has sent to rank d, and every rank keeps the
+// number it has sent itself (`local_count`; the same on every rank at the same point of the same sequence).
+// One warp of ONE CTA: count this CTA's arrival with every rank.  The release makes everything the warp stored
+// before (peer stores included: the lanes met at the __syncwarp) visible to a rank that then sees the count, so a
+// CTA needs neither a fence of its own nor a last-CTA election, and a rank sees a launch complete as soon as its
+// last CTA's count lands.  No waiting.
+__device__ __forceinline__ void peer_arrive(unsigned long long* const* sig, int rank, int world, unsigned long long* local_count,
                                             int lane) {
-    unsigned long long epoch = 0;
-    if (lane == 0) {
-        epoch = *local_epoch + 1;
-        *local_epoch = epoch;
-    }
-    epoch = __shfl_sync(0xffffffffu, epoch, 0);
-    __threadfence_system();
-    if (lane < world) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(sig[lane] + rank), "l"(epoch) : "memory");
+    __syncwarp();
+    if (lane < world) asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(sig[lane] + rank), "l"(1ull) : "memory");
+    if (lane == 0) atomicAdd(local_count, 1ull);
 }
 
 // One warp: wait (bounded) until every rank has published at least the epoch this GPU itself has reached,
