@@ -148,12 +148,12 @@ __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const floa
     }
 }
 
-enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2, kFlagSplitStages = 4 };
+enum : int { kFlagEarlyWeights = 1, kFlagPrepared = 2 };
 
 // NM / NL: main and low sets of 8 digit columns (gemv_prepare.cuh; NL > 0: batches of three rows or
 // more); NWARPS: consumer warps (16, or 8 in the compact two-CTAs-per-SM form); HALF: one row, only
 // even columns carry data and the odd accumulators are skipped.
-template <int NM, int NL, int NWARPS, bool HALF>
+template <int NM, int NL, int NWARPS, bool HALF, bool SPLIT>
 __global__ void __launch_bounds__((NWARPS + 2) * 32, NWARPS == 8 ? 2 : 1)
 gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                     const float* __restrict__ x, const uint8_t* __restrict__ planes, const float* __restrict__ bias,
@@ -195,7 +195,8 @@ gemv_int4_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int ring_slots = nstages / kGroups;          // stage slots per warp group (nstages >= kGroups)
     // Split form (no CTA has more than one tile, so one warp group would idle): the stages of the tile alternate
     // between the groups, each group leaves its partial sums in a slot of its own and the reducer adds both.
-    const bool split = (flags & kFlagSplitStages) != 0;
+    // (a template parameter: the checks below cost the whole-tile form 3 % when they are decided at run time)
+    constexpr bool split = SPLIT;
     constexpr int kSPG = kSlots / kGroups;             // partial-sum slots per group
 
     pdl_launch_dependents();            // the next kernel may begin its prologue; it waits for this grid before touching data
@@ -675,11 +676,14 @@ int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
     return 0;
 }
 
-template <int NM, int NL, int NWARPS, bool HALF>
+template <int NM, int NL, int NWARPS, bool HALF, bool SPLIT = false>
 int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w, const CUtensorMap& map_s, int grid,
                    bool planes_ready) {
+    // no CTA with more than one tile, tiles of two stages or more, one phase: the stages alternate between the warp groups
+    if (!SPLIT && NWARPS == 16 && ceil_div(a.N, kRows) <= grid && p.nphases == 1 && a.K / kStepK > kStepsPerStage)
+        return launch_variant<NM, NL, NWARPS, HALF, NWARPS == 16>(a, p, map_w, map_s, grid, planes_ready);
     static SmemOptIn optin;
-    auto kernel = gemv_int4_nk_kernel<NM, NL, NWARPS, HALF>;
+    auto kernel = gemv_int4_nk_kernel<NM, NL, NWARPS, HALF, SPLIT>;
     SGQ_CUDA_TRY(optin.ensure(kernel, NWARPS == 8 ? kCompactSmem : kSmemLimit));
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
     const bool overlap = stream_overlap_enabled();
@@ -687,10 +691,7 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M), static_cast<unsigned>(ceil_div(a.K / 8, kPrepThreads))), dim3(kPrepThreads), 0, a.stream, overlap,
                                    a.x, a.K, p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace)));
     }
-    // no CTA with more than one tile, tiles of two stages or more, one phase: the stages alternate between the warp groups
-    const int64_t ntiles = ceil_div(a.N, kRows);
-    const bool split = ntiles <= grid && p.nphases == 1 && a.K / kStepK > kStepsPerStage;
-    const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0) | (split ? kFlagSplitStages : 0);
+    const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
                                map_s, a.x, planes, a.bias, a.y, static_cast<int>(a.M), a.K, a.N, a.ldy, p.nstages, p.nphases, flags,
                                a.peers));
