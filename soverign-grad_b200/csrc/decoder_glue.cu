@@ -399,39 +399,32 @@ __global__ void __launch_bounds__(kNormThreads) silu_mul_prepare_kernel(const fl
     prepare_row_block<kNormThreads>(orow, blockIdx.x, gridDim.x, hidden, pmode, nmain, nlow, planes);
 }
 
-// The register-resident form of the same (hidden % 256 == 0, hidden <= 8192): one pass over memory.
-constexpr int kSiluThreads = 512;
+// The one-pass form of the same (hidden % 256 == 0): grid (rows, hidden / 1024), a thread owns eight consecutive
+// values, i.e. a quarter of a 32-k group, so nothing crosses a warp and a handful of rows still spreads over
+// many SMs (one CTA per row took 5.7 us for 8 rows of 5632 in a decode step).
+constexpr int kSiluThreads = 128;
 __global__ void __launch_bounds__(kSiluThreads) silu_mul_prepare_row_kernel(const float* __restrict__ gu, int64_t hidden,
                                                                            float* __restrict__ out, int pmode, int nmain, int nlow,
                                                                            uint8_t* __restrict__ planes) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int CH = 2;
     const int chunks = static_cast<int>(hidden / 8);
+    const int c = blockIdx.y * kSiluThreads + threadIdx.x;
+    if (c >= chunks) return;                                    // chunks % 32 == 0: whole warps
     const float* g = gu + blockIdx.x * 2 * hidden;
     const float* u = g + hidden;
     float* orow = out + blockIdx.x * hidden;
-    float v[CH][8];
+    const float4 ga = *(reinterpret_cast<const float4*>(g) + 2 * c), gb = *(reinterpret_cast<const float4*>(g) + 2 * c + 1);
+    const float4 ua = *(reinterpret_cast<const float4*>(u) + 2 * c), ub = *(reinterpret_cast<const float4*>(u) + 2 * c + 1);
+    const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+    const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+    float v[8];
 #pragma unroll
-    for (int r = 0; r < CH; ++r) {
-        const int c = threadIdx.x + r * kSiluThreads;
-        if (c < chunks) {
-            const float4 ga = *(reinterpret_cast<const float4*>(g) + 2 * c), gb = *(reinterpret_cast<const float4*>(g) + 2 * c + 1);
-            const float4 ua = *(reinterpret_cast<const float4*>(u) + 2 * c), ub = *(reinterpret_cast<const float4*>(u) + 2 * c + 1);
-            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-            const float uu[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[r][j] = gg[j] / (1.0f + expf(-gg[j])) * uu[j];
-            *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
-            *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[r][4], v[r][5], v[r][6], v[r][7]);
-        }
-    }
+    for (int j = 0; j < 8; ++j) v[j] = gg[j] / (1.0f + expf(-gg[j])) * uu[j];
+    *(reinterpret_cast<float4*>(orow) + 2 * c) = make_float4(v[0], v[1], v[2], v[3]);
+    *(reinterpret_cast<float4*>(orow) + 2 * c + 1) = make_float4(v[4], v[5], v[6], v[7]);
     const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(hidden / 32), nmain, nlow);
-#pragma unroll
-    for (int r = 0; r < CH; ++r) {
-        const int c = threadIdx.x + r * kSiluThreads;           // whole warps
-        if (c < chunks) convert_groups<kOrderNibble>(v[r], blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nlow, 0.0625f, pp);
-    }
+    convert_groups<kOrderNibble>(v, blockIdx.x, gridDim.x, static_cast<size_t>(c >> 5) * 8, pmode, nmain, nlow, 0.0625f, pp);
 }
 
 // Causal attention of a block of new tokens (the prompt pass): token i of a sequence, at position *pos0 + i,
@@ -812,8 +805,9 @@ int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out
     rc = check_device();
     if (rc != SGQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (prepared_out && (hidden % 256) == 0 && hidden <= 8192) {
-        SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_row_kernel, dim3(static_cast<unsigned>(rows)), dim3(kSiluThreads), 0, s,
+    if (prepared_out && (hidden % 256) == 0 && hidden / 8 <= 65535LL * kSiluThreads) {
+        SGQ_CUDA_TRY(launch_kernel(silu_mul_prepare_row_kernel,
+                                   dim3(static_cast<unsigned>(rows), static_cast<unsigned>(ceil_div(hidden / 8, kSiluThreads))), dim3(kSiluThreads), 0, s,
                                    stream_overlap_enabled(), gate_up, hidden, out, L.mode, L.nmain, L.nlow,
                                    static_cast<uint8_t*>(prepared_out)));
         return SGQ_OK;
