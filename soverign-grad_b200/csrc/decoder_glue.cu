@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ 
 
 constexpr int kAttnWarps = 8;
 constexpr int kKeysPerIter = 4;
-constexpr int kAttnCtasPerSm = 4;      // 256 threads x <= 64 registers
+constexpr int kAttnCtasPerSm = 2;      // 256 threads x <= 128 registers: two sets of key/value rows in flight per warp
 
 // Rotary pair (d, d + HD/2) when a warp holds one head with VEC consecutive elements per lane:
 // lane l < 16 holds x1 of the pairs whose x2 sits in lane l + 16.  src/ops.cpp:1737-1738.
@@ -251,8 +251,9 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
 
-    for (int64_t t = t0 + warp * kKeysPerIter; t < t1; t += kAttnWarps * kKeysPerIter) {
-        float kk[kKeysPerIter][VEC], vv[kKeysPerIter][VEC], s[kKeysPerIter];
+    // Two register sets of key / value rows: the loads of the next four keys are issued before the current four are
+    // used, so a warp waits for memory once, not once per iteration.
+    auto load_rows = [&](int64_t t, float (&kk)[kKeysPerIter][VEC], float (&vv)[kKeysPerIter][VEC]) {
 #pragma unroll
         for (int i = 0; i < kKeysPerIter; ++i) {
             const int64_t tt = (t + i < t1) ? t + i : t1 - 1;          // clamped: the tail reloads a valid row
@@ -268,6 +269,9 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
                 vv[i][0] = c.x; vv[i][1] = c.y;
             }
         }
+    };
+    auto use_rows = [&](int64_t t, const float (&kk)[kKeysPerIter][VEC], const float (&vv)[kKeysPerIter][VEC]) {
+        float s[kKeysPerIter];
         float mx = m;
 #pragma unroll
         for (int i = 0; i < kKeysPerIter; ++i) {
@@ -290,6 +294,21 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
             for (int j = 0; j < VEC; ++j) acc[j] = fmaf(p, vv[i][j], acc[j]);
         }
         m = mx;
+    };
+    {
+        constexpr int64_t kStride = kAttnWarps * kKeysPerIter;
+        float ka[kKeysPerIter][VEC], va[kKeysPerIter][VEC], kb2[kKeysPerIter][VEC], vb2[kKeysPerIter][VEC];
+        int64_t t = t0 + warp * kKeysPerIter;
+        if (t < t1) load_rows(t, ka, va);
+        for (; t < t1; t += 2 * kStride) {
+            const bool second = t + kStride < t1;
+            if (second) load_rows(t + kStride, kb2, vb2);
+            use_rows(t, ka, va);
+            if (second) {
+                if (t + 2 * kStride < t1) load_rows(t + 2 * kStride, ka, va);
+                use_rows(t + kStride, kb2, vb2);
+            }
+        }
     }
 
     // the new token: warp 0 of the last split rotates its key, appends key and value to the cache
