@@ -4,6 +4,7 @@
 // absmax from 1e-8f, scale = max/qmax and inv = qmax/max as two IEEE divisions, code =
 // clamp(round_half_away(x * inv)).  No fast-math: `/` is div.rn, products are __fmul_rn.
 #include "sgq_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace sgq {
 namespace {
@@ -111,6 +112,14 @@ __global__ void __launch_bounds__(kThreads) scale_from_absmax_kernel(float* __re
     for (; i < n; i += stride) scales[i] = scales[i] / qmax;
 }
 
+__global__ void __launch_bounds__(kThreads) scale_from_absmax_pdl_kernel(float* __restrict__ scales, int64_t n, float qmax) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (; i < n; i += stride) scales[i] = scales[i] / qmax;
+}
+
 // ------------------------------------------------------------------------------------------
 // INT8 per row: one CTA per row.  VEC path (cols % 4 == 0, 16-byte aligned rows): the row is
 // read once into registers when it fits (<= CACHE float4 per thread), else read twice (the
@@ -202,11 +211,19 @@ __global__ void __launch_bounds__(kThreads) quantize_int8_rows_scalar_kernel(con
 // Compulsory bytes per element: 4 read + 1 written; 8 read + 1 written when the tensor does
 // not stay in L2 between steps 2 and 3.
 // ------------------------------------------------------------------------------------------
-__global__ void set_f32_kernel(float* p, float v) { *p = v; }
+// The four kernels of this path are launched with programmatic stream serialization when overlap is on: each lets
+// the next one start its launch and waits for the one before it before it touches the cell or the tensor.
+__global__ void set_f32_kernel(float* p, float v) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *p = v;
+}
 
 __global__ void __launch_bounds__(kThreads) tensor_absmax_kernel(const float* __restrict__ x, int64_t n,
                                                                  float* __restrict__ cell) {
     __shared__ float red[kThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
     float m = 1e-8f;
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
@@ -233,6 +250,8 @@ __global__ void __launch_bounds__(kThreads) tensor_absmax_kernel(const float* __
 __global__ void __launch_bounds__(kThreads) quantize_int8_tensor_kernel(const float* __restrict__ x, int64_t n,
                                                                         const float* __restrict__ cell,
                                                                         int8_t* __restrict__ codes) {
+    pdl_launch_dependents();
+    pdl_wait();
     const float inv = 127.0f / *cell;
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
@@ -365,17 +384,15 @@ int launch_quantize_int8(const float* x, int64_t rows, int64_t cols, int scheme,
                          cudaStream_t s) {
     const int64_t n = rows * cols;
     if (scheme == SGQ_PER_TENSOR) {
-        set_f32_kernel<<<1, 1, 0, s>>>(scales, 1e-8f);
-        SGQ_LAUNCH_CHECK("set_f32_kernel");
+        const bool ov = stream_overlap_enabled();
+        SGQ_CUDA_TRY(launch_kernel(set_f32_kernel, dim3(1), dim3(1), 0, s, ov, scales, 1e-8f));
         if (n > 0) {
             const int grid = grid_for(n, kThreads * 16, 8);
-            tensor_absmax_kernel<<<grid, kThreads, 0, s>>>(x, n, scales);
-            SGQ_LAUNCH_CHECK("tensor_absmax_kernel");
-            quantize_int8_tensor_kernel<<<grid, kThreads, 0, s>>>(x, n, scales, codes);
-            SGQ_LAUNCH_CHECK("quantize_int8_tensor_kernel");
+            SGQ_CUDA_TRY(launch_kernel(tensor_absmax_kernel, dim3(grid), dim3(kThreads), 0, s, ov, x, n, scales));
+            SGQ_CUDA_TRY(launch_kernel(quantize_int8_tensor_kernel, dim3(grid), dim3(kThreads), 0, s, ov, x, n,
+                                       static_cast<const float*>(scales), codes));
         }
-        scale_from_absmax_kernel<<<1, kThreads, 0, s>>>(scales, 1, 127.0f);
-        SGQ_LAUNCH_CHECK("scale_from_absmax_kernel");
+        SGQ_CUDA_TRY(launch_kernel(scale_from_absmax_pdl_kernel, dim3(1), dim3(kThreads), 0, s, ov, scales, static_cast<int64_t>(1), 127.0f));
         return SGQ_OK;
     }
     if (rows == 0) return SGQ_OK;
