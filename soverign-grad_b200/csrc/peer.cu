@@ -3,10 +3,12 @@
 // NVLink, no multicast), and sgq_peer_barrier tells every GPU that all slices have landed.
 //
 // Signals: every rank owns an array of `world` 64-bit slots in memory that all ranks can write;
-// slot r of rank q is written only by rank r.  A barrier publishes this rank's epoch (a counter
-// kept in local device memory, +1 per barrier, so recorded launches stay valid) into slot `rank` of
-// every rank and waits until each of its own slots has reached the epoch.  Ranks must call the
-// barrier the same number of times.  The wait is bounded (sgq_set_peer_wait_budget): if a peer
+// slot r of rank q is written only by rank r and counts the signals rank r has sent.  Every rank
+// keeps the number it has sent itself in local device memory (so recorded launches stay valid).  A
+// barrier adds one to that number, stores it into slot `rank` of every rank and waits until each of
+// its own slots has reached it; the deferred form of the fused all-gather (gemv.cu) adds one per
+// thread block instead and leaves the waiting to the next kernel.  Ranks must run the same sequence
+// of signalling launches.  The wait is bounded (sgq_set_peer_wait_budget): if a peer
 // never arrives the kernel records kDevErrPeerWait in the status word and returns; the caller
 // reads it on the host (sgq_device_status).
 #include "sgq_common.cuh"
