@@ -76,6 +76,14 @@ SGQ_API int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batc
                               const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
                               int64_t out_stride, void* stream);
 
+/* The same attention on the tensor cores, for prompt passes whose linears run on the bf16 tensor-core path anyway
+ * (SGQ_PATH_TC_BF16): q, k, v and the softmax weights are rounded to bf16, the products accumulate in fp32, the
+ * softmax is fp32.  Within 2e-2 of the largest output of sgqd_attn_prefill (measured ~3e-3).  head_dim must be 128.
+ * (No counterpart in the reference, whose attention is fp32.) */
+SGQ_API int sgqd_attn_prefill_bf16(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,
+                              const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
+                              int64_t out_stride, void* stream);
+
 /* gate_up[rows, 2 * hidden] = [gate | up] per row; out[rows, hidden] = gate / (1 + exp(-gate)) * up.
  * prepared_out: as for sgqd_add_rmsnorm, the prepared form of out[rows, hidden]. */
 SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out,

@@ -573,6 +573,161 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const float* __restri
     }
 }
 
+// The same causal attention on the tensor cores (head dimension 128), for prompt passes whose linears run on the
+// bf16 tensor-core path anyway: q, k, v and the softmax weights are rounded to bf16, scores and outputs accumulate in
+// fp32 (mma.sync m16n8k16), the softmax itself is fp32.  grid (ceil(t_new / 64), batch * heads), 128 threads: a
+// warp owns 16 query rows, their q fragments live in registers; K and V tiles of 64 keys are converted to bf16 on the
+// way into shared memory (rows padded to 272 bytes: ldmatrix reads are conflict free) and are shared by the four
+// warps; the score accumulators become the A fragments of the second product without leaving registers.
+constexpr int kTcQ = 64, kTcKeys = 64, kTcLd = 128 + 8;
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(128) attn_prefill_tc_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int t_new, int n_heads,
+                                                              const float* __restrict__ kc, const float* __restrict__ vc,
+                                                              int64_t max_seq, const int32_t* __restrict__ pos0,
+                                                              float* __restrict__ out, int64_t out_stride) {
+    constexpr int HD = 128;
+    __shared__ __align__(16) uint16_t ks[kTcKeys * kTcLd];
+    __shared__ __align__(16) uint16_t vs[kTcKeys * kTcLd];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int bh = blockIdx.y, b = bh / n_heads, h = bh - b * n_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int q0 = blockIdx.x * kTcQ;
+    int64_t p0 = static_cast<int64_t>(*pos0);
+    p0 = p0 < 0 ? 0 : p0;
+    // 1/sqrt(HD) and log2(e) go into q: the softmax then works with exp2
+    const float qscale = rsqrtf(static_cast<float>(HD)) * 1.4426950408889634f;
+    const int row_lo = q0 + 16 * warp + g, row_hi = row_lo + 8;         // this lane's two query rows
+    uint32_t qa[HD / 16][4];
+    {
+        const float* qlo = qkv + (static_cast<int64_t>(b) * t_new + (row_lo < t_new ? row_lo : 0)) * qkv_stride + h * HD;
+        const float* qhi = qkv + (static_cast<int64_t>(b) * t_new + (row_hi < t_new ? row_hi : 0)) * qkv_stride + h * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const float2 a = *reinterpret_cast<const float2*>(qlo + 16 * kk + 2 * t), c = *reinterpret_cast<const float2*>(qlo + 16 * kk + 8 + 2 * t);
+            const float2 e = *reinterpret_cast<const float2*>(qhi + 16 * kk + 2 * t), f = *reinterpret_cast<const float2*>(qhi + 16 * kk + 8 + 2 * t);
+            qa[kk][0] = pack_bf16(a.x * qscale, a.y * qscale);
+            qa[kk][1] = pack_bf16(e.x * qscale, e.y * qscale);
+            qa[kk][2] = pack_bf16(c.x * qscale, c.y * qscale);
+            qa[kk][3] = pack_bf16(f.x * qscale, f.y * qscale);
+        }
+    }
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.f, l_hi = 0.f;
+    const int last_q = (q0 + kTcQ - 1 < t_new - 1) ? q0 + kTcQ - 1 : t_new - 1;
+    int64_t nk = p0 + last_q + 1;                  // keys this block needs
+    nk = nk > max_seq ? max_seq : nk;
+    const float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD;
+    const float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD;
+    const int64_t lim_lo = p0 + row_lo, lim_hi = p0 + row_hi;           // last key each row may see
+    const uint32_t ks_u = smem_u32(ks), vs_u = smem_u32(vs);
+    for (int64_t j0 = 0; j0 < nk; j0 += kTcKeys) {
+        __syncthreads();                           // the tiles of the last round have been read by everyone
+        for (int it = threadIdx.x; it < kTcKeys * (HD / 4); it += 128) {
+            const int r = it / (HD / 4), c = (it - r * (HD / 4)) * 4;
+            const int64_t j = (j0 + r < nk) ? j0 + r : nk - 1;                         // clamped: masked below
+            const float4 kv = __ldg(reinterpret_cast<const float4*>(kb + j * HD + c));
+            const float4 vv = __ldg(reinterpret_cast<const float4*>(vb + j * HD + c));
+            *reinterpret_cast<uint2*>(ks + r * kTcLd + c) = make_uint2(pack_bf16(kv.x, kv.y), pack_bf16(kv.z, kv.w));
+            *reinterpret_cast<uint2*>(vs + r * kTcLd + c) = make_uint2(pack_bf16(vv.x, vv.y), pack_bf16(vv.z, vv.w));
+        }
+        __syncthreads();
+        // scores of 16 rows x 64 keys: 8 key tiles of 8, 8 steps of 16 head dimensions each
+        float sc[kTcKeys / 8][4];
+#pragma unroll
+        for (int j = 0; j < kTcKeys / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+        for (int j = 0; j < kTcKeys / 8; ++j) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; kk += 2) {
+                // four 8x8 matrices: keys 8j.., head dimensions 16kk + {0, 8, 16, 24}..: (b0, b1) of steps kk and kk + 1
+                uint32_t bfr[4];
+                ldsm_x4(bfr, ks_u + ((8 * j + (lane & 7)) * kTcLd + 16 * kk + 8 * (lane >> 3)) * 2);
+                mma_bf16_16816(sc[j], qa[kk], bfr[0], bfr[1]);
+                mma_bf16_16816(sc[j], qa[kk + 1], bfr[2], bfr[3]);
+            }
+        }
+        // mask (causal and end of range), row maxima over the quad that shares a row
+        float t_lo = -CUDART_INF_F, t_hi = -CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < kTcKeys / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int64_t key = j0 + 8 * j + 2 * t + e;
+                const bool in = key < nk;
+                if (!(in && key <= lim_lo && row_lo < t_new)) sc[j][e] = -CUDART_INF_F;
+                if (!(in && key <= lim_hi && row_hi < t_new)) sc[j][2 + e] = -CUDART_INF_F;
+                t_lo = fmaxf(t_lo, sc[j][e]);
+                t_hi = fmaxf(t_hi, sc[j][2 + e]);
+            }
+        }
+        t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1)); t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
+        t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1)); t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+        const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
+        // a row whose every key so far is masked keeps m = -inf: its weights and its rescaling are zero
+        const float a_lo = (n_lo == -CUDART_INF_F) ? 0.f : exp2f(m_lo - n_lo), a_hi = (n_hi == -CUDART_INF_F) ? 0.f : exp2f(m_hi - n_hi);
+        m_lo = n_lo; m_hi = n_hi;
+        float s_lo = 0.f, s_hi = 0.f;
+        uint32_t pa[kTcKeys / 16][4];               // the weights as A fragments: keys 16kk.. = score tiles 2kk, 2kk + 1
+#pragma unroll
+        for (int j = 0; j < kTcKeys / 8; ++j) {
+            const float p0v = (n_lo == -CUDART_INF_F) ? 0.f : exp2f(sc[j][0] - n_lo), p1v = (n_lo == -CUDART_INF_F) ? 0.f : exp2f(sc[j][1] - n_lo);
+            const float p2v = (n_hi == -CUDART_INF_F) ? 0.f : exp2f(sc[j][2] - n_hi), p3v = (n_hi == -CUDART_INF_F) ? 0.f : exp2f(sc[j][3] - n_hi);
+            s_lo += p0v + p1v;
+            s_hi += p2v + p3v;
+            pa[j >> 1][(j & 1) * 2] = pack_bf16(p0v, p1v);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2v, p3v);
+        }
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1); s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+        s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1); s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+        l_lo = l_lo * a_lo + s_lo;
+        l_hi = l_hi * a_hi + s_hi;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
+        // weighted values: 16 tiles of 8 head dimensions, 4 steps of 16 keys
+#pragma unroll
+        for (int kk = 0; kk < kTcKeys / 16; ++kk) {
+#pragma unroll
+            for (int j = 0; j < HD / 8; j += 2) {
+                // transposed 8x8 matrices: keys 16kk + {0, 8}.., head dimensions 8j.. and 8(j+1)..: (b0, b1) of tiles j and j + 1
+                uint32_t bfr[4];
+                ldsm_x4_trans(bfr, vs_u + ((16 * kk + 8 * ((lane >> 3) & 1) + (lane & 7)) * kTcLd + 8 * (j + (lane >> 4))) * 2);
+                mma_bf16_16816(o[j], pa[kk], bfr[0], bfr[1]);
+                mma_bf16_16816(o[j + 1], pa[kk], bfr[2], bfr[3]);
+            }
+        }
+    }
+    const float i_lo = l_lo > 0.f ? 1.0f / l_lo : 0.f, i_hi = l_hi > 0.f ? 1.0f / l_hi : 0.f;
+    if (row_lo < t_new) {
+        float* orow = out + (static_cast<int64_t>(b) * t_new + row_lo) * out_stride + h * HD + 2 * t;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) *reinterpret_cast<float2*>(orow + 8 * j) = make_float2(o[j][0] * i_lo, o[j][1] * i_lo);
+    }
+    if (row_hi < t_new) {
+        float* orow = out + (static_cast<int64_t>(b) * t_new + row_hi) * out_stride + h * HD + 2 * t;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) *reinterpret_cast<float2*>(orow + 8 * j) = make_float2(o[j][2] * i_hi, o[j][3] * i_hi);
+    }
+}
+
 // Embedding lookup: one block per index.  An index outside [0, vocab) yields a row of zeros, as the
 // reference's lookup does (src/ops.cpp:2643-2649); nothing is ever read outside the table.
 __global__ void __launch_bounds__(256) embedding_kernel(const float* __restrict__ table, int64_t vocab, int64_t dim,
@@ -786,6 +941,26 @@ int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batch, int64
     else
         SGQ_CUDA_TRY(launch_kernel(attn_prefill_kernel<64>, grid, dim3(256), 0, s, stream_overlap_enabled(), qkv, qkv_stride,
                                    static_cast<int>(t_new), static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out, out_stride));
+    return SGQ_OK;
+}
+
+int sgqd_attn_prefill_bf16(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,
+                           const float* k_cache, const float* v_cache, int64_t max_seq, const int32_t* pos0, float* out,
+                           int64_t out_stride, void* stream) {
+    if (batch < 0 || t_new < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 65535 || t_new > 0x3fffffff)
+        return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
+    if (head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 128");
+    if (qkv_stride < 3 * n_heads * head_dim || out_stride < n_heads * head_dim) return bad(SGQ_ERR_BAD_SHAPE, "row stride too small");
+    if (batch * t_new == 0) return SGQ_OK;
+    if (!qkv || !k_cache || !v_cache || !pos0 || !out) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (!aligned(qkv, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(out, 16) || (qkv_stride & 3) || (out_stride & 3))
+        return bad(SGQ_ERR_ALIGNMENT, "rows and caches must be 16-byte aligned");
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    const dim3 grid(static_cast<unsigned>(ceil_div(t_new, kTcQ)), static_cast<unsigned>(batch * n_heads));
+    SGQ_CUDA_TRY(launch_kernel(attn_prefill_tc_kernel, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), stream_overlap_enabled(), qkv,
+                               qkv_stride, static_cast<int>(t_new), static_cast<int>(n_heads), k_cache, v_cache, max_seq, pos0, out,
+                               out_stride));
     return SGQ_OK;
 }
 

@@ -29,7 +29,7 @@ import torch
 import contextlib
 import ctypes as C
 
-from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
+from . import (LAYOUT_NK, PATH_AUTO, PATH_GEMV, PATH_TC_BF16, QuantizedTensor, Workspace, _ptr, _stream, check, interleave_slices, lib,
                linear_int4_prepared, prepared_x_bytes, quantize_int4, quantized_matmul, set_stream_overlap)
 
 
@@ -313,7 +313,7 @@ class NanoLlamaInt4:
                 check(lib.sgqd_rope_kv_store(_ptr(b["qkv"]), B, t_new, self.h_local, c.head_dim, _ptr(self.cos), _ptr(self.sin),
                                              _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
                 self._count()
-                self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"])
+                self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"], bf16=path in (PATH_AUTO, PATH_TC_BF16) and M >= 64)
             attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"), "attn")
             if p_attn is not None:
                 self._linear(L["wo"], attn, b["o"], path, p_attn)
@@ -335,10 +335,12 @@ class NanoLlamaInt4:
         self._final_planes = p_dim
         return n
 
-    def _prefill_attention(self, qkv, kc, vc, T: int, out):
-        """Causal attention of the prompt: q from the rotated qkv rows, k and v from the cache rows just written."""
-        check(lib.sgqd_attn_prefill(_ptr(qkv), 3 * self.dim_local, self.batch, T, self.h_local, self.cfg.head_dim, _ptr(kc), _ptr(vc),
-                                    self.cfg.max_seq, _ptr(self.pos), _ptr(out), self.dim_local, _stream()), "sgqd_attn_prefill")
+    def _prefill_attention(self, qkv, kc, vc, T: int, out, bf16: bool = False):
+        """Causal attention of the prompt: q from the rotated qkv rows, k and v from the cache rows just written.
+        bf16: the pass runs its linears on the bf16 tensor cores (2e-2 contract), so the attention does too."""
+        fn = lib.sgqd_attn_prefill_bf16 if (bf16 and self.cfg.head_dim == 128) else lib.sgqd_attn_prefill
+        check(fn(_ptr(qkv), 3 * self.dim_local, self.batch, T, self.h_local, self.cfg.head_dim, _ptr(kc), _ptr(vc),
+                 self.cfg.max_seq, _ptr(self.pos), _ptr(out), self.dim_local, _stream()), "sgqd_attn_prefill")
         self._count()
 
     def _logits(self, n_rows: torch.Tensor, path: int, planes=None) -> torch.Tensor:

@@ -216,6 +216,14 @@ def test_attn_prefill(sgq, B, H, hd, T, pos0):
     scores = np.where(mask, -np.inf, scores)
     want = np.einsum("bhts,bhsd->bhtd", no.softmax(scores), v).transpose(0, 2, 1, 3).reshape(B * T, dim)
     assert norm_err(out.cpu().numpy(), want) <= 5e-6
+    if hd == 128:       # the tensor-core form of the same attention: operands and weights in bf16, fp32 accumulation and softmax
+        out16 = torch.full((B * T, dim), float("nan"), device="cuda")
+        sgq.check(sgq.lib.sgqd_attn_prefill_bf16(ptr(qt), 3 * dim, B, T, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out16), dim, stream()))
+        got = out16.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert norm_err(got, want) <= 2e-2, norm_err(got, want)
+    else:
+        assert sgq.lib.sgqd_attn_prefill_bf16(ptr(qt), 3 * dim, B, T, H, hd, ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(out), dim, stream()) == 4
 
 
 def test_embedding_lookup_and_out_of_range_ids(sgq):
