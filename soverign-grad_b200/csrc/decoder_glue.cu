@@ -236,17 +236,10 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
     const float* row = qkv + static_cast<int64_t>(b) * qkv_stride + h * HD + lane * VEC;
     const float* cos_row = cos_t + (in_range ? pos : 0) * (HD / 2);
     const float* sin_row = sin_t + (in_range ? pos : 0) * (HD / 2);
-    float qv[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) qv[j] = row[j];
-    rope_lanes<VEC>(qv, cos_row, sin_row, lane);
-    const float scale = rsqrtf(static_cast<float>(HD));
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) qv[j] *= scale;
-
     float* kb = kc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
     float* vb = vc + static_cast<int64_t>(bh) * max_seq * HD + lane * VEC;
 
+    float qv[VEC];                                         // the rotated, scaled query: filled below, behind the first loads
     float m = -CUDART_INF_F, l = 0.f, acc[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
@@ -299,7 +292,37 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
         constexpr int64_t kStride = kAttnWarps * kKeysPerIter;
         float ka[kKeysPerIter][VEC], va[kKeysPerIter][VEC], kb2[kKeysPerIter][VEC], vb2[kKeysPerIter][VEC];
         int64_t t = t0 + warp * kKeysPerIter;
+        // The first cache rows are asked for before anything else: they need the position only, and the query's
+        // own loads and rotation (and the new token's, below) then run while those rows are on their way.
         if (t < t1) load_rows(t, ka, va);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) qv[j] = row[j];
+        const bool appends = split == S - 1 && warp == 0;  // this warp takes the new token
+        float kn[VEC], vn[VEC];
+        if (appends) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) { kn[j] = row[dim + j]; vn[j] = row[2 * dim + j]; }
+        }
+        rope_lanes<VEC>(qv, cos_row, sin_row, lane);
+        const float scale = rsqrtf(static_cast<float>(HD));
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) qv[j] *= scale;
+        if (appends) {
+            // the new token: its key is rotated and both rows are appended to the cache; it is the first key of this
+            // warp's running softmax (m = its score, l = 1, acc = its value)
+            rope_lanes<VEC>(kn, cos_row, sin_row, lane);
+            if (in_range) {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) { kb[pos * HD + j] = kn[j]; vb[pos * HD + j] = vn[j]; }
+                float d = 0.f;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) d = fmaf(qv[j], kn[j], d);
+                m = warp_sum(d);
+                l = 1.f;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[j] = vn[j];
+            }
+        }
         for (; t < t1; t += 2 * kStride) {
             const bool second = t + kStride < t1;
             if (second) load_rows(t + kStride, kb2, vb2);
@@ -311,27 +334,6 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
         }
     }
 
-    // the new token: warp 0 of the last split rotates its key, appends key and value to the cache
-    if (split == S - 1 && warp == 0) {
-        float kn[VEC], vn[VEC];
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) { kn[j] = row[dim + j]; vn[j] = row[2 * dim + j]; }
-        rope_lanes<VEC>(kn, cos_row, sin_row, lane);
-        if (in_range) {
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) { kb[pos * HD + j] = kn[j]; vb[pos * HD + j] = vn[j]; }
-            float d = 0.f;
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) d = fmaf(qv[j], kn[j], d);
-            d = warp_sum(d);
-            const float mx = fmaxf(m, d);
-            const float corr = expf(m - mx), p = expf(d - mx);
-            l = l * corr + p;
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[j] = fmaf(p, vn[j], acc[j] * corr);
-            m = mx;
-        }
-    }
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) sm_acc[warp][lane * VEC + j] = acc[j];
