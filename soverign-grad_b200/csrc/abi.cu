@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <set>
+#include <utility>
 
 #include "sgq_common.cuh"
 #include "sm100_ptx.cuh"
@@ -109,6 +111,18 @@ unsigned int g_peer_wait_budget = 1u << 21;     // about half a second with the 
 unsigned int peer_wait_budget() { return __atomic_load_n(&g_peer_wait_budget, __ATOMIC_RELAXED); }
 bool stream_overlap_enabled() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) != 0; }
 bool stream_overlap_compact() { return __atomic_load_n(&g_stream_overlap, __ATOMIC_RELAXED) == 2; }
+
+void prefer_max_shared(const void* kernel) {
+    static std::mutex mu;
+    static std::set<std::pair<int, const void*>> done;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done.insert({dev, kernel}).second) return;
+    // a preference, not a requirement: a failure changes timing only
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        (void)cudaGetLastError();
+}
 
 int check_device() {
     if (device_info().major != 10) {

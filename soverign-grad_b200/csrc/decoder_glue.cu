@@ -820,6 +820,7 @@ int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = stream_overlap_enabled() ? 2 : 1;
+    if (stream_overlap_enabled()) prefer_max_shared(reinterpret_cast<const void*>(attn_decode_kernel<HD>));
     SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0, out,
                                     out_stride, static_cast<int>(batch), L.mode, L.nmain, L.nlow, planes));
     return SGQ_OK;

@@ -91,10 +91,31 @@ struct Params {
     const float* wscales;   // [N, K/32]
     int vec_store;          // y is 16-byte aligned with ldy % 4 == 0: 128-bit stores
     int split_last;         // the tiles of the last, partial round are taken as two 128-row halves by two CTAs
+    // kBF16Plain behind an ordered expansion launch (see expand_nk_ordered_kernel): the operands are still being
+    // written when this kernel starts.  They become complete slice of K by slice of K; ready[q] counts the
+    // expansion CTAs that have finished slice q of x and of W.
+    const uint32_t* ready;      // null: both operands are complete before the launch
+    uint32_t ready_target;      // CTAs of the expansion launch
+    int ready_part_kblocks;     // k-blocks per slice
 };
 
 __device__ __forceinline__ void report(uint32_t code, uint32_t detail) {
     atomicCAS(&g_status_gemm, 0u, (code << 24) | (detail & 0xFFFFFFu));
+}
+
+// Waits (bounded: about a second) until `target` CTAs of the expansion launch have counted themselves into *cnt,
+// then orders the TMA loads that follow behind what those CTAs wrote.  false = gave up.
+__device__ __forceinline__ bool wait_expanded(const uint32_t* cnt, uint32_t target) {
+    for (uint32_t n = 0; n < (1u << 22); ++n) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if (v >= target) {
+            fence_proxy_async_all();
+            return true;
+        }
+        __nanosleep(200);
+    }
+    return false;
 }
 
 // Position in a ring of N slots and the mbarrier phase that goes with it, advanced by steps of
@@ -204,8 +225,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             };
             int32_t m0 = row0();
             uint32_t seen_tile = 0;
+            int parts_seen = 0;                             // slices of K known to be complete (they fill in order)
             for (int64_t it = 0; it < total_its; ++it, ra.advance(), w.advance(1, kblocks, gridDim.x)) {
                 if (w.tcount != seen_tile) { seen_tile = w.tcount; m0 = row0(); }
+                if (MODE == kBF16Plain && p.ready != nullptr && w.kb >= parts_seen * p.ready_part_kblocks) {
+                    const int q = w.kb / p.ready_part_kblocks;
+                    if (!wait_expanded(p.ready + q, p.ready_target)) { report(kDevErrFullWait, 0x400000u | q); break; }
+                    parts_seen = q + 1;
+                }
                 const int s = ra.slot;
                 if (!mbar_wait(&a_empty[s], ra.phase ^ 1u)) { report(kDevErrEmptyWait, static_cast<uint32_t>(it)); break; }
                 mbar_arrive_expect_tx(&a_full[s], kABytes);
@@ -221,8 +248,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             Walk w(blockIdx.x, switch_at, last_tile);
             int32_t n0 = static_cast<int32_t>((w.tile / m_tiles) * BN);
             uint32_t seen_tile = 0;
+            int parts_seen = 0;
             for (int64_t it = 0; it < total_its; ++it, rb.advance(), rr.advance(), w.advance(1, kblocks, gridDim.x)) {
                 if (w.tcount != seen_tile) { seen_tile = w.tcount; n0 = static_cast<int32_t>((w.tile / m_tiles) * BN); }
+                if (MODE == kBF16Plain && p.ready != nullptr && w.kb >= parts_seen * p.ready_part_kblocks) {
+                    const int q = w.kb / p.ready_part_kblocks;
+                    if (!wait_expanded(p.ready + q, p.ready_target)) { report(kDevErrFullWait, 0x410000u | q); break; }
+                    parts_seen = q + 1;
+                }
                 if (direct_b(MODE)) {
                     const int s = rb.slot;
                     if (!mbar_wait(&b_empty[s], rb.phase ^ 1u)) { report(kDevErrEmptyWait, 0x800000u | static_cast<uint32_t>(it)); break; }
@@ -578,49 +611,105 @@ __global__ void __launch_bounds__(256) dequant_kn_to_nk_bf16_kernel(const uint8_
     }
 }
 
-// Weights stored [N,K] -> bf16 [N,K] in global memory, eight elements per thread (one packed word, or eight code
-// bytes).  INT4 g=32: code * scale in fp32, rounded once.  INT8: the codes themselves (exact in bf16); their scale
-// (per tensor or per output row) is applied by the GEMM's epilogue in fp32.
-// The same launch converts the activations (x fp32 [M,K] -> bf16, natural order): both operands of the GEMM
-// behind it are ready after one kernel.
+// Weights stored [N,K] -> bf16 [N,K] in global memory, eight elements per step (one packed word, or eight code
+// bytes).  INT4: code * scale in fp32, rounded once.  INT8: the codes themselves (exact in bf16); their scale (per
+// tensor or per output row) is applied by the GEMM's epilogue in fp32.  The same launch converts the activations
+// (x fp32 [M,K] -> bf16, natural order), and the GEMM starts while it runs: the grid is one resident wave that
+// leaves room for the GEMM's CTA on every SM, and the work is ordered by `parts` equal slices of K: slice 0 of x,
+// slice 0 of W, slice 1 of x, ...  ready[q] counts the CTAs that have finished slice q of both; a CTA counts
+// itself after a fence behind all of its stores, so a reader that sees gridDim.x in ready[q] (acquire load) may
+// read slices 0 .. q.  The counters must be zero at launch.  Indices are 32-bit: the host takes one slice when
+// the weight has 2^31 steps or more.
+constexpr int kExpandCtasPerSm = 2;
+constexpr int kReadyParts = 8;            // at most
+constexpr size_t kReadyBytes = 256;       // reserved behind the expanded weight for the counters
 template <int BITS>
-__global__ void __launch_bounds__(256) expand_nk_bf16_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales,
-                                                            int64_t group, int64_t chunks, uint4* __restrict__ out,
-                                                            const float* __restrict__ x, int64_t xchunks, uint4* __restrict__ xout) {
+__global__ void __maxnreg__(48)            // per SM quarter: 4 of these warps (4 x 48 x 32) beside 2 of the GEMM (2 x 160 x 32)
+expand_nk_ordered_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scales, uint32_t group, uint32_t N, uint32_t K,
+                         uint32_t parts, uint4* __restrict__ out, const float* __restrict__ x, uint32_t M, uint4* __restrict__ xout,
+                         uint32_t* __restrict__ ready) {
+    pdl_launch_dependents();             // the GEMM behind this launch may take its places now; it waits on `ready`
     auto pk = [](float lo, float hi) {
         return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
                (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
     };
-    int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
-    for (int64_t j = i; j < xchunks; j += stride) {
-        const float4 a = reinterpret_cast<const float4*>(x)[2 * j];
-        const float4 b = reinterpret_cast<const float4*>(x)[2 * j + 1];
-        xout[j] = make_uint4(pk(a.x, a.y), pk(a.z, a.w), pk(b.x, b.y), pk(b.z, b.w));
-    }
-    for (; i < chunks; i += stride) {
+    const uint32_t first = blockIdx.x * 256u + threadIdx.x, stride = gridDim.x * 256u;
+    const uint32_t row = K / 8, slice = row / parts;                     // steps per row / per row and slice (x and W alike)
+    auto step_of = [&](uint32_t v, uint32_t part) {                      // v-th step of the slice -> index in the whole tensor
+        const uint32_t r = v / slice;
+        return r * row + part * slice + (v - r * slice);
+    };
+    auto expand = [&](uint32_t i, uint32_t lo, uint32_t hi, float sc) {
         float v[8];
         if (BITS == 4) {
-            const uint32_t w = reinterpret_cast<const uint32_t*>(wq)[i];
-            const float sc = scales[(8 * i) / group];       // group % 8 == 0: a word never straddles groups
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(static_cast<float>(static_cast<int>(w << (28 - 4 * j)) >> 28), sc);
+            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(static_cast<float>(static_cast<int>(lo << (28 - 4 * j)) >> 28), sc);
         } else {
-            const uint2 w = reinterpret_cast<const uint2*>(wq)[i];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                v[j] = static_cast<float>(static_cast<int>(w.x << (24 - 8 * j)) >> 24);
-                v[4 + j] = static_cast<float>(static_cast<int>(w.y << (24 - 8 * j)) >> 24);
+                v[j] = static_cast<float>(static_cast<int>(lo << (24 - 8 * j)) >> 24);
+                v[4 + j] = static_cast<float>(static_cast<int>(hi << (24 - 8 * j)) >> 24);
             }
         }
         out[i] = make_uint4(pk(v[0], v[1]), pk(v[2], v[3]), pk(v[4], v[5]), pk(v[6], v[7]));
+    };
+    auto signal = [&](uint32_t part) {                                   // called by whole CTAs only
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(ready + part, 1u);
+    };
+    for (uint32_t part = 0; part < parts; ++part) {
+        const uint32_t xtotal = M * slice;
+        for (uint32_t v0 = blockIdx.x * 256u; v0 < xtotal; v0 += 2 * stride) {      // two chunks in flight per thread;
+            const uint32_t v = v0 + threadIdx.x;                                    // the trip count is the CTA's
+            const bool one = v < xtotal, two = v + stride < xtotal;
+            const uint32_t j0 = step_of(one ? v : 0, part), j1 = two ? step_of(v + stride, part) : j0;
+            const float4 a0 = reinterpret_cast<const float4*>(x)[2 * static_cast<size_t>(j0)], b0 = reinterpret_cast<const float4*>(x)[2 * static_cast<size_t>(j0) + 1];
+            const float4 a1 = reinterpret_cast<const float4*>(x)[2 * static_cast<size_t>(j1)], b1 = reinterpret_cast<const float4*>(x)[2 * static_cast<size_t>(j1) + 1];
+            if (one) xout[j0] = make_uint4(pk(a0.x, a0.y), pk(a0.z, a0.w), pk(b0.x, b0.y), pk(b0.z, b0.w));
+            if (two) xout[j1] = make_uint4(pk(a1.x, a1.y), pk(a1.z, a1.w), pk(b1.x, b1.y), pk(b1.z, b1.w));
+        }
+        // Four words and their scales per thread and pass, and the loads of the next pass are issued before the
+        // current one is converted: with two CTAs per SM the loads have to overlap the arithmetic inside a thread.
+        const uint32_t total = N * slice;
+        uint32_t i[4], in[4];
+        uint32_t lo[4], hi[4], lon[4], hin[4];
+        float sc[4], scn[4];
+        auto fetch = [&](uint32_t v, uint32_t (&ii)[4], uint32_t (&l)[4], uint32_t (&h)[4], float (&f)[4]) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t vq = v + q * stride;
+                ii[q] = step_of(vq < total ? vq : v, part);
+                if (BITS == 4) {
+                    l[q] = reinterpret_cast<const uint32_t*>(wq)[ii[q]];
+                    h[q] = 0;
+                    f[q] = scales[ii[q] / (group / 8)];                    // group % 8 == 0: a word never straddles groups
+                } else {
+                    const uint2 w = reinterpret_cast<const uint2*>(wq)[ii[q]];
+                    l[q] = w.x;
+                    h[q] = w.y;
+                    f[q] = 1.0f;
+                }
+            }
+        };
+        if (first < total) fetch(first, i, lo, hi, sc);
+        for (uint32_t v = first; v < total; v += 4 * stride) {
+            const uint32_t vn = v + 4 * stride;
+            if (vn < total) fetch(vn, in, lon, hin, scn);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (q == 0 || v + q * stride < total) expand(i[q], lo[q], hi[q], sc[q]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { i[q] = in[q]; lo[q] = lon[q]; hi[q] = hin[q]; sc[q] = scn[q]; }
+        }
+        signal(part);
     }
 }
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 template <int MODE>
-int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream_t stream, bool overlap = false) {
     using C = Cfg<MODE>;
     p.vec_store = (aligned(p.y, 16) && (p.ldy % 4) == 0) ? 1 : 0;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
@@ -636,8 +725,9 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
     }
     static SmemOptIn optin;   // one per MODE instantiation
     SGQ_CUDA_TRY(optin.ensure(linear_tc_kernel<MODE>, C::kSmemBytes));
-    linear_tc_kernel<MODE><<<grid, C::kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
-    SGQ_LAUNCH_CHECK("linear_tc_kernel");
+    // overlap: the kernel may start while the expansion launch in front of it is still running (it waits on p.ready)
+    SGQ_CUDA_TRY(launch_kernel(linear_tc_kernel<MODE>, dim3(static_cast<unsigned>(grid)), dim3(C::kThreads), C::kSmemBytes, stream,
+                               overlap, ma, mb, p));
     return SGQ_OK;
 }
 
@@ -658,7 +748,7 @@ bool tc_bf16_supported(int bits, int64_t M, int64_t K, int64_t N, int layout, in
 size_t tc_bf16_workspace_bytes(int bits, int64_t M, int64_t K, int64_t N, int layout) {
     (void)bits; (void)layout;
     return round_up(static_cast<size_t>(M) * static_cast<size_t>(K) * 2, 256) +
-           round_up(static_cast<size_t>(N) * static_cast<size_t>(K) * 2, 256);
+           round_up(static_cast<size_t>(N) * static_cast<size_t>(K) * 2, 256) + kReadyBytes;
 }
 
 // the least the path runs with: weights stored [N,K] can be dequantized tile by tile in shared memory instead
@@ -716,27 +806,49 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
                                                                             a.scheme == SGQ_PER_ROW ? 1 : 0, 32, a.K, a.N, wt);
             SGQ_LAUNCH_CHECK("dequant_kn_to_nk_bf16_kernel");
         } else {
-            const int64_t wchunks = a.N * a.K / 8;
-            const int64_t wblocks = ceil_div(wchunks > chunks ? wchunks : chunks, 256);
-            const int wgrid = static_cast<int>(wblocks < cap ? wblocks : cap);
+            // One resident wave converts x and the weight slice of K by slice of K, counting finished slices into
+            // `ready`; the GEMM is launched behind it with programmatic serialization and starts on the first slice
+            // while the rest is still being expanded.
+            const int64_t wsteps = a.N * a.K / 8;
+            const int64_t most = wsteps > chunks ? wsteps : chunks;
+            const int64_t wave = static_cast<int64_t>(sm_count()) * kExpandCtasPerSm;
+            const int egrid = static_cast<int>(ceil_div(most, 1024) < wave ? ceil_div(most, 1024) : wave);
+            const int64_t kblocks = a.K / 64;
+            int parts = kReadyParts;
+            while (kblocks % parts) parts /= 2;
+            if (most >= (1LL << 31) - 4LL * egrid * 256) {
+                set_error("bf16 tensor-core path: more than 2^31 expansion steps");
+                return SGQ_ERR_UNSUPPORTED;
+            }
+            uint32_t* ready = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(wt) +
+                                                          round_up(static_cast<size_t>(a.N) * static_cast<size_t>(a.K) * 2, 256));
+            SGQ_CUDA_TRY(cudaMemsetAsync(ready, 0, kReadyBytes, a.stream));
+            const uint32_t N32 = static_cast<uint32_t>(a.N), K32 = static_cast<uint32_t>(a.K), M32 = static_cast<uint32_t>(a.M);
+            if (stream_overlap_enabled())     // the GEMM's CTA can only join an SM that runs under the same memory split
+                prefer_max_shared(a.bits == 4 ? reinterpret_cast<const void*>(expand_nk_ordered_kernel<4>)
+                                              : reinterpret_cast<const void*>(expand_nk_ordered_kernel<8>));
             if (a.bits == 4)
-                expand_nk_bf16_kernel<4><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, a.group, wchunks,
-                                                                     reinterpret_cast<uint4*>(wt), a.x, chunks,
-                                                                     static_cast<uint4*>(a.workspace));
+                expand_nk_ordered_kernel<4><<<egrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales,
+                                                                        static_cast<uint32_t>(a.group), N32, K32, parts,
+                                                                        reinterpret_cast<uint4*>(wt), a.x, M32,
+                                                                        static_cast<uint4*>(a.workspace), ready);
             else
-                expand_nk_bf16_kernel<8><<<wgrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 32, wchunks,
-                                                                     reinterpret_cast<uint4*>(wt), a.x, chunks,
-                                                                     static_cast<uint4*>(a.workspace));
-            SGQ_LAUNCH_CHECK("expand_nk_bf16_kernel");
+                expand_nk_ordered_kernel<8><<<egrid, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.wq), a.scales, 32u, N32, K32, parts,
+                                                                        reinterpret_cast<uint4*>(wt), a.x, M32,
+                                                                        static_cast<uint4*>(a.workspace), ready);
+            SGQ_LAUNCH_CHECK("expand_nk_ordered_kernel");
             if (a.bits == 8) {          // codes are exact in bf16: their scale goes to the epilogue
                 p.sw = a.scales;
                 p.sw_per_row = (a.scheme == SGQ_PER_ROW) ? 1 : 0;
             }
+            p.ready = ready;
+            p.ready_target = static_cast<uint32_t>(egrid);
+            p.ready_part_kblocks = static_cast<int>(kblocks / parts);
         }
         if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, wt, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
                                 static_cast<uint64_t>(a.K) * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B))
             return SGQ_ERR_CUDA;
-        return launch_tc<kBF16Plain>(ma, mb, p, a.stream);
+        return launch_tc<kBF16Plain>(ma, mb, p, a.stream, p.ready != nullptr && stream_overlap_enabled());
     }
     if (a.bits == 8) {
         if (!make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.wq, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),

@@ -84,7 +84,7 @@ def test_argument_validation_needs_no_device(sgq):
 
 def test_workspace_queries(sgq):
     assert sgq.linear_workspace_bytes(4, 1, 4096, 11008, sgq.LAYOUT_NK, sgq.PATH_GEMV) == 0
-    assert sgq.linear_workspace_bytes(4, 2048, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2 + 4096 * 4096 * 2   # bf16 x + expanded weight
+    assert sgq.linear_workspace_bytes(4, 2048, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2 + 4096 * 4096 * 2 + 256   # bf16 x + expanded weight + progress counters
     assert sgq.linear_workspace_bytes(4, 2048, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_SIMT) == 0
     assert sgq.linear_workspace_bytes(4, 0, 4096, 4096, sgq.LAYOUT_NK, sgq.PATH_AUTO) == 0
     assert int(sgq.lib.sgq_linear_w8a8_workspace_bytes(128, 1024, 1024)) == 128 * 1024 + 512
@@ -92,7 +92,7 @@ def test_workspace_queries(sgq):
     # (16 rows: 4 main sets + 2 low sets), 16 flag bytes per group
     assert sgq.linear_workspace_bytes(8, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (6 * 288 + 16)
     assert sgq.linear_workspace_bytes(8, 4, 100, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == 0          # K % 128 != 0: no such path
-    assert sgq.linear_workspace_bytes(8, 2048, 4096, 64, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2 + 64 * 4096 * 2
+    assert sgq.linear_workspace_bytes(8, 2048, 4096, 64, sgq.LAYOUT_NK, sgq.PATH_TC_BF16) == 2048 * 4096 * 2 + 64 * 4096 * 2 + 256
     # an INT4 batch of more than 8 rows whose planes exceed shared memory runs as blocks of at most 8 rows
     # that share one scratch: 2 main sets + 1 low set
     assert sgq.linear_workspace_bytes(4, 16, 8192, 64, sgq.LAYOUT_NK, sgq.PATH_GEMV) == (8192 // 32) * (3 * 288 + 16)

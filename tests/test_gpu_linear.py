@@ -276,6 +276,36 @@ def test_tc_bf16_against_port(sgq, port, M, K, N):
         assert rel_err(y, want) <= (TOL_BF16 if K >= 1024 else 8e-2), rel_err(y, want)
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,K,N", [(2048, 4096, 11008), (512, 2048, 4096), (200, 192, 1000), (64, 64, 40)])
+def test_tc_bf16_gemm_that_starts_during_the_expansion(sgq, bits, M, K, N):
+    """With overlapped launches the GEMM starts while the weight is still being expanded into the scratch and waits
+    on per-part counters.  Forwards with DIFFERENT weights through the SAME scratch, back to back, must give the
+    bits of the serial launches: a tile read before its rows were rewritten would show the previous weight."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + bits)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    ws = []
+    for i in range(4):
+        w = torch.randn(N, K, device="cuda", generator=g) * (0.02 * (i + 1))
+        ws.append(sgq.quantize_int4(w, 32) if bits == 4 else sgq.quantize_int8(w, cases.PER_ROW))
+    space = sgq.Workspace(torch.device("cuda"))
+    outs = {}
+    for mode in (0, 1):
+        prev = sgq.set_stream_overlap(mode)
+        try:
+            ys = [torch.empty(M, N, device="cuda") for _ in range(12)]
+            for i, y in enumerate(ys):
+                sgq.quantized_matmul(x, ws[i % 4], None, layout=cases.LAYOUT_NK, path=sgq.PATH_TC_BF16, out=y, workspace=space)
+            torch.cuda.synchronize()
+            outs[mode] = ys
+        finally:
+            sgq.set_stream_overlap(prev)
+    check_status(sgq)
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    assert not torch.equal(outs[1][0], outs[1][1])
+
+
 @pytest.mark.parametrize("M,K,N", TC_SHAPES)
 def test_tc_bf16_int8_weights_against_port(sgq, port, M, K, N):
     """INT8 weight codes on the bf16 tensor-core path: the codes are exact in bf16 and the weight
