@@ -79,7 +79,10 @@ enum {
                              With the scratch sgq_linear_workspace_bytes() asks for, a launch in front expands the weight
                              to bf16 [N,K] (INT4: code * scale in fp32, rounded once; INT8 stored [N,K]: the exact codes,
                              scale applied in fp32 afterwards) and both operands reach the tensor cores by TMA; weights
-                             stored [K,N] (N % 32 == 0) are transposed by that launch.  With scratch for the activations
+                             stored [K,N] (N % 32 == 0) are transposed by that launch.  For weights stored [N,K] and
+                             with sgq_set_stream_overlap on, the GEMM starts while that launch is still running: the
+                             expansion goes slice of K by slice of K and counts finished slices in the last 256 bytes of
+                             the scratch, which the GEMM's loads wait on (bounded).  With scratch for the activations
                              only (M * K * 2 bytes, rounded up to 256), INT4 g=32 and INT8 weights stored [N,K] are dequantized tile by tile in
                              shared memory instead (slower).  Bound 2e-2 of the largest output. */
     SGQ_PATH_TC_I8 = 4    /* prefill, INT8 weights only: activations quantized per row, tcgen05 kind::i8 */
