@@ -277,7 +277,8 @@ def test_tc_bf16_against_port(sgq, port, M, K, N):
 
 
 @pytest.mark.parametrize("bits", [4, 8])
-@pytest.mark.parametrize("M,K,N", [(2048, 4096, 11008), (512, 2048, 4096), (200, 192, 1000), (64, 64, 40)])
+@pytest.mark.parametrize("M,K,N", [(2048, 4096, 11008), (512, 2048, 4096), (200, 192, 1000), (64, 64, 40), (300, 384, 520),
+                                   (130, 256, 70), (1100, 5632, 2048)])
 def test_tc_bf16_gemm_that_starts_during_the_expansion(sgq, bits, M, K, N):
     """With overlapped launches the GEMM starts while the weight is still being expanded into the scratch and waits
     on per-part counters.  Forwards with DIFFERENT weights through the SAME scratch, back to back, must give the
