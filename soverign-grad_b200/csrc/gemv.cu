@@ -133,9 +133,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
 // a CTA converts 1024 consecutive k of one row, so that even a few rows spread over many SMs.
 constexpr int kPrepThreads = 128;
 __global__ void __launch_bounds__(kPrepThreads) gemv_prepare_x_kernel(const float* __restrict__ x, int64_t K, int mode, int nmain,
-                                                                     int nlow, uint8_t* __restrict__ planes) {
+                                                                     int nlow, uint8_t* __restrict__ planes,
+                                                                     const unsigned long long* wait_slots, int wait_world,
+                                                                     const unsigned long long* wait_epoch, unsigned int wait_budget) {
     pdl_launch_dependents();
     pdl_wait();                                        // x comes from the kernel before this one
+    // Deferred exchange between GPUs: x may hold slices that other GPUs store, so this kernel waits as the decode
+    // kernel itself does in its prologue (every rank has finished the exchanges this GPU has finished).
+    if (wait_slots != nullptr && !peer_wait_epoch(wait_slots, wait_world, wait_epoch, threadIdx.x & 31, wait_budget)) {
+        if ((threadIdx.x & 31) == 0) report(kDevErrPeerWait, 0x30000u);
+    }
     const int m = blockIdx.x, M = gridDim.x;
     const int chunks = static_cast<int>(K / 8);
     const PreparedParts pp = prepared_parts(planes, static_cast<size_t>(K / 32), nmain, nlow);
@@ -661,7 +668,7 @@ bool make_plan(int64_t M, int64_t K, bool have_workspace, Plan* p, bool compact 
 // planes fit in shared memory next to the pipeline stages (0: not even one row fits).  Larger
 // batches then run as several launches over row blocks; each streams the weights again, which is
 // still far better than the any-shape kernel.
-int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
+int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace, bool allow_phases = true) {
     Plan p;
     // the whole batch in one pass over K — unless it is a wide batch that leaves the pipeline fewer than four stages
     if (make_plan(M, K, have_workspace, &p, false, false) && (M <= 8 || p.nstages >= 4)) return M;
@@ -670,9 +677,9 @@ int64_t rows_per_launch(int64_t M, int64_t K, bool have_workspace) {
         const int64_t blocks = (M + 7) / 8, rows = (M + blocks - 1) / blocks;
         if (make_plan(rows, K, have_workspace, &p, false, false)) return rows;
     }
-    if (make_plan(M, K, have_workspace, &p)) return M;                           // K phases
+    if (allow_phases && make_plan(M, K, have_workspace, &p)) return M;           // K phases
     for (int64_t m = M - 1; m >= 1; --m)
-        if (make_plan(m, K, have_workspace, &p)) return m;
+        if (make_plan(m, K, have_workspace, &p, false, allow_phases)) return m;
     return 0;
 }
 
@@ -688,8 +695,10 @@ int launch_variant(const LinearArgs& a, const Plan& p, const CUtensorMap& map_w,
     const uint8_t* planes = static_cast<const uint8_t*>(a.workspace);
     const bool overlap = stream_overlap_enabled();
     if (p.pre && !planes_ready) {
+        const bool wait = a.peers.n > 0 && a.peers.deferred && a.peers.sig[0] != nullptr;
         SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(a.M), static_cast<unsigned>(ceil_div(a.K / 8, kPrepThreads))), dim3(kPrepThreads), 0, a.stream, overlap,
-                                   a.x, a.K, p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace)));
+                                   a.x, a.K, p.L.mode, p.L.nmain, p.L.nlow, static_cast<uint8_t*>(a.workspace),
+                                   wait ? a.peers.sig[a.peers.rank] : nullptr, a.peers.n, a.peers.state, a.peers.poll_budget));
     }
     const int flags = (overlap ? kFlagEarlyWeights : 0) | (p.pre ? kFlagPrepared : 0);
     SGQ_CUDA_TRY(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3((NWARPS + 2) * 32), p.smem, a.stream, overlap, map_w,
@@ -746,7 +755,8 @@ size_t gemv_prepared_bytes(int64_t M, int64_t K) {
 int launch_prepare_x(const float* x, int64_t M, int64_t K, void* prepared, cudaStream_t s) {
     const PreparedLayout L = prepared_layout(M, K);
     SGQ_CUDA_TRY(launch_kernel(gemv_prepare_x_kernel, dim3(static_cast<unsigned>(M), static_cast<unsigned>(ceil_div(K / 8, kPrepThreads))), dim3(kPrepThreads), 0, s,
-                               stream_overlap_enabled(), x, K, L.mode, L.nmain, L.nlow, static_cast<uint8_t*>(prepared)));
+                               stream_overlap_enabled(), x, K, L.mode, L.nmain, L.nlow, static_cast<uint8_t*>(prepared),
+                               static_cast<const unsigned long long*>(nullptr), 0, static_cast<const unsigned long long*>(nullptr), 0u));
     return SGQ_OK;
 }
 
@@ -754,11 +764,14 @@ namespace {
 int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     Plan p;
     const size_t want = planes_ready ? gemv_prepared_bytes(a.M, a.K) : gemv_workspace_bytes(a.bits, a.M, a.K, a.N, a.layout);
-    // K phases add into y in place, which the fused all-gather (stores into other GPUs) cannot do
-    const bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
-    const bool phases_ok = have_ws && a.peers.n == 0;
+    // K phases add into y in place, which the fused all-gather (stores into other GPUs) cannot do; the planes in
+    // the scratch (converted by the kernel in front) it can use like any other launch
+    bool have_ws = a.workspace != nullptr && want > 0 && a.workspace_bytes >= want;
+    const bool phases_ok = a.peers.n == 0;
+    // (a batch whose planes fit in shared memory keeps the conversion inside the CTAs there: one launch less)
+    if (a.peers.n > 0 && !planes_ready && rows_per_launch(a.M, a.K, false, false) >= a.M) have_ws = false;
     if (!planes_ready && a.bits == 4 && shape_ok(a.M, a.K, a.N)) {
-        const int64_t rows = rows_per_launch(a.M, a.K, phases_ok);
+        const int64_t rows = rows_per_launch(a.M, a.K, have_ws, phases_ok);
         if (rows >= 1 && rows < a.M) {               // planes of the whole batch do not fit: row blocks
             for (int64_t m0 = 0; m0 < a.M; m0 += rows) {
                 LinearArgs sub = a;
@@ -778,7 +791,7 @@ int launch_gemv_impl(const LinearArgs& a, bool planes_ready) {
     if (planes_ready) probe.x = static_cast<const float*>(a.workspace);      // x is not read: only its alignment rule is waived
     const bool compact = stream_overlap_compact();
     if (!gemv_supported(probe) || (planes_ready && !have_ws) ||
-        !((compact && make_plan(a.M, a.K, phases_ok, &p, true)) || make_plan(a.M, a.K, phases_ok, &p))) {
+        !((compact && make_plan(a.M, a.K, have_ws, &p, true, phases_ok)) || make_plan(a.M, a.K, have_ws, &p, false, phases_ok))) {
         set_error("decode path needs INT4 g=32, layout NK, M<=16, K%%256==0, x digits fitting in shared memory, "
                   "16-byte aligned x/packed/scales");
         return SGQ_ERR_UNSUPPORTED;

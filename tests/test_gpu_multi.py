@@ -45,7 +45,8 @@ def worker(rank, world, port, out_dir):
         lin8 = sh.cuda_sharded_linear(sh.slice_quantized(q8, n0, n1), b[n0:n1].contiguous(), N, path=sgq.PATH_SIMT)
         assert torch.equal(lin8(x), want8)
     # fused all-gather: peer stores from the decode kernel + the barrier kernel, no NCCL on the data path
-    for (M, K, N) in [(1, 1024, 512), (8, 2048, 1024), (16, 1024, 256)]:
+    # (16 rows at K = 8192: the planes do not fit in shared memory, so two blocks of 8 rows converted by a kernel in front)
+    for (M, K, N) in [(1, 1024, 512), (8, 2048, 1024), (16, 1024, 256), (16, 8192, 512)]:
         x = torch.randn(M, K, device="cuda", generator=g)
         w = torch.randn(N, K, device="cuda", generator=g) * 0.02
         b = torch.randn(N, device="cuda", generator=g)
