@@ -811,10 +811,13 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
             // while the rest is still being expanded.
             const int64_t wsteps = a.N * a.K / 8;
             const int64_t most = wsteps > chunks ? wsteps : chunks;
-            const int64_t wave = static_cast<int64_t>(sm_count()) * kExpandCtasPerSm;
+            // (without overlapped launches the GEMM starts behind the whole expansion anyway: then the grid fills the
+            // machine and the weight is one slice)
+            const bool beside = stream_overlap_enabled();
+            const int64_t wave = static_cast<int64_t>(sm_count()) * (beside ? kExpandCtasPerSm : 16);
             const int egrid = static_cast<int>(ceil_div(most, 1024) < wave ? ceil_div(most, 1024) : wave);
             const int64_t kblocks = a.K / 64;
-            int parts = kReadyParts;
+            int parts = beside ? kReadyParts : 1;
             while (kblocks % parts) parts /= 2;
             if (most >= (1LL << 31) - 4LL * egrid * 256) {
                 set_error("bf16 tensor-core path: more than 2^31 expansion steps");
