@@ -16,8 +16,9 @@ peer mappings and signals; the next forward's kernel waits for all ranks' signal
 + NCCL all-gather + interleave instead.  value = bytes streamed by all ranks / max-over-ranks device
 time.  Before anything is timed the gathered output of one forward is compared, bit for bit, with the
 NCCL all-gather of the single-GPU results of the slices ("sharded_check").  `extra` then carries the
-column-sharded configurations: W[28672,8192] split over the ranks (strong scaling, M = 1 and 16) and
-the NanoLLaMA-INT4 generation with every linear split over the ranks.
+column-sharded configurations: W[28672,8192] split over the ranks (strong scaling; M = 1 and 16 on the
+decode kernel with the fused exchange, M = 128, 1024 and 8192 on the tensor cores with an NCCL all-gather)
+and the NanoLLaMA-INT4 generation with every linear split over the ranks.
 
 `--impl reference` times the reference's own CPU QuantizedLinear forward (oracle/_ref, the
 unmodified sources compiled for the host) on the same workload: one forward per step.
@@ -373,8 +374,10 @@ def extras(torch, sgq, peaks, copies_w, only=None, eager=False):
         r = out.get(f"prefill_i8_2048x4096x{N}")
         if i8_peak and r and "tflops" in r:
             r["frac_of_measured_int8"] = r["tflops"] / i8_peak
-    # configuration 5's largest prefill: 3.85 TFLOP per forward, a 470 MB expanded weight
-    guard("prefill_bf16_8192x8192x28672", lambda: gemm(28672, sgq.PATH_TC_BF16, M=8192, K=8192))
+    # configuration 5's batch sweep on the tensor cores (M = 1 and 16 are the decode lines above); the largest is
+    # 3.85 TFLOP per forward with a 470 MB expanded weight
+    for M5 in (128, 1024, 8192):
+        guard(f"prefill_bf16_{M5}x8192x28672", lambda M5=M5: gemm(28672, sgq.PATH_TC_BF16, M=M5, K=8192))
     status = sgq.device_status()
     out["device_status_word"] = status
     return out
@@ -422,6 +425,36 @@ def sharded_extras(torch, sgq, sh, dist, dev, rank: int, world: int, peaks):
             out[f"sharded_int4_g32_M{M}_28672x8192"] = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.synchronize()
         dist.barrier()
+    # the prefill sizes of the same sweep: every rank runs its slice on the tensor cores, the slices are exchanged
+    # by an NCCL all-gather and put in place by the interleave kernel (eager launches, CUDA events, max over ranks)
+    for M in (128, 1024, 8192):
+        try:
+            lin = sh.cuda_sharded_linear(qs[0], None, N, path=sgq.PATH_TC_BF16)
+            x = torch.randn(M, K, device=dev, generator=g)
+            for _ in range(3):
+                lin(x)
+            torch.cuda.synchronize()
+            dist.barrier()
+            reps = 5
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                lin(x)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item()) / reps
+            tf = 2.0 * M * N * K / ms / 1e9
+            out[f"sharded_prefill_bf16_{M}x8192x28672"] = {
+                "ms": ms, "tflops_all_gpus": tf, "frac_of_measured_bf16_burst_all_gpus": tf / (world * peaks["bf16_tflops"]),
+                "n_local": n1 - n0, "scaling": "strong", "exchange": "NCCL all-gather of the [M, n_local] slices + interleave kernel"}
+            del lin, x
+        except Exception as e:  # noqa: BLE001
+            out[f"sharded_prefill_bf16_{M}x8192x28672"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.empty_cache()
     del qs
     torch.cuda.empty_cache()
     try:
