@@ -17,7 +17,7 @@ peer mappings and signals; the next forward's kernel waits for all ranks' signal
 time.  Before anything is timed the gathered output of one forward is compared, bit for bit, with the
 NCCL all-gather of the single-GPU results of the slices ("sharded_check").  `extra` then carries the
 column-sharded configurations: W[28672,8192] split over the ranks (strong scaling; M = 1 and 16 on the
-decode kernel with the fused exchange, M = 128, 1024 and 8192 on the tensor cores with an NCCL all-gather)
+decode kernel, M = 128, 1024 and 8192 on the tensor cores; the kernels' epilogues store into every rank's output)
 and the NanoLLaMA-INT4 generation with every linear split over the ranks.
 
 `--impl reference` times the reference's own CPU QuantizedLinear forward (oracle/_ref, the
@@ -425,11 +425,13 @@ def sharded_extras(torch, sgq, sh, dist, dev, rank: int, world: int, peaks):
             out[f"sharded_int4_g32_M{M}_28672x8192"] = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.synchronize()
         dist.barrier()
-    # the prefill sizes of the same sweep: every rank runs its slice on the tensor cores, the slices are exchanged
-    # by an NCCL all-gather and put in place by the interleave kernel (eager launches, CUDA events, max over ranks)
+    # the prefill sizes of the same sweep: every rank runs its slice on the tensor cores and the GEMM's epilogue
+    # stores the tiles into every rank's full-width output; a barrier kernel ends each forward (eager launches,
+    # CUDA events, max over ranks)
     for M in (128, 1024, 8192):
         try:
-            lin = sh.cuda_sharded_linear(qs[0], None, N, path=sgq.PATH_TC_BF16)
+            ex = sh.PeerExchange(M, N, dev, n_buffers=1)
+            lin = sh.PeerShardedLinear(qs[0], None, N, ex)
             x = torch.randn(M, K, device=dev, generator=g)
             for _ in range(3):
                 lin(x)
@@ -448,8 +450,8 @@ def sharded_extras(torch, sgq, sh, dist, dev, rank: int, world: int, peaks):
             tf = 2.0 * M * N * K / ms / 1e9
             out[f"sharded_prefill_bf16_{M}x8192x28672"] = {
                 "ms": ms, "tflops_all_gpus": tf, "frac_of_measured_bf16_burst_all_gpus": tf / (world * peaks["bf16_tflops"]),
-                "n_local": n1 - n0, "scaling": "strong", "exchange": "NCCL all-gather of the [M, n_local] slices + interleave kernel"}
-            del lin, x
+                "n_local": n1 - n0, "scaling": "strong", "exchange": "peer stores from the GEMM's epilogue + barrier kernel"}
+            del lin, x, ex
         except Exception as e:  # noqa: BLE001
             out[f"sharded_prefill_bf16_{M}x8192x28672"] = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.synchronize()

@@ -484,6 +484,17 @@ static int linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N
     a.y = a.peers.p[0];
     a.ldy = ldy;
     // validate_linear wants ldy >= N for the single-output case; here rows are ldy apart and N_local wide
+    if (M >= kTensorCoreRows && tc_bf16_supported(4, M, K, N_local, SGQ_LAYOUT_NK, 32) && workspace &&
+        workspace_bytes >= tc_bf16_min_workspace_bytes(4, M, K, N_local, SGQ_LAYOUT_NK, 32)) {
+        // Prefill-sized batches: the tcgen05 GEMM's epilogue stores its tiles into every rank's output.  It has no
+        // barrier of its own: with signals the barrier kernel follows it on the stream; the deferred form is for
+        // decode batches only (its wait sits in the decode kernel's prologue).
+        if (deferred) return bad(SGQ_ERR_UNSUPPORTED, "the deferred exchange takes decode batches (M <= 16) only");
+        a.peers.sig[0] = nullptr;
+        const int rc = run_linear(a, SGQ_PATH_TC_BF16);
+        if (rc != SGQ_OK || !signals) return rc;
+        return sgq_peer_barrier(signals, rank, world, local_state, stream);
+    }
     return run_linear(a, SGQ_PATH_GEMV);
 }
 

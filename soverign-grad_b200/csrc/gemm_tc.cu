@@ -94,6 +94,10 @@ struct Params {
     // kBF16Plain behind an ordered expansion launch (see expand_nk_ordered_kernel): the operands are still being
     // written when this kernel starts.  They become complete slice of K by slice of K; ready[q] counts the
     // expansion CTAs that have finished slice q of x and of W.
+    // Column-sharded layer: the output tile goes into every GPU's full-width output (plain peer stores from the
+    // epilogue), so the all-gather needs no pass of its own.  n_peers == 0: y only.
+    float* peer_y[kMaxPeers];
+    int n_peers;
     const uint32_t* ready;      // null: both operands are complete before the launch
     uint32_t ready_target;      // CTAs of the expansion launch
     int ready_part_kblocks;     // k-blocks per slice
@@ -153,7 +157,9 @@ struct Walk {
     }
 };
 
-template <int MODE>
+// PEERS: the epilogue stores every tile into p.n_peers outputs (a column-sharded layer; a form of its own so that
+// the single-output epilogue keeps its straight-line stores).
+template <int MODE, bool PEERS = false>
 __global__ void __launch_bounds__(Cfg<MODE>::kThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Params p) {
     using C = Cfg<MODE>;
@@ -390,15 +396,32 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             if (p.bias) {
                                 o.x = __fadd_rn(o.x, bv[0]); o.y = __fadd_rn(o.y, bv[1]); o.z = __fadd_rn(o.z, bv[2]); o.w = __fadd_rn(o.w, bv[3]);
                             }
-                            if (mm < p.M) {
-                                float* dst = p.y + mm * p.ldy + n4;
-                                if (vec) {
-                                    *reinterpret_cast<float4*>(dst) = o;
-                                } else {
-                                    if (n4 + 0 < p.N) dst[0] = o.x;
-                                    if (n4 + 1 < p.N) dst[1] = o.y;
-                                    if (n4 + 2 < p.N) dst[2] = o.z;
-                                    if (n4 + 3 < p.N) dst[3] = o.w;
+                            if constexpr (PEERS) {
+                                if (mm < p.M) {
+#pragma unroll 1
+                                    for (int r = 0; r < p.n_peers; ++r) {
+                                        float* dst = p.peer_y[r] + mm * p.ldy + n4;
+                                        if (vec) {
+                                            *reinterpret_cast<float4*>(dst) = o;
+                                        } else {
+                                            if (n4 + 0 < p.N) dst[0] = o.x;
+                                            if (n4 + 1 < p.N) dst[1] = o.y;
+                                            if (n4 + 2 < p.N) dst[2] = o.z;
+                                            if (n4 + 3 < p.N) dst[3] = o.w;
+                                        }
+                                    }
+                                }
+                            } else {
+                                if (mm < p.M) {
+                                    float* dst = p.y + mm * p.ldy + n4;
+                                    if (vec) {
+                                        *reinterpret_cast<float4*>(dst) = o;
+                                    } else {
+                                        if (n4 + 0 < p.N) dst[0] = o.x;
+                                        if (n4 + 1 < p.N) dst[1] = o.y;
+                                        if (n4 + 2 < p.N) dst[2] = o.z;
+                                        if (n4 + 3 < p.N) dst[3] = o.w;
+                                    }
                                 }
                             }
                         }
@@ -712,6 +735,8 @@ template <int MODE>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream_t stream, bool overlap = false) {
     using C = Cfg<MODE>;
     p.vec_store = (aligned(p.y, 16) && (p.ldy % 4) == 0) ? 1 : 0;
+    for (int r = 0; r < p.n_peers; ++r)
+        if (!aligned(p.peer_y[r], 16)) p.vec_store = 0;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN);
     int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     p.split_last = 0;
@@ -723,9 +748,20 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, Params p, cudaStream
             if (tiles < sms) grid = static_cast<int>(2 * tiles);
         }
     }
+    // overlap: the kernel may start while the expansion launch in front of it is still running (it waits on p.ready)
+    if (p.n_peers > 0) {
+        if (MODE != kBF16Plain) {
+            set_error("the fused all-gather of the tensor-core path needs the scratch for the expanded weight");
+            return SGQ_ERR_WORKSPACE;
+        }
+        static SmemOptIn optin_peers;
+        SGQ_CUDA_TRY(optin_peers.ensure(linear_tc_kernel<kBF16Plain, true>, Cfg<kBF16Plain>::kSmemBytes));
+        SGQ_CUDA_TRY(launch_kernel(linear_tc_kernel<kBF16Plain, true>, dim3(static_cast<unsigned>(grid)), dim3(Cfg<kBF16Plain>::kThreads),
+                                   Cfg<kBF16Plain>::kSmemBytes, stream, overlap, ma, mb, p));
+        return SGQ_OK;
+    }
     static SmemOptIn optin;   // one per MODE instantiation
     SGQ_CUDA_TRY(optin.ensure(linear_tc_kernel<MODE>, C::kSmemBytes));
-    // overlap: the kernel may start while the expansion launch in front of it is still running (it waits on p.ready)
     SGQ_CUDA_TRY(launch_kernel(linear_tc_kernel<MODE>, dim3(static_cast<unsigned>(grid)), dim3(C::kThreads), C::kSmemBytes, stream,
                                overlap, ma, mb, p));
     return SGQ_OK;
@@ -792,6 +828,8 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
         return SGQ_ERR_CUDA;
     Params p{};
     p.bias = a.bias; p.y = a.y; p.ldy = a.ldy; p.M = a.M; p.N = a.N; p.K = a.K;
+    p.n_peers = a.peers.n;
+    for (int r = 0; r < a.peers.n; ++r) p.peer_y[r] = a.peers.p[r];
     if (expand) {
         // expand the stored weight to bf16 [N,K] behind the activations in the workspace, then a GEMM whose
         // operands both arrive by TMA
@@ -813,7 +851,14 @@ int launch_linear_tc_bf16(const LinearArgs& a) {
             const int64_t most = wsteps > chunks ? wsteps : chunks;
             // (without overlapped launches the GEMM starts behind the whole expansion anyway: then the grid fills the
             // machine and the weight is one slice)
-            const bool beside = stream_overlap_enabled();
+            // Beside the GEMM only while the register budget of an SM quarter holds: 2 GEMM warps of at most 160
+            // registers a thread next to 4 expansion warps of 48 (16384 in all); a compiler that needs more for
+            // the GEMM gets the serial form instead of a silent loss of the overlap.
+            static const bool fits = [] {
+                cudaFuncAttributes fa{};
+                return cudaFuncGetAttributes(&fa, linear_tc_kernel<kBF16Plain>) == cudaSuccess && fa.numRegs <= 160;
+            }();
+            const bool beside = stream_overlap_enabled() && fits && a.peers.n == 0;
             const int64_t wave = static_cast<int64_t>(sm_count()) * (beside ? kExpandCtasPerSm : 16);
             const int egrid = static_cast<int>(ceil_div(most, 1024) < wave ? ceil_div(most, 1024) : wave);
             const int64_t kblocks = a.K / 64;

@@ -141,10 +141,10 @@ class PeerExchange:
 
 
 class PeerShardedLinear:
-    """Column-sharded decode forward with the all-gather fused into the kernel's epilogue: every rank's
-    decode kernel stores its [M, n_local] slice into all ranks' [M, n_total] outputs and runs the
-    barrier between the ranks in its own tail (fused_barrier) or as a second small kernel.  No
-    collective library on the data path."""
+    """Column-sharded forward with the all-gather fused into the kernel's epilogue: every rank's kernel (the
+    decode kernel up to 16 rows, the tcgen05 GEMM from 64 rows on) stores its [M, n_local] slice into all
+    ranks' [M, n_total] outputs; the barrier between the ranks runs in the decode kernel's own tail
+    (fused_barrier) or as a second small kernel.  No collective library on the data path."""
 
     def __init__(self, q_local, bias_local, n_total: int, exchange: PeerExchange, fused_barrier: bool = True,
                  deferred: bool = False):
@@ -160,10 +160,12 @@ class PeerShardedLinear:
         self.ws = Workspace(q_local.qdata.device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        from . import LAYOUT_NK, PATH_GEMV, _ptr, _stream, check, lib, linear_workspace_bytes
+        from . import LAYOUT_NK, PATH_AUTO, _ptr, _stream, check, lib, linear_workspace_bytes
         M, K = x.shape
         i = self.ex.next_buffer()
-        need = linear_workspace_bytes(4, M, K, self.n_local, LAYOUT_NK, PATH_GEMV)
+        # decode batches: the decode kernel's planes; from 64 rows on the tensor-core GEMM's operands (its epilogue
+        # stores the tiles into every rank's output, the barrier kernel follows it)
+        need = linear_workspace_bytes(4, M, K, self.n_local, LAYOUT_NK, PATH_AUTO)
         ws = self.ws.get(need) if need else None
         fn = lib.sgq_linear_int4_allgather_deferred if self.deferred else lib.sgq_linear_int4_allgather
         check(fn(_ptr(x), M, K, self.n_local, _ptr(self.q.qdata), _ptr(self.q.scales), _ptr(self.bias),

@@ -72,6 +72,28 @@ def worker(rank, world, port, out_dir):
         torch.cuda.synchronize()
         assert torch.equal(ys[5], wants[5]), ("deferred, last", M, K, N)
         assert torch.equal(ex.local[(ex.turn + 0) % 2], wants[4]), ("deferred, one before last", M, K, N)
+    # prefill-sized batches: the tcgen05 GEMM's epilogue stores its tiles into every rank's output, a barrier kernel
+    # follows; every output element is accumulated in the same order as on one GPU, so the bits agree
+    for (M, K, N) in [(128, 512, 512), (300, 1024, 1536)]:
+        x = torch.randn(M, K, device="cuda", generator=g)
+        w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+        b = torch.randn(N, device="cuda", generator=g)
+        q_full = sgq.quantize_int4(w, 32)
+        n0, n1 = sh.shard_bounds(N, world, rank)
+        ex = sh.PeerExchange(M, N, torch.device("cuda", rank), n_buffers=1)
+        lin = sh.PeerShardedLinear(sh.slice_quantized(q_full, n0, n1), b[n0:n1].contiguous(), N, ex)
+        for overlap in (0, 1):
+            prev = sgq.set_stream_overlap(overlap)
+            try:
+                for rep in range(3):
+                    xr = x * (rep + 1)
+                    want = sgq.quantized_matmul(xr, q_full, b, layout=sgq.LAYOUT_NK, path=sgq.PATH_TC_BF16)
+                    y = lin(xr)
+                    torch.cuda.synchronize()
+                    assert torch.equal(y, want), ("tensor-core peer stores", M, K, N, rep, overlap)
+                    dist.barrier()
+            finally:
+                sgq.set_stream_overlap(prev)
     # the sharded decoder (heads, SwiGLU columns, wo / w_down outputs and the vocabulary split by column) against
     # the same model on one GPU: every output element is computed by the same instructions, so logits are equal
     nl = importlib.import_module("sgq_b200.nanollama")
