@@ -218,7 +218,11 @@ SGQ_API int sgq_linear_int4_prepared(const void* prepared, size_t prepared_bytes
  * memory, 8-byte aligned, shared by all calls that use the same signals) and the barrier runs in the
  * tail of the kernel itself, or pass signals = NULL and call sgq_peer_barrier afterwards.  Alternate
  * between two sets of output buffers from one forward to the next: a rank that runs ahead then
- * writes the other set while a slower rank still reads this one. */
+ * writes the other set while a slower rank still reads this one.
+ * Prefill-sized batches (M >= 64, K % 64 == 0, workspace of sgq_linear_workspace_bytes(4, M, K, N_local,
+ * SGQ_LAYOUT_NK, SGQ_PATH_TC_BF16) bytes) take the tcgen05 GEMM of SGQ_PATH_TC_BF16 instead, whose epilogue
+ * stores every output tile into all ranks' outputs in the same way (bound 2e-2, bit-equal to the single-GPU
+ * result of that path); with `signals` the barrier kernel is launched behind the GEMM by this call. */
 SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
                                       const float* scales, const float* bias, float* const* y_ranks, int world,
                                       int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
@@ -237,7 +241,8 @@ SGQ_API int sgq_linear_int4_allgather(const float* x, int64_t M, int64_t K, int6
  *    point or sgq_peer_barrier) has been enqueued behind it and has run; end a sequence with
  *    sgq_peer_barrier before reading the last outputs;
  *  - as with the other form, alternate between two sets of output buffers;
- *  - signals, rank and local_state are required (same objects as for sgq_peer_barrier). */
+ *  - signals, rank and local_state are required (same objects as for sgq_peer_barrier);
+ *  - decode batches only (M <= 16): SGQ_ERR_UNSUPPORTED for the prefill-sized batches of the other form. */
 SGQ_API int sgq_linear_int4_allgather_deferred(const float* x, int64_t M, int64_t K, int64_t N_local, const uint8_t* packed,
                                                const float* scales, const float* bias, float* const* y_ranks, int world,
                                                int64_t ldy, int64_t n_offset, void* workspace, size_t workspace_bytes,
