@@ -112,7 +112,7 @@ class _PeerSites:
     the barriers.  One buffer per site is enough: a rank can run at most one exchange ahead of another,
     and a site is reused only four exchanges later."""
 
-    def __init__(self, cfg: NanoLlamaConfig, M: int, device, group):
+    def __init__(self, cfg: NanoLlamaConfig, M: int, device, group, with_logits: bool = True):
         import ctypes as C
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -120,7 +120,9 @@ class _PeerSites:
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        widths = {"attn": cfg.dim, "o": cfg.dim, "act": cfg.hidden, "d": cfg.dim, "logits": cfg.vocab}
+        widths = {"attn": cfg.dim, "o": cfg.dim, "act": cfg.hidden, "d": cfg.dim}
+        if with_logits:
+            widths["logits"] = cfg.vocab
         offs, total = {}, 0
         for k, w in widths.items():
             offs[k] = total
@@ -154,10 +156,11 @@ class NanoLlamaInt4:
         # written by the kernel in front of the linear that reads it
         self.overlap = overlap
         # world > 1, decode steps: "peer" = slices stored into every rank's buffers by this library's kernels +
-        # sgq_peer_barrier (graph-capturable); "nccl" = all-gather + interleave (eager).  The prompt pass always
-        # uses NCCL (one pass, large slices).
+        # sgq_peer_barrier (graph-capturable); "nccl" = all-gather + interleave (eager).  A prompt pass of fewer
+        # than 64 rows, or one held to the fp32 contract, uses NCCL in both cases.
         self.exchange = exchange if world > 1 else "none"
         self._sites = None
+        self._prompt_sites = {}
         init = init or default_init(cfg, self.device, seed)
         dev = self.device
         self.ws = Workspace(dev)
@@ -213,12 +216,20 @@ class NanoLlamaInt4:
         return self._bufs[M]
 
     def _peer(self, M: int):
-        """The symmetric buffers, if this pass exchanges through peer stores (decode steps of a sharded model)."""
-        if self.exchange != "peer" or M != self.batch:
+        """The symmetric buffers, if this pass exchanges through peer stores: the decode steps of a sharded model,
+        and a prompt pass of 64 rows or more on the tensor-core path (the GEMM's epilogue stores into every rank's
+        buffers).  The logits always belong to the decode-sized set."""
+        if self.exchange != "peer":
             return None
-        if self._sites is None:
-            self._sites = _PeerSites(self.cfg, M, self.device, self.group)
-        return self._sites
+        if M == self.batch:
+            if self._sites is None:
+                self._sites = _PeerSites(self.cfg, M, self.device, self.group)
+            return self._sites
+        if M < 64 or self.prefill_path not in (PATH_AUTO, PATH_TC_BF16) or self.cfg.dim % 64 or self.cfg.hidden % 64:
+            return None
+        if M not in self._prompt_sites:
+            self._prompt_sites[M] = _PeerSites(self.cfg, M, self.device, self.group, with_logits=False)
+        return self._prompt_sites[M]
 
     def _barrier(self, sites):
         check(lib.sgq_peer_barrier(sites.signals, self.rank, self.world, _ptr(sites.state), _stream()), "sgq_peer_barrier")
@@ -259,13 +270,13 @@ class NanoLlamaInt4:
             self._linear(lin, x, out, path)
             return self._gather(out, gathered, full)
         M, K = x.shape
-        need = int(lib.sgq_linear_workspace_bytes(4, M, K, lin.n_local, LAYOUT_NK, PATH_GEMV))
+        need = int(lib.sgq_linear_workspace_bytes(4, M, K, lin.n_local, LAYOUT_NK, PATH_AUTO))
         ws = self.ws.get(need) if need else None
         check(lib.sgq_linear_int4_allgather(_ptr(x), M, K, lin.n_local, _ptr(lin.q.qdata), _ptr(lin.q.scales), None,
                                             sites.y_ranks[site], self.world, sites.width[site], self.rank * lin.n_local,
                                             _ptr(ws), ws.numel() if ws is not None else 0, None, self.rank, None, _stream()),
               "sgq_linear_int4_allgather")
-        self._count(2 if M * (K // 8) > 1024 else 1)
+        self._count(2 if (M > 16 or M * (K // 8) > 1024) else 1)
         self._barrier(sites)
         return sites.local[site]
 

@@ -114,6 +114,18 @@ def worker(rank, world, port, out_dir):
             assert torch.equal(tok4, tok1)
         torch.cuda.synchronize()
         dist.barrier()
+    # a prompt of 64 rows or more: the tensor-core GEMMs of the sharded model store into every rank's buffers
+    long_prompt = torch.randint(0, cfg.vocab, (2, 40), generator=torch.Generator().manual_seed(5))
+    single = nl.NanoLlamaInt4(cfg, "cuda", 2, seed=11)
+    tok1, log1 = single.generate(long_prompt, 4, use_graph=False, keep_logits=True)
+    sharded = nl.NanoLlamaInt4(cfg, "cuda", 2, seed=11, rank=rank, world=world, exchange="peer")
+    tok2, log2 = sharded.generate(long_prompt, 4, use_graph=False, keep_logits=True)
+    assert sharded._prompt_sites, "the prompt pass did not take the peer exchange"
+    assert torch.equal(tok2, tok1)
+    for a, b2 in zip(log1, log2):
+        assert torch.equal(a, b2)
+    torch.cuda.synchronize()
+    dist.barrier()
     assert sgq.device_status() == 0
     dist.barrier()
     if rank == 0:
