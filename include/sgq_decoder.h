@@ -89,6 +89,18 @@ SGQ_API int sgqd_attn_prefill_bf16(const float* qkv, int64_t qkv_stride, int64_t
 SGQ_API int sgqd_silu_mul(const float* gate_up, int64_t rows, int64_t hidden, float* out, void* prepared_out,
                           size_t prepared_bytes, void* stream);
 
+/* Column-sharded forms of the two operators whose output is a column slice per GPU (the heads of this rank, the
+ * SwiGLU columns of this rank): the result goes straight into the full-width buffer of EVERY rank,
+ * out_ranks[r][row * stride + col_offset + c] (plain peer stores; out_ranks is a HOST array of `world` device
+ * pointers, as for sgq_linear_int4_allgather), so no copy kernel stands between the operator and sgq_peer_barrier.
+ * Otherwise as sgqd_attn_decode (without the prepared form) and sgqd_silu_mul. */
+SGQ_API int sgqd_attn_decode_allgather(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
+                                       const float* cos_table, const float* sin_table, float* k_cache, float* v_cache,
+                                       int64_t max_seq, const int32_t* pos0, float* const* out_ranks, int world,
+                                       int64_t out_stride, int64_t col_offset, void* stream);
+SGQ_API int sgqd_silu_mul_allgather(const float* gate_up, int64_t rows, int64_t hidden, float* const* out_ranks, int world,
+                                    int64_t ld, int64_t col_offset, void* stream);
+
 /* out[i, :] = table[ids[i], :] for rows indices (ids: DEVICE int64).  An id outside [0, vocab) gives a row
  * of zeros, as in the reference (src/ops.cpp:2643-2649); the table is never read out of bounds. */
 SGQ_API int sgqd_embedding(const float* table, int64_t vocab, int64_t dim, const int64_t* ids, int64_t rows, float* out,

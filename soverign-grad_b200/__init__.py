@@ -40,7 +40,8 @@ EXPORTS = [
 
 # every symbol include/sgq_decoder.h declares
 DECODER_EXPORTS = ["sgqd_add_rmsnorm", "sgqd_rope_kv_store", "sgqd_attn_decode", "sgqd_silu_mul", "sgqd_embedding",
-                   "sgqd_argmax_rows", "sgqd_attn_prefill", "sgqd_attn_prefill_bf16"]
+                   "sgqd_argmax_rows", "sgqd_attn_prefill", "sgqd_attn_prefill_bf16", "sgqd_attn_decode_allgather",
+                   "sgqd_silu_mul_allgather"]
 
 
 class SgqError(RuntimeError):
@@ -98,6 +99,8 @@ def _load() -> C.CDLL:
     lib.sgqd_attn_prefill.argtypes = [p, i64, i64, i64, i64, i64, p, p, i64, p, p, i64, p]
     lib.sgqd_attn_prefill_bf16.argtypes = [p, i64, i64, i64, i64, i64, p, p, i64, p, p, i64, p]
     lib.sgqd_embedding.argtypes = [p, i64, i64, p, i64, p, p]
+    lib.sgqd_attn_decode_allgather.argtypes = [p, i64, i64, i64, i64, p, p, p, p, i64, p, p, C.c_int, i64, i64, p]
+    lib.sgqd_silu_mul_allgather.argtypes = [p, i64, i64, p, C.c_int, i64, i64, p]
     lib.sgqd_argmax_rows.argtypes = [p, i64, i64, i64, p, p]
     return lib
 

@@ -184,6 +184,13 @@ __global__ void __launch_bounds__(256) rope_kv_store_kernel(float* __restrict__ 
     }
 }
 
+// Outputs of a column-sharded operator: the slice goes into every GPU's full-width buffer (plain peer stores),
+// so no copy kernel is needed between the operator and the barrier.  n == 0: the local output only.
+struct PeerPtrs {
+    float* p[kMaxPeers];
+    int n;
+};
+
 constexpr int kAttnWarps = 8;
 constexpr int kKeysPerIter = 4;
 constexpr int kAttnCtasPerSm = 2;      // 256 threads x <= 128 registers: two sets of key/value rows in flight per warp
@@ -207,12 +214,12 @@ __device__ __forceinline__ void rope_lanes(float (&v)[VEC], const float* cos_row
 // later steps).  Each warp walks its keys four at a time with K and V rows loaded together, keeps
 // a running max / sum / weighted value (online softmax); warps are merged through shared memory
 // and the CTAs of the cluster through distributed shared memory, rank 0 writing the output.
-template <int HD>
+template <int HD, bool PEERS = false>
 __global__ void __launch_bounds__(kAttnWarps * 32, kAttnCtasPerSm)
 attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_heads, const float* __restrict__ cos_t,
                    const float* __restrict__ sin_t, float* __restrict__ kc, float* __restrict__ vc, int64_t max_seq,
                    const int32_t* __restrict__ pos0, float* __restrict__ out, int64_t out_stride, int batch, int pmode, int nmain,
-                   int nlow, uint8_t* __restrict__ planes) {
+                   int nlow, uint8_t* __restrict__ planes, PeerPtrs peers) {
     constexpr int VEC = HD / 32;
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -368,7 +375,12 @@ attn_decode_kernel(const float* __restrict__ qkv, int64_t qkv_stride, int n_head
             }
             // LL > 0 whenever there is at least one key; an out-of-range position with an empty cache yields 0
             const float o = LL > 0.f ? AA / LL : 0.f;
-            out[static_cast<int64_t>(b) * out_stride + h * HD + threadIdx.x] = o;
+            const int64_t at = static_cast<int64_t>(b) * out_stride + h * HD + threadIdx.x;
+            if constexpr (PEERS) {
+                for (int r = 0; r < peers.n; ++r) peers.p[r][at] = o;
+            } else {
+                out[at] = o;
+            }
             sm_out[threadIdx.x] = o;
         }
         if (planes != nullptr) {
@@ -397,6 +409,21 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
         const int64_t r = i / hidden, c = i - r * hidden;
         const float g = gu[r * 2 * hidden + c], u = gu[r * 2 * hidden + hidden + c];
         out[i] = g / (1.0f + expf(-g)) * u;              // include/sovereigngrad/simd.hpp:103-108, then gate * up
+    }
+}
+
+// The same with the output slice stored into every GPU's buffer: out_r[r * ld + c] for the local column c (the
+// pointers already stand at this rank's column offset).
+__global__ void __launch_bounds__(256) silu_mul_peers_kernel(const float* __restrict__ gu, int64_t rows, int64_t hidden, int64_t ld,
+                                                             PeerPtrs peers) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t n = rows * hidden;
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += gridDim.x * 256ll) {
+        const int64_t r = i / hidden, c = i - r * hidden;
+        const float g = gu[r * 2 * hidden + c], u = gu[r * 2 * hidden + hidden + c];
+        const float v = g / (1.0f + expf(-g)) * u;
+        for (int q = 0; q < peers.n; ++q) peers.p[q][r * ld + c] = v;
     }
 }
 
@@ -804,7 +831,7 @@ int attn_splits(int64_t batch, int64_t n_heads, int64_t max_seq) {
 template <int HD>
 int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads, const float* cos_t, const float* sin_t, float* kc,
                 float* vc, int64_t max_seq, const int32_t* pos0, float* out, int64_t out_stride, const PreparedLayout& L,
-                uint8_t* planes, cudaStream_t s) {
+                uint8_t* planes, cudaStream_t s, const PeerPtrs& peers = PeerPtrs{}) {
     const int S = attn_splits(batch, n_heads, max_seq);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(batch * n_heads), static_cast<unsigned>(S), 1);
@@ -820,9 +847,15 @@ int launch_attn(const float* qkv, int64_t qkv_stride, int64_t batch, int n_heads
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = stream_overlap_enabled() ? 2 : 1;
-    if (stream_overlap_enabled()) prefer_max_shared(reinterpret_cast<const void*>(attn_decode_kernel<HD>));
-    SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0, out,
-                                    out_stride, static_cast<int>(batch), L.mode, L.nmain, L.nlow, planes));
+    if (peers.n > 0) {
+        SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, true>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0,
+                                        out, out_stride, static_cast<int>(batch), L.mode, L.nmain, L.nlow, planes, peers));
+        return SGQ_OK;
+    }
+    // (no preference for the largest shared-memory split here: this kernel fills the register file, so no dependent
+    // kernel can join its SMs anyway, and its streaming loads want the L1 they get by default)
+    SGQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, false>, qkv, qkv_stride, n_heads, cos_t, sin_t, kc, vc, max_seq, pos0,
+                                    out, out_stride, static_cast<int>(batch), L.mode, L.nmain, L.nlow, planes, peers));
     return SGQ_OK;
 }
 
@@ -921,6 +954,58 @@ int sgqd_attn_decode(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_he
                                 out, out_stride, L, pl, s);
     return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0, out,
                            out_stride, L, pl, s);
+}
+
+int sgqd_attn_decode_allgather(float* qkv, int64_t qkv_stride, int64_t batch, int64_t n_heads, int64_t head_dim,
+                               const float* cos_table, const float* sin_table, float* k_cache, float* v_cache, int64_t max_seq,
+                               const int32_t* pos0, float* const* out_ranks, int world, int64_t out_stride, int64_t col_offset,
+                               void* stream) {
+    if (batch < 0 || n_heads <= 0 || max_seq <= 0 || batch * n_heads > 0x7fffffff) return bad(SGQ_ERR_BAD_SHAPE, "bad decoder shape");
+    if (head_dim != 64 && head_dim != 128) return bad(SGQ_ERR_UNSUPPORTED, "head_dim must be 64 or 128");
+    if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
+    if (qkv_stride < 3 * n_heads * head_dim || col_offset < 0 || out_stride < col_offset + n_heads * head_dim)
+        return bad(SGQ_ERR_BAD_SHAPE, "row stride too small");
+    if (batch == 0) return SGQ_OK;
+    if (!qkv || !cos_table || !sin_table || !k_cache || !v_cache || !pos0 || !out_ranks) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    if (!aligned(qkv, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || (qkv_stride & 3))
+        return bad(SGQ_ERR_ALIGNMENT, "qkv rows and caches must be 16-byte aligned");
+    PeerPtrs peers = {};
+    for (int r = 0; r < world; ++r) {
+        if (!out_ranks[r]) return bad(SGQ_ERR_NULL_POINTER, "an output pointer is NULL");
+        peers.p[r] = out_ranks[r] + col_offset;
+    }
+    peers.n = world;
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    const PreparedLayout L = {};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_dim == 128)
+        return launch_attn<128>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0,
+                                peers.p[0], out_stride, L, nullptr, s, peers);
+    return launch_attn<64>(qkv, qkv_stride, batch, static_cast<int>(n_heads), cos_table, sin_table, k_cache, v_cache, max_seq, pos0,
+                           peers.p[0], out_stride, L, nullptr, s, peers);
+}
+
+int sgqd_silu_mul_allgather(const float* gate_up, int64_t rows, int64_t hidden, float* const* out_ranks, int world, int64_t ld,
+                            int64_t col_offset, void* stream) {
+    if (rows < 0 || hidden < 0 || col_offset < 0 || ld < col_offset + hidden) return bad(SGQ_ERR_BAD_SHAPE, "bad slice shape");
+    if (world < 1 || world > kMaxPeers) return bad(SGQ_ERR_BAD_ARGUMENT, "world must be 1..8");
+    if (rows * hidden == 0) return SGQ_OK;
+    if (!gate_up || !out_ranks) return bad(SGQ_ERR_NULL_POINTER, "NULL argument");
+    PeerPtrs peers = {};
+    for (int r = 0; r < world; ++r) {
+        if (!out_ranks[r]) return bad(SGQ_ERR_NULL_POINTER, "an output pointer is NULL");
+        peers.p[r] = out_ranks[r] + col_offset;
+    }
+    peers.n = world;
+    int rc = check_device();
+    if (rc != SGQ_OK) return rc;
+    int64_t blocks = ceil_div(rows * hidden, 256);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    SGQ_CUDA_TRY(launch_kernel(silu_mul_peers_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                               stream_overlap_enabled(), gate_up, rows, hidden, ld, peers));
+    return SGQ_OK;
 }
 
 int sgqd_attn_prefill(const float* qkv, int64_t qkv_stride, int64_t batch, int64_t t_new, int64_t n_heads, int64_t head_dim,

@@ -52,16 +52,16 @@ bool stream_overlap_compact();     // mode 2: the decode kernel also takes its t
 
 #ifdef __CUDACC__
 // An SM splits one memory between L1 and shared memory, and a CTA cannot join an SM whose running CTAs were placed
-// under another split.  The large kernels of this library take the largest shared-memory split, so a small kernel
-// in front of them must prefer that split too, or programmatic serialization cannot start them early.  Once per
-// kernel and device; a hint only.
+// under another split.  A small kernel that a large-shared-memory kernel is meant to run BESIDE (the weight
+// expansion in front of the prefill GEMM) must therefore prefer the largest shared-memory split too.  Not applied to
+// every kernel: a streaming kernel loses with the small L1 it leaves (the cache attention: 14.8 -> 18 us).  Once
+// per kernel and device; a hint only.
 void prefer_max_shared(const void* kernel);
 
 // kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute when `overlap`.
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool overlap,
                           Args&&... args) {
-    if (overlap) prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

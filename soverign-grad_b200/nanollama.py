@@ -311,7 +311,18 @@ class NanoLlamaInt4:
             self._linear(L["qkv"], n, b["qkv"], path, p_dim)
             kc, vc = self.k_cache[li], self.v_cache[li]
             p_attn = None
-            if t_new == 1:       # rotary embedding, cache append and attention of the new token in one kernel
+            sites = self._peer(M) if self.world > 1 else None
+            attn = None
+            if t_new == 1 and sites is not None:
+                # sharded: the kernel stores this rank's heads into every rank's full-width buffer itself
+                check(lib.sgqd_attn_decode_allgather(_ptr(b["qkv"]), 3 * self.dim_local, B, self.h_local, c.head_dim, _ptr(self.cos),
+                                                     _ptr(self.sin), _ptr(kc), _ptr(vc), c.max_seq, _ptr(self.pos),
+                                                     sites.y_ranks["attn"], self.world, sites.width["attn"],
+                                                     self.rank * self.dim_local, _stream()), "sgqd_attn_decode_allgather")
+                self._count()
+                self._barrier(sites)
+                attn = sites.local["attn"]
+            elif t_new == 1:     # rotary embedding, cache append and attention of the new token in one kernel
                 # unsharded: the kernel also emits the prepared form of its output for the output projection
                 # (the planes of the normed hidden state have been consumed by the q/k/v projection by then)
                 p_attn = p_dim if self.world == 1 else None
@@ -325,7 +336,8 @@ class NanoLlamaInt4:
                                              _ptr(self.pos), _ptr(kc), _ptr(vc), c.max_seq, _stream()), "sgqd_rope_kv_store")
                 self._count()
                 self._prefill_attention(b["qkv"], kc, vc, t_new, b["attn"], bf16=path in (PATH_AUTO, PATH_TC_BF16) and M >= 64)
-            attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"), "attn")
+            if attn is None:
+                attn = self._gather(b["attn"], b.get("g_attn"), b.get("attn_full"), "attn")
             if p_attn is not None:
                 self._linear(L["wo"], attn, b["o"], path, p_attn)
                 o = b["o"]
@@ -333,10 +345,17 @@ class NanoLlamaInt4:
                 o = self._linear_gathered(L["wo"], attn, b["o"], path, b.get("g_o"), b.get("o_full"), "o")
             self._add_rmsnorm(h, o, L["ffn_norm"], n, p_dim)
             self._linear(L["gu"], n, b["gu"], path, p_dim)
-            check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _ptr(p_hid),
-                                    p_hid.numel() if p_hid is not None else 0, _stream()), "sgqd_silu_mul")
-            self._count()
-            act = self._gather(b["act"], b.get("g_act"), b.get("act_full"), "act")
+            if sites is not None:
+                check(lib.sgqd_silu_mul_allgather(_ptr(b["gu"]), M, self.hid_local, sites.y_ranks["act"], self.world,
+                                                  sites.width["act"], self.rank * self.hid_local, _stream()), "sgqd_silu_mul_allgather")
+                self._count()
+                self._barrier(sites)
+                act = sites.local["act"]
+            else:
+                check(lib.sgqd_silu_mul(_ptr(b["gu"]), M, self.hid_local, _ptr(b["act"]), _ptr(p_hid),
+                                        p_hid.numel() if p_hid is not None else 0, _stream()), "sgqd_silu_mul")
+                self._count()
+                act = self._gather(b["act"], b.get("g_act"), b.get("act_full"), "act")
             if self.world == 1:
                 self._linear(L["down"], act, b["d"], path, p_hid)
                 delta = b["d"]

@@ -180,6 +180,48 @@ def test_attn_decode(sgq, B, H, hd, length, max_seq):
     np.testing.assert_array_equal(qt.cpu().numpy(), qkv)                          # qkv is read only
 
 
+def test_column_sharded_operators_store_into_every_output(sgq):
+    """sgqd_attn_decode_allgather / sgqd_silu_mul_allgather with two output buffers on one GPU standing in for
+    two ranks: both receive the slice at the column offset, bit-equal to the plain operators, the columns
+    beside it stay untouched; bad arguments are refused."""
+    B, H, hd, max_seq, length = 3, 2, 128, 32, 9
+    r = np.random.default_rng(21)
+    dim, pos0, wide, off = H * hd, length - 1, 3 * H * hd, H * hd
+    qkv = dev(r.standard_normal((B, 3 * dim)).astype(np.float32))
+    kc0, vc0 = r.standard_normal((B, H, max_seq, hd)).astype(np.float32), r.standard_normal((B, H, max_seq, hd)).astype(np.float32)
+    cos, sin = no.rope_tables(hd, max_seq)
+    ct, st = dev(cos), dev(sin)
+    pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    ref = torch.empty(B, dim, device="cuda")
+    kt, vt = dev(kc0), dev(vc0)
+    sgq.check(sgq.lib.sgqd_attn_decode(ptr(qkv), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt), ptr(vt), max_seq, ptr(pos), ptr(ref),
+                                       dim, None, 0, stream()))
+    outs = [torch.full((B, wide), 7.0, device="cuda") for _ in range(2)]
+    ranks = (C.c_void_p * 2)(*[o.data_ptr() for o in outs])
+    kt2, vt2 = dev(kc0), dev(vc0)
+    sgq.check(sgq.lib.sgqd_attn_decode_allgather(ptr(qkv), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt2), ptr(vt2), max_seq, ptr(pos),
+                                                 ranks, 2, wide, off, stream()))
+    for o in outs:
+        assert torch.equal(o[:, off:off + dim], ref)
+        assert bool((o[:, :off] == 7.0).all()) and bool((o[:, off + dim:] == 7.0).all())
+    assert torch.equal(kt2, kt) and torch.equal(vt2, vt)
+    assert sgq.lib.sgqd_attn_decode_allgather(ptr(qkv), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt2), ptr(vt2), max_seq, ptr(pos),
+                                              ranks, 9, wide, off, stream()) == 3
+    assert sgq.lib.sgqd_attn_decode_allgather(ptr(qkv), 3 * dim, B, H, hd, ptr(ct), ptr(st), ptr(kt2), ptr(vt2), max_seq, ptr(pos),
+                                              ranks, 2, dim, off, stream()) == 2
+    rows, hidden = 5, 704
+    gu = dev(r.standard_normal((rows, 2 * hidden)).astype(np.float32))
+    plain = torch.empty(rows, hidden, device="cuda")
+    sgq.check(sgq.lib.sgqd_silu_mul(ptr(gu), rows, hidden, ptr(plain), None, 0, stream()))
+    outs = [torch.full((rows, 3 * hidden), 7.0, device="cuda") for _ in range(2)]
+    ranks = (C.c_void_p * 2)(*[o.data_ptr() for o in outs])
+    sgq.check(sgq.lib.sgqd_silu_mul_allgather(ptr(gu), rows, hidden, ranks, 2, 3 * hidden, 2 * hidden, stream()))
+    for o in outs:
+        assert torch.equal(o[:, 2 * hidden:], plain)
+        assert bool((o[:, :2 * hidden] == 7.0).all())
+    assert sgq.lib.sgqd_silu_mul_allgather(ptr(gu), rows, hidden, ranks, 2, hidden, 2 * hidden, stream()) == 2
+
+
 def test_attn_decode_position_out_of_range_stores_nothing(sgq):
     B, H, hd, max_seq = 2, 2, 128, 16
     r = np.random.default_rng(5)
